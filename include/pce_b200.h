@@ -1,0 +1,194 @@
+/*
+ * pce_b200.h — C ABI of libpce_b200.so, a Blackwell (sm_100a) sparse-convolution
+ * inference core that replaces the CUDA backend of hkeee21/PCEngine.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - the caller owns every buffer (as the reference's Python layer does: it
+ *     allocates all map arrays and passes them in, script/spconv.py:345-352,390-403);
+ *   - nothing here allocates device memory unless stated; scratch is the caller's
+ *     `workspace` (size from the matching *_workspace_bytes query);
+ *   - all work is enqueued on `stream` (a cudaStream_t passed as void*); calls do
+ *     not synchronise unless stated;
+ *   - every function returns a pce status code and never throws.
+ *
+ * Coordinates are int32 rows (b, x, y, z), b in [0, 65534], x/y/z in
+ * [-32768, 32767]; rows must be unique.  Geometry triples use the reference's
+ * x, y, z order (script/utils.py:233-242).
+ *
+ * Paths cited as "ref:" are relative to the reference project's root.
+ */
+#ifndef PCE_B200_H_
+#define PCE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PCE_API __attribute__((visibility("default")))
+#else
+#define PCE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  PCE_OK = 0,
+  PCE_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, channel mismatch) */
+  PCE_ERR_CUDA = 2,        /* a CUDA runtime call or launch failed; see pce_last_cuda_error */
+  PCE_ERR_WORKSPACE = 3,   /* workspace smaller than the *_workspace_bytes answer */
+  PCE_ERR_RANGE = 4,       /* a coordinate lies outside the packable range */
+  PCE_ERR_TABLE_FULL = 5,  /* hash insert ran out of probes (duplicate-free input never does) */
+  PCE_ERR_UNSUPPORTED = 6, /* shape/dtype combination that no kernel covers */
+  PCE_ERR_TIMEOUT = 7,     /* a bounded device-side wait expired */
+  PCE_ERR_CAPACITY = 8     /* an output buffer's stated capacity is too small */
+};
+
+enum { PCE_F32 = 0, PCE_F16 = 1 };
+enum { PCE_ACT_NONE = 0, PCE_ACT_RELU = 1, PCE_ACT_LEAKY = 2 };
+/* which convolution kernel family pce_conv_fwd may use */
+enum { PCE_KERNEL_AUTO = 0, PCE_KERNEL_SIMT = 1, PCE_KERNEL_UMMA = 2 };
+
+/* Layer geometry; replaces the integer codes 94273*x + 311*y + z that the
+ * reference decodes again in C++ (ref: backend/hash.cu:57-76). */
+typedef struct pce_geom {
+  int32_t ks[3];
+  int32_t stride[3];
+  int32_t pad[3];
+  int32_t cmin[3];     /* output-coordinate lower bound (ref: script/spconv.py:339) */
+  int32_t cmax[3];     /* output-coordinate upper bound (ref: script/spconv.py:355-360) */
+  int32_t submanifold; /* 1: outputs are the inputs, centre offset kept apart */
+} pce_geom;
+
+/* Fused epilogue applied to the fp32 accumulator before the single store of an
+ * output row: y = act(acc * scale[c] + shift[c] + residual[row][c]).
+ * Replaces the separate passes of ref: script/batchnorm.py:7-11,
+ * script/activation.py:6-15, the bias add at script/spconv.py:325,453 and the
+ * residual add of script/sptensor.py:80-91.  Any pointer may be NULL. */
+typedef struct pce_epilogue {
+  const float* scale;   /* [c_out] */
+  const float* shift;   /* [c_out] */
+  const void* residual; /* [n_out, c_out], same dtype as the features */
+  int32_t act;
+  float slope;
+} pce_epilogue;
+
+PCE_API const char* pce_strerror(int status);
+PCE_API int pce_version(void);
+/* cudaError_t of the most recent failing CUDA call made by this library on the
+ * calling thread (0 if none). */
+PCE_API int pce_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ maps -- */
+
+/* Scratch bytes needed by the map-building calls below for n_in inputs. */
+PCE_API size_t pce_map_workspace_bytes(int32_t n_in, int32_t kv, int32_t n_out_cap);
+
+/* Output coordinates of a strided convolution: the unique, ascending-(b,x,y,z)
+ * set of (in + pad - k) / stride that divide exactly and lie in [cmin, cmax].
+ * Replaces coordsDownsampleExpand + thrust remove/sort/unique + coordsGenerator
+ * (ref: backend/hash.cuh:535-641, backend/hash.cu:141-175,364-398); the same rule
+ * is used when ks == stride, where the reference's shortcut (hash.cu:333-362)
+ * disagrees with its own query kernel.  out_coords has room for out_cap rows.
+ * SYNCHRONISES `stream` once to return *n_out_host (the reference does the same
+ * through thrust's end pointer). */
+PCE_API int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom* g,
+                          void* workspace, size_t workspace_bytes,
+                          int32_t* out_coords, int32_t out_cap, int32_t* n_out_host, void* stream);
+
+/* The fetch-on-demand map (ref: HashMapD2, backend/hash.cu:258-435, declared at
+ * backend/hash.h:37-58): map[kp*n_in + in] = out or -1, knnz[kv], kpos[kv+1],
+ * qkpos[kv+1] (segments padded to 128, ref: backend/hash.cuh:478-497).  Buffers need
+ * no initialisation.  For a submanifold map pass out_coords = in_coords; the centre
+ * offset row of `map` is left at -1 as in the reference.  map_out (optional, may
+ * be NULL) receives the transposed table map_out[kp*n_out + out] = in or -1.
+ * `status` (optional) is a device int that receives PCE_ERR_RANGE / TABLE_FULL. */
+PCE_API int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32_t* out_coords, int32_t n_out,
+                     const pce_geom* g, void* workspace, size_t workspace_bytes,
+                     int32_t* map, int32_t* knnz, int32_t* kpos, int32_t* qkpos,
+                     int32_t* map_out, int32_t* status, void* stream);
+
+/* Indicator -> pair lists ordered by (kp, in): the device form of
+ * `nonzero(map != -1)`, `omap = map[idx]`, `imap = idx % n_in`
+ * (ref: script/spconv.py:370-372).  Lists have room for pair_cap entries; the
+ * pair count is kpos[kv]. */
+PCE_API int pce_map_pairs(const int32_t* map, int32_t kv, int32_t n_in, void* workspace, size_t workspace_bytes,
+                  int32_t* imap, int32_t* omap, int32_t pair_cap, void* stream);
+
+/* The CSR-coded gather/scatter map (ref: HashMapD1, backend/hash.cu:20-255,
+ * declared at backend/hash.h:11-34) derived from the two dense tables:
+ * icsr[n_in+1] / ocsr[n_out+1] row pointers and row entries kp*1186111 + pos,
+ * kp-ascending, where pos is the pair's index inside its offset's segment of
+ * the (kp, in)-ordered pair list (the reference takes pos from an atomic
+ * counter, ref: backend/hash.cuh:161-165, so only this canonical numbering is
+ * reproducible).  map_out may be NULL for a submanifold map. */
+PCE_API int pce_map_build_d1(const int32_t* map, const int32_t* map_out, int32_t kv, int32_t n_in, int32_t n_out,
+                     int32_t submanifold, const int32_t* kpos, void* workspace, size_t workspace_bytes,
+                     int32_t* imap_coded, int32_t* icsr, int32_t* omap_coded, int32_t* ocsr, void* stream);
+
+/* Row-major neighbour lists + indicator bitmask from a dense table
+ * table[kp*n_rows + row] (-1 absent): mask[n_rows * ceil(kv/32)], rowptr[n_rows+1],
+ * nbr[<= nbr_cap] (kp-ascending per row).  reverse_kp reads table[(kv-1-kp)*n_rows+row]
+ * (a submanifold map is its own transpose under kp -> kv-1-kp); identity_kp >= 0
+ * adds the pair (row, identity_kp, row), which is how the centre offset that
+ * the reference applies as a separate dense GEMM (ref: backend/spconv.cu:273-298)
+ * is folded in.  This is the form pce_conv_fwd consumes; the reference has no
+ * literal bitmask, its indicator is the -1 sentinel of `map`. */
+PCE_API int pce_csr_from_dense(const int32_t* table, int32_t kv, int32_t n_rows, int32_t reverse_kp,
+                       int32_t identity_kp, void* workspace, size_t workspace_bytes,
+                       uint32_t* mask, int32_t* rowptr, int32_t* nbr, int32_t nbr_cap, void* stream);
+
+/* Same output as pce_csr_from_dense, built from (kp, in)-ordered pair lists as
+ * the reference's forward takes them (ref: backend/spconv.h:28-40); used by the
+ * drop-in conv_fwd_d2_cuda, which receives nothing else.  rows = the side that
+ * becomes the output, nbrs = the other side; n_pairs is a host value. */
+PCE_API int pce_csr_from_pairs(const int32_t* rows, const int32_t* nbrs, const int32_t* kpos, int32_t kv,
+                       int32_t n_pairs, int32_t n_rows, int32_t identity_kp,
+                       void* workspace, size_t workspace_bytes,
+                       uint32_t* mask, int32_t* rowptr, int32_t* nbr, int32_t nbr_cap, void* stream);
+PCE_API size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_rows);
+
+/* ----------------------------------------------------------- convolution -- */
+
+/* Fused gather-matmul-scatter, output stationary: every output row is
+ * accumulated in registers / tensor memory over its neighbour list and stored
+ * once, with the epilogue applied; no atomics and no intermediate buffer.
+ * Replaces ConvolutionForwardD2 and its kernel family
+ * (ref: backend/spconv.cu:224-398, backend/spconv.cuh:427-735,832-935,1162-1413,
+ * 1567-1730) including the centre-offset cuBLAS call and the zero fill of
+ * script/spconv.py:247.  weights [kv, c_in, c_out] as the reference's `kernel`
+ * parameter (ref: script/spconv.py:61-65).  fp16 features accumulate in fp32. */
+PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
+                 int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
+                 int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
+                 int32_t kernel_choice, void* stream);
+
+/* Explicit gather -> GEMM -> scatter over a caller-provided buffer of at least
+ * qsum*(c_in+c_out) elements (ref: ConvolutionForwardD1, backend/spconv.cu:24-222,
+ * declared at backend/spconv.h:11-25; buffer sizing script/spconv.py:426-429).
+ * Takes the CSR-coded maps of pce_map_build_d1; centre_kp >= 0 adds in @ W[centre_kp]
+ * (the reference's cuBLAS beta=1 call, backend/spconv.cu:163-221) inside the
+ * scatter pass.  Products are stored in the feature dtype in the buffer and
+ * summed in fp32. */
+PCE_API int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
+                            int32_t c_out, const int32_t* qkpos, int32_t qsum, const int32_t* imap_coded,
+                            const int32_t* icsr, const int32_t* omap_coded, const int32_t* ocsr, int32_t n_out,
+                            void* buffer, size_t buffer_bytes, void* out_feats, int32_t dtype, int32_t centre_kp,
+                            const pce_epilogue* ep, void* stream);
+
+/* Dense rows x matrix with the same epilogue: the 1x1x1 stride-1 shortcut
+ * (ref: script/spconv.py:297-304). */
+PCE_API int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights, int32_t c_out,
+                   void* out_feats, int32_t dtype, const pce_epilogue* ep, void* stream);
+
+/* Stand-alone y = act(x*scale + shift) over feature rows for BatchNorm / ReLU
+ * modules that were not fused into a convolution (ref: script/utils.py:141-149). */
+PCE_API int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dtype,
+                        const pce_epilogue* ep, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCE_B200_H_ */

@@ -1,0 +1,111 @@
+"""ctypes binding of libpce_b200.so (the C ABI declared in include/pce_b200.h).
+
+There is no CPU fallback: importing this module without the built library, or
+calling into it without a CUDA device, raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpce_b200.so")
+
+PCE_OK = 0
+PCE_ERR_INVALID = 1
+PCE_F32, PCE_F16 = 0, 1
+ACT_NONE, ACT_RELU, ACT_LEAKY = 0, 1, 2
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_UMMA = 0, 1, 2
+
+EXPORTS = [
+    "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_map_workspace_bytes", "pce_downsample_coords",
+    "pce_map_build_d2", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
+    "pce_csr_from_pairs_workspace_bytes", "pce_conv_fwd", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
+]
+
+
+class Geom(C.Structure):
+    _fields_ = [("ks", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("pad", C.c_int32 * 3),
+                ("cmin", C.c_int32 * 3), ("cmax", C.c_int32 * 3), ("submanifold", C.c_int32)]
+
+
+class Epilogue(C.Structure):
+    _fields_ = [("scale", C.c_void_p), ("shift", C.c_void_p), ("residual", C.c_void_p),
+                ("act", C.c_int32), ("slope", C.c_float)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python pcengine_b200/csrc/build.py` "
+            "(nvcc, sm_100a). pcengine_b200 has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+    lib.pce_strerror.restype = C.c_char_p
+    lib.pce_strerror.argtypes = [C.c_int]
+    lib.pce_version.restype = C.c_int
+    lib.pce_last_cuda_error.restype = C.c_int
+    lib.pce_map_workspace_bytes.restype = sz
+    lib.pce_map_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.pce_downsample_coords.argtypes = [vp, i32, C.POINTER(Geom), vp, sz, vp, i32, C.POINTER(i32), vp]
+    lib.pce_map_build_d2.argtypes = [vp, i32, vp, i32, C.POINTER(Geom), vp, sz, vp, vp, vp, vp, vp, vp, vp]
+    lib.pce_map_pairs.argtypes = [vp, i32, i32, vp, sz, vp, vp, i32, vp]
+    lib.pce_map_build_d1.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, sz, vp, vp, vp, vp, vp]
+    lib.pce_csr_from_dense.argtypes = [vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
+    lib.pce_csr_from_pairs.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
+    lib.pce_csr_from_pairs_workspace_bytes.restype = sz
+    lib.pce_csr_from_pairs_workspace_bytes.argtypes = [i32, i32]
+    lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, i32, i32, vp, vp, vp, i32, vp, i32, C.POINTER(Epilogue), i32, vp]
+    lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
+                                    C.POINTER(Epilogue), vp]
+    lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, i32, vp, i32, C.POINTER(Epilogue), vp]
+    lib.pce_scale_shift_act.argtypes = [vp, i64, i32, vp, i32, C.POINTER(Epilogue), vp]
+    for name in EXPORTS:
+        fn = getattr(lib, name)
+        if fn.restype is C.c_int and name not in ("pce_version", "pce_last_cuda_error"):
+            fn.restype = C.c_int
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int, what: str = "") -> None:
+    """Raise like the reference's pybind layer does: invalid arguments become
+    ValueError (std::invalid_argument, backend/spconv.cu:39,234), the rest RuntimeError."""
+    if status == PCE_OK:
+        return
+    msg = f"{what}: {lib.pce_strerror(status).decode()} (status {status}"
+    if status == 2:
+        msg += f", cudaError {lib.pce_last_cuda_error()}"
+    msg += ")"
+    if status == PCE_ERR_INVALID:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def require_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"pcengine_b200: `{name}` must be a CUDA tensor; there is no CPU path")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return PCE_F32
+    if dt == torch.float16:
+        return PCE_F16
+    raise NotImplementedError(f"pcengine_b200 supports float32 and float16 features, got {dt}")
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)

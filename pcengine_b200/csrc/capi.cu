@@ -1,0 +1,51 @@
+// C-ABI entry points that dispatch between kernel families, plus the status
+// helpers.  See include/pce_b200.h for the contract of every function.
+#include "common.cuh"
+
+namespace pce {
+int conv_simt(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
+              int cin, int cout, int kv, void* out, int dtype, const pce_epilogue* ep, bool ident, cudaStream_t st);
+bool conv_umma_supported(int cin, int cout, int dtype);
+int conv_umma(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
+              int cin, int cout, int kv, void* out, const pce_epilogue* ep, cudaStream_t st);
+}  // namespace pce
+
+using namespace pce;
+
+extern "C" {
+
+const char* pce_strerror(int status) {
+  switch (status) {
+    case PCE_OK: return "ok";
+    case PCE_ERR_INVALID: return "invalid argument";
+    case PCE_ERR_CUDA: return "CUDA runtime error";
+    case PCE_ERR_WORKSPACE: return "workspace too small";
+    case PCE_ERR_RANGE: return "coordinate outside the packable range";
+    case PCE_ERR_TABLE_FULL: return "hash table full";
+    case PCE_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case PCE_ERR_TIMEOUT: return "bounded device wait expired";
+    case PCE_ERR_CAPACITY: return "output capacity too small";
+    default: return "unknown status";
+  }
+}
+
+int pce_version(void) { return 100; }
+
+int pce_last_cuda_error(void) { return g_last_cuda_error; }
+
+int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv, int32_t c_out,
+                 const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, int32_t n_out, void* out_feats,
+                 int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice, void* stream) {
+  if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1) return PCE_ERR_INVALID;
+  if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
+  if (n_out == 0) return PCE_OK;
+  if (!weights || !mask || !rowptr || !out_feats || (n_in > 0 && (!in_feats || !nbr))) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bool umma_ok = conv_umma_supported(c_in, c_out, dtype);
+  if (kernel_choice == PCE_KERNEL_UMMA && !umma_ok) return PCE_ERR_UNSUPPORTED;
+  bool use_umma = umma_ok && kernel_choice != PCE_KERNEL_SIMT;
+  if (use_umma) return conv_umma(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, ep, st);
+  return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
+}
+
+}  // extern "C"

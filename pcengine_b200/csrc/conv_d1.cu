@@ -1,0 +1,168 @@
+// Explicit gather -> GEMM -> scatter dataflow over a caller-provided buffer
+// (role of ConvolutionForwardD1, ref: backend/spconv.cu:24-222).  Buffer rows
+// are addressed as qkpos[kp] + pos with (kp, pos) decoded from the CSR-coded
+// maps (kp*1186111 + pos, ref: backend/hash.cuh:7-9); row/element offsets are
+// 64-bit.  The scatter pass sums each output row's products in kp order, adds
+// the centre offset product for a submanifold layer, applies the fused
+// epilogue and stores the row once.
+#include "common.cuh"
+
+namespace pce {
+
+struct EpiDev {
+  const float* scale;
+  const float* shift;
+  const void* residual;
+  int act;
+  float slope;
+};
+__device__ __forceinline__ float d1_to_f(float v) { return v; }
+__device__ __forceinline__ float d1_to_f(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T d1_from_f(float v);
+template <>
+__device__ __forceinline__ float d1_from_f<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __half d1_from_f<__half>(float v) {
+  return __float2half_rn(v);
+}
+
+constexpr int kCode = 1186111;
+
+// One warp per input row: copy the row to every buffer slot its CSR entries name
+// (ref: backend/spconv.cuh:48-81 gather_all_input_major_csr_*).
+template <typename T>
+__global__ void k_d1_gather(const T* __restrict__ in, int n_in, int cin, const int* __restrict__ qkpos,
+                            const int* __restrict__ icsr, const int* __restrict__ imap, T* __restrict__ buf) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n_in) return;
+  const int a = __ldg(icsr + warp), b = __ldg(icsr + warp + 1);
+  const T* src = in + static_cast<size_t>(warp) * cin;
+  for (int e = a; e < b; ++e) {
+    const int code = __ldg(imap + e);
+    const size_t pos = static_cast<size_t>(__ldg(qkpos + code / kCode)) + code % kCode;
+    T* dst = buf + pos * cin;
+    for (int c = lane; c < cin; c += 32) dst[c] = src[c];
+  }
+}
+
+// buf_out[row] = buf_in[row] @ W[segment(row)] for every padded row; four
+// output channels per thread, G threads per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    k_d1_gemm(const T* __restrict__ bin, const T* __restrict__ w, const int* __restrict__ qkpos, int kv, int qsum,
+              int cin, int cout, T* __restrict__ bout, int g_threads) {
+  const int rows_per_block = blockDim.x / g_threads;
+  const int row = blockIdx.x * rows_per_block + threadIdx.x / g_threads;
+  const int g = threadIdx.x % g_threads;
+  if (row >= qsum) return;
+  int lo = 0, hi = kv;  // largest kp with qkpos[kp] <= row
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (__ldg(qkpos + mid) <= row)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  const T* wk = w + static_cast<size_t>(lo) * cin * cout;
+  const T* x = bin + static_cast<size_t>(row) * cin;
+  for (int co0 = g * 4; co0 < cout; co0 += g_threads * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ci = 0; ci < cin; ++ci) {
+      const float xv = d1_to_f(x[ci]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (co0 + j < cout) acc[j] = fmaf(xv, d1_to_f(wk[static_cast<size_t>(ci) * cout + co0 + j]), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (co0 + j < cout) bout[static_cast<size_t>(row) * cout + co0 + j] = d1_from_f<T>(acc[j]);
+  }
+}
+
+// One thread per (output row, channel): fp32 sum over the row's buffer rows,
+// plus the centre product, then the epilogue
+// (ref: backend/spconv.cuh:337-422 scatter_all_output_major_csr_*).
+template <typename T>
+__global__ void k_d1_scatter(const T* __restrict__ bout, const int* __restrict__ qkpos,
+                             const int* __restrict__ ocsr, const int* __restrict__ omap, int n_out, int cout,
+                             const T* __restrict__ in, const T* __restrict__ wmid, int cin, T* __restrict__ out,
+                             EpiDev ep) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int row = static_cast<int>(t / cout);
+  const int c = static_cast<int>(t % cout);
+  if (row >= n_out) return;
+  float acc = 0.f;
+  const int a = __ldg(ocsr + row), b = __ldg(ocsr + row + 1);
+  for (int e = a; e < b; ++e) {
+    const int code = __ldg(omap + e);
+    const size_t pos = static_cast<size_t>(__ldg(qkpos + code / kCode)) + code % kCode;
+    acc += d1_to_f(bout[pos * cout + c]);
+  }
+  if (wmid != nullptr) {
+    const T* x = in + static_cast<size_t>(row) * cin;
+    for (int ci = 0; ci < cin; ++ci) acc = fmaf(d1_to_f(x[ci]), d1_to_f(wmid[static_cast<size_t>(ci) * cout + c]), acc);
+  }
+  if (ep.scale) acc *= __ldg(ep.scale + c);
+  if (ep.shift) acc += __ldg(ep.shift + c);
+  if (ep.residual) acc += d1_to_f(static_cast<const T*>(ep.residual)[static_cast<size_t>(row) * cout + c]);
+  if (ep.act == PCE_ACT_RELU) acc = acc > 0.f ? acc : 0.f;
+  if (ep.act == PCE_ACT_LEAKY) acc = acc > 0.f ? acc : acc * ep.slope;
+  out[static_cast<size_t>(row) * cout + c] = d1_from_f<T>(acc);
+}
+
+template <typename T>
+static int run_d1(const void* in, int n_in, int cin, const void* w, int kv, int cout, const int* qkpos, int qsum,
+                  const int* imap, const int* icsr, const int* omap, const int* ocsr, int n_out, void* buffer,
+                  void* out, int centre_kp, const EpiDev& ep, cudaStream_t st) {
+  T* bin = static_cast<T*>(buffer);
+  T* bout = bin + static_cast<size_t>(qsum) * cin;
+  const T* in_t = static_cast<const T*>(in);
+  const T* w_t = static_cast<const T*>(w);
+  if (n_in > 0 && qsum > 0) {
+    k_d1_gather<T><<<div_up(static_cast<long long>(n_in) * 32, 256), 256, 0, st>>>(in_t, n_in, cin, qkpos, icsr, imap,
+                                                                                    bin);
+    PCE_LAUNCH_CHECK();
+    int need = (cout + 3) / 4, g = 1;
+    while (g < need && g < 32) g <<= 1;
+    k_d1_gemm<T><<<div_up(qsum, 256 / g), 256, 0, st>>>(bin, w_t, qkpos, kv, qsum, cin, cout, bout, g);
+    PCE_LAUNCH_CHECK();
+  }
+  if (n_out > 0) {
+    const T* wmid = centre_kp >= 0 ? w_t + static_cast<size_t>(centre_kp) * cin * cout : nullptr;
+    k_d1_scatter<T><<<div_up(static_cast<long long>(n_out) * cout, 256), 256, 0, st>>>(
+        bout, qkpos, ocsr, omap, n_out, cout, in_t, wmid, cin, static_cast<T*>(out), ep);
+    PCE_LAUNCH_CHECK();
+  }
+  return PCE_OK;
+}
+
+}  // namespace pce
+
+using namespace pce;
+
+extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
+                               int32_t c_out, const int32_t* qkpos, int32_t qsum, const int32_t* imap_coded,
+                               const int32_t* icsr, const int32_t* omap_coded, const int32_t* ocsr, int32_t n_out,
+                               void* buffer, size_t buffer_bytes, void* out_feats, int32_t dtype, int32_t centre_kp,
+                               const pce_epilogue* ep, void* stream) {
+  if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1 || qsum < 0) return PCE_ERR_INVALID;
+  if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
+  if (n_out == 0) return PCE_OK;
+  if (!weights || !out_feats || !qkpos || !ocsr || !icsr) return PCE_ERR_INVALID;
+  if (qsum > 0 && (!imap_coded || !omap_coded || !buffer || !in_feats)) return PCE_ERR_INVALID;
+  if (centre_kp >= kv || (centre_kp >= 0 && n_in != n_out)) return PCE_ERR_INVALID;
+  const size_t esize = dtype == PCE_F32 ? 4 : 2;
+  if (static_cast<size_t>(qsum) * (c_in + c_out) * esize > buffer_bytes) return PCE_ERR_WORKSPACE;
+  EpiDev e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
+  if (ep) e = EpiDev{ep->scale, ep->shift, ep->residual, ep->act, ep->slope};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PCE_F32)
+    return run_d1<float>(in_feats, n_in, c_in, weights, kv, c_out, qkpos, qsum, imap_coded, icsr, omap_coded, ocsr,
+                         n_out, buffer, out_feats, centre_kp, e, st);
+  return run_d1<__half>(in_feats, n_in, c_in, weights, kv, c_out, qkpos, qsum, imap_coded, icsr, omap_coded, ocsr,
+                        n_out, buffer, out_feats, centre_kp, e, st);
+}

@@ -1,0 +1,610 @@
+// Kernel-map construction for sm_100a: coordinate hash table on 64-bit packed
+// (b,x,y,z) keys, input-major neighbour query, per-offset scans, and the
+// derived forms (pair lists, CSR-coded gather/scatter maps, neighbour CSR with
+// indicator bitmask).  Replaces backend/hash.cu + backend/hash.cuh of the
+// reference and the tensor post-pass of script/spconv.py:370-376.
+//
+// Table layout: 16-byte slots {u64 key, i32 value, i32 pad}; a probe is one
+// 16-byte load, so a lookup that hits on its first slot costs one L2 access
+// (the tables are 1-70 MB and live in the 126 MB L2).  Linear probing on a
+// power-of-two table at load <= 0.5; every probe loop is bounded by the table
+// size and reports PCE_ERR_TABLE_FULL through the status word instead of
+// spinning.
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
+
+#include "common.cuh"
+
+namespace pce {
+
+thread_local int g_last_cuda_error = 0;
+
+struct __align__(16) Slot {
+  unsigned long long key;
+  int val;
+  int pad;
+};
+
+struct GeomDev {
+  int ks[3], st[3], pd[3], lo[3], hi[3];
+  int subm, kv, mid;
+};
+
+static GeomDev to_dev(const pce_geom* g) {
+  GeomDev d;
+  for (int i = 0; i < 3; ++i) {
+    d.ks[i] = g->ks[i];
+    d.st[i] = g->stride[i];
+    d.pd[i] = g->pad[i];
+    d.lo[i] = g->cmin[i];
+    d.hi[i] = g->cmax[i];
+  }
+  d.subm = g->submanifold;
+  d.kv = g->ks[0] * g->ks[1] * g->ks[2];
+  d.mid = (g->ks[0] - 1) / 2 * g->ks[1] * g->ks[2] + (g->ks[1] - 1) / 2 * g->ks[2] + (g->ks[2] - 1) / 2;
+  return d;
+}
+
+static unsigned table_size_for(long long n) {
+  unsigned t = 1024;
+  while (static_cast<long long>(t) < 2 * n) t <<= 1;
+  return t;
+}
+
+// Offset of weight index kp (x slowest).  Submanifold: centred
+// (ref: backend/hash.cuh:313-315); strided: +1 for odd sizes above one
+// (ref: backend/hash.cuh:396-401).
+__device__ __forceinline__ void offset_of(const GeomDev& g, int kp, int& kx, int& ky, int& kz) {
+  kx = kp / (g.ks[2] * g.ks[1]) - (g.ks[0] - 1) / 2;
+  ky = (kp / g.ks[2]) % g.ks[1] - (g.ks[1] - 1) / 2;
+  kz = kp % g.ks[2] - (g.ks[2] - 1) / 2;
+  if (!g.subm) {
+    kx += (g.ks[0] % 2 == 0 || g.ks[0] == 1) ? 0 : 1;
+    ky += (g.ks[1] % 2 == 0 || g.ks[1] == 1) ? 0 : 1;
+    kz += (g.ks[2] % 2 == 0 || g.ks[2] == 1) ? 0 : 1;
+  }
+}
+
+// The output voxel that input (x,y,z) feeds through offset kp, if any:
+// (in + pad - k) / stride, exact, inside [lo, hi]
+// (ref: backend/hash.cuh:591-604; for a submanifold map stride = 1, pad = 0 and
+// the bounds do not apply, ref: backend/hash.cuh:313-319 read from the input side).
+__device__ __forceinline__ bool candidate(const GeomDev& g, int kp, int x, int y, int z, int& qx, int& qy,
+                                          int& qz) {
+  int kx, ky, kz;
+  offset_of(g, kp, kx, ky, kz);
+  if (g.subm) {
+    qx = x - kx;
+    qy = y - ky;
+    qz = z - kz;
+    return true;
+  }
+  int cx = x - kx + g.pd[0], cy = y - ky + g.pd[1], cz = z - kz + g.pd[2];
+  qx = cx / g.st[0];
+  qy = cy / g.st[1];
+  qz = cz / g.st[2];
+  if (qx < g.lo[0] || qx > g.hi[0] || cx % g.st[0] != 0) return false;
+  if (qy < g.lo[1] || qy > g.hi[1] || cy % g.st[1] != 0) return false;
+  if (qz < g.lo[2] || qz > g.hi[2] || cz % g.st[2] != 0) return false;
+  return true;
+}
+
+__device__ __forceinline__ Slot load_slot(const Slot* t, unsigned s) {
+  const int4 v = __ldg(reinterpret_cast<const int4*>(t) + s);
+  Slot r;
+  r.key = (static_cast<unsigned long long>(static_cast<unsigned>(v.y)) << 32) | static_cast<unsigned>(v.x);
+  r.val = v.z;
+  r.pad = v.w;
+  return r;
+}
+
+// Returns the value stored for `key`, or -1.
+__device__ __forceinline__ int table_find(const Slot* t, unsigned tmask, unsigned long long key) {
+  unsigned s = static_cast<unsigned>(mix64(key)) & tmask;
+  for (unsigned n = 0; n <= tmask; ++n) {
+    Slot sl = load_slot(t, s);
+    if (sl.key == key) return sl.val;
+    if (sl.key == kEmptyKey) return -1;
+    s = (s + 1) & tmask;
+  }
+  return -1;
+}
+
+// Claims a slot for `key`.  Returns the slot index, sets `fresh` when this
+// call inserted the key; returns 0xFFFFFFFF when the table is full.
+__device__ __forceinline__ unsigned table_claim(Slot* t, unsigned tmask, unsigned long long key, bool& fresh) {
+  unsigned s = static_cast<unsigned>(mix64(key)) & tmask;
+  fresh = false;
+  for (unsigned n = 0; n <= tmask; ++n) {
+    unsigned long long prev = atomicCAS(&t[s].key, kEmptyKey, key);
+    if (prev == kEmptyKey) {
+      fresh = true;
+      return s;
+    }
+    if (prev == key) return s;
+    s = (s + 1) & tmask;
+  }
+  return 0xFFFFFFFFu;
+}
+
+// ---- kernels ---------------------------------------------------------------
+
+// value = row index (duplicate coordinates are outside the contract; the largest row wins).
+__global__ void k_insert_rows(const int4* __restrict__ coords, int n, Slot* table, unsigned tmask, int* status) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int4 c = __ldg(coords + i);
+  if (!packable(c.x, c.y, c.z, c.w)) {
+    atomicMax(status, PCE_ERR_RANGE);
+    return;
+  }
+  bool fresh;
+  unsigned s = table_claim(table, tmask, pack_key(c.x, c.y, c.z, c.w), fresh);
+  if (s == 0xFFFFFFFFu) {
+    atomicMax(status, PCE_ERR_TABLE_FULL);
+    return;
+  }
+  (void)fresh;
+  atomicMax(&table[s].val, i);  // slots start at -1; duplicate rows keep the largest index
+}
+
+// Strided output coordinates, step 1: every valid candidate is inserted into a
+// set; first-time keys are appended to ukeys (unordered).
+__global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev g, Slot* table, unsigned tmask,
+                             unsigned long long* ukeys, int ucap, int* counter, int* status) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int kp = blockIdx.y;
+  if (i >= n_in) return;
+  int4 c = __ldg(coords + i);
+  int qx, qy, qz;
+  if (!candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) return;
+  if (!packable(c.x, qx, qy, qz)) {
+    atomicMax(status, PCE_ERR_RANGE);
+    return;
+  }
+  unsigned long long key = pack_key(c.x, qx, qy, qz);
+  bool fresh;
+  unsigned s = table_claim(table, tmask, key, fresh);
+  if (s == 0xFFFFFFFFu) {
+    atomicMax(status, PCE_ERR_TABLE_FULL);
+    return;
+  }
+  if (fresh) {
+    int pos = atomicAdd(counter, 1);
+    if (pos < ucap)
+      ukeys[pos] = key;
+    else
+      atomicMax(status, PCE_ERR_CAPACITY);
+  }
+}
+
+__global__ void k_decode_keys(const unsigned long long* __restrict__ keys, int n, int4* coords) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int b, x, y, z;
+  unpack_key(keys[i], b, x, y, z);
+  coords[i] = make_int4(b, x, y, z);
+}
+
+// Input-major query: one thread per (input row, offset).  Writes the dense
+// indicator table map[kp][in] (= the reference's D2 `map`), optionally the
+// transposed table map_out[kp][out], and per-offset hit counts.
+__global__ void k_query(const int4* __restrict__ in_coords, int n_in, GeomDev g, const Slot* __restrict__ table,
+                        unsigned tmask, int* __restrict__ map, int* __restrict__ map_out, int n_out,
+                        int* knnz, int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int kp = blockIdx.y;
+  int res = -1;
+  if (i < n_in && !(g.subm && kp == g.mid)) {
+    int4 c = __ldg(in_coords + i);
+    int qx, qy, qz;
+    if (candidate(g, kp, c.y, c.z, c.w, qx, qy, qz) && packable(c.x, qx, qy, qz)) {
+      res = table_find(table, tmask, pack_key(c.x, qx, qy, qz));
+    }
+  }
+  if (i < n_in) map[static_cast<size_t>(kp) * n_in + i] = res;
+  if (res >= 0 && map_out != nullptr) map_out[static_cast<size_t>(kp) * n_out + res] = i;
+  int cnt = __syncthreads_count(res >= 0);
+  if (threadIdx.x == 0 && cnt) atomicAdd(&knnz[kp], cnt);
+}
+
+// kpos / qkpos (segments padded to 128), kv+1 entries each
+// (ref: backend/hash.cuh:478-497).
+__global__ void k_offset_scans(const int* __restrict__ knnz, int kv, int* kpos, int* qkpos) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int a = 0, q = 0;
+    kpos[0] = 0;
+    qkpos[0] = 0;
+    for (int k = 0; k < kv; ++k) {
+      a += knnz[k];
+      q += (knnz[k] + 127) / 128 * 128;
+      kpos[k + 1] = a;
+      qkpos[k + 1] = q;
+    }
+  }
+}
+
+struct FlagOf {
+  const int* map;
+  __host__ __device__ int operator()(const int& idx) const { return map[idx] != -1 ? 1 : 0; }
+};
+
+__global__ void k_flags(const int* __restrict__ map, long long n, int* flags) {
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) flags[i] = map[i] != -1 ? 1 : 0;
+}
+
+__global__ void k_emit_pairs(const int* __restrict__ map, const int* __restrict__ rank, int kv, int n_in,
+                             int* imap, int* omap, int cap) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int kp = blockIdx.y;
+  if (i >= n_in) return;
+  size_t idx = static_cast<size_t>(kp) * n_in + i;
+  int o = map[idx];
+  if (o < 0) return;
+  int p = rank[idx];
+  if (p < cap) {
+    imap[p] = i;
+    omap[p] = o;
+  }
+}
+
+// Row-wise passes over a dense [kv][n_rows] table.
+//   MODE 0: neighbour CSR     value = the table entry (or the row itself for identity_kp)
+//   MODE 1: coded input rows  value = kp*1186111 + rank[kp][row] - kpos[kp]
+//   MODE 2: coded output rows value = kp*1186111 + rank[kp][entry] - kpos[kp]
+struct RowArgs {
+  const int* table;
+  int kv, n_rows, reverse, identity_kp;
+  const int* rank;  // [kv][n_in] global pair index (modes 1, 2)
+  const int* kpos;
+  int n_in;
+};
+
+__device__ __forceinline__ int row_entry(const RowArgs& a, int kp, int r) {
+  if (kp == a.identity_kp) return r;
+  int src = a.reverse ? (a.kv - 1 - kp) : kp;
+  return a.table[static_cast<size_t>(src) * a.n_rows + r];
+}
+
+__global__ void k_row_count(RowArgs a, uint32_t* mask, int* counts) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r > a.n_rows) return;
+  if (r == a.n_rows) {
+    counts[r] = 0;
+    return;
+  }
+  const int words = (a.kv + 31) / 32;
+  int cnt = 0;
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = 0;
+    int kend = min(32, a.kv - w * 32);
+    for (int b = 0; b < kend; ++b) {
+      if (row_entry(a, w * 32 + b, r) >= 0) m |= (1u << b);
+    }
+    cnt += __popc(m);
+    if (mask) mask[static_cast<size_t>(r) * words + w] = m;
+  }
+  counts[r] = cnt;
+}
+
+template <int MODE>
+__global__ void k_row_fill(RowArgs a, const int* __restrict__ rowptr, int* out, int cap) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= a.n_rows) return;
+  int p = rowptr[r];
+  for (int kp = 0; kp < a.kv; ++kp) {
+    int v = row_entry(a, kp, r);
+    if (v < 0) continue;
+    int val;
+    if (MODE == 0) {
+      val = v;
+    } else {
+      int in_row = (MODE == 1) ? r : v;
+      val = kp * 1186111 + a.rank[static_cast<size_t>(kp) * a.n_in + in_row] - a.kpos[kp];
+    }
+    if (p < cap) out[p] = val;
+    ++p;
+  }
+}
+
+// Pair lists -> sortable (row, index) arrays with the identity pairs spliced in
+// at the centre offset so that a stable sort by row keeps kp ascending.
+__global__ void k_pairs_keys(const int* __restrict__ rows, const int* __restrict__ kpos, int n_pairs, int n_rows,
+                             int identity_kp, int* keys, int* vals) {
+  int e = blockIdx.x * blockDim.x + threadIdx.x;
+  int total = n_pairs + (identity_kp >= 0 ? n_rows : 0);
+  if (e >= total) return;
+  int row;
+  if (identity_kp >= 0) {
+    int km = kpos[identity_kp];
+    if (e < km)
+      row = rows[e];
+    else if (e < km + n_rows)
+      row = e - km;
+    else
+      row = rows[e - n_rows];
+  } else {
+    row = rows[e];
+  }
+  keys[e] = row;
+  vals[e] = e;
+}
+
+__global__ void k_pairs_rows(const int* __restrict__ skeys, const int* __restrict__ svals,
+                             const int* __restrict__ nbrs, const int* __restrict__ kpos, int kv, int n_pairs,
+                             int n_rows, int identity_kp, uint32_t* mask, int* counts, int* nbr, int cap) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  int total = n_pairs + (identity_kp >= 0 ? n_rows : 0);
+  if (j >= total) return;
+  int row = skeys[j];
+  int e = svals[j];
+  int kp, v;
+  int km = identity_kp >= 0 ? kpos[identity_kp] : 0;
+  int p = e;
+  bool ident = false;
+  if (identity_kp >= 0) {
+    if (e >= km && e < km + n_rows) {
+      ident = true;
+    } else if (e >= km + n_rows) {
+      p = e - n_rows;
+    }
+  }
+  if (ident) {
+    kp = identity_kp;
+    v = row;
+  } else {
+    // largest kp with kpos[kp] <= p
+    int lo = 0, hi = kv;
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (kpos[mid] <= p)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    kp = lo;
+    v = nbrs[p];
+  }
+  const int words = (kv + 31) / 32;
+  atomicOr(&mask[static_cast<size_t>(row) * words + (kp >> 5)], 1u << (kp & 31));
+  atomicAdd(&counts[row], 1);
+  if (j < cap) nbr[j] = v;
+}
+
+// ---- host helpers ------------------------------------------------------------
+
+static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, cudaStream_t st) {
+  size_t need = 0;
+  PCE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, in, out, static_cast<int>(n), st));
+  char* tmp = ar.take<char>(need);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, need, in, out, static_cast<int>(n), st));
+  return PCE_OK;
+}
+
+}  // namespace pce
+
+using namespace pce;
+
+extern "C" {
+
+size_t pce_map_workspace_bytes(int32_t n_in, int32_t kv, int32_t n_out_cap) {
+  long long n = n_in > n_out_cap ? n_in : n_out_cap;
+  if (n < 1) n = 1;
+  size_t table = sizeof(Slot) * static_cast<size_t>(table_size_for(n));
+  size_t keys = 2 * pad256(sizeof(unsigned long long) * static_cast<size_t>(n));
+  size_t dense = 2 * pad256(sizeof(int) * static_cast<size_t>(kv) * static_cast<size_t>(n_in > 0 ? n_in : 1));
+  size_t counts = 2 * pad256(sizeof(int) * (static_cast<size_t>(n) + 1));
+  size_t cub_tmp = 16ull * static_cast<size_t>(n) + (static_cast<size_t>(kv) * n_in) / 64 + (8u << 20);
+  return table + keys + dense + counts + cub_tmp + 4096;
+}
+
+int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom* g, void* workspace,
+                          size_t workspace_bytes, int32_t* out_coords, int32_t out_cap, int32_t* n_out_host,
+                          void* stream) {
+  if (!in_coords || !g || !out_coords || !n_out_host || n_in < 0 || out_cap < 0) return PCE_ERR_INVALID;
+  for (int i = 0; i < 3; ++i)
+    if (g->ks[i] < 1 || g->stride[i] < 1) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  *n_out_host = 0;
+  if (n_in == 0) return PCE_OK;
+  GeomDev gd = to_dev(g);
+  gd.subm = 0;
+  Arena ar(workspace, workspace_bytes);
+  unsigned tsize = table_size_for(out_cap);
+  Slot* table = ar.take<Slot>(tsize);
+  unsigned long long* ukeys = ar.take<unsigned long long>(out_cap);
+  unsigned long long* skeys = ar.take<unsigned long long>(out_cap);
+  int* ctr = ar.take<int>(64);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * tsize, st));
+  PCE_CUDA(cudaMemsetAsync(ctr, 0, 2 * sizeof(int), st));
+  dim3 grid(div_up(n_in, 256), gd.kv);
+  k_candidates<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, ukeys,
+                                     out_cap, ctr, ctr + 1);
+  PCE_LAUNCH_CHECK();
+  int host[2] = {0, 0};
+  PCE_CUDA(cudaMemcpyAsync(host, ctr, sizeof(host), cudaMemcpyDeviceToHost, st));
+  PCE_CUDA(cudaStreamSynchronize(st));
+  if (host[1] != 0) return host[1];
+  int n_out = host[0];
+  if (n_out > out_cap) return PCE_ERR_CAPACITY;
+  *n_out_host = n_out;
+  if (n_out == 0) return PCE_OK;
+  size_t need = 0;
+  PCE_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, need, ukeys, skeys, n_out, 0, 64, st));
+  char* tmp = ar.take<char>(need);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cub::DeviceRadixSort::SortKeys(tmp, need, ukeys, skeys, n_out, 0, 64, st));
+  k_decode_keys<<<div_up(n_out, 256), 256, 0, st>>>(skeys, n_out, reinterpret_cast<int4*>(out_coords));
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32_t* out_coords, int32_t n_out,
+                     const pce_geom* g, void* workspace, size_t workspace_bytes, int32_t* map, int32_t* knnz,
+                     int32_t* kpos, int32_t* qkpos, int32_t* map_out, int32_t* status, void* stream) {
+  if (!g || !knnz || !kpos || !qkpos || n_in < 0 || n_out < 0) return PCE_ERR_INVALID;
+  if ((n_in > 0 && (!in_coords || !map)) || (n_out > 0 && !out_coords)) return PCE_ERR_INVALID;
+  for (int i = 0; i < 3; ++i)
+    if (g->ks[i] < 1 || g->stride[i] < 1) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GeomDev gd = to_dev(g);
+  if (static_cast<long long>(gd.kv) * n_in >= (1ll << 31)) return PCE_ERR_UNSUPPORTED;
+  Arena ar(workspace, workspace_bytes);
+  unsigned tsize = table_size_for(n_out);
+  Slot* table = ar.take<Slot>(tsize);
+  int* st_word = status ? status : ar.take<int>(64);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cudaMemsetAsync(knnz, 0, sizeof(int) * gd.kv, st));
+  if (!status) PCE_CUDA(cudaMemsetAsync(st_word, 0, sizeof(int), st));
+  if (n_in > 0 && n_out > 0) {
+    PCE_CUDA(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * tsize, st));
+    if (map_out) PCE_CUDA(cudaMemsetAsync(map_out, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_out, st));
+    k_insert_rows<<<div_up(n_out, 256), 256, 0, st>>>(reinterpret_cast<const int4*>(out_coords), n_out, table,
+                                                      tsize - 1, st_word);
+    PCE_LAUNCH_CHECK();
+    dim3 grid(div_up(n_in, 256), gd.kv);
+    k_query<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                  map_out, n_out, knnz, st_word);
+    PCE_LAUNCH_CHECK();
+  } else if (n_in > 0) {
+    PCE_CUDA(cudaMemsetAsync(map, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_in, st));
+  }
+  k_offset_scans<<<1, 32, 0, st>>>(knnz, gd.kv, kpos, qkpos);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int pce_map_pairs(const int32_t* map, int32_t kv, int32_t n_in, void* workspace, size_t workspace_bytes,
+                  int32_t* imap, int32_t* omap, int32_t pair_cap, void* stream) {
+  if (kv < 1 || n_in < 0 || pair_cap < 0) return PCE_ERR_INVALID;
+  if (n_in == 0 || pair_cap == 0) return PCE_OK;
+  if (!map || !imap || !omap) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long total = static_cast<long long>(kv) * n_in;
+  if (total >= (1ll << 31)) return PCE_ERR_UNSUPPORTED;
+  Arena ar(workspace, workspace_bytes);
+  int* flags = ar.take<int>(total);
+  int* rank = ar.take<int>(total);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  k_flags<<<div_up(total, 256), 256, 0, st>>>(map, total, flags);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, flags, rank, total, st));
+  dim3 grid(div_up(n_in, 256), kv);
+  k_emit_pairs<<<grid, 256, 0, st>>>(map, rank, kv, n_in, imap, omap, pair_cap);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int pce_map_build_d1(const int32_t* map, const int32_t* map_out, int32_t kv, int32_t n_in, int32_t n_out,
+                     int32_t submanifold, const int32_t* kpos, void* workspace, size_t workspace_bytes,
+                     int32_t* imap_coded, int32_t* icsr, int32_t* omap_coded, int32_t* ocsr, void* stream) {
+  if (kv < 1 || n_in < 0 || n_out < 0 || !kpos || !icsr || !ocsr) return PCE_ERR_INVALID;
+  if (!submanifold && !map_out && n_out > 0) return PCE_ERR_INVALID;
+  if (submanifold && n_in != n_out) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_in == 0 || n_out == 0) {
+    PCE_CUDA(cudaMemsetAsync(icsr, 0, sizeof(int) * (n_in + 1), st));
+    PCE_CUDA(cudaMemsetAsync(ocsr, 0, sizeof(int) * (n_out + 1), st));
+    return PCE_OK;
+  }
+  if (!map || !imap_coded || !omap_coded) return PCE_ERR_INVALID;
+  long long total = static_cast<long long>(kv) * n_in;
+  if (total >= (1ll << 31)) return PCE_ERR_UNSUPPORTED;
+  Arena ar(workspace, workspace_bytes);
+  int* flags = ar.take<int>(total);
+  int* rank = ar.take<int>(total);
+  int* counts = ar.take<int>(static_cast<size_t>(n_in > n_out ? n_in : n_out) + 1);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  k_flags<<<div_up(total, 256), 256, 0, st>>>(map, total, flags);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, flags, rank, total, st));
+  const int cap = 0x7FFFFFFF;
+  // input-major rows
+  RowArgs a{map, kv, n_in, 0, -1, rank, kpos, n_in};
+  k_row_count<<<div_up(n_in + 1, 256), 256, 0, st>>>(a, nullptr, counts);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, counts, icsr, n_in + 1, st));
+  k_row_fill<1><<<div_up(n_in, 256), 256, 0, st>>>(a, icsr, imap_coded, cap);
+  PCE_LAUNCH_CHECK();
+  // output-major rows
+  RowArgs b{submanifold ? map : map_out, kv, n_out, submanifold ? 1 : 0, -1, rank, kpos, n_in};
+  k_row_count<<<div_up(n_out + 1, 256), 256, 0, st>>>(b, nullptr, counts);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, counts, ocsr, n_out + 1, st));
+  k_row_fill<2><<<div_up(n_out, 256), 256, 0, st>>>(b, ocsr, omap_coded, cap);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int pce_csr_from_dense(const int32_t* table, int32_t kv, int32_t n_rows, int32_t reverse_kp, int32_t identity_kp,
+                       void* workspace, size_t workspace_bytes, uint32_t* mask, int32_t* rowptr, int32_t* nbr,
+                       int32_t nbr_cap, void* stream) {
+  if (kv < 1 || n_rows < 0 || !rowptr || nbr_cap < 0) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0) {
+    PCE_CUDA(cudaMemsetAsync(rowptr, 0, sizeof(int), st));
+    return PCE_OK;
+  }
+  if (!table || !mask || !nbr) return PCE_ERR_INVALID;
+  Arena ar(workspace, workspace_bytes);
+  int* counts = ar.take<int>(static_cast<size_t>(n_rows) + 1);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  RowArgs a{table, kv, n_rows, reverse_kp, identity_kp, nullptr, nullptr, n_rows};
+  k_row_count<<<div_up(n_rows + 1, 256), 256, 0, st>>>(a, mask, counts);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, counts, rowptr, n_rows + 1, st));
+  k_row_fill<0><<<div_up(n_rows, 256), 256, 0, st>>>(a, rowptr, nbr, nbr_cap);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_rows) {
+  size_t total = static_cast<size_t>(n_pairs > 0 ? n_pairs : 0) + static_cast<size_t>(n_rows > 0 ? n_rows : 0) + 1;
+  return 4 * pad256(sizeof(int) * total) + pad256(sizeof(int) * (static_cast<size_t>(n_rows) + 1)) +
+         16 * total + (8u << 20);
+}
+
+int pce_csr_from_pairs(const int32_t* rows, const int32_t* nbrs, const int32_t* kpos, int32_t kv, int32_t n_pairs,
+                       int32_t n_rows, int32_t identity_kp, void* workspace, size_t workspace_bytes,
+                       uint32_t* mask, int32_t* rowptr, int32_t* nbr, int32_t nbr_cap, void* stream) {
+  if (kv < 1 || n_pairs < 0 || n_rows < 0 || !rowptr || !kpos) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_rows == 0) {
+    PCE_CUDA(cudaMemsetAsync(rowptr, 0, sizeof(int), st));
+    return PCE_OK;
+  }
+  if (!mask || !nbr || (n_pairs > 0 && (!rows || !nbrs))) return PCE_ERR_INVALID;
+  const int total = n_pairs + (identity_kp >= 0 ? n_rows : 0);
+  if (nbr_cap < total) return PCE_ERR_CAPACITY;
+  const int words = (kv + 31) / 32;
+  Arena ar(workspace, workspace_bytes);
+  int* keys = ar.take<int>(total + 1);
+  int* vals = ar.take<int>(total + 1);
+  int* skeys = ar.take<int>(total + 1);
+  int* svals = ar.take<int>(total + 1);
+  int* counts = ar.take<int>(static_cast<size_t>(n_rows) + 1);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cudaMemsetAsync(mask, 0, sizeof(uint32_t) * static_cast<size_t>(n_rows) * words, st));
+  PCE_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (static_cast<size_t>(n_rows) + 1), st));
+  if (total > 0) {
+    k_pairs_keys<<<div_up(total, 256), 256, 0, st>>>(rows, kpos, n_pairs, n_rows, identity_kp, keys, vals);
+    PCE_LAUNCH_CHECK();
+    int bits = 1;
+    while ((1ll << bits) < n_rows) ++bits;
+    size_t need = 0;
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, keys, skeys, vals, svals, total, 0, bits, st));
+    char* tmp = ar.take<char>(need);
+    if (!ar.ok) return PCE_ERR_WORKSPACE;
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, keys, skeys, vals, svals, total, 0, bits, st));
+    k_pairs_rows<<<div_up(total, 256), 256, 0, st>>>(skeys, svals, nbrs, kpos, kv, n_pairs, n_rows, identity_kp,
+                                                     mask, counts, nbr, nbr_cap);
+    PCE_LAUNCH_CHECK();
+  }
+  PCE_TRY(exclusive_scan_i32(ar, counts, rowptr, n_rows + 1, st));
+  return PCE_OK;
+}
+
+}  // extern "C"

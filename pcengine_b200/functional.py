@@ -1,0 +1,96 @@
+"""Thin tensor-level wrappers over the convolution entry points of the C ABI."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import lib
+from .kmap import NeighbourCSR
+
+_ACT = {None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "leaky": _lib.ACT_LEAKY}
+_KERNEL = {"auto": _lib.KERNEL_AUTO, "simt": _lib.KERNEL_SIMT, "umma": _lib.KERNEL_UMMA}
+
+
+class FusedEpilogue:
+    """y = act(acc*scale + shift + residual); scale/shift are fp32 [C_out] CUDA tensors."""
+
+    __slots__ = ("scale", "shift", "residual", "act", "slope")
+
+    def __init__(self, scale=None, shift=None, residual=None, act=None, slope=0.01):
+        self.scale, self.shift, self.residual, self.act, self.slope = scale, shift, residual, act, slope
+
+    def pack(self, c_out: int, n_out: int, dtype) -> _lib.Epilogue:
+        e = _lib.Epilogue()
+        for name in ("scale", "shift"):
+            t = getattr(self, name)
+            if t is not None:
+                if t.dtype != torch.float32 or not t.is_cuda or t.numel() != c_out or not t.is_contiguous():
+                    raise ValueError(f"epilogue {name} must be a contiguous fp32 CUDA tensor of {c_out} elements")
+                setattr(e, name, t.data_ptr())
+        if self.residual is not None:
+            r = self.residual
+            if r.dtype != dtype or tuple(r.shape) != (n_out, c_out) or not r.is_contiguous():
+                raise ValueError("epilogue residual must match the output's shape and dtype")
+            e.residual = r.data_ptr()
+        e.act = _ACT[self.act]
+        e.slope = float(self.slope)
+        return e
+
+
+def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype):
+    return C.byref(ep.pack(c_out, n_out, dtype)) if ep is not None else None
+
+
+def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, epilogue: Optional[FusedEpilogue] = None,
+                 kernel_choice: str = "auto") -> torch.Tensor:
+    """Fused gather-matmul-scatter over a neighbour CSR; returns [csr.n_rows, C_out]."""
+    _lib.require_cuda(feats, "feats")
+    _lib.require_cuda(kernel, "kernel")
+    if kernel.dim() == 2:
+        kernel = kernel.unsqueeze(0)
+    feats = feats.contiguous()
+    kernel = kernel.contiguous()
+    if kernel.dtype != feats.dtype:
+        kernel = kernel.to(feats.dtype)
+    if feats.size(1) != kernel.size(1):
+        raise ValueError("Input feature size and kernel size mismatch")
+    if feats.size(0) != csr.n_src:
+        raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({csr.n_src})")
+    kv, c_in, c_out = kernel.shape
+    out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), kv, c_out,
+                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), csr.n_rows,
+                                out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
+                                _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
+    return out
+
+
+def linear_forward(feats: torch.Tensor, weight: torch.Tensor, epilogue: Optional[FusedEpilogue] = None) -> torch.Tensor:
+    """feats [N,C_in] @ weight [C_in,C_out] with the fused epilogue (the 1x1x1 shortcut)."""
+    _lib.require_cuda(feats, "feats")
+    feats = feats.contiguous()
+    weight = weight.contiguous().to(feats.dtype)
+    if feats.size(1) != weight.size(0):
+        raise ValueError("Input feature size and kernel size mismatch")
+    n, c_in = feats.shape
+    c_out = weight.size(1)
+    out = torch.empty((n, c_out), dtype=feats.dtype, device=feats.device)
+    _lib.check(lib.pce_linear_fwd(feats.data_ptr(), n, c_in, weight.data_ptr(), c_out, out.data_ptr(),
+                                  _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, n, feats.dtype),
+                                  _lib.stream_ptr(feats.device)), "pce_linear_fwd")
+    return out
+
+
+def scale_shift_act(feats: torch.Tensor, epilogue: FusedEpilogue) -> torch.Tensor:
+    """Stand-alone per-channel affine + activation over feature rows."""
+    _lib.require_cuda(feats, "feats")
+    feats = feats.contiguous()
+    n, c = feats.shape
+    out = torch.empty_like(feats)
+    _lib.check(lib.pce_scale_shift_act(feats.data_ptr(), n, c, out.data_ptr(), _lib.dtype_code(feats.dtype),
+                                       _pack(epilogue, c, n, feats.dtype), _lib.stream_ptr(feats.device)),
+               "pce_scale_shift_act")
+    return out

@@ -1,0 +1,184 @@
+"""Host-side kernel-map object: owns the device arrays the C ABI fills and
+derives the other forms lazily.  Mirrors what the reference keeps per
+(kernel size, tensor stride, layer stride) in ``spTensor.kmaps``
+(script/spconv.py:333,382-384,431-433)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import lib
+
+D1_CODE = 1186111  # backend/hash.cuh:7-9
+
+
+def make_geom(ks, stride, pad, cmin, cmax, subm: bool) -> _lib.Geom:
+    g = _lib.Geom()
+    for i in range(3):
+        g.ks[i] = int(ks[i])
+        g.stride[i] = int(stride[i])
+        g.pad[i] = int(pad[i])
+        g.cmin[i] = int(cmin[i])
+        g.cmax[i] = int(cmax[i])
+    g.submanifold = 1 if subm else 0
+    return g
+
+
+def candidates_per_input(ks, stride) -> int:
+    """Upper bound on the outputs one input voxel can feed in a strided conv."""
+    n = 1
+    for k, s in zip(ks, stride):
+        n *= (k + s - 1) // s
+    return n
+
+
+class NeighbourCSR:
+    """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap]."""
+
+    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src")
+
+    def __init__(self, mask, rowptr, nbr, n_rows, n_src):
+        self.mask, self.rowptr, self.nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
+
+
+class KernelMap:
+    def __init__(self, in_coords: torch.Tensor, ks, stride, pad, cmin, cmax_out, subm: bool):
+        _lib.require_cuda(in_coords, "coords")
+        if in_coords.dtype != torch.int32 or in_coords.dim() != 2 or in_coords.size(1) != 4:
+            raise ValueError("coords must be an int32 [N,4] tensor of (b,x,y,z)")
+        in_coords = in_coords.contiguous()
+        dev = in_coords.device
+        self.device = dev
+        self.ks, self.stride, self.pad = tuple(ks), tuple(stride), tuple(pad)
+        self.subm = bool(subm)
+        self.kv = int(ks[0] * ks[1] * ks[2])
+        self.mid = (ks[0] - 1) // 2 * ks[1] * ks[2] + (ks[1] - 1) // 2 * ks[2] + (ks[2] - 1) // 2
+        self.n_in = int(in_coords.size(0))
+        self.in_coords = in_coords
+        self.geom = make_geom(ks, stride, pad, cmin, cmax_out, subm)
+        st = _lib.stream_ptr(dev)
+        kv = self.kv
+        if subm:
+            self.out_coords = in_coords
+            self.n_out = self.n_in
+            ws = _lib.workspace(lib.pce_map_workspace_bytes(self.n_in, kv, self.n_in), dev)
+        else:
+            cap = max(1, self.n_in * candidates_per_input(ks, stride))
+            ws = _lib.workspace(lib.pce_map_workspace_bytes(self.n_in, kv, cap), dev)
+            oc = torch.empty((cap, 4), dtype=torch.int32, device=dev)
+            n_out = C.c_int32(0)
+            _lib.check(lib.pce_downsample_coords(in_coords.data_ptr(), self.n_in, C.byref(self.geom), ws.data_ptr(),
+                                                 ws.numel(), oc.data_ptr(), cap, C.byref(n_out), st),
+                       "pce_downsample_coords")
+            self.n_out = int(n_out.value)
+            self.out_coords = oc[: self.n_out]
+        self.map = torch.empty((kv * self.n_in,), dtype=torch.int32, device=dev)
+        self.map_out = None if subm else torch.empty((kv * self.n_out,), dtype=torch.int32, device=dev)
+        self.knnz = torch.empty((kv,), dtype=torch.int32, device=dev)
+        self.kpos = torch.empty((kv + 1,), dtype=torch.int32, device=dev)
+        self.qkpos = torch.empty((kv + 1,), dtype=torch.int32, device=dev)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=dev)
+        _lib.check(lib.pce_map_build_d2(in_coords.data_ptr(), self.n_in, self.out_coords.data_ptr(), self.n_out,
+                                        C.byref(self.geom), ws.data_ptr(), ws.numel(), _lib.ptr(self.map),
+                                        self.knnz.data_ptr(), self.kpos.data_ptr(), self.qkpos.data_ptr(),
+                                        _lib.ptr(self.map_out), self.status.data_ptr(), st), "pce_map_build_d2")
+        self._csr: dict = {}
+        self._pairs = None
+        self._d1 = None
+        self._sizes = None
+        self.dataflow = "D2"
+
+    # -- sizes that live on the device -------------------------------------
+    def sizes(self):
+        """(pairs, qsum) read back once (one synchronisation), also validates the status word.
+        The reference reads qkpos[-1] the same way (script/spconv.py:376,421)."""
+        if self._sizes is None:
+            host = torch.stack([self.kpos[-1], self.qkpos[-1], self.status[0]]).cpu()
+            if int(host[2]) != 0:
+                _lib.check(int(host[2]), "kernel map build")
+            self._sizes = (int(host[0]), int(host[1]))
+        return self._sizes
+
+    # -- neighbour CSR + bitmask (what pce_conv_fwd consumes) ---------------
+    def csr(self, transposed: bool = False) -> NeighbourCSR:
+        key = bool(transposed)
+        if key in self._csr:
+            return self._csr[key]
+        dev, kv = self.device, self.kv
+        st = _lib.stream_ptr(dev)
+        if self.subm:
+            # out == in; the table read with kp reversed is the output-major one, and
+            # under `transposed` (roles swapped) the table itself is.
+            table, n_rows, n_src, reverse = self.map, self.n_out, self.n_in, (0 if transposed else 1)
+            ident = self.mid
+        elif transposed:
+            table, n_rows, n_src, reverse, ident = self.map, self.n_in, self.n_out, 0, -1
+        else:
+            table, n_rows, n_src, reverse, ident = self.map_out, self.n_out, self.n_in, 0, -1
+        words = (kv + 31) // 32
+        cap = max(1, kv * min(self.n_in, self.n_out) if not self.subm else kv * self.n_in)
+        if self._sizes is not None:
+            cap = max(1, self._sizes[0] + (self.n_in if self.subm else 0))
+        mask = torch.empty((max(n_rows, 1), words), dtype=torch.int32, device=dev)
+        rowptr = torch.empty((n_rows + 1,), dtype=torch.int32, device=dev)
+        nbr = torch.empty((cap,), dtype=torch.int32, device=dev)
+        ws = _lib.workspace(8 * (n_rows + 1) + (8 << 20), dev)
+        _lib.check(lib.pce_csr_from_dense(_lib.ptr(table), kv, n_rows, reverse, ident, ws.data_ptr(), ws.numel(),
+                                          mask.data_ptr(), rowptr.data_ptr(), nbr.data_ptr(), cap, st),
+                   "pce_csr_from_dense")
+        out = NeighbourCSR(mask, rowptr, nbr, n_rows, n_src)
+        self._csr[key] = out
+        return out
+
+    # -- reference forms -----------------------------------------------------
+    def pairs(self):
+        """(imap, omap) int32 [P], ordered by (kp, in): script/spconv.py:370-372."""
+        if self._pairs is None:
+            p, _ = self.sizes()
+            dev = self.device
+            imap = torch.empty((p,), dtype=torch.int32, device=dev)
+            omap = torch.empty((p,), dtype=torch.int32, device=dev)
+            ws = _lib.workspace(8 * self.kv * max(self.n_in, 1) + (16 << 20), dev)
+            _lib.check(lib.pce_map_pairs(_lib.ptr(self.map), self.kv, self.n_in, ws.data_ptr(), ws.numel(),
+                                         imap.data_ptr(), omap.data_ptr(), p, _lib.stream_ptr(dev)), "pce_map_pairs")
+            self._pairs = (imap, omap)
+        return self._pairs
+
+    def d1(self):
+        """(imap_coded [P], icsr [n_in+1], omap_coded [P], ocsr [n_out+1]): the CSR-coded
+        gather/scatter map of backend/hash.cu:20-255 with canonical positions."""
+        if self._d1 is None:
+            p, _ = self.sizes()
+            dev = self.device
+            imap_c = torch.empty((max(p, 1),), dtype=torch.int32, device=dev)
+            omap_c = torch.empty((max(p, 1),), dtype=torch.int32, device=dev)
+            icsr = torch.empty((self.n_in + 1,), dtype=torch.int32, device=dev)
+            ocsr = torch.empty((self.n_out + 1,), dtype=torch.int32, device=dev)
+            ws = _lib.workspace(8 * self.kv * max(self.n_in, 1) + 8 * (max(self.n_in, self.n_out) + 1) + (16 << 20), dev)
+            _lib.check(lib.pce_map_build_d1(_lib.ptr(self.map), _lib.ptr(self.map_out), self.kv, self.n_in, self.n_out,
+                                            1 if self.subm else 0, self.kpos.data_ptr(), ws.data_ptr(), ws.numel(),
+                                            imap_c.data_ptr(), icsr.data_ptr(), omap_c.data_ptr(), ocsr.data_ptr(),
+                                            _lib.stream_ptr(dev)), "pce_map_build_d1")
+            self._d1 = (imap_c[:p], icsr, omap_c[:p], ocsr)
+        return self._d1
+
+
+def csr_from_pairs(rows: torch.Tensor, nbrs: torch.Tensor, kpos: torch.Tensor, kv: int, n_rows: int,
+                   n_src: int, identity_kp: int = -1) -> NeighbourCSR:
+    """Neighbour CSR from (kp, in)-ordered pair lists (the only map data the reference's
+    conv_fwd_d2_cuda receives, backend/spconv.h:28-40)."""
+    dev = rows.device
+    n_pairs = int(rows.numel())
+    words = (kv + 31) // 32
+    cap = max(1, n_pairs + (n_rows if identity_kp >= 0 else 0))
+    mask = torch.empty((max(n_rows, 1), words), dtype=torch.int32, device=dev)
+    rowptr = torch.empty((n_rows + 1,), dtype=torch.int32, device=dev)
+    nbr = torch.empty((cap,), dtype=torch.int32, device=dev)
+    ws = _lib.workspace(lib.pce_csr_from_pairs_workspace_bytes(n_pairs, n_rows), dev)
+    _lib.check(lib.pce_csr_from_pairs(_lib.ptr(rows), _lib.ptr(nbrs), kpos.data_ptr(), kv, n_pairs, n_rows,
+                                      identity_kp, ws.data_ptr(), ws.numel(), mask.data_ptr(), rowptr.data_ptr(),
+                                      nbr.data_ptr(), cap, _lib.stream_ptr(dev)), "pce_csr_from_pairs")
+    return NeighbourCSR(mask, rowptr, nbr, n_rows, n_src)

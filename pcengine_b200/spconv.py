@@ -1,0 +1,160 @@
+"""``conv3d`` and ``conv_func``: the sparse-convolution operator
+(counterpart of script/spconv.py; forward / inference only).
+
+Dispatch follows script/spconv.py:291-464: a 1x1x1 stride-1 layer is a dense
+product; a transposed layer reuses the kernel map its matching strided layer
+registered, with the two sides swapped; anything else builds (or fetches) the
+map keyed by (kernel-size code, tensor-stride code, layer-stride code).
+Differences, all on the host: the map is a :class:`KernelMap` object instead of
+a list of tensors, the bias / BatchNorm / activation / residual may be fused
+into the convolution's single output store, and the tag ``'auto'`` lets the
+engine choose the dataflow.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Union
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import functional as PF
+from .functional import FusedEpilogue
+from .kmap import KernelMap
+from .sptensor import spTensor
+from .utils import conv_info_decoder, conv_info_encoder, output_stride_compute
+
+_ONES = conv_info_encoder([1, 1, 1])
+_TAGS = ("D1", "D2", "auto")
+
+
+def _triple(v, what):
+    if isinstance(v, int):
+        return [v, v, v]
+    if isinstance(v, (list, tuple)) and len(v) == 3:
+        return list(v)
+    raise NotImplementedError(f"{what} must be an int or a list of three ints")
+
+
+class conv3d(nn.Module):
+    """Sparse 3-D convolution with the reference's constructor and parameters
+    (script/spconv.py:15-106): ``kernel`` is [kv, C_in, C_out] (or [C_in, C_out] for a
+    1x1x1 kernel), ``bias`` is [C_out] or None, both initialised U(+-1/sqrt(C_out*kv))."""
+
+    def __init__(self, in_channels: int = 16, out_channels: int = 32, kernel_size: Union[int, List[int]] = 3,
+                 stride: Union[int, List[int]] = 1, padding: Union[int, List[int]] = 0, bias: bool = False,
+                 transposed: bool = False, tc_mode: bool = True) -> None:
+        super().__init__()
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.transposed = transposed
+        self.kernel_size = _triple(kernel_size, "kernel_size")
+        self.kernel_size_code = conv_info_encoder(self.kernel_size)
+        self.kernel_volume = int(np.prod(self.kernel_size, dtype=int))
+        self.stride = _triple(stride, "stride")
+        self.stride_code = conv_info_encoder(self.stride)
+        self.padding = _triple(padding, "padding")
+        self.padding_code = conv_info_encoder(self.padding)
+        self.tensorcore = tc_mode
+        shape = (self.kernel_volume, in_channels, out_channels) if self.kernel_volume > 1 else (in_channels, out_channels)
+        self.kernel = nn.Parameter(torch.zeros(shape))
+        self.bias = nn.Parameter(torch.zeros((out_channels,))) if bias else None
+        self.reset_parameters()
+
+    def extra_repr(self) -> str:
+        s = f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}"
+        if self.stride_code != _ONES:
+            s += f", stride={self.stride}"
+        if self.bias is None:
+            s += ", bias=False"
+        if self.transposed:
+            s += ", transposed=True"
+        return s
+
+    def reset_parameters(self):
+        bound = 1.0 / math.sqrt(self.out_channels * self.kernel_volume)
+        self.kernel.data.uniform_(-bound, bound)
+        if self.bias is not None:
+            self.bias.data.uniform_(-bound, bound)
+
+    def forward(self, input: spTensor, epilogue: Optional[FusedEpilogue] = None) -> spTensor:
+        return conv_func(input=input, in_channel=self.in_channels, out_channel=self.out_channels, kernel=self.kernel,
+                         kernel_size_code=self.kernel_size_code, stride_code=self.stride_code,
+                         padding_code=self.padding_code, bias=self.bias, transposed=self.transposed,
+                         tensorcore=self.tensorcore, epilogue=epilogue)
+
+
+def _with_bias(epilogue: Optional[FusedEpilogue], bias) -> Optional[FusedEpilogue]:
+    """Fold the layer bias into the epilogue: (acc + b)*s + t = acc*s + (b*s + t)."""
+    if bias is None:
+        return epilogue
+    b = bias.detach().float()
+    if epilogue is None:
+        return FusedEpilogue(shift=b.contiguous())
+    shift = b * epilogue.scale if epilogue.scale is not None else b
+    if epilogue.shift is not None:
+        shift = shift + epilogue.shift
+    return FusedEpilogue(epilogue.scale, shift.contiguous(), epilogue.residual, epilogue.act, epilogue.slope)
+
+
+def _choose_dataflow(tag: str, in_channel: int, out_channel: int) -> str:
+    if tag != "auto":
+        return tag
+    return "D2"
+
+
+def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_code, padding_code, bias, transposed,
+              tensorcore, epilogue: Optional[FusedEpilogue] = None):
+    """Run one sparse convolution on ``input`` and return the output ``spTensor``."""
+    ep = _with_bias(epilogue, bias)
+    w = kernel.detach()
+
+    if kernel_size_code == _ONES and stride_code == _ONES:
+        out_feats = PF.linear_forward(input.feats, w if w.dim() == 2 else w[0], ep)
+        output = spTensor(coords=input.coords, feats=out_feats, buffer=input.buffer, batchsize=input.batchsize,
+                          stride=input.stride, init_tag=input.init_tag, coords_max=input.coords_max,
+                          coords_min=input.coords_min)
+
+    elif transposed:
+        output_stride = output_stride_compute(stride_code, input.stride, 1)
+        kmap = input.kmaps.get((kernel_size_code, output_stride, stride_code))
+        if kmap is None or output_stride not in input.cbook:
+            raise RuntimeError("transposed conv3d needs the kernel map of its matching strided conv3d "
+                               "(same kernel size and stride) built earlier on this tensor's network")
+        out_coords = input.cbook[output_stride]
+        out_feats = PF.conv_forward(input.feats, w, kmap.csr(transposed=True), ep)
+        output = spTensor(feats=out_feats, coords=out_coords, buffer=input.buffer, batchsize=input.batchsize,
+                          stride=output_stride, init_tag=input.init_tag, coords_max=input.coords_max,
+                          coords_min=input.coords_min)
+
+    else:
+        output_stride = output_stride_compute(stride_code, input.stride, 0)
+        key = (kernel_size_code, input.stride, stride_code)
+        kmap = input.kmaps.get(key)
+        subm = stride_code == _ONES
+        coords_max = [input.coords_max[i] for i in range(3)]
+        coords_min = [input.coords_min[i] for i in range(3)]
+        ks = conv_info_decoder(kernel_size_code)
+        stride = conv_info_decoder(stride_code)
+        padding = conv_info_decoder(padding_code)
+        if not subm:
+            coords_max = [(input.coords_max[i] + 2 * padding[i] - (ks[i] - 1)) // stride[i] for i in range(3)]
+        if kmap is None:
+            tag = input.init_tag[0] if len(input.init_tag) else "end"
+            if tag not in _TAGS:
+                raise NotImplementedError(f"no dataflow tag left for a new kernel map (init_tag[0] = {tag!r})")
+            kmap = KernelMap(input.coords, ks, stride, padding, coords_min, coords_max, subm)
+            kmap.dataflow = _choose_dataflow(tag, in_channel, out_channel)
+            input.kmaps[key] = kmap
+            input.cbook[output_stride] = kmap.out_coords
+            if not (tag == "auto" and len(input.init_tag) == 1):
+                input.init_tag = input.init_tag[1:]
+        out_feats = PF.conv_forward(input.feats, w, kmap.csr(transposed=False), ep)
+        output = spTensor(feats=out_feats, coords=kmap.out_coords, buffer=input.buffer, batchsize=input.batchsize,
+                          stride=output_stride, init_tag=input.init_tag, coords_max=coords_max,
+                          coords_min=coords_min)
+
+    output.kmaps = input.kmaps
+    output.cbook = input.cbook
+    return output

@@ -1,0 +1,162 @@
+"""Feature parity of the CUDA convolutions against the CPU oracle (GPU).
+Tolerances: rel-L2 <= 1e-5 for fp32, <= 1e-3 for fp16 (fp32 accumulate)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import conv_oracle as co
+from oracle import kmap_oracle as ko
+from tests.helpers import cmax_of, random_cloud, surface_cloud
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-5, torch.float16: 1e-3}
+
+
+def _tensor(pce, coords, feats, tags=("D2", "D2", "D2", "end")):
+    dev = torch.device("cuda:0")
+    return pce.spTensor(feats.to(dev), torch.from_numpy(coords).to(dev), None, [0, 0, 0], cmax_of(coords),
+                        init_tag=list(tags))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("cin,cout", [(16, 16), (4, 32), (32, 32), (64, 64), (32, 64), (96, 96), (128, 128), (24, 19),
+                                      (3, 5)])
+@pytest.mark.parametrize("kernel_choice", ["auto", "simt"])
+def test_submanifold_features(dtype, cin, cout, kernel_choice):
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(3, 72, batch=2)
+    torch.manual_seed(1)
+    feats = torch.randn(len(coords), cin).to(dtype)
+    w = (torch.randn(27, cin, cout) / (27 * cin) ** 0.5).to(dtype)
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    out = PF.conv_forward(feats.cuda(), w.cuda(), km.csr(), None, kernel_choice)
+    ref = co.conv_forward(feats, w, d2)
+    assert co.rel_l2(out.float().cpu(), ref) <= TOL[dtype]
+    # run to run the result is bit-identical (no atomics anywhere)
+    out2 = PF.conv_forward(feats.cuda(), w.cuda(), km.csr(), None, kernel_choice)
+    assert torch.equal(out, out2)
+
+
+def test_config1_fp32_c16():
+    """The fp32 benchmark case: 20,000 voxels in 64^3, C 16->16, weights N(0, 1/(27*16))."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import synth
+    coords = synth.with_batch(synth.uniform_grid(20000, 64, 1001))
+    g = torch.Generator().manual_seed(1001)
+    feats = torch.randn(20000, 16, generator=g)
+    w = torch.randn(27, 16, 16, generator=g) / (27 * 16) ** 0.5
+    x = _tensor(pce, coords, feats)
+    conv = pce.conv3d(16, 16, 3, 1).cuda()
+    conv.kernel.data.copy_(w)
+    y = conv(x)
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    km = x.kmaps[(conv.kernel_size_code, x.stride, conv.stride_code)]
+    assert np.array_equal(km.map.cpu().numpy(), d2["map"])
+    assert co.rel_l2(y.feats.cpu(), co.conv_forward(feats, w, d2)) <= 1e-5
+    assert y.coords.data_ptr() == x.coords.data_ptr()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("ks,stride,pad,cin,cout", [(2, 2, 0, 32, 64), (3, 2, 1, 16, 32), (3, 2, 0, 8, 8)])
+def test_strided_then_transposed(dtype, ks, stride, pad, cin, cout):
+    import pcengine_b200 as pce
+    coords = random_cloud(9, 40, 9000, batch=2)
+    torch.manual_seed(2)
+    feats = torch.randn(len(coords), cin).to(dtype)
+    x = _tensor(pce, coords, feats)
+    down = pce.conv3d(cin, cout, ks, stride, pad, bias=True).cuda().to(dtype)
+    up = pce.conv3d(cout, cin, ks, stride, pad, transposed=True).cuda().to(dtype)
+    z = down(x)
+    u = up(z)
+    d2 = ko.build_d2(coords, (ks,) * 3, (stride,) * 3, (pad,) * 3, [0, 0, 0], cmax_of(coords), False)
+    assert np.array_equal(z.coords.cpu().numpy(), d2["out_coords"])
+    assert z.stride == pce.conv_info_encoder([stride] * 3) and u.stride == x.stride
+    assert list(z.coords_max) == list(d2["cmax_out"])
+    refz = co.conv_forward(feats, down.kernel.detach().cpu(), d2, bias=down.bias.detach().cpu())
+    assert co.rel_l2(z.feats.float().cpu(), refz) <= TOL[dtype]
+    refu = co.conv_forward(z.feats.cpu(), up.kernel.detach().cpu(), d2, transposed=True)
+    assert co.rel_l2(u.feats.float().cpu(), refu) <= TOL[dtype]
+    assert u.coords.data_ptr() == x.coords.data_ptr() and u.feats.shape == (len(coords), cin)
+
+
+def test_kmap_cache_and_tags():
+    import pcengine_b200 as pce
+    coords = random_cloud(4, 20, 1500)
+    feats = torch.randn(len(coords), 8)
+    x = _tensor(pce, coords, feats, tags=("D2", "end"))
+    c1 = pce.conv3d(8, 8, 3).cuda()
+    c2 = pce.conv3d(8, 8, 3).cuda()
+    y = c1(x)
+    assert y.init_tag == ["end"] and len(y.kmaps) == 1
+    z = c2(y)  # same key: cached map, no tag consumed
+    assert len(z.kmaps) == 1 and z.kmaps is x.kmaps
+    with pytest.raises(NotImplementedError):
+        pce.conv3d(8, 8, 5).cuda()(z)  # new map needed but the tag list is exhausted
+    with pytest.raises(RuntimeError):
+        pce.conv3d(8, 8, 2, 2, transposed=True).cuda()(z)  # no matching strided map
+    with pytest.raises(ValueError):
+        pce.conv3d(4, 8, 3).cuda()(z)  # channel mismatch
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_fused_epilogue_bn_relu_residual_and_modules(dtype):
+    import pcengine_b200 as pce
+    coords = surface_cloud(8, 48)
+    torch.manual_seed(5)
+    c = 32
+    feats = torch.randn(len(coords), c).to(dtype)
+    x = _tensor(pce, coords, feats)
+    conv = pce.conv3d(c, c, 3, bias=True).cuda().to(dtype)
+    bn = pce.BatchNorm(c).cuda()
+    bn.running_mean.uniform_(-0.5, 0.5)
+    bn.running_var.uniform_(0.5, 2.0)
+    bn.weight.data.uniform_(0.5, 1.5)
+    bn.bias.data.uniform_(-0.5, 0.5)
+    bn.eval()
+    relu = pce.ReLU()
+    leaky = pce.LeakyReLU(0.1)
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    raw = co.conv_forward(feats, conv.kernel.detach().cpu(), d2, bias=conv.bias.detach().cpu())
+    bnref = co.batchnorm_eval(raw, bn.weight.cpu(), bn.bias.cpu(), bn.running_mean.cpu(), bn.running_var.cpu(), bn.eps)
+    # unfused modules
+    y = relu(bn(conv(x)))
+    assert co.rel_l2(y.feats.float().cpu(), torch.relu(bnref)) <= TOL[dtype] * 2
+    y2 = leaky(bn(conv(x)))
+    assert co.rel_l2(y2.feats.float().cpu(), co.activation(bnref, "leaky", 0.1)) <= TOL[dtype] * 2
+    # fused into the convolution's store
+    scale, shift = pce.bn_scale_shift(bn)
+    res = torch.randn(len(coords), c).to(dtype)
+    ep = pce.FusedEpilogue(scale=scale, shift=shift, residual=res.cuda(), act="relu")
+    yf = conv(x, epilogue=ep)
+    assert co.rel_l2(yf.feats.float().cpu(), torch.relu(bnref + res.float())) <= TOL[dtype]
+    # cat / add keep coordinates and maps
+    s = pce.cat([y, y2])
+    assert s.feats.shape[1] == 2 * c and s.kmaps is x.kmaps
+    a = y + y2
+    assert torch.allclose(a.feats, y.feats + y2.feats)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_pointwise_conv(dtype):
+    import pcengine_b200 as pce
+    coords = random_cloud(6, 16, 1000)
+    feats = torch.randn(len(coords), 96).to(dtype)
+    x = _tensor(pce, coords, feats)
+    head = pce.conv3d(96, 19, 1, bias=True).cuda().to(dtype)
+    y = head(x)
+    ref = co.pointwise_conv(feats, head.kernel.detach().cpu(), head.bias.detach().cpu())
+    assert co.rel_l2(y.feats.float().cpu(), ref) <= TOL[dtype]
+    assert len(y.kmaps) == 0
+
+
+def test_5x5x5_submanifold_fp16():
+    import pcengine_b200 as pce
+    coords = surface_cloud(12, 40)
+    feats = torch.randn(len(coords), 64).half()
+    x = _tensor(pce, coords, feats)
+    conv = pce.conv3d(64, 64, 5).cuda().half()
+    y = conv(x)
+    d2 = ko.build_d2(coords, (5, 5, 5), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    assert co.rel_l2(y.feats.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3

@@ -1,0 +1,78 @@
+"""Host-side pieces of the operator surface that need no GPU."""
+import numpy as np
+import torch
+
+import pcengine_b200 as pce
+from oracle import kmap_oracle as ko
+from pcengine_b200 import synth
+
+
+def test_codes_round_trip_and_stride_composition():
+    for v in ([1, 1, 1], [3, 3, 3], [2, 1, 5], [0, 0, 0]):
+        assert list(pce.conv_info_decoder(pce.conv_info_encoder(v))) == v
+        assert pce.conv_info_encoder(v) == ko.encode3(v)
+    assert pce.conv_info_encoder([1, 1, 1]) == 94585  # default tensor stride of spTensor
+    s2 = pce.conv_info_encoder([2, 2, 2])
+    s4 = pce.output_stride_compute(s2, s2, 0)
+    assert pce.conv_info_decoder(s4) == (4, 4, 4)
+    assert pce.output_stride_compute(s2, s4, 1) == s2
+
+
+def test_sptensor_surface():
+    feats = torch.randn(5, 3)
+    coords = torch.tensor([[0, 1, 2, 3]] * 5, dtype=torch.int32)
+    x = pce.spTensor(feats, coords, None, [0, 0, 0], [1, 2, 3])
+    assert x.stride == 94585 and x.init_tag == ["end"] and x.batchsize == 1
+    assert x.F is feats and x.C is coords and pce.SparseTensor is pce.spTensor
+    y = x + x
+    assert torch.equal(y.feats, feats * 2) and y.kmaps is x.kmaps and y.cbook is x.cbook
+    z = pce.cat([x, y])
+    assert z.feats.shape == (5, 6)
+    r = pce.ReLU()(x)
+    assert (r.feats >= 0).all() and r.coords is coords
+    bn = pce.BatchNorm(3).eval()
+    assert pce.BatchNorm.__mro__[1] is torch.nn.BatchNorm1d
+    out = bn(x)  # CPU tensors go through nn.BatchNorm1d itself
+    assert out.feats.shape == (5, 3)
+    x.build_buffer({"in": [4], "out": [8], "kernel": [3]}, "cpu")
+    assert x.buffer.numel() == 12 * 5 * 16
+
+
+def test_conv3d_parameters_match_reference_layout():
+    c = pce.conv3d(8, 16, 3, 1, bias=True)
+    assert c.kernel.shape == (27, 8, 16) and c.bias.shape == (16,)
+    bound = 1.0 / (16 * 27) ** 0.5
+    assert float(c.kernel.abs().max()) <= bound
+    assert pce.conv3d(8, 16, 1).kernel.shape == (8, 16)
+    assert pce.conv3d(4, 4, [3, 1, 5]).kernel_volume == 15
+    assert "transposed=True" in repr(pce.conv3d(4, 4, 2, 2, transposed=True))
+    assert set(c.state_dict().keys()) == {"kernel", "bias"}
+
+
+def test_quantize_and_collate():
+    rng = np.random.default_rng(0)
+    pts = rng.uniform(0, 4, (2000, 3))
+    v, idx, inv = pce.sparse_quantize(pts, 0.5, return_index=True, return_inverse=True)
+    assert len(np.unique(v, axis=0)) == len(v) and (v[inv] == np.floor(pts / 0.5).astype(np.int32)).all()
+    a = pce.spTensor(torch.randn(len(v), 2), torch.from_numpy(v), None, [0, 0, 0], v.max(0).tolist(), init_tag=["D2", "end"])
+    b = pce.spTensor(torch.randn(len(v), 2), torch.from_numpy(v), None, [0, 0, 0], v.max(0).tolist())
+    c = pce.sparse_collate([a, b])
+    assert c.coords.shape == (2 * len(v), 4) and c.batchsize == 2 and c.init_tag == ["D2", "end"]
+    assert c.coords[:, 0].unique().tolist() == [0, 1]
+    out = pce.sparse_collate_fn([{"x": a, "y": np.zeros(3)}, {"x": b, "y": np.ones(3)}])
+    assert out["x"].batchsize == 2 and out["y"].shape == (6,)
+
+
+def test_layer_scheduler():
+    assert pce.init_layer_scheduler({"stride": [1, 1, 2], "in": [4, 32, 32], "out": [32, 32, 64]}) == "simple"
+    assert pce.init_layer_scheduler({"stride": [1, 1, 2], "in": [4, 64, 64], "out": [64, 64, 64]}) == "whole"
+
+
+def test_generators_are_seeded_and_unique():
+    a = synth.uniform_grid(20000, 64, 1001)
+    assert a.shape == (20000, 3) and len(np.unique(a, axis=0)) == 20000 and a.max() < 64
+    assert np.array_equal(a, synth.uniform_grid(20000, 64, 1001))
+    s = synth.lidar_scan(2000)
+    assert 40000 < len(s) < 130000 and s.min() == 0 and len(np.unique(s, axis=0)) == len(s)
+    r, m = synth.indoor_room(3001, 20000)
+    assert abs(len(r) - 20000) <= 600

@@ -1,0 +1,100 @@
+"""Kernel maps from the CUDA path must equal the oracle's bit for bit (GPU)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kmap_oracle as ko
+from tests.helpers import cmax_of, random_cloud, surface_cloud
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(coords, ks, stride, pad, subm):
+    import pcengine_b200 as pce
+    dev = torch.device("cuda:0")
+    cmax_in = cmax_of(coords)
+    d2 = ko.build_d2(coords, ks, stride, pad, [0, 0, 0], cmax_in, subm)
+    km = pce.KernelMap(torch.from_numpy(coords).to(dev), ks, stride, pad, [0, 0, 0], d2["cmax_out"], subm)
+    assert km.n_out == d2["n_out"]
+    assert np.array_equal(km.out_coords.cpu().numpy().reshape(-1, 4), d2["out_coords"].reshape(-1, 4))
+    assert np.array_equal(km.map.cpu().numpy(), d2["map"])
+    assert np.array_equal(km.knnz.cpu().numpy(), d2["knnz"])
+    assert np.array_equal(km.kpos.cpu().numpy(), d2["kpos"])
+    assert np.array_equal(km.qkpos.cpu().numpy(), d2["qkpos"])
+    p, q = km.sizes()
+    assert p == len(d2["imap"]) and q == d2["qsum"]
+    imap, omap = km.pairs()
+    assert np.array_equal(imap.cpu().numpy(), d2["imap"])
+    assert np.array_equal(omap.cpu().numpy(), d2["omap"])
+    d1 = ko.build_d1(d2)
+    imap_c, icsr, omap_c, ocsr = km.d1()
+    assert np.array_equal(icsr.cpu().numpy(), d1["icsr"])
+    assert np.array_equal(ocsr.cpu().numpy(), d1["ocsr"])
+    assert np.array_equal(imap_c.cpu().numpy(), d1["imap"])
+    assert np.array_equal(omap_c.cpu().numpy(), d1["omap"])
+    for tr in (False, True):
+        nb = ko.neighbour_csr(d2, transposed=tr)
+        csr = km.csr(transposed=tr)
+        total = int(nb["rowptr"][-1])
+        assert np.array_equal(csr.rowptr.cpu().numpy(), nb["rowptr"])
+        assert np.array_equal(csr.mask.cpu().numpy().view(np.uint32)[: nb["n_out"]], nb["mask"])
+        assert np.array_equal(csr.nbr.cpu().numpy()[:total], nb["nbr"])
+    # the pair-list route used by the drop-in conv entry point gives the same CSR
+    from pcengine_b200.kmap import csr_from_pairs
+    nb = ko.neighbour_csr(d2)
+    c2 = csr_from_pairs(omap, imap, km.kpos, km.kv, km.n_out, km.n_in, km.mid if subm else -1)
+    assert np.array_equal(c2.rowptr.cpu().numpy(), nb["rowptr"])
+    assert np.array_equal(c2.mask.cpu().numpy().view(np.uint32)[: nb["n_out"]], nb["mask"])
+    assert np.array_equal(c2.nbr.cpu().numpy()[: int(nb["rowptr"][-1])], nb["nbr"])
+    return d2
+
+
+@pytest.mark.parametrize("ks", [(3, 3, 3), (5, 5, 5), (2, 2, 2), (3, 1, 5), (1, 1, 1)])
+def test_submanifold_random(ks):
+    _check(random_cloud(1, 24, 3000, batch=2), ks, (1, 1, 1), (0, 0, 0), True)
+
+
+def test_submanifold_config1_shape():
+    """20,000 voxels in 64^3 (the fp32 C=16 benchmark case)."""
+    from pcengine_b200 import synth
+    coords = synth.with_batch(synth.uniform_grid(20000, 64, 1001))
+    d2 = _check(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+    assert d2["n_in"] == 20000
+
+
+def test_submanifold_surface():
+    _check(surface_cloud(4, 96, batch=2), (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+
+
+@pytest.mark.parametrize("ks,stride,pad", [((2, 2, 2), (2, 2, 2), (0, 0, 0)), ((3, 3, 3), (2, 2, 2), (0, 0, 0)),
+                                           ((3, 3, 3), (2, 2, 2), (1, 1, 1)), ((2, 2, 2), (1, 2, 2), (0, 0, 0)),
+                                           ((3, 3, 3), (3, 3, 3), (0, 0, 0)), ((2, 3, 2), (2, 1, 2), (0, 1, 0))])
+def test_strided(ks, stride, pad):
+    _check(random_cloud(2, 30, 4000, batch=2), ks, stride, pad, False)
+    _check(surface_cloud(5, 64), ks, stride, pad, False)
+
+
+def test_degenerate_inputs():
+    one = np.array([[0, 5, 5, 5]], np.int32)
+    _check(one, (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+    _check(one, (2, 2, 2), (2, 2, 2), (0, 0, 0), False)
+    # isolated voxels: no neighbour anywhere
+    iso = np.array([[0, 4 * i, 4 * j, 4 * k] for i in range(5) for j in range(5) for k in range(5)], np.int32)
+    d2 = _check(iso, (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+    assert d2["kpos"][-1] == 0
+    # fully dense block: every interior voxel has all 27
+    blk = np.array([[0, i, j, k] for i in range(9) for j in range(9) for k in range(9)], np.int32)
+    d2 = _check(blk, (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+    assert d2["knnz"][0] == 8 ** 3
+    # coordinates at zero and far out, several batches
+    far = np.array([[0, 0, 0, 0], [0, 0, 0, 1], [1, 3000, 3000, 100], [1, 3000, 3001, 100], [2, 0, 0, 0]], np.int32)
+    _check(far, (3, 3, 3), (1, 1, 1), (0, 0, 0), True)
+    _check(far, (2, 2, 2), (2, 2, 2), (0, 0, 0), False)
+
+
+def test_out_of_range_coordinate_reports_status():
+    import pcengine_b200 as pce
+    bad = torch.tensor([[0, 1, 1, 1], [0, 70000, 1, 1]], dtype=torch.int32, device="cuda:0")
+    km = pce.KernelMap(bad, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], [70000, 1, 1], True)
+    with pytest.raises(RuntimeError):
+        km.sizes()
