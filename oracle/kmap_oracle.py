@@ -62,8 +62,8 @@ def kernel_offsets(ks, strided: bool) -> np.ndarray:
     return np.stack([kx, ky, kz], axis=1).astype(np.int64)
 
 
-_BIAS = 1 << 20
-_SPAN = 1 << 21
+_BIAS = 1 << 16  # coordinates in [-65536, 65535], batch index below 4096: 3*17 + 12 = 63 bits
+_SPAN = 1 << 17
 
 
 def _pack(b, x, y, z) -> np.ndarray:

@@ -65,7 +65,8 @@ def _build_d2(in_coords, k_size_code, k_vol, l_stride_code, padding_code, mins, 
     n_out = out_coords.size(0)
     ws = _lib.workspace(lib.pce_map_workspace_bytes(n_in, k_vol, n_out), dev)
     map_out = None
-    if want_map_out and not separate_mid:
+    symmetric = bool(separate_mid) and all(k % 2 == 1 for k in ks)
+    if want_map_out and not symmetric:
         map_out = torch.empty((k_vol * max(n_out, 1),), dtype=torch.int32, device=dev)
     kpos_full = kpos if kpos.numel() >= k_vol + 1 else torch.empty((k_vol + 1,), dtype=torch.int32, device=dev)
     _lib.check(lib.pce_map_build_d2(in_coords.data_ptr(), n_in, out_coords.data_ptr(), n_out, C.byref(geom),
@@ -73,7 +74,7 @@ def _build_d2(in_coords, k_size_code, k_vol, l_stride_code, padding_code, mins, 
                                     qkpos.data_ptr(), _lib.ptr(map_out), None, st), "pce_map_build_d2")
     if kpos_full is not kpos:  # the reference's D1 caller allocates kv entries only (script/spconv.py:396)
         kpos.copy_(kpos_full[: kpos.numel()])
-    return out_coords, map_out, kpos_full, n_in, n_out
+    return out_coords, map_out, kpos_full, n_in, n_out, symmetric
 
 
 def mapping_d2_cuda(in_coords, batch_size, k_size_code, k_vol, c_in, c_out, l_stride_code, t_stride_code,
@@ -81,7 +82,7 @@ def mapping_d2_cuda(in_coords, batch_size, k_size_code, k_vol, c_in, c_out, l_st
                     kernel_qkpos, separate_mid):
     """HashMapD2 (backend/hash.h:37-58): fills ``map`` [kv*N_in], ``kernel_nnz`` [kv],
     ``kernel_kpos`` / ``kernel_qkpos`` [kv+1] in place and returns the output coordinates."""
-    out_coords, _, _, _, _ = _build_d2(in_coords, k_size_code, k_vol, l_stride_code, padding_code,
+    out_coords, _, _, _, _, _ = _build_d2(in_coords, k_size_code, k_vol, l_stride_code, padding_code,
                                        (min_x, min_y, min_z), (max_x, max_y, max_z), map, kernel_nnz, kernel_kpos,
                                        kernel_qkpos, separate_mid, False)
     return out_coords
@@ -95,7 +96,7 @@ def mapping_d1_cuda(in_coords, k_size_code, k_vol, c_in, c_out, l_stride_code, t
     dev = in_coords.device
     n_in = in_coords.size(0)
     dense = torch.empty((k_vol * max(n_in, 1),), dtype=torch.int32, device=dev)
-    out_coords, map_out, kpos_full, n_in, n_out = _build_d2(
+    out_coords, map_out, kpos_full, n_in, n_out, symmetric = _build_d2(
         in_coords, k_size_code, k_vol, l_stride_code, padding_code, (min_x, min_y, min_z), (max_x, max_y, max_z),
         dense, kernel_nnz, kernel_kpos, kernel_qkpos, separate_mid, True)
     if imap.numel() < k_vol * n_in or omap.numel() < k_vol * n_out or icsr.numel() < n_in + 1 \
@@ -103,7 +104,7 @@ def mapping_d1_cuda(in_coords, k_size_code, k_vol, c_in, c_out, l_stride_code, t
         raise ValueError("mapping_d1_cuda: a map array is smaller than the reference's allocation")
     ws = _lib.workspace(8 * k_vol * max(n_in, 1) + 8 * (max(n_in, n_out) + 1) + (16 << 20), dev)
     _lib.check(lib.pce_map_build_d1(dense.data_ptr(), _lib.ptr(map_out), k_vol, n_in, n_out,
-                                    1 if separate_mid else 0, kpos_full.data_ptr(), ws.data_ptr(), ws.numel(),
+                                    1 if symmetric else 0, kpos_full.data_ptr(), ws.data_ptr(), ws.numel(),
                                     imap.data_ptr(), icsr.data_ptr(), omap.data_ptr(), ocsr.data_ptr(),
                                     _lib.stream_ptr(dev)), "pce_map_build_d1")
     return out_coords

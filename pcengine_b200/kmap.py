@@ -76,7 +76,10 @@ class KernelMap:
             self.n_out = int(n_out.value)
             self.out_coords = oc[: self.n_out]
         self.map = torch.empty((kv * self.n_in,), dtype=torch.int32, device=dev)
-        self.map_out = None if subm else torch.empty((kv * self.n_out,), dtype=torch.int32, device=dev)
+        # A submanifold map with odd kernel sizes is its own transpose under kp -> kv-1-kp, so
+        # the output-major table is read out of `map`; otherwise it is written separately.
+        self.symmetric = self.subm and all(k % 2 == 1 for k in ks)
+        self.map_out = None if self.symmetric else torch.empty((kv * max(self.n_out, 1),), dtype=torch.int32, device=dev)
         self.knnz = torch.empty((kv,), dtype=torch.int32, device=dev)
         self.kpos = torch.empty((kv + 1,), dtype=torch.int32, device=dev)
         self.qkpos = torch.empty((kv + 1,), dtype=torch.int32, device=dev)
@@ -109,15 +112,15 @@ class KernelMap:
             return self._csr[key]
         dev, kv = self.device, self.kv
         st = _lib.stream_ptr(dev)
-        if self.subm:
-            # out == in; the table read with kp reversed is the output-major one, and
-            # under `transposed` (roles swapped) the table itself is.
+        ident = self.mid if self.subm else -1
+        if self.symmetric:
+            # the table read with kp reversed is the output-major one; under `transposed`
+            # (roles swapped) the table itself is.
             table, n_rows, n_src, reverse = self.map, self.n_out, self.n_in, (0 if transposed else 1)
-            ident = self.mid
         elif transposed:
-            table, n_rows, n_src, reverse, ident = self.map, self.n_in, self.n_out, 0, -1
+            table, n_rows, n_src, reverse = self.map, self.n_in, self.n_out, 0
         else:
-            table, n_rows, n_src, reverse, ident = self.map_out, self.n_out, self.n_in, 0, -1
+            table, n_rows, n_src, reverse = self.map_out, self.n_out, self.n_in, 0
         words = (kv + 31) // 32
         cap = max(1, kv * min(self.n_in, self.n_out) if not self.subm else kv * self.n_in)
         if self._sizes is not None:
@@ -159,7 +162,7 @@ class KernelMap:
             ocsr = torch.empty((self.n_out + 1,), dtype=torch.int32, device=dev)
             ws = _lib.workspace(8 * self.kv * max(self.n_in, 1) + 8 * (max(self.n_in, self.n_out) + 1) + (16 << 20), dev)
             _lib.check(lib.pce_map_build_d1(_lib.ptr(self.map), _lib.ptr(self.map_out), self.kv, self.n_in, self.n_out,
-                                            1 if self.subm else 0, self.kpos.data_ptr(), ws.data_ptr(), ws.numel(),
+                                            1 if self.symmetric else 0, self.kpos.data_ptr(), ws.data_ptr(), ws.numel(),
                                             imap_c.data_ptr(), icsr.data_ptr(), omap_c.data_ptr(), ocsr.data_ptr(),
                                             _lib.stream_ptr(dev)), "pce_map_build_d1")
             self._d1 = (imap_c[:p], icsr, omap_c[:p], ocsr)

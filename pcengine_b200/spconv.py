@@ -119,10 +119,12 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
     elif transposed:
         output_stride = output_stride_compute(stride_code, input.stride, 1)
         kmap = input.kmaps.get((kernel_size_code, output_stride, stride_code))
-        if kmap is None or output_stride not in input.cbook:
+        if kmap is None:
             raise RuntimeError("transposed conv3d needs the kernel map of its matching strided conv3d "
                                "(same kernel size and stride) built earlier on this tensor's network")
-        out_coords = input.cbook[output_stride]
+        # the reference reads cbook[output_stride] and fails when no layer registered that
+        # stride (script/spconv.py:309); the map itself remembers its fine side.
+        out_coords = input.cbook.get(output_stride, kmap.in_coords)
         out_feats = PF.conv_forward(input.feats, w, kmap.csr(transposed=True), ep)
         output = spTensor(feats=out_feats, coords=out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=input.coords_max,
