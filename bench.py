@@ -1,0 +1,345 @@
+"""Benchmark of the sparse-convolution hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched through torchrun)
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Workload (``config.workload`` = "minkunet_lidar_batch8"): one step is one inference pass of the
+MinkUNet-shaped network (fp16, random-init, seed 4001) over a collated batch of 8 synthetic
+64-beam LiDAR scans per GPU (seeds 2000 + 8*rank + i), kernel-map construction included.
+Every rank works on its own scans and no collective touches the data path (weak scaling).
+
+The single JSON line carries: the device-timed whole-job throughput with inputs resident in HBM
+(``value``), the same metric through host buffers with the copies inside the timed region
+(``e2e``), the roofline of the dominant convolution kernel from per-launch CUDA events recorded
+inside the timed steps, per-layer figures for the single LiDAR layers (``layers``), the CPU
+oracle timed on the host cores (``cpu_baseline``) and the GPU clocks sampled during the run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SCANS_PER_GPU = 8
+IN_CHANNELS = 4
+NUM_CLASSES = 19
+WEIGHT_SEED = 4001
+METRIC = "minkunet_scans_per_s"
+UNIT = "scans/s"
+
+
+# ----------------------------------------------------------------------------- inputs
+def make_batch(rank: int, n_scans: int = SCANS_PER_GPU):
+    """Collated int32 coords [N,4] and fp16 features [N,4] of this rank's scans (host, NumPy/torch)."""
+    from pcengine_b200 import synth
+    coords, sizes = [], []
+    for i in range(n_scans):
+        xyz = synth.lidar_scan(2000 + SCANS_PER_GPU * rank + i)
+        coords.append(synth.with_batch(xyz, i))
+        sizes.append(len(xyz))
+    coords = np.concatenate(coords)
+    g = torch.Generator().manual_seed(9000 + rank)
+    feats = torch.randn(len(coords), IN_CHANNELS, generator=g).half()
+    return coords, feats, sizes
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=float(p["hbm_gbs"]), tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def oracle_scans_per_s(rank: int, steps: int, warmup: int, n_scans: int = SCANS_PER_GPU):
+    """The CPU restatement (oracle) on ``n_scans`` of this rank's scans per step."""
+    import pcengine_b200 as pce
+    from oracle import minkunet_oracle as mo
+    torch.set_num_threads(os.cpu_count() or 1)
+    coords, feats, sizes = make_batch(rank, n_scans)
+    torch.manual_seed(WEIGHT_SEED)
+    model = pce.MinkUNet(IN_CHANNELS, NUM_CLASSES)
+    pce.randomize_batchnorm(model, WEIGHT_SEED)
+    sd = model.half().eval().state_dict()
+    for _ in range(warmup):
+        mo.forward(sd, coords, feats)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        mo.forward(sd, coords, feats)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return n_scans / dt, dt, torch.get_num_threads(), f"{n_scans} scan(s) of the batch ({sum(sizes)} voxels) per step"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    v, dt, cores, sample = oracle_scans_per_s(0, max(1, min(args.steps, 3)), min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "minkunet_lidar_batch8", "note": "CPU oracle (NumPy maps + PyTorch CPU gather-matmul-scatter, "
+                   "fp32 arithmetic on fp16 values); the reference has no CPU implementation and its CUDA build is not "
+                   "run here", "sample": sample, "timed_steps": max(1, min(args.steps, 3))},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def layer_table(dev, pk):
+    """Single LiDAR-shaped layers (one scan, seed 2000): kernel-only time per layer with an L2 flush
+    between launches; algorithmic bytes / flops per launch against the measured peaks."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    from pcengine_b200 import synth
+    xyz = synth.lidar_scan(2000)
+    coords = torch.from_numpy(synth.with_batch(xyz)).to(dev)
+    cmax = xyz.max(0).tolist()
+    n = len(xyz)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    sub = pce.KernelMap(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
+    cmax2 = [(c - 1) // 2 for c in cmax]
+    dwn = pce.KernelMap(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], cmax2, False)
+    cases = [("subm3_32x32", sub.csr(), 27, 32, 32), ("subm3_64x64", sub.csr(), 27, 64, 64),
+             ("subm3_128x128", sub.csr(), 27, 128, 128), ("down2s2_32x64", dwn.csr(), 8, 32, 64),
+             ("up2s2_64x32", dwn.csr(transposed=True), 8, 64, 32)]
+    rows = []
+    g = torch.Generator().manual_seed(5)
+    for name, csr, kv, cin, cout in cases:
+        x = torch.randn(csr.n_src, cin, generator=g).half().to(dev)
+        w = (torch.randn(kv, cin, cout, generator=g) / (kv * cin) ** 0.5).half().to(dev)
+        pairs = int(csr.rowptr[-1].item())
+        for _ in range(3):
+            PF.conv_forward(x, w, csr)
+        ts = []
+        for _ in range(10):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            PF.conv_forward(x, w, csr)
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        t = float(np.median(ts))
+        by = 2 * (csr.n_src * cin + csr.n_rows * cout) + 2 * kv * cin * cout + 4 * pairs
+        fl = 2.0 * pairs * cin * cout
+        rows.append({"layer": name, "n_in": csr.n_src, "n_out": csr.n_rows, "pairs": pairs, "us": t * 1e6,
+                     "GB/s": by / t / 1e9, "TFLOP/s": fl / t / 1e12, "hbm_frac": by / t / 1e9 / pk["hbm_gbs"],
+                     "tensor_frac": fl / t / 1e12 / pk["tflops"]})
+    return rows, n
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import pcengine_b200 as pce
+    from pcengine_b200 import _lib
+    from pcengine_b200 import functional as PF
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    pk = peaks()
+    coords_h, feats_h, sizes = make_batch(rank)
+    cmax = coords_h[:, 1:].max(0).tolist()
+    coords_pin = torch.from_numpy(coords_h).pin_memory()
+    feats_pin = feats_h.pin_memory()
+    coords_d = coords_pin.to(dev)
+    feats_d = feats_pin.to(dev)
+    torch.manual_seed(WEIGHT_SEED)
+    model = pce.MinkUNet(IN_CHANNELS, NUM_CLASSES)
+    pce.randomize_batchnorm(model, WEIGHT_SEED)
+    model = model.half().eval().to(dev)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    logits_pin = torch.empty((len(coords_h), NUM_CLASSES), dtype=torch.float16).pin_memory()
+
+    def step(c, f):
+        x = pce.spTensor(f, c, None, [0, 0, 0], cmax, batchsize=SCANS_PER_GPU, init_tag=pce.MinkUNet.tags())
+        with torch.no_grad():
+            return model(x).feats
+
+    for _ in range(max(args.warmup, 3)):
+        step(coords_d, feats_d)
+    # ---- device-resident timing ------------------------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    PF.PROFILE = []
+    launches0 = _lib.lib.pce_kernel_launches()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        flush.zero_()
+        step(coords_d, feats_d)
+    e1.record()
+    barrier()
+    dt = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+    launches = int(_lib.lib.pce_kernel_launches() - launches0)
+    prof, PF.PROFILE = PF.PROFILE, None
+    # ---- end to end: pinned host -> device, forward, logits -> pinned host -----------------
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        c = coords_pin.to(dev, non_blocking=True)
+        f = feats_pin.to(dev, non_blocking=True)
+        flush.zero_()
+        out = step(c, f)
+        logits_pin.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    dt_e2e = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.stop() if rank == 0 else None
+    # ---- roofline of the dominant convolution kernel ---------------------------------------
+    by_kernel = {}
+    for rec in prof:
+        t = rec["start"].elapsed_time(rec["end"]) * 1e-3
+        pairs = int(rec["rowptr"][-1].item())
+        e = rec["esize"]
+        byt = e * (rec["n_in"] * rec["cin"] + rec["n_out"] * rec["cout"]) + e * rec["kv"] * rec["cin"] * rec["cout"] + 4 * pairs
+        k = by_kernel.setdefault(rec["kernel"], dict(t=0.0, bytes=0.0, flops=0.0, n=0))
+        k["t"] += t
+        k["bytes"] += byt
+        k["flops"] += 2.0 * pairs * rec["cin"] * rec["cout"]
+        k["n"] += 1
+    roof = None
+    if by_kernel:
+        name, k = max(by_kernel.items(), key=lambda kv: kv[1]["t"])
+        ach = k["bytes"] / k["t"] / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+                "traffic": None, "kernel": name, "launches_timed": k["n"], "avg_launch_us": k["t"] / k["n"] * 1e6,
+                "share_of_step": k["t"] / (dt if dt > 0 else 1.0),
+                "tensor_tflops": k["flops"] / k["t"] / 1e12, "tensor_frac": k["flops"] / k["t"] / 1e12 / pk["tflops"],
+                "peak_source": pk["source"], "note": "sum of algorithmic bytes of every launch of this kernel in the "
+                "timed steps / sum of their CUDA-event durations"}
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    layers, n_one = layer_table(dev, pk)
+    cpu_v, cpu_dt, cores, sample = oracle_scans_per_s(0, 1, 1)
+    total_scans = SCANS_PER_GPU * world * args.steps
+    line = {
+        "metric": METRIC, "value": total_scans / dt, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "minkunet_lidar_batch8", "scans_per_gpu": SCANS_PER_GPU, "voxels_per_gpu": int(len(coords_h)),
+                   "voxels_per_scan": sizes, "in_channels": IN_CHANNELS, "classes": NUM_CLASSES,
+                   "widths": "32-32-64-128-256-256-128-96-96", "map_build": "inside the timed step",
+                   "l2": "192 MiB memset between steps, inside the timed region", "accumulate": "fp32"},
+        "e2e": {"value": total_scans / dt_e2e, "unit": UNIT,
+                "h2d_bytes_per_step": int(coords_pin.numel() * 4 + feats_pin.numel() * 2),
+                "d2h_bytes_per_step": int(logits_pin.numel() * 2), "ms_per_step": dt_e2e / args.steps * 1e3},
+        "gpu_launches": launches,
+        "roofline": roof,
+        "kernels": {k: {"launches": v["n"], "ms": v["t"] * 1e3} for k, v in by_kernel.items()},
+        "layers": layers,
+        "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -80,6 +80,9 @@ PCE_API int pce_version(void);
 /* cudaError_t of the most recent failing CUDA call made by this library on the
  * calling thread (0 if none). */
 PCE_API int pce_last_cuda_error(void);
+/* Number of this library's own kernels launched by the process so far (library
+ * primitives such as radix sort / scan passes and memsets are not counted). */
+PCE_API uint64_t pce_kernel_launches(void);
 
 /* ------------------------------------------------------------------ maps -- */
 
@@ -164,6 +167,10 @@ PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const
                  int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
                  int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
                  int32_t kernel_choice, void* stream);
+
+/* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
+ * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */
+PCE_API int pce_conv_kernel_choice(int32_t c_in, int32_t c_out, int32_t dtype, int32_t kernel_choice);
 
 /* Explicit gather -> GEMM -> scatter over a caller-provided buffer of at least
  * qsum*(c_in+c_out) elements (ref: ConvolutionForwardD1, backend/spconv.cu:24-222,

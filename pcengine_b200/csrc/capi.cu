@@ -33,6 +33,14 @@ int pce_version(void) { return 100; }
 
 int pce_last_cuda_error(void) { return g_last_cuda_error; }
 
+uint64_t pce_kernel_launches(void) { return __atomic_load_n(&g_kernel_launches, __ATOMIC_RELAXED); }
+
+int pce_conv_kernel_choice(int32_t c_in, int32_t c_out, int32_t dtype, int32_t kernel_choice) {
+  bool umma_ok = conv_umma_supported(c_in, c_out, dtype);
+  if (kernel_choice == PCE_KERNEL_UMMA) return umma_ok ? PCE_KERNEL_UMMA : -1;
+  return (umma_ok && kernel_choice != PCE_KERNEL_SIMT) ? PCE_KERNEL_UMMA : PCE_KERNEL_SIMT;
+}
+
 int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv, int32_t c_out,
                  const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, int32_t n_out, void* out_feats,
                  int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice, void* stream) {

@@ -11,6 +11,7 @@
 namespace pce {
 
 extern thread_local int g_last_cuda_error;
+extern unsigned long long g_kernel_launches;  // kernels of this library launched so far (all threads)
 
 inline int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
@@ -23,7 +24,11 @@ inline int cuda_fail(cudaError_t e) {
     if (e__ != cudaSuccess) return ::pce::cuda_fail(e__); \
   } while (0)
 
-#define PCE_LAUNCH_CHECK() PCE_CUDA(cudaPeekAtLastError())
+#define PCE_LAUNCH_CHECK()                                  \
+  do {                                                      \
+    __atomic_fetch_add(&::pce::g_kernel_launches, 1ull, __ATOMIC_RELAXED); \
+    PCE_CUDA(cudaPeekAtLastError());                        \
+  } while (0)
 
 #define PCE_TRY(expr)              \
   do {                             \

@@ -18,6 +18,7 @@
 namespace pce {
 
 thread_local int g_last_cuda_error = 0;
+unsigned long long g_kernel_launches = 0;
 
 struct __align__(16) Slot {
   unsigned long long key;

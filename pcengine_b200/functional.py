@@ -12,6 +12,11 @@ from .kmap import NeighbourCSR
 
 _ACT = {None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "leaky": _lib.ACT_LEAKY}
 _KERNEL = {"auto": _lib.KERNEL_AUTO, "simt": _lib.KERNEL_SIMT, "umma": _lib.KERNEL_UMMA}
+_KERNEL_NAME = {_lib.KERNEL_SIMT: "conv_simt", _lib.KERNEL_UMMA: "conv_umma"}
+
+# When set to a list, every conv_forward call appends a record with CUDA events around its
+# kernel launch (used by the benchmark to time the convolution kernels inside a model).
+PROFILE = None
 
 
 class FusedEpilogue:
@@ -61,10 +66,20 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({csr.n_src})")
     kv, c_in, c_out = kernel.shape
     out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    rec = None
+    if PROFILE is not None:
+        which = lib.pce_conv_kernel_choice(c_in, c_out, _lib.dtype_code(feats.dtype), _KERNEL[kernel_choice])
+        rec = dict(kernel=_KERNEL_NAME.get(which, "none"), n_in=feats.size(0), n_out=csr.n_rows, cin=c_in, cout=c_out,
+                   kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
+                   start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
+        rec["start"].record()
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
+    if rec is not None:
+        rec["end"].record()
+        PROFILE.append(rec)
     return out
 
 

@@ -1,0 +1,144 @@
+"""A MinkUNet-shaped segmentation network composed from the operator surface
+(conv3d / BatchNorm / ReLU / cat and residual adds).  The reference ships no model;
+this one follows the description it is benchmarked on: a 3x3x3 submanifold stem,
+four encoder stages (2x2x2 stride-2 down conv, then two residual 3x3x3 blocks), four
+decoder stages (transposed 2x2x2 up conv, skip concatenation, two residual blocks)
+and a 1x1x1 classifier.  Widths: stem 32; encoder 32, 64, 128, 256; decoder 256, 128,
+96, 96 (the width list 32-64-128-256-256-128-96-96 scaled by ``cr``).
+
+In eval mode on a CUDA tensor every BatchNorm + ReLU (+ residual add) is folded into
+the producing convolution's epilogue; in training mode or on CPU tensors the plain
+modules run.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+from torch import nn
+
+from .activation import ReLU
+from .batchnorm import BatchNorm, bn_scale_shift
+from .functional import FusedEpilogue
+from .spconv import conv3d
+from .sptensor import spTensor
+from .utils import cat
+
+
+class _Fusable(nn.Module):
+    """Caches folded BatchNorm constants while the module stays in eval mode."""
+
+    def __init__(self):
+        super().__init__()
+        self._folded = {}
+
+    def train(self, mode: bool = True):
+        self._folded = {}
+        return super().train(mode)
+
+    def _apply(self, fn, *args, **kwargs):
+        self._folded = {}
+        return super()._apply(fn, *args, **kwargs)
+
+    def _fold(self, name: str, bn: nn.BatchNorm1d):
+        if name not in self._folded:
+            self._folded[name] = bn_scale_shift(bn)
+        return self._folded[name]
+
+    def _fused(self, x: spTensor) -> bool:
+        return (not self.training) and x.feats.is_cuda
+
+
+class ConvBNReLU(_Fusable):
+    def __init__(self, cin, cout, ks=3, stride=1, transposed=False):
+        super().__init__()
+        self.conv = conv3d(cin, cout, ks, stride, transposed=transposed)
+        self.bn = BatchNorm(cout)
+        self.relu = ReLU(True)
+
+    def forward(self, x: spTensor) -> spTensor:
+        if self._fused(x):
+            s, t = self._fold("bn", self.bn)
+            return self.conv(x, epilogue=FusedEpilogue(scale=s, shift=t, act="relu"))
+        return self.relu(self.bn(self.conv(x)))
+
+
+class ResidualBlock(_Fusable):
+    def __init__(self, cin, cout, ks=3):
+        super().__init__()
+        self.conv1 = conv3d(cin, cout, ks, 1)
+        self.bn1 = BatchNorm(cout)
+        self.conv2 = conv3d(cout, cout, ks, 1)
+        self.bn2 = BatchNorm(cout)
+        self.relu = ReLU(True)
+        if cin != cout:
+            self.short_conv = conv3d(cin, cout, 1, 1)
+            self.short_bn = BatchNorm(cout)
+        else:
+            self.short_conv = None
+            self.short_bn = None
+
+    def forward(self, x: spTensor) -> spTensor:
+        if self._fused(x):
+            s1, t1 = self._fold("bn1", self.bn1)
+            y = self.conv1(x, epilogue=FusedEpilogue(scale=s1, shift=t1, act="relu"))
+            if self.short_conv is not None:
+                ss, ts = self._fold("short_bn", self.short_bn)
+                sc = self.short_conv(x, epilogue=FusedEpilogue(scale=ss, shift=ts)).feats
+            else:
+                sc = x.feats.contiguous()
+            s2, t2 = self._fold("bn2", self.bn2)
+            return self.conv2(y, epilogue=FusedEpilogue(scale=s2, shift=t2, residual=sc, act="relu"))
+        y = self.bn2(self.conv2(self.relu(self.bn1(self.conv1(x)))))
+        sc = x if self.short_conv is None else self.short_bn(self.short_conv(x))
+        return self.relu(y + sc)
+
+
+class MinkUNet(nn.Module):
+    def __init__(self, in_channels: int = 4, num_classes: int = 19, cr: float = 1.0):
+        super().__init__()
+        cs = [int(cr * c) for c in (32, 32, 64, 128, 256, 256, 128, 96, 96)]
+        self.widths = cs
+        self.stem = nn.Sequential(ConvBNReLU(in_channels, cs[0], 3), ConvBNReLU(cs[0], cs[0], 3))
+        self.down = nn.ModuleList()
+        self.enc = nn.ModuleList()
+        for i in range(4):
+            self.down.append(ConvBNReLU(cs[i], cs[i], 2, 2))
+            self.enc.append(nn.Sequential(ResidualBlock(cs[i], cs[i + 1]), ResidualBlock(cs[i + 1], cs[i + 1])))
+        self.up = nn.ModuleList()
+        self.dec = nn.ModuleList()
+        skips = [cs[3], cs[2], cs[1], cs[0]]
+        for i in range(4):
+            self.up.append(ConvBNReLU(cs[4 + i], cs[5 + i], 2, 2, transposed=True))
+            self.dec.append(nn.Sequential(ResidualBlock(cs[5 + i] + skips[i], cs[5 + i]),
+                                          ResidualBlock(cs[5 + i], cs[5 + i])))
+        self.classifier = conv3d(cs[8], num_classes, 1, 1, bias=True)
+
+    def forward(self, x: spTensor) -> spTensor:
+        feats: List[spTensor] = [self.stem(x)]
+        for i in range(4):
+            feats.append(self.enc[i](self.down[i](feats[-1])))
+        y = feats[4]
+        for i in range(4):
+            y = self.up[i](y)
+            y = self.dec[i](cat([y, feats[3 - i]]))
+        return self.classifier(y)
+
+    @staticmethod
+    def tags() -> list:
+        """Dataflow tags for the nine kernel maps a forward pass builds (five submanifold
+        resolutions, four down-sampling layers; the transposed layers reuse those)."""
+        return ["auto"]
+
+
+def randomize_batchnorm(model: nn.Module, seed: int = 0) -> None:
+    """Give every BatchNorm non-trivial running statistics and affine terms (seeded), so a
+    randomly initialised network exercises the fused epilogues."""
+    g = torch.Generator().manual_seed(seed)
+    for m in model.modules():
+        if isinstance(m, nn.BatchNorm1d):
+            n = m.num_features
+            m.running_mean.copy_((torch.rand(n, generator=g) - 0.5) * 0.2)
+            m.running_var.copy_(0.8 + 0.4 * torch.rand(n, generator=g))
+            m.weight.data.copy_(0.8 + 0.4 * torch.rand(n, generator=g))
+            m.bias.data.copy_((torch.rand(n, generator=g) - 0.5) * 0.2)
