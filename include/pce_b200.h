@@ -162,11 +162,27 @@ PCE_API size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_row
  * (ref: backend/spconv.cu:224-398, backend/spconv.cuh:427-735,832-935,1162-1413,
  * 1567-1730) including the centre-offset cuBLAS call and the zero fill of
  * script/spconv.py:247.  weights [kv, c_in, c_out] as the reference's `kernel`
- * parameter (ref: script/spconv.py:61-65).  fp16 features accumulate in fp32. */
-PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
-                 int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
-                 int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
-                 int32_t kernel_choice, void* stream);
+ * parameter (ref: script/spconv.py:61-65).  fp16 features accumulate in fp32.
+ * packed_weights (may be NULL) is the same tensor re-laid by pce_pack_weights for
+ * the tensor-core kernel; without it only the CUDA-core kernel can run.  Either
+ * `weights` or `packed_weights` may be NULL when the kernel that needs it is not
+ * the one chosen. */
+PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights,
+                         const void* packed_weights, int32_t kv, int32_t c_out, const uint32_t* mask,
+                         const int32_t* rowptr, const int32_t* nbr, int32_t n_out, void* out_feats, int32_t dtype,
+                         const pce_epilogue* ep, int32_t kernel_choice, void* stream);
+
+/* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
+ * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index
+ * (the shared-memory layout tcgen05.mma reads), zero padded in K.  Weights are
+ * static at inference, so this runs once per layer. */
+PCE_API size_t pce_packed_weights_bytes(int32_t kv, int32_t c_in, int32_t c_out);
+PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int32_t c_out, int32_t dtype,
+                             void* packed, void* stream);
+
+/* Reads (and optionally clears) the library's device status word, where a kernel whose
+ * bounded wait expired records PCE_ERR_TIMEOUT.  SYNCHRONISES the device. */
+PCE_API int pce_device_status(int32_t* status_host, int32_t reset);
 
 /* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
  * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */

@@ -143,7 +143,9 @@ def conv_fwd_d2_cuda(in_feats, kernel, ksize_code, sum_nnz, out_feats, kpos, qkp
     w = kernel.contiguous()
     if w.dtype != feats.dtype or out_feats.dtype != feats.dtype:
         raise ValueError("in_feats, kernel and out_feats must share one dtype")
-    _lib.check(lib.pce_conv_fwd(feats.data_ptr(), n_in, c_in, w.data_ptr(), kv, c_out, csr.mask.data_ptr(),
+    from .functional import packed_weights
+    _lib.check(lib.pce_conv_fwd(feats.data_ptr(), n_in, c_in, w.data_ptr(), _lib.ptr(packed_weights(w)), kv, c_out,
+                                csr.mask.data_ptr(),
                                 csr.rowptr.data_ptr(), csr.nbr.data_ptr(), n_out, out_feats.data_ptr(),
                                 _lib.dtype_code(feats.dtype), None, _lib.KERNEL_AUTO, _lib.stream_ptr(feats.device)),
                "pce_conv_fwd")

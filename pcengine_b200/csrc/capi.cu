@@ -6,6 +6,9 @@ namespace pce {
 int conv_simt(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
               int cin, int cout, int kv, void* out, int dtype, const pce_epilogue* ep, bool ident, cudaStream_t st);
 bool conv_umma_supported(int cin, int cout, int dtype);
+size_t umma_packed_bytes(int kv, int cin, int cout);
+int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
+int umma_status_fetch(int* host_status, bool reset);
 int conv_umma(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
               int cin, int cout, int kv, void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -41,18 +44,46 @@ int pce_conv_kernel_choice(int32_t c_in, int32_t c_out, int32_t dtype, int32_t k
   return (umma_ok && kernel_choice != PCE_KERNEL_SIMT) ? PCE_KERNEL_UMMA : PCE_KERNEL_SIMT;
 }
 
-int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv, int32_t c_out,
-                 const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, int32_t n_out, void* out_feats,
-                 int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice, void* stream) {
+size_t pce_packed_weights_bytes(int32_t kv, int32_t c_in, int32_t c_out) {
+  if (kv < 1 || c_in < 1 || c_out < 1) return 0;
+  return umma_packed_bytes(kv, c_in, c_out);
+}
+
+int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int32_t c_out, int32_t dtype, void* packed,
+                     void* stream) {
+  if (!weights || !packed || kv < 1) return PCE_ERR_INVALID;
+  if (!conv_umma_supported(c_in, c_out, dtype)) return PCE_ERR_UNSUPPORTED;
+  return umma_pack_weights(weights, kv, c_in, c_out, packed, static_cast<cudaStream_t>(stream));
+}
+
+int pce_device_status(int32_t* status_host, int32_t reset) {
+  if (!status_host) return PCE_ERR_INVALID;
+  int v = 0;
+  PCE_TRY(umma_status_fetch(&v, reset != 0));
+  *status_host = v;
+  return PCE_OK;
+}
+
+int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, const void* packed_weights,
+                 int32_t kv, int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
+                 int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice,
+                 void* stream) {
   if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1) return PCE_ERR_INVALID;
   if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
   if (n_out == 0) return PCE_OK;
-  if (!weights || !mask || !rowptr || !out_feats || (n_in > 0 && (!in_feats || !nbr))) return PCE_ERR_INVALID;
+  if (!mask || !rowptr || !out_feats || (n_in > 0 && (!in_feats || !nbr))) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  bool umma_ok = conv_umma_supported(c_in, c_out, dtype);
+  const bool umma_ok = conv_umma_supported(c_in, c_out, dtype) && kv <= 128;
   if (kernel_choice == PCE_KERNEL_UMMA && !umma_ok) return PCE_ERR_UNSUPPORTED;
-  bool use_umma = umma_ok && kernel_choice != PCE_KERNEL_SIMT;
-  if (use_umma) return conv_umma(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, ep, st);
+  const bool use_umma = umma_ok && kernel_choice != PCE_KERNEL_SIMT && (packed_weights || kernel_choice == PCE_KERNEL_UMMA);
+  if (use_umma) {
+    if (!packed_weights) return PCE_ERR_INVALID;
+    if ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
+         reinterpret_cast<uintptr_t>(packed_weights)) & 15)
+      return PCE_ERR_INVALID;
+    return conv_umma(in_feats, packed_weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, ep, st);
+  }
+  if (!weights) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
 }
 

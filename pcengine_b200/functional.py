@@ -49,6 +49,36 @@ def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype):
     return C.byref(ep.pack(c_out, n_out, dtype)) if ep is not None else None
 
 
+def packed_weights(kernel: torch.Tensor) -> Optional[torch.Tensor]:
+    """The tensor-core layout of ``kernel`` [kv,C_in,C_out], or None when the tensor-core kernel
+    does not cover these channel counts.  The result is cached ON the tensor object (together
+    with its version counter and address), so it lives and dies with the weights; a tensor
+    that is rebuilt on every call is simply packed again."""
+    kv, c_in, c_out = kernel.shape
+    code = _lib.dtype_code(kernel.dtype)
+    if lib.pce_conv_kernel_choice(c_in, c_out, code, _lib.KERNEL_UMMA) != _lib.KERNEL_UMMA or kv > 128:
+        return None
+    tag = (kernel._version, kernel.data_ptr(), tuple(kernel.shape))
+    hit = getattr(kernel, "_pce_packed", None)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    out = torch.empty((lib.pce_packed_weights_bytes(kv, c_in, c_out),), dtype=torch.uint8, device=kernel.device)
+    _lib.check(lib.pce_pack_weights(kernel.data_ptr(), kv, c_in, c_out, code, out.data_ptr(),
+                                    _lib.stream_ptr(kernel.device)), "pce_pack_weights")
+    try:
+        kernel._pce_packed = (tag, out)
+    except AttributeError:
+        pass
+    return out
+
+
+def device_status(reset: bool = True) -> int:
+    """The library's device status word (0 = ok); synchronises the device."""
+    v = C.c_int32(0)
+    _lib.check(lib.pce_device_status(C.byref(v), 1 if reset else 0), "pce_device_status")
+    return int(v.value)
+
+
 def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, epilogue: Optional[FusedEpilogue] = None,
                  kernel_choice: str = "auto") -> torch.Tensor:
     """Fused gather-matmul-scatter over a neighbour CSR; returns [csr.n_rows, C_out]."""
@@ -57,23 +87,23 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
     if kernel.dim() == 2:
         kernel = kernel.unsqueeze(0)
     feats = feats.contiguous()
-    kernel = kernel.contiguous()
-    if kernel.dtype != feats.dtype:
-        kernel = kernel.to(feats.dtype)
+    if not kernel.is_contiguous() or kernel.dtype != feats.dtype:
+        kernel = kernel.detach().contiguous().to(feats.dtype)
     if feats.size(1) != kernel.size(1):
         raise ValueError("Input feature size and kernel size mismatch")
     if feats.size(0) != csr.n_src:
         raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({csr.n_src})")
     kv, c_in, c_out = kernel.shape
     out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    packed = packed_weights(kernel) if kernel_choice != "simt" else None
     rec = None
     if PROFILE is not None:
-        which = lib.pce_conv_kernel_choice(c_in, c_out, _lib.dtype_code(feats.dtype), _KERNEL[kernel_choice])
+        which = _lib.KERNEL_UMMA if packed is not None else _lib.KERNEL_SIMT
         rec = dict(kernel=_KERNEL_NAME.get(which, "none"), n_in=feats.size(0), n_out=csr.n_rows, cin=c_in, cout=c_out,
                    kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
-    _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), kv, c_out,
+    _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")

@@ -108,7 +108,7 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
               tensorcore, epilogue: Optional[FusedEpilogue] = None):
     """Run one sparse convolution on ``input`` and return the output ``spTensor``."""
     ep = _with_bias(epilogue, bias)
-    w = kernel.detach()
+    w = kernel  # the Parameter itself: the packed tensor-core layout is cached on it
 
     if kernel_size_code == _ONES and stride_code == _ONES:
         out_feats = PF.linear_forward(input.feats, w if w.dim() == 2 else w[0], ep)

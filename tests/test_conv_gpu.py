@@ -160,3 +160,25 @@ def test_5x5x5_submanifold_fp16():
     y = conv(x)
     d2 = ko.build_d2(coords, (5, 5, 5), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     assert co.rel_l2(y.feats.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3
+
+
+def test_weight_repacking_follows_the_tensor():
+    """Fresh weight tensors that reuse a freed allocation, and in-place updates, must never meet
+    a stale tensor-core layout."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(2, 40)
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    x = torch.randn(len(coords), 32).half()
+    xd = x.cuda()
+    for scale in (1.0, 0.05, 3.0):
+        w = (torch.rand(27, 32, 32) * scale).half()
+        wd = w.cuda()
+        y = PF.conv_forward(xd, wd, km.csr())
+        assert co.rel_l2(y.float().cpu(), co.conv_forward(x, w, d2)) <= 1e-3
+        wd.mul_(0.5)  # in-place update bumps the version counter
+        y = PF.conv_forward(xd, wd, km.csr())
+        assert co.rel_l2(y.float().cpu(), co.conv_forward(x, w * 0.5, d2)) <= 1e-3
+        del wd, y
+    assert PF.device_status() == 0
