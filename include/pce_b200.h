@@ -113,6 +113,24 @@ PCE_API int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32
                      int32_t* map, int32_t* knnz, int32_t* kpos, int32_t* qkpos,
                      int32_t* map_out, int32_t* status, void* stream);
 
+/* pce_map_build_d2 for callers that cannot hand over a workspace and must not trigger a
+ * device allocation: a vehicle or robot perception loop whose memory is fixed at start-up
+ * and whose safety rules forbid allocating once the loop runs, or a host runtime that owns
+ * all device memory and gives a plug-in nothing but its input and output buffers.  It has
+ * no counterpart in the reference (whose map builders allocate their hash tables through
+ * ATen on every call).  Same inputs, outputs and results as pce_map_build_d2; the hash table
+ * and the fallback status word live in a 4 MiB device array inside the library image, which
+ * every GPU that loads the library holds until the process exits.
+ *   - Limit: n_out <= 131072 output rows; more returns PCE_ERR_CAPACITY and launches nothing.
+ *   - The first call on each device looks the array's address up; make that call during
+ *     set-up, before any stream capture begins.  No call allocates or frees device memory.
+ *   - All calls on a device share the array and it keeps the previous call's contents (the
+ *     part a call uses is cleared first), so two calls whose GPU work can overlap - different
+ *     streams, or threads - race on it: serialise them on one stream. */
+PCE_API int pce_map_build_d2_noalloc(const int32_t* in_coords, int32_t n_in, const int32_t* out_coords,
+                                     int32_t n_out, const pce_geom* g, int32_t* map, int32_t* knnz, int32_t* kpos,
+                                     int32_t* qkpos, int32_t* map_out, int32_t* status, void* stream);
+
 /* Indicator -> pair lists ordered by (kp, in): the device form of
  * `nonzero(map != -1)`, `omap = map[idx]`, `imap = idx % n_in`
  * (ref: script/spconv.py:370-372).  Lists have room for pair_cap entries; the

@@ -21,7 +21,7 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_UMMA = 0, 1, 2
 
 EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
-    "pce_map_build_d2", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
+    "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
     "pce_pack_weights", "pce_device_status", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
 ]
@@ -53,6 +53,7 @@ def _load() -> C.CDLL:
     lib.pce_map_workspace_bytes.argtypes = [i32, i32, i32]
     lib.pce_downsample_coords.argtypes = [vp, i32, C.POINTER(Geom), vp, sz, vp, i32, C.POINTER(i32), vp]
     lib.pce_map_build_d2.argtypes = [vp, i32, vp, i32, C.POINTER(Geom), vp, sz, vp, vp, vp, vp, vp, vp, vp]
+    lib.pce_map_build_d2_noalloc.argtypes = [vp, i32, vp, i32, C.POINTER(Geom), vp, vp, vp, vp, vp, vp, vp]
     lib.pce_map_pairs.argtypes = [vp, i32, i32, vp, sz, vp, vp, i32, vp]
     lib.pce_map_build_d1.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, sz, vp, vp, vp, vp, vp]
     lib.pce_csr_from_dense.argtypes = [vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]

@@ -478,6 +478,71 @@ int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32_t* out_
   return PCE_OK;
 }
 
+// ---- allocation-free variant of pce_map_build_d2 -----------------------------------------
+// Scratch (hash table + status word) lives in one file-scope device array instead of a
+// caller workspace.  2^18 slots of 16 bytes cover 131072 output rows at load <= 0.5; the
+// array (4 MiB + 256 B) is part of the module image, so every GPU that loads the library
+// holds it until the process exits.
+constexpr int kNoAllocMaxRows = 131072;
+constexpr unsigned kNoAllocSlots = 262144;
+constexpr size_t kNoAllocBytes = sizeof(Slot) * kNoAllocSlots + 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address:
+// the address is looked up once per device (with that device current) and kept.
+static void* g_noalloc_addr[64] = {};
+
+static int noalloc_scratch_address(void** out) {
+  int dev = -1;
+  PCE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
+  void* p = __atomic_load_n(&g_noalloc_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    PCE_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (p == nullptr) return PCE_ERR_CUDA;
+    __atomic_store_n(&g_noalloc_addr[dev], p, __ATOMIC_RELEASE);  // every thread finds the same address
+  }
+  *out = p;
+  return PCE_OK;
+}
+
+int pce_map_build_d2_noalloc(const int32_t* in_coords, int32_t n_in, const int32_t* out_coords, int32_t n_out,
+                             const pce_geom* g, int32_t* map, int32_t* knnz, int32_t* kpos, int32_t* qkpos,
+                             int32_t* map_out, int32_t* status, void* stream) {
+  if (!g || !knnz || !kpos || !qkpos || n_in < 0 || n_out < 0) return PCE_ERR_INVALID;
+  if ((n_in > 0 && (!in_coords || !map)) || (n_out > 0 && !out_coords)) return PCE_ERR_INVALID;
+  for (int i = 0; i < 3; ++i)
+    if (g->ks[i] < 1 || g->stride[i] < 1) return PCE_ERR_INVALID;
+  if (n_out > kNoAllocMaxRows) return PCE_ERR_CAPACITY;  // the built-in table holds 131072 output rows
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GeomDev gd = to_dev(g);
+  if (static_cast<long long>(gd.kv) * n_in >= (1ll << 31)) return PCE_ERR_UNSUPPORTED;
+  void* base = nullptr;
+  PCE_TRY(noalloc_scratch_address(&base));
+  Slot* table = static_cast<Slot*>(base);
+  int* st_word = status ? status : reinterpret_cast<int*>(static_cast<unsigned char*>(base) + sizeof(Slot) * kNoAllocSlots);
+  const unsigned tsize = table_size_for(n_out);  // <= kNoAllocSlots by the row limit above
+  PCE_CUDA(cudaMemsetAsync(knnz, 0, sizeof(int) * gd.kv, st));
+  if (!status) PCE_CUDA(cudaMemsetAsync(st_word, 0, sizeof(int), st));
+  if (n_in > 0 && n_out > 0) {
+    // the array keeps the previous call's table: every slot this call can probe is emptied first
+    PCE_CUDA(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * tsize, st));
+    if (map_out) PCE_CUDA(cudaMemsetAsync(map_out, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_out, st));
+    k_insert_rows<<<div_up(n_out, 256), 256, 0, st>>>(reinterpret_cast<const int4*>(out_coords), n_out, table,
+                                                      tsize - 1, st_word);
+    PCE_LAUNCH_CHECK();
+    dim3 grid(div_up(n_in, 256), gd.kv);
+    k_query<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                  map_out, n_out, knnz, st_word);
+    PCE_LAUNCH_CHECK();
+  } else if (n_in > 0) {
+    PCE_CUDA(cudaMemsetAsync(map, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_in, st));
+  }
+  k_offset_scans<<<1, 32, 0, st>>>(knnz, gd.kv, kpos, qkpos);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
 int pce_map_pairs(const int32_t* map, int32_t kv, int32_t n_in, void* workspace, size_t workspace_bytes,
                   int32_t* imap, int32_t* omap, int32_t pair_cap, void* stream) {
   if (kv < 1 || n_in < 0 || pair_cap < 0) return PCE_ERR_INVALID;
