@@ -302,8 +302,11 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
-    layers, n_one = layer_table(dev, pk)
-    cpu_v, cpu_dt, cores, sample = oracle_scans_per_s(0, 1, 1)
+    layers, cpu = None, None
+    if not args.lean:
+        layers, _ = layer_table(dev, pk)
+        cpu_v, cpu_dt, cores, sample = oracle_scans_per_s(0, 1, 1)
+        cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     total_scans = SCANS_PER_GPU * world * args.steps
     line = {
         "metric": METRIC, "value": total_scans / dt, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -320,7 +323,7 @@ def run_ours(args):
         "roofline": roof,
         "kernels": {k: {"launches": v["n"], "ms": v["t"] * 1e3} for k, v in by_kernel.items()},
         "layers": layers,
-        "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": cpu,
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -334,6 +337,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--lean", action="store_true",
+                    help="skip the per-layer table and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
