@@ -154,33 +154,47 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def layer_table(dev, pk):
-    """Single LiDAR-shaped layers (one scan, seed 2000): kernel-only time per layer with an L2 flush
-    between launches; algorithmic bytes / flops per launch against the measured peaks."""
+LAYERS = {  # name: (map kind, kv, c_in, c_out)
+    "subm3_32x32": ("subm", 27, 32, 32), "subm3_64x64": ("subm", 27, 64, 64), "subm3_128x128": ("subm", 27, 128, 128),
+    "subm3_256x256": ("subm", 27, 256, 256), "down2s2_32x64": ("down", 8, 32, 64), "up2s2_64x32": ("up", 8, 64, 32),
+}
+DEFAULT_LAYERS = ["subm3_32x32", "subm3_64x64", "subm3_128x128", "down2s2_32x64", "up2s2_64x32"]
+
+
+def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: int = 3):
+    """Single LiDAR-shaped layers on ``scans`` collated scans (seeds 2000..): kernel-only time per layer
+    with an L2 flush between launches; algorithmic bytes / flops per launch against the measured peaks."""
     import pcengine_b200 as pce
     from pcengine_b200 import functional as PF
-    from pcengine_b200 import synth
-    xyz = synth.lidar_scan(2000)
-    coords = torch.from_numpy(synth.with_batch(xyz)).to(dev)
-    cmax = xyz.max(0).tolist()
-    n = len(xyz)
+    coords_h, _, _ = make_batch(0, scans)
+    coords = torch.from_numpy(coords_h).to(dev)
+    cmax = coords_h[:, 1:].max(0).tolist()
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
-    sub = pce.KernelMap(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
-    cmax2 = [(c - 1) // 2 for c in cmax]
-    dwn = pce.KernelMap(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], cmax2, False)
-    cases = [("subm3_32x32", sub.csr(), 27, 32, 32), ("subm3_64x64", sub.csr(), 27, 64, 64),
-             ("subm3_128x128", sub.csr(), 27, 128, 128), ("down2s2_32x64", dwn.csr(), 8, 32, 64),
-             ("up2s2_64x32", dwn.csr(transposed=True), 8, 64, 32)]
+    names = list(names or DEFAULT_LAYERS)
+    maps = {}
+
+    def csr_for(kind):
+        if kind == "subm":
+            if "subm" not in maps:
+                maps["subm"] = pce.KernelMap(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
+            return maps["subm"].csr()
+        if "down" not in maps:
+            maps["down"] = pce.KernelMap(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0],
+                                         [(c - 1) // 2 for c in cmax], False)
+        return maps["down"].csr(transposed=(kind == "up"))
+
     rows = []
     g = torch.Generator().manual_seed(5)
-    for name, csr, kv, cin, cout in cases:
+    for name in names:
+        kind, kv, cin, cout = LAYERS[name]
+        csr = csr_for(kind)
         x = torch.randn(csr.n_src, cin, generator=g).half().to(dev)
         w = (torch.randn(kv, cin, cout, generator=g) / (kv * cin) ** 0.5).half().to(dev)
         pairs = int(csr.rowptr[-1].item())
-        for _ in range(3):
+        for _ in range(warmup):
             PF.conv_forward(x, w, csr)
         ts = []
-        for _ in range(10):
+        for _ in range(iters):
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -193,8 +207,19 @@ def layer_table(dev, pk):
         fl = 2.0 * pairs * cin * cout
         rows.append({"layer": name, "n_in": csr.n_src, "n_out": csr.n_rows, "pairs": pairs, "us": t * 1e6,
                      "GB/s": by / t / 1e9, "TFLOP/s": fl / t / 1e12, "hbm_frac": by / t / 1e9 / pk["hbm_gbs"],
-                     "tensor_frac": fl / t / 1e12 / pk["tflops"]})
-    return rows, n
+                     "tensor_frac": fl / t / 1e12 / pk["tflops"], "alg_bytes": by, "alg_flops": fl})
+    return rows, int(coords.size(0))
+
+
+def run_layer(args):
+    """``--layer NAME``: only that single layer on ``--scans`` collated scans (a small, short case for
+    a profiler capture).  Prints one JSON line with the kernel-only figures."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    rows, n = layer_table(dev, peaks(), [args.layer], scans=args.scans, iters=args.steps, warmup=args.warmup)
+    print(json.dumps({"workload": "single_layer", "voxels": n, "scans": args.scans, **rows[0]}))
 
 
 def run_ours(args):
@@ -337,10 +362,15 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layer", type=str, default=None, choices=sorted(LAYERS),
+                    help="run one single layer only (kernel-only timing); see --scans")
+    ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
     ap.add_argument("--lean", action="store_true",
                     help="skip the per-layer table and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.layer is not None:
+        run_layer(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -184,11 +184,22 @@ PCE_API size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_row
  * packed_weights (may be NULL) is the same tensor re-laid by pce_pack_weights for
  * the tensor-core kernel; without it only the CUDA-core kernel can run.  Either
  * `weights` or `packed_weights` may be NULL when the kernel that needs it is not
- * the one chosen. */
+ * the one chosen.  row_order (may be NULL) is a permutation of the output rows
+ * from pce_csr_sort_rows: the tensor-core kernel forms its 128-row tiles in that
+ * order so that a tile's rows share offsets; results do not depend on it. */
 PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights,
                          const void* packed_weights, int32_t kv, int32_t c_out, const uint32_t* mask,
-                         const int32_t* rowptr, const int32_t* nbr, int32_t n_out, void* out_feats, int32_t dtype,
-                         const pce_epilogue* ep, int32_t kernel_choice, void* stream);
+                         const int32_t* rowptr, const int32_t* nbr, const int32_t* row_order, int32_t n_out,
+                         void* out_feats, int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice,
+                         void* stream);
+
+/* Processing order for the tensor-core kernel: output rows sorted by their indicator
+ * bitmask (stable radix sort), so rows with the same neighbourhood pattern land in the
+ * same 128-row tile and the tile skips every offset none of them has.  Purely a
+ * scheduling aid with no reference counterpart.  order[n_rows] receives the permutation;
+ * workspace >= 24*n_rows + 8 MiB bytes. */
+PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace,
+                              size_t workspace_bytes, int32_t* order, void* stream);
 
 /* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
  * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index
@@ -221,8 +232,9 @@ PCE_API int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, co
 
 /* Dense rows x matrix with the same epilogue: the 1x1x1 stride-1 shortcut
  * (ref: script/spconv.py:297-304). */
-PCE_API int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights, int32_t c_out,
-                   void* out_feats, int32_t dtype, const pce_epilogue* ep, void* stream);
+PCE_API int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights,
+                           const void* packed_weights, int32_t c_out, void* out_feats, int32_t dtype,
+                           const pce_epilogue* ep, void* stream);
 
 /* Stand-alone y = act(x*scale + shift) over feature rows for BatchNorm / ReLU
  * modules that were not fused into a convolution (ref: script/utils.py:141-149). */

@@ -9,8 +9,9 @@ bool conv_umma_supported(int cin, int cout, int dtype);
 size_t umma_packed_bytes(int kv, int cin, int cout);
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
 int umma_status_fetch(int* host_status, bool reset);
-int conv_umma(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
-              int cin, int cout, int kv, void* out, const pce_epilogue* ep, cudaStream_t st);
+int conv_umma(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr,
+              const int* order, int n_out, int cin, int cout, int kv, void* out, const pce_epilogue* ep,
+              cudaStream_t st);
 }  // namespace pce
 
 using namespace pce;
@@ -66,8 +67,8 @@ int pce_device_status(int32_t* status_host, int32_t reset) {
 
 int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, const void* packed_weights,
                  int32_t kv, int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
-                 int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice,
-                 void* stream) {
+                 const int32_t* row_order, int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
+                 int32_t kernel_choice, void* stream) {
   if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1) return PCE_ERR_INVALID;
   if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
   if (n_out == 0) return PCE_OK;
@@ -81,10 +82,25 @@ int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* w
     if ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
          reinterpret_cast<uintptr_t>(packed_weights)) & 15)
       return PCE_ERR_INVALID;
-    return conv_umma(in_feats, packed_weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, ep, st);
+    return conv_umma(in_feats, packed_weights, mask, rowptr, nbr, row_order, n_out, c_in, c_out, kv, out_feats, ep, st);
   }
   if (!weights) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
+}
+
+
+int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights, const void* packed_weights,
+                   int32_t c_out, void* out_feats, int32_t dtype, const pce_epilogue* ep, void* stream) {
+  if (n < 0 || c_in < 1 || c_out < 1) return PCE_ERR_INVALID;
+  if (n == 0) return PCE_OK;
+  if (!in_feats || !out_feats || (!weights && !packed_weights)) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
+                         reinterpret_cast<uintptr_t>(packed_weights)) & 15) == 0;
+  if (packed_weights && aligned && conv_umma_supported(c_in, c_out, dtype))
+    return conv_umma(in_feats, packed_weights, nullptr, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, ep, st);
+  if (!weights) return PCE_ERR_INVALID;
+  return conv_simt(in_feats, weights, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, dtype, ep, true, st);
 }
 
 }  // extern "C"

@@ -234,15 +234,6 @@ using namespace pce;
 
 extern "C" {
 
-int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights, int32_t c_out,
-                   void* out_feats, int32_t dtype, const pce_epilogue* ep, void* stream) {
-  if (n < 0 || c_in < 1 || c_out < 1) return PCE_ERR_INVALID;
-  if (n == 0) return PCE_OK;
-  if (!in_feats || !weights || !out_feats) return PCE_ERR_INVALID;
-  return conv_simt(in_feats, weights, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, dtype, ep, true,
-                   static_cast<cudaStream_t>(stream));
-}
-
 int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dtype, const pce_epilogue* ep,
                         void* stream) {
   if (n < 0 || c < 1) return PCE_ERR_INVALID;

@@ -30,8 +30,7 @@ __device__ int g_umma_status = 0;
 namespace umma {
 
 constexpr int kTileM = 128;
-constexpr int kStages = 4;
-constexpr int kLookahead = 2;      // cp.async groups in flight per producer thread before arriving
+constexpr int kMaxStages = 4;
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows x 64 fp16
 constexpr int kMaxWords = 4;       // kernel volume <= 128
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s at 2 GHz
@@ -45,9 +44,9 @@ struct Epi {
 };
 
 struct SharedCtl {
-  unsigned long long afull[kStages];
-  unsigned long long bfull[kStages];
-  unsigned long long empty[kStages];
+  unsigned long long afull[kMaxStages];
+  unsigned long long bfull[kMaxStages];
+  unsigned long long empty[kMaxStages];
   unsigned long long accbar;
   uint32_t tmem_base;
   uint32_t tile_mask[kMaxWords];
@@ -176,10 +175,12 @@ __global__ void k_pack_weights(const __half* __restrict__ w, int kv, int cin, in
   }
 }
 
+// NS = pipeline stages; each producer thread keeps NS-1 cp.async groups in flight.
+template <int NS>
 __global__ void __launch_bounds__(160, 1)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, const uint32_t* __restrict__ mask,
-                const int* __restrict__ rowptr, const int* __restrict__ nbr, int n_out, int cin, int cout, int kv,
-                __half* __restrict__ out, Epi ep, int tmem_cols) {
+                const int* __restrict__ rowptr, const int* __restrict__ nbr, const int* __restrict__ order, int n_out,
+                int cin, int cout, int kv, __half* __restrict__ out, Epi ep, int tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(160, 1)
   const uint32_t tiles_addr = raw_addr + pad;
   const int b_bytes = cout * 128;
   const int stage_bytes = kABytes + b_bytes;       // both multiples of 1024
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * stage_bytes);
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + NS * stage_bytes);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(160, 1)
   const int row0 = blockIdx.x * kTileM;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl->afull[s]), 128);
       mbar_init(smem_u32(&ctl->bfull[s]), 1);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
@@ -220,11 +221,19 @@ __global__ void __launch_bounds__(160, 1)
   // ---- per-row map state (producer threads own one output row each) ----
   uint32_t my_mask[kMaxWords] = {0, 0, 0, 0};
   int cursor = 0;
-  const int my_row = row0 + tid;
+  // Output row of this thread: slot (row0 + tid) of the processing order (rows sorted by
+  // bitmask so that a tile shares offsets), or the slot itself without an order.
+  // mask == nullptr means "every row has exactly the pair (row, offset 0, row)": the dense product.
+  int my_row = n_out;  // n_out = no row
+  if (warp < 4 && row0 + tid < n_out) my_row = order ? __ldg(order + row0 + tid) : row0 + tid;
   if (warp < 4) {
     if (my_row < n_out) {
-      for (int w = 0; w < words; ++w) my_mask[w] = __ldg(mask + static_cast<size_t>(my_row) * words + w);
-      cursor = __ldg(rowptr + my_row);
+      if (mask != nullptr) {
+        for (int w = 0; w < words; ++w) my_mask[w] = __ldg(mask + static_cast<size_t>(my_row) * words + w);
+        cursor = __ldg(rowptr + my_row);
+      } else {
+        my_mask[0] = 1u;
+      }
     }
     for (int w = 0; w < words; ++w) {
       const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, my_mask[w]);
@@ -244,7 +253,9 @@ __global__ void __launch_bounds__(160, 1)
     // =========================== producers ===========================
     int j = 0;            // running stage counter
     int pending_arrive = 0;  // next stage index this thread still has to arrive on
-    int next_nid = (my_row < n_out && (my_mask[0] | my_mask[1] | my_mask[2] | my_mask[3])) ? __ldg(nbr + cursor) : -1;
+    int next_nid = -1;
+    if (my_row < n_out && (my_mask[0] | my_mask[1] | my_mask[2] | my_mask[3]))
+      next_nid = mask != nullptr ? __ldg(nbr + cursor) : my_row;
     const int rsub = lane >> 3;   // row inside a 4-row group
     const int chunk = lane & 7;   // 16-byte chunk inside a 128-byte row
     bool ok = true;
@@ -262,11 +273,11 @@ __global__ void __launch_bounds__(160, 1)
           uint32_t rest = my_mask[w] & ~((2u << bit) - 1u);
           bool more = rest != 0;
           for (int w2 = w + 1; w2 < words; ++w2) more |= my_mask[w2] != 0;
-          next_nid = more ? __ldg(nbr + cursor) : -1;
+          next_nid = (more && mask != nullptr) ? __ldg(nbr + cursor) : -1;
         }
         for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
-          const int s = j % kStages;
-          const int n = j / kStages;
+          const int s = j % NS;
+          const int n = j / NS;
           if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
           ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
           if (!ok) break;
@@ -289,10 +300,10 @@ __global__ void __launch_bounds__(160, 1)
             }
           }
           cp_async_commit();
-          if (j >= kLookahead) {
-            cp_async_wait<kLookahead>();
+          if (j >= (NS - 1)) {
+            cp_async_wait<(NS - 1)>();
             fence_proxy_async();
-            mbar_arrive(smem_u32(&ctl->afull[pending_arrive % kStages]));
+            mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
             ++pending_arrive;
           }
         }
@@ -301,15 +312,15 @@ __global__ void __launch_bounds__(160, 1)
     cp_async_wait<0>();
     fence_proxy_async();
     if (ok) {
-      for (; pending_arrive < j; ++pending_arrive) mbar_arrive(smem_u32(&ctl->afull[pending_arrive % kStages]));
+      for (; pending_arrive < j; ++pending_arrive) mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
     }
 
     // =========================== epilogue ===========================
     if (!ok && tid == 0) {
       // aborting: give this thread's bulk copies a bounded chance to land before the CTA leaves
-      for (int u = max(0, j - kStages); u < j; ++u) {
-        const uint32_t bar = smem_u32(&ctl->bfull[u % kStages]);
-        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (u / kStages) & 1); ++spin) {
+      for (int u = max(0, j - NS); u < j; ++u) {
+        const uint32_t bar = smem_u32(&ctl->bfull[u % NS]);
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (u / NS) & 1); ++spin) {
         }
       }
     }
@@ -397,8 +408,8 @@ __global__ void __launch_bounds__(160, 1)
         while (tm && ok) {
           tm &= tm - 1;
           for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
-            const int s = j % kStages;
-            const uint32_t par = (j / kStages) & 1;
+            const int s = j % NS;
+            const uint32_t par = (j / NS) & 1;
             ok = mbar_wait(smem_u32(&ctl->afull[s]), par, ctl) && mbar_wait(smem_u32(&ctl->bfull[s]), par, ctl);
             if (!ok) break;
             tc_fence_after();
@@ -449,27 +460,36 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   return PCE_OK;
 }
 
-int conv_umma(const void* in, const void* wpacked, const uint32_t* mask, const int* rowptr, const int* nbr, int n_out,
-              int cin, int cout, int kv, void* out, const pce_epilogue* ep, cudaStream_t st) {
+int conv_umma(const void* in, const void* wpacked, const uint32_t* mask, const int* rowptr, const int* nbr,
+              const int* order, int n_out, int cin, int cout, int kv, void* out, const pce_epilogue* ep,
+              cudaStream_t st) {
   if (kv > 32 * umma::kMaxWords) return PCE_ERR_UNSUPPORTED;
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
   if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
   int tmem_cols = 32;
   while (tmem_cols < cout) tmem_cols <<= 1;
-  const size_t smem = static_cast<size_t>(umma::kStages) * (umma::kABytes + cout * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
+  const int ns = (umma::kABytes + cout * 128) * 2 + 4096 <= 56 * 1024 ? 2 : 4;
+  const size_t smem = static_cast<size_t>(ns) * (umma::kABytes + cout * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
   static bool configured[64] = {};
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    const size_t max_smem = static_cast<size_t>(umma::kStages) * (umma::kABytes + 256 * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const size_t max_smem = static_cast<size_t>(umma::kMaxStages) * (umma::kABytes + 256 * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(max_smem)));
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(max_smem)));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = div_up(n_out, umma::kTileM);
-  umma::k_conv_umma<<<grid, 160, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked), mask,
-                                             rowptr, nbr, n_out, cin, cout, kv, static_cast<__half*>(out), e,
-                                             tmem_cols);
+  if (ns == 2)
+    umma::k_conv_umma<2><<<grid, 160, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
+                                                  mask, rowptr, nbr, order, n_out, cin, cout, kv,
+                                                  static_cast<__half*>(out), e, tmem_cols);
+  else
+    umma::k_conv_umma<4><<<grid, 160, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
+                                                  mask, rowptr, nbr, order, n_out, cin, cout, kv,
+                                                  static_cast<__half*>(out), e, tmem_cols);
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }

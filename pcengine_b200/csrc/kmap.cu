@@ -373,6 +373,25 @@ __global__ void k_pairs_rows(const int* __restrict__ skeys, const int* __restric
   if (j < cap) nbr[j] = v;
 }
 
+// Sort key of an output row: its indicator bitmask (one word), or the words folded into
+// 64 bits for larger kernels.  Only used to group similar rows, never for correctness.
+__global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int words, unsigned long long* keys,
+                            int* vals) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  unsigned long long k = mask[static_cast<size_t>(r) * words];
+  if (words > 1) {
+    unsigned long long hi = mask[static_cast<size_t>(r) * words + 1];
+    for (int w = 2; w < words; ++w) {
+      const unsigned m = mask[static_cast<size_t>(r) * words + w];
+      hi ^= (static_cast<unsigned long long>(m) << (8 * (w - 1))) | (m >> (32 - 8 * (w - 1)));
+    }
+    k |= hi << 32;
+  }
+  keys[r] = k;
+  vals[r] = r;
+}
+
 // ---- host helpers ------------------------------------------------------------
 
 static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, cudaStream_t st) {
@@ -624,6 +643,29 @@ int pce_csr_from_dense(const int32_t* table, int32_t kv, int32_t n_rows, int32_t
   PCE_TRY(exclusive_scan_i32(ar, counts, rowptr, n_rows + 1, st));
   k_row_fill<0><<<div_up(n_rows, 256), 256, 0, st>>>(a, rowptr, nbr, nbr_cap);
   PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace, size_t workspace_bytes,
+                      int32_t* order, void* stream) {
+  if (n_rows < 0 || kv < 1) return PCE_ERR_INVALID;
+  if (n_rows == 0) return PCE_OK;
+  if (!mask || !order) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int words = (kv + 31) / 32;
+  Arena ar(workspace, workspace_bytes);
+  unsigned long long* keys = ar.take<unsigned long long>(n_rows);
+  unsigned long long* skeys = ar.take<unsigned long long>(n_rows);
+  int* vals = ar.take<int>(n_rows);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  k_mask_keys<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, keys, vals);
+  PCE_LAUNCH_CHECK();
+  const int bits = words == 1 ? (kv < 32 ? kv : 32) : 64;
+  size_t need = 0;
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, keys, skeys, vals, order, n_rows, 0, bits, st));
+  char* tmp = ar.take<char>(need);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, keys, skeys, vals, order, n_rows, 0, bits, st));
   return PCE_OK;
 }
 

@@ -17,6 +17,8 @@ _KERNEL_NAME = {_lib.KERNEL_SIMT: "conv_simt", _lib.KERNEL_UMMA: "conv_umma"}
 # When set to a list, every conv_forward call appends a record with CUDA events around its
 # kernel launch (used by the benchmark to time the convolution kernels inside a model).
 PROFILE = None
+# Form the tensor-core kernel's tiles in bitmask-sorted row order (scheduling only; results are unchanged).
+SORT_ROWS = True
 
 
 class FusedEpilogue:
@@ -49,12 +51,12 @@ def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype):
     return C.byref(ep.pack(c_out, n_out, dtype)) if ep is not None else None
 
 
-def packed_weights(kernel: torch.Tensor) -> Optional[torch.Tensor]:
+def packed_weights(kernel: torch.Tensor, as_linear: bool = False) -> Optional[torch.Tensor]:
     """The tensor-core layout of ``kernel`` [kv,C_in,C_out], or None when the tensor-core kernel
     does not cover these channel counts.  The result is cached ON the tensor object (together
     with its version counter and address), so it lives and dies with the weights; a tensor
     that is rebuilt on every call is simply packed again."""
-    kv, c_in, c_out = kernel.shape
+    kv, c_in, c_out = ((1,) + tuple(kernel.shape)) if as_linear else kernel.shape
     code = _lib.dtype_code(kernel.dtype)
     if lib.pce_conv_kernel_choice(c_in, c_out, code, _lib.KERNEL_UMMA) != _lib.KERNEL_UMMA or kv > 128:
         return None
@@ -103,8 +105,9 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                    kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
+    order = csr.order() if (packed is not None and SORT_ROWS) else None
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
-                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), csr.n_rows,
+                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), _lib.ptr(order), csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
@@ -117,13 +120,15 @@ def linear_forward(feats: torch.Tensor, weight: torch.Tensor, epilogue: Optional
     """feats [N,C_in] @ weight [C_in,C_out] with the fused epilogue (the 1x1x1 shortcut)."""
     _lib.require_cuda(feats, "feats")
     feats = feats.contiguous()
-    weight = weight.contiguous().to(feats.dtype)
+    if not weight.is_contiguous() or weight.dtype != feats.dtype:
+        weight = weight.detach().contiguous().to(feats.dtype)
     if feats.size(1) != weight.size(0):
         raise ValueError("Input feature size and kernel size mismatch")
     n, c_in = feats.shape
     c_out = weight.size(1)
     out = torch.empty((n, c_out), dtype=feats.dtype, device=feats.device)
-    _lib.check(lib.pce_linear_fwd(feats.data_ptr(), n, c_in, weight.data_ptr(), c_out, out.data_ptr(),
+    packed = packed_weights(weight, as_linear=True)
+    _lib.check(lib.pce_linear_fwd(feats.data_ptr(), n, c_in, weight.data_ptr(), _lib.ptr(packed), c_out, out.data_ptr(),
                                   _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, n, feats.dtype),
                                   _lib.stream_ptr(feats.device)), "pce_linear_fwd")
     return out

@@ -38,10 +38,24 @@ def candidates_per_input(ks, stride) -> int:
 class NeighbourCSR:
     """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap]."""
 
-    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src")
+    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src", "kv", "_order")
 
-    def __init__(self, mask, rowptr, nbr, n_rows, n_src):
+    def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None):
         self.mask, self.rowptr, self.nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
+        self.kv = kv
+        self._order = None
+
+    def order(self):
+        """Output rows sorted by indicator bitmask (int32 [n_rows], built once): the order in which
+        the tensor-core kernel forms its 128-row tiles."""
+        if self._order is None and self.kv is not None and self.n_rows > 0:
+            dev = self.mask.device
+            out = torch.empty((self.n_rows,), dtype=torch.int32, device=dev)
+            ws = _lib.workspace(24 * self.n_rows + (8 << 20), dev)
+            _lib.check(lib.pce_csr_sort_rows(self.mask.data_ptr(), self.n_rows, self.kv, ws.data_ptr(), ws.numel(),
+                                             out.data_ptr(), _lib.stream_ptr(dev)), "pce_csr_sort_rows")
+            self._order = out
+        return self._order
 
 
 class KernelMap:
@@ -132,7 +146,7 @@ class KernelMap:
         _lib.check(lib.pce_csr_from_dense(_lib.ptr(table), kv, n_rows, reverse, ident, ws.data_ptr(), ws.numel(),
                                           mask.data_ptr(), rowptr.data_ptr(), nbr.data_ptr(), cap, st),
                    "pce_csr_from_dense")
-        out = NeighbourCSR(mask, rowptr, nbr, n_rows, n_src)
+        out = NeighbourCSR(mask, rowptr, nbr, n_rows, n_src, kv)
         self._csr[key] = out
         return out
 
@@ -184,4 +198,4 @@ def csr_from_pairs(rows: torch.Tensor, nbrs: torch.Tensor, kpos: torch.Tensor, k
     _lib.check(lib.pce_csr_from_pairs(_lib.ptr(rows), _lib.ptr(nbrs), kpos.data_ptr(), kv, n_pairs, n_rows,
                                       identity_kp, ws.data_ptr(), ws.numel(), mask.data_ptr(), rowptr.data_ptr(),
                                       nbr.data_ptr(), cap, _lib.stream_ptr(dev)), "pce_csr_from_pairs")
-    return NeighbourCSR(mask, rowptr, nbr, n_rows, n_src)
+    return NeighbourCSR(mask, rowptr, nbr, n_rows, n_src, kv)

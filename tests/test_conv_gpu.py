@@ -182,3 +182,40 @@ def test_weight_repacking_follows_the_tensor():
         assert co.rel_l2(y.float().cpu(), co.conv_forward(x, w * 0.5, d2)) <= 1e-3
         del wd, y
     assert PF.device_status() == 0
+
+
+def test_row_order_is_only_scheduling():
+    """Tiles formed in bitmask-sorted order give bit-identical features to natural order, and the
+    order is a permutation grouped by bitmask."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(9, 80, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    order = csr.order().cpu().numpy()
+    assert np.array_equal(np.sort(order), np.arange(km.n_out))
+    keys = csr.mask.cpu().numpy().view(np.uint32)[:, 0][order]
+    assert (np.diff(keys.astype(np.int64)) >= 0).all()
+    x = torch.randn(len(coords), 64).half().cuda()
+    w = (torch.randn(27, 64, 96) / 40).half().cuda()
+    try:
+        PF.SORT_ROWS = True
+        a = PF.conv_forward(x, w, csr)
+        PF.SORT_ROWS = False
+        b = PF.conv_forward(x, w, csr)
+    finally:
+        PF.SORT_ROWS = True
+    assert torch.equal(a, b)
+    assert PF.device_status() == 0
+
+
+def test_dense_product_on_tensor_cores():
+    """1x1x1 layers with tensor-core friendly widths run the tcgen05 kernel in identity mode."""
+    import pcengine_b200 as pce
+    coords = random_cloud(6, 24, 5000)
+    feats = torch.randn(len(coords), 192).half()
+    x = _tensor(pce, coords, feats)
+    lin = pce.conv3d(192, 128, 1, bias=True).cuda().half()
+    y = lin(x)
+    ref = co.pointwise_conv(feats, lin.kernel.detach().cpu(), lin.bias.detach().cpu())
+    assert co.rel_l2(y.feats.float().cpu(), ref) <= 1e-3
