@@ -30,7 +30,7 @@ __device__ int g_umma_status = 0;
 namespace umma {
 
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 6;
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows x 64 fp16
 constexpr int kMaxWords = 4;       // kernel volume <= 128
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s at 2 GHz
@@ -47,9 +47,14 @@ struct SharedCtl {
   unsigned long long afull[kMaxStages];
   unsigned long long bfull[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long accbar;
+  unsigned long long tfull[2];
+  unsigned long long tempty[2];
+  unsigned long long accfull[2];
+  unsigned long long accempty[2];
   uint32_t tmem_base;
-  uint32_t tile_mask[kMaxWords];
+  uint32_t warp_mask[2][4][kMaxWords];  // per tile-ring slot, per producer warp: OR of its rows' bitmasks
+  int tile_stages[2];
+  int acc_stages[2];
   volatile int abort_flag;
 };
 
@@ -175,19 +180,27 @@ __global__ void k_pack_weights(const __half* __restrict__ w, int kv, int cin, in
   }
 }
 
-// NS = pipeline stages; each producer thread keeps NS-1 cp.async groups in flight.
+// Persistent, warp-specialised kernel.  288 threads:
+//   warps 0-3  producers: one thread per output row of the current tile (gather + weight copy)
+//   warp  4    MMA issuer (one elected lane)
+//   warps 5-8  epilogue: tensor memory -> registers -> scale/shift/residual/activation -> fp16 rows
+// Each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Three rings decouple the roles:
+//   stage ring  (NS slots: afull/bfull/empty)  producers -> MMA, runs on across tile boundaries;
+//   tile ring   (2 slots: tfull/tempty)        producers -> MMA: number of stages of a tile;
+//   acc ring    (2 TMEM accumulators: accfull/accempty)  MMA -> epilogue.
+// So the gather of tile i+1, the MMAs of tile i and the stores of tile i-1 overlap.
 template <int NS>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(288, 1)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, const uint32_t* __restrict__ mask,
                 const int* __restrict__ rowptr, const int* __restrict__ nbr, const int* __restrict__ order, int n_out,
                 int cin, int cout, int kv, __half* __restrict__ out, Epi ep, int tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
-  uint8_t* tiles = smem_raw + pad;                 // 1024-byte aligned
+  uint8_t* tiles = smem_raw + pad;  // 1024-byte aligned
   const uint32_t tiles_addr = raw_addr + pad;
   const int b_bytes = cout * 128;
-  const int stage_bytes = kABytes + b_bytes;       // both multiples of 1024
+  const int stage_bytes = kABytes + b_bytes;  // both multiples of 1024
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + NS * stage_bytes);
 
   const int tid = threadIdx.x;
@@ -195,7 +208,7 @@ __global__ void __launch_bounds__(160, 1)
   const int lane = tid & 31;
   const int words = (kv + 31) >> 5;
   const int kblocks = (cin + 63) >> 6;
-  const int row0 = blockIdx.x * kTileM;
+  const int n_tiles = (n_out + kTileM - 1) / kTileM;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -203,8 +216,14 @@ __global__ void __launch_bounds__(160, 1)
       mbar_init(smem_u32(&ctl->bfull[s]), 1);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
-    mbar_init(smem_u32(&ctl->accbar), 1);
-    for (int w = 0; w < kMaxWords; ++w) ctl->tile_mask[w] = 0;
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctl->tfull[s]), 1);
+      mbar_init(smem_u32(&ctl->tempty[s]), 1);
+      mbar_init(smem_u32(&ctl->accfull[s]), 2);  // the MMA thread's own arrive + the tcgen05.commit
+      mbar_init(smem_u32(&ctl->accempty[s]), 128);
+      ctl->tile_stages[s] = 0;
+      ctl->acc_stages[s] = 0;
+    }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -217,106 +236,128 @@ __global__ void __launch_bounds__(160, 1)
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-
-  // ---- per-row map state (producer threads own one output row each) ----
-  uint32_t my_mask[kMaxWords] = {0, 0, 0, 0};
-  int cursor = 0;
-  // Output row of this thread: slot (row0 + tid) of the processing order (rows sorted by
-  // bitmask so that a tile shares offsets), or the slot itself without an order.
-  // mask == nullptr means "every row has exactly the pair (row, offset 0, row)": the dense product.
-  int my_row = n_out;  // n_out = no row
-  if (warp < 4 && row0 + tid < n_out) my_row = order ? __ldg(order + row0 + tid) : row0 + tid;
-  if (warp < 4) {
-    if (my_row < n_out) {
-      if (mask != nullptr) {
-        for (int w = 0; w < words; ++w) my_mask[w] = __ldg(mask + static_cast<size_t>(my_row) * words + w);
-        cursor = __ldg(rowptr + my_row);
-      } else {
-        my_mask[0] = 1u;
-      }
-    }
-    for (int w = 0; w < words; ++w) {
-      const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, my_mask[w]);
-      if (lane == 0 && m) atomicOr(&ctl->tile_mask[w], m);
-    }
-  }
-  __syncthreads();
-  uint32_t tile_mask[kMaxWords];
-  bool any = false;
-  for (int w = 0; w < kMaxWords; ++w) {
-    tile_mask[w] = (w < words) ? ctl->tile_mask[w] : 0u;
-    any |= tile_mask[w] != 0;
-  }
-  const uint32_t tmem_acc = ctl->tmem_base;
+  const uint32_t tmem_base = ctl->tmem_base;
 
   if (warp < 4) {
     // =========================== producers ===========================
-    int j = 0;            // running stage counter
-    int pending_arrive = 0;  // next stage index this thread still has to arrive on
-    int next_nid = -1;
-    if (my_row < n_out && (my_mask[0] | my_mask[1] | my_mask[2] | my_mask[3]))
-      next_nid = mask != nullptr ? __ldg(nbr + cursor) : my_row;
-    const int rsub = lane >> 3;   // row inside a 4-row group
-    const int chunk = lane & 7;   // 16-byte chunk inside a 128-byte row
-    bool ok = true;
-    for (int w = 0; w < words && ok; ++w) {
-      uint32_t tm = tile_mask[w];
-      while (tm && ok) {
-        const int bit = __ffs(tm) - 1;
-        tm &= tm - 1;
-        const int kp = w * 32 + bit;
-        int nid = -1;
-        if ((my_mask[w] >> bit) & 1u) {
-          nid = next_nid;
-          ++cursor;
-          // prefetch the next neighbour id of this row, if it has one left
-          uint32_t rest = my_mask[w] & ~((2u << bit) - 1u);
-          bool more = rest != 0;
-          for (int w2 = w + 1; w2 < words; ++w2) more |= my_mask[w2] != 0;
-          next_nid = (more && mask != nullptr) ? __ldg(nbr + cursor) : -1;
+    int j = 0;               // stages issued so far by this CTA (continuous over tiles)
+    int pending_arrive = 0;  // next stage this thread still has to arrive on
+    const int rsub = lane >> 3;  // row inside a 4-row group
+    const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
+    // row bookkeeping of the NEXT tile is fetched while the current one is gathered
+    int nxt_row = n_out;
+    uint32_t nxt_mask[kMaxWords] = {0, 0, 0, 0};
+    int nxt_cursor = 0;
+    auto fetch_row = [&](int tile) {
+      nxt_row = n_out;
+      for (int w = 0; w < kMaxWords; ++w) nxt_mask[w] = 0;
+      nxt_cursor = 0;
+      const int slot = tile * kTileM + tid;
+      if (tile < n_tiles && slot < n_out) {
+        nxt_row = order ? __ldg(order + slot) : slot;
+        if (mask != nullptr) {
+          for (int w = 0; w < words; ++w) nxt_mask[w] = __ldg(mask + static_cast<size_t>(nxt_row) * words + w);
+          nxt_cursor = __ldg(rowptr + nxt_row);
+        } else {
+          nxt_mask[0] = 1u;  // dense product: the row itself at offset 0
         }
-        for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
-          const int s = j % NS;
-          const int n = j / NS;
-          if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
-          ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
-          if (!ok) break;
-          const uint32_t a_addr = tiles_addr + s * stage_bytes;
-          if (tid == 0) {
-            const uint32_t bbar = smem_u32(&ctl->bfull[s]);
-            mbar_arrive_expect_tx(bbar, b_bytes);
-            bulk_copy_g2s(a_addr + kABytes, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes,
-                          bbar);
+      }
+    };
+    fetch_row(blockIdx.x);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const int slot2 = it & 1;
+      const int my_row = nxt_row;
+      uint32_t my_mask[kMaxWords];
+      for (int w = 0; w < kMaxWords; ++w) my_mask[w] = nxt_mask[w];
+      int cursor = nxt_cursor;
+      int next_nid = -1;
+      if (my_row < n_out && (my_mask[0] | my_mask[1] | my_mask[2] | my_mask[3]))
+        next_nid = mask != nullptr ? __ldg(nbr + cursor) : my_row;
+      // Each producer warp publishes the OR of its rows' bitmasks in its own cell of the slot;
+      // after the barrier everyone ORs the four cells.  A slot's cells are rewritten two tiles
+      // later, after a barrier that all readers of this tile have passed: no clearing needed.
+      for (int w = 0; w < words; ++w) {
+        const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, my_mask[w]);
+        if (lane == 0) ctl->warp_mask[slot2][warp][w] = m;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ctl->abort_flag) break;  // uniform: every producer reads it after the barrier
+      uint32_t tile_mask[kMaxWords];
+      int n_off = 0;
+      for (int w = 0; w < kMaxWords; ++w) {
+        tile_mask[w] = 0u;
+        if (w < words)
+          tile_mask[w] = ctl->warp_mask[slot2][0][w] | ctl->warp_mask[slot2][1][w] | ctl->warp_mask[slot2][2][w] |
+                         ctl->warp_mask[slot2][3][w];
+        n_off += __popc(tile_mask[w]);
+      }
+      bool ok = true;
+      if (tid == 0) {
+        // the tile-ring slot must have been consumed by the MMA warp (two tiles ago)
+        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->tempty[slot2]), ((it >> 1) - 1) & 1, ctl);
+        if (ok) {
+          ctl->tile_stages[slot2] = n_off * kblocks;
+          mbar_arrive(smem_u32(&ctl->tfull[slot2]));
+        }
+      }
+      fetch_row(tile + gridDim.x);  // loads for the next tile fly during this tile's gather
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      for (int w = 0; w < words && ok; ++w) {
+        uint32_t tm = tile_mask[w];
+        while (tm && ok) {
+          const int bit = __ffs(tm) - 1;
+          tm &= tm - 1;
+          const int kp = w * 32 + bit;
+          int nid = -1;
+          if ((my_mask[w] >> bit) & 1u) {
+            nid = next_nid;
+            ++cursor;
+            uint32_t rest = my_mask[w] & ~((2u << bit) - 1u);
+            bool more = rest != 0;
+            for (int w2 = w + 1; w2 < words; ++w2) more |= my_mask[w2] != 0;
+            next_nid = (more && mask != nullptr) ? __ldg(nbr + cursor) : -1;
           }
-          const int kchunks = min(8, (cin - kb * 64) >> 3);
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + rsub;  // row inside this warp's 32
-            const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
-            if (chunk < kchunks) {
-              const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-              const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + kb * 64 + chunk * 8 : 0);
-              cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+          for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
+            const int s = j % NS;
+            const int n = j / NS;
+            if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
+            ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
+            if (!ok) break;
+            const uint32_t a_addr = tiles_addr + s * stage_bytes;
+            if (tid == 0) {
+              const uint32_t bbar = smem_u32(&ctl->bfull[s]);
+              mbar_arrive_expect_tx(bbar, b_bytes);
+              bulk_copy_g2s(a_addr + kABytes, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes,
+                            bbar);
             }
-          }
-          cp_async_commit();
-          if (j >= (NS - 1)) {
-            cp_async_wait<(NS - 1)>();
-            fence_proxy_async();
-            mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
-            ++pending_arrive;
+            const int kchunks = min(8, (cin - kb * 64) >> 3);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int r = q * 4 + rsub;  // row inside this warp's 32
+              const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
+              if (chunk < kchunks) {
+                const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
+                const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + kb * 64 + chunk * 8 : 0);
+                cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+              }
+            }
+            cp_async_commit();
+            if (j >= NS - 1) {
+              cp_async_wait<NS - 1>();
+              fence_proxy_async();
+              mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
+              ++pending_arrive;
+            }
           }
         }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async();
-    if (ok) {
+    if (!ctl->abort_flag) {
       for (; pending_arrive < j; ++pending_arrive) mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
-    }
-
-    // =========================== epilogue ===========================
-    if (!ok && tid == 0) {
+    } else if (tid == 0) {
       // aborting: give this thread's bulk copies a bounded chance to land before the CTA leaves
       for (int u = max(0, j - NS); u < j; ++u) {
         const uint32_t bar = smem_u32(&ctl->bfull[u % NS]);
@@ -324,15 +365,78 @@ __global__ void __launch_bounds__(160, 1)
         }
       }
     }
-    bool acc_ok = ok;
-    if (any && ok) acc_ok = mbar_wait(smem_u32(&ctl->accbar), 0, ctl);
-    acc_ok = __all_sync(0xFFFFFFFFu, acc_ok);
-    tc_fence_after();
-    const bool store_row = my_row < n_out;
-    if (acc_ok) {  // warp-uniform: the tensor-memory loads below are warp-collective
-      const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
-      __half* orow = out + static_cast<size_t>(my_row) * cout;
-      const __half* rrow = ep.residual ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
+  } else if (warp == 4) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+      int j = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+        const int slot2 = it & 1;
+        const uint32_t par2 = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&ctl->tfull[slot2]), par2, ctl);
+        if (!ok) break;
+        const int nst = ctl->tile_stages[slot2];
+        mbar_arrive(smem_u32(&ctl->tempty[slot2]));
+        // the accumulator must have been drained by the epilogue (two tiles ago)
+        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->accempty[slot2]), (par2 ^ 1), ctl);
+        if (!ok) break;
+        tc_fence_after();
+        ctl->acc_stages[slot2] = nst;
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(slot2 * cout);
+        uint32_t accumulate = 0;
+        for (int st = 0; st < nst && ok; ++st, ++j) {
+          const int s = j % NS;
+          const uint32_t par = (j / NS) & 1;
+          ok = mbar_wait(smem_u32(&ctl->afull[s]), par, ctl) && mbar_wait(smem_u32(&ctl->bfull[s]), par, ctl);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = tiles_addr + s * stage_bytes;
+          const uint64_t da = make_desc(a_addr);
+          const uint64_t db = make_desc(a_addr + kABytes);
+          const int kb = st % kblocks;
+          const int ksteps = min(4, (cin - kb * 64) >> 4);
+          for (int k = 0; k < ksteps; ++k) {
+            tc_mma_f16(tmem_acc, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc, accumulate);
+            accumulate = 1;
+          }
+          tc_commit(smem_u32(&ctl->empty[s]));
+        }
+        if (!ok) break;
+        // two arrivals complete the phase: this thread's own (release: publishes acc_stages) and
+        // the commit's, which lands when every MMA of the tile has finished
+        mbar_arrive(smem_u32(&ctl->accfull[slot2]));
+        if (nst > 0)
+          tc_commit(smem_u32(&ctl->accfull[slot2]));
+        else
+          mbar_arrive(smem_u32(&ctl->accfull[slot2]));  // no MMA was issued: the epilogue writes zeros
+      }
+    }
+    __syncwarp();
+    tc_fence_before();
+  } else {
+    // =========================== epilogue ===========================
+    const int et = tid - 160;            // 0..127: accumulator lane == row slot of the tile
+    const int lane_quarter = warp & 3;   // the TMEM lanes this warp may read: 32*(warp%4)..+31
+    const int slot_in_tile = lane_quarter * 32 + lane;
+    (void)et;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const int slot2 = it & 1;
+      const uint32_t par2 = (it >> 1) & 1;
+      const int slot = tile * kTileM + slot_in_tile;
+      int my_row = n_out;
+      if (slot < n_out) my_row = order ? __ldg(order + slot) : slot;
+      bool ok = mbar_wait(smem_u32(&ctl->accfull[slot2]), par2, ctl);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool any = ctl->acc_stages[slot2] > 0;
+      const bool store_row = my_row < n_out;
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(slot2 * cout) + (static_cast<uint32_t>(lane_quarter * 32) << 16);
+      __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
+      const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
       for (int c0 = 0; c0 < cout; c0 += 16) {
         uint32_t r[16];
         if (any) {
@@ -365,7 +469,7 @@ __global__ void __launch_bounds__(160, 1)
             v[q + 3] += s4.w;
           }
         }
-        if (rrow && store_row) {
+        if (rrow) {
           const uint4 ra = *reinterpret_cast<const uint4*>(rrow + c0);
           const uint4 rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
           const __half2* ha = reinterpret_cast<const __half2*>(&ra);
@@ -394,47 +498,15 @@ __global__ void __launch_bounds__(160, 1)
           *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
         }
       }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->accempty[slot2]));  // 128 arrivals hand the accumulator back
     }
-    tc_fence_before();
-  } else {
-    // =========================== MMA issuer ===========================
-    if (lane == 0 && any) {
-      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
-      int j = 0;
-      bool ok = true;
-      uint32_t accumulate = 0;
-      for (int w = 0; w < words && ok; ++w) {
-        uint32_t tm = tile_mask[w];
-        while (tm && ok) {
-          tm &= tm - 1;
-          for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
-            const int s = j % NS;
-            const uint32_t par = (j / NS) & 1;
-            ok = mbar_wait(smem_u32(&ctl->afull[s]), par, ctl) && mbar_wait(smem_u32(&ctl->bfull[s]), par, ctl);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_addr = tiles_addr + s * stage_bytes;
-            const uint64_t da = make_desc(a_addr);
-            const uint64_t db = make_desc(a_addr + kABytes);
-            const int ksteps = min(4, (cin - kb * 64) >> 4);
-            for (int k = 0; k < ksteps; ++k) {
-              tc_mma_f16(tmem_acc, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
-                         accumulate);
-              accumulate = 1;
-            }
-            tc_commit(smem_u32(&ctl->empty[s]));
-          }
-        }
-      }
-      if (ok) tc_commit(smem_u32(&ctl->accbar));
-    }
-    __syncwarp();
     tc_fence_before();
   }
   __syncthreads();
   if (warp == 4) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(tmem_cols))
                  : "memory");
   }
@@ -467,29 +539,33 @@ int conv_umma(const void* in, const void* wpacked, const uint32_t* mask, const i
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
   if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
   int tmem_cols = 32;
-  while (tmem_cols < cout) tmem_cols <<= 1;
-  const int ns = (umma::kABytes + cout * 128) * 2 + 4096 <= 56 * 1024 ? 2 : 4;
-  const size_t smem = static_cast<size_t>(ns) * (umma::kABytes + cout * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
-  static bool configured[64] = {};
+  while (tmem_cols < 2 * cout) tmem_cols <<= 1;  // two accumulators
+  const size_t stage = static_cast<size_t>(umma::kABytes + cout * 128);
+  const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
+  const int ns = 4;
+  const size_t smem = ns * stage + fixed;
+  static int sm_count[64] = {};
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    const size_t max_smem = static_cast<size_t>(umma::kMaxStages) * (umma::kABytes + 256 * 128) + sizeof(umma::SharedCtl) + 1024 + 64;
+  if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
+  if (sm_count[dev] == 0) {
+    const size_t max_smem = static_cast<size_t>(umma::kMaxStages) * (umma::kABytes + 256 * 128) + fixed;
     PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(max_smem)));
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(max_smem)));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+                                  static_cast<int>(max_smem > 232448 ? 232448 : max_smem)));
+    int n = 0;
+    PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    sm_count[dev] = n > 0 ? n : 1;
   }
-  const int grid = div_up(n_out, umma::kTileM);
-  if (ns == 2)
-    umma::k_conv_umma<2><<<grid, 160, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
-                                                  mask, rowptr, nbr, order, n_out, cin, cout, kv,
-                                                  static_cast<__half*>(out), e, tmem_cols);
-  else
-    umma::k_conv_umma<4><<<grid, 160, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
-                                                  mask, rowptr, nbr, order, n_out, cin, cout, kv,
-                                                  static_cast<__half*>(out), e, tmem_cols);
+  // CTAs that fit one SM: shared memory (227 KB), tensor memory (512 columns), at most 3
+  int per_sm = static_cast<int>((227 * 1024) / (smem + 1024));
+  if (per_sm > 512 / tmem_cols) per_sm = 512 / tmem_cols;
+  if (per_sm > 3) per_sm = 3;
+  if (per_sm < 1) per_sm = 1;
+  const int n_tiles = div_up(n_out, umma::kTileM);
+  const int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
+  umma::k_conv_umma<4><<<grid, 288, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
+                                                mask, rowptr, nbr, order, n_out, cin, cout, kv,
+                                                static_cast<__half*>(out), e, tmem_cols);
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }
