@@ -75,6 +75,20 @@ typedef struct pce_epilogue {
   float slope;
 } pce_epilogue;
 
+/* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output
+ * rows in bitmask-sorted `order`, cut into tiles of 128; tile t owns the stages
+ * tile_ptr[t] .. tile_ptr[t+1]-1, one per offset that any of its rows has;
+ * stage g applies offset stage_kp[g] and fetches input row stage_nbr[g*128 + r] for
+ * the tile's r-th row (-1: that row lacks the offset).  No reference counterpart:
+ * it is the CSR-coded map + indicator in the layout a 128-row tensor-memory tile
+ * consumes with coalesced reads. */
+typedef struct pce_tile_lists {
+  const int32_t* order;     /* [n_rows] */
+  const int32_t* tile_ptr;  /* [ceil(n_rows/128) + 1] */
+  const int32_t* stage_kp;  /* [stages] */
+  const int32_t* stage_nbr; /* [stages * 128] */
+} pce_tile_lists;
+
 PCE_API const char* pce_strerror(int status);
 PCE_API int pce_version(void);
 /* cudaError_t of the most recent failing CUDA call made by this library on the
@@ -184,12 +198,13 @@ PCE_API size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_row
  * packed_weights (may be NULL) is the same tensor re-laid by pce_pack_weights for
  * the tensor-core kernel; without it only the CUDA-core kernel can run.  Either
  * `weights` or `packed_weights` may be NULL when the kernel that needs it is not
- * the one chosen.  row_order (may be NULL) is a permutation of the output rows
- * from pce_csr_sort_rows: the tensor-core kernel forms its 128-row tiles in that
- * order so that a tile's rows share offsets; results do not depend on it. */
+ * the one chosen.  The CUDA-core kernel walks mask/rowptr/nbr; the tensor-core
+ * kernel needs `tiles` (from pce_build_tile_lists) and runs only when both
+ * `tiles` and `packed_weights` are given.  Results do not depend on the kernel's
+ * processing order. */
 PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights,
                          const void* packed_weights, int32_t kv, int32_t c_out, const uint32_t* mask,
-                         const int32_t* rowptr, const int32_t* nbr, const int32_t* row_order, int32_t n_out,
+                         const int32_t* rowptr, const int32_t* nbr, const pce_tile_lists* tiles, int32_t n_out,
                          void* out_feats, int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice,
                          void* stream);
 
@@ -200,6 +215,15 @@ PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const
  * workspace >= 24*n_rows + 8 MiB bytes. */
 PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace,
                               size_t workspace_bytes, int32_t* order, void* stream);
+
+/* Fills the arrays of a pce_tile_lists from the neighbour CSR and a row order (NULL =
+ * natural order).  tile_ptr needs ceil(n_rows/128)+1 entries; stage_kp / stage_nbr have
+ * room for stage_cap stages (ceil(n_rows/128)*kv always suffices; the stage count ends up
+ * in tile_ptr[last]).  kv <= 128.  workspace >= 8*(tiles+1) + 1 MiB bytes. */
+PCE_API int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
+                                 const int32_t* order, int32_t n_rows, int32_t kv, void* workspace,
+                                 size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr,
+                                 int32_t stage_cap, void* stream);
 
 /* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
  * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index

@@ -22,7 +22,7 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_UMMA = 0, 1, 2
 EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
-    "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
+    "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
     "pce_pack_weights", "pce_device_status", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
 ]
 
@@ -30,6 +30,10 @@ EXPORTS = [
 class Geom(C.Structure):
     _fields_ = [("ks", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("pad", C.c_int32 * 3),
                 ("cmin", C.c_int32 * 3), ("cmax", C.c_int32 * 3), ("submanifold", C.c_int32)]
+
+
+class TileLists(C.Structure):
+    _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p)]
 
 
 class Epilogue(C.Structure):
@@ -60,7 +64,9 @@ def _load() -> C.CDLL:
     lib.pce_csr_from_pairs.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
     lib.pce_csr_from_pairs_workspace_bytes.restype = sz
     lib.pce_csr_from_pairs_workspace_bytes.argtypes = [i32, i32]
-    lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, vp, i32, vp, i32, C.POINTER(Epilogue), i32, vp]
+    lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, C.POINTER(TileLists), i32, vp, i32,
+                                 C.POINTER(Epilogue), i32, vp]
+    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, vp, sz, vp, vp, vp, i32, vp]
     lib.pce_csr_sort_rows.argtypes = [vp, i32, i32, vp, sz, vp, vp]
     lib.pce_packed_weights_bytes.restype = sz
     lib.pce_packed_weights_bytes.argtypes = [i32, i32, i32]

@@ -145,7 +145,7 @@ def conv_fwd_d2_cuda(in_feats, kernel, ksize_code, sum_nnz, out_feats, kpos, qkp
         raise ValueError("in_feats, kernel and out_feats must share one dtype")
     from .functional import packed_weights
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), n_in, c_in, w.data_ptr(), _lib.ptr(packed_weights(w)), kv, c_out,
-                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), _lib.ptr(csr.order()),
+                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), C.byref(csr.tiles()),
                                 n_out, out_feats.data_ptr(),
                                 _lib.dtype_code(feats.dtype), None, _lib.KERNEL_AUTO, _lib.stream_ptr(feats.device)),
                "pce_conv_fwd")

@@ -9,9 +9,8 @@ bool conv_umma_supported(int cin, int cout, int dtype);
 size_t umma_packed_bytes(int kv, int cin, int cout);
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
 int umma_status_fetch(int* host_status, bool reset);
-int conv_umma(const void* in, const void* w, const uint32_t* mask, const int* rowptr, const int* nbr,
-              const int* order, int n_out, int cin, int cout, int kv, void* out, const pce_epilogue* ep,
-              cudaStream_t st);
+int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
+              void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
 
 using namespace pce;
@@ -67,27 +66,26 @@ int pce_device_status(int32_t* status_host, int32_t reset) {
 
 int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, const void* packed_weights,
                  int32_t kv, int32_t c_out, const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
-                 const int32_t* row_order, int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
+                 const pce_tile_lists* tiles, int32_t n_out, void* out_feats, int32_t dtype, const pce_epilogue* ep,
                  int32_t kernel_choice, void* stream) {
   if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1) return PCE_ERR_INVALID;
   if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
   if (n_out == 0) return PCE_OK;
-  if (!mask || !rowptr || !out_feats || (n_in > 0 && (!in_feats || !nbr))) return PCE_ERR_INVALID;
+  if (!out_feats || (n_in > 0 && !in_feats)) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool umma_ok = conv_umma_supported(c_in, c_out, dtype) && kv <= 128;
   if (kernel_choice == PCE_KERNEL_UMMA && !umma_ok) return PCE_ERR_UNSUPPORTED;
-  const bool use_umma = umma_ok && kernel_choice != PCE_KERNEL_SIMT && (packed_weights || kernel_choice == PCE_KERNEL_UMMA);
-  if (use_umma) {
-    if (!packed_weights) return PCE_ERR_INVALID;
+  const bool have_tc = packed_weights && tiles && tiles->order && tiles->tile_ptr && tiles->stage_kp && tiles->stage_nbr;
+  if (kernel_choice == PCE_KERNEL_UMMA && !have_tc) return PCE_ERR_INVALID;
+  if (umma_ok && have_tc && kernel_choice != PCE_KERNEL_SIMT) {
     if ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
          reinterpret_cast<uintptr_t>(packed_weights)) & 15)
       return PCE_ERR_INVALID;
-    return conv_umma(in_feats, packed_weights, mask, rowptr, nbr, row_order, n_out, c_in, c_out, kv, out_feats, ep, st);
+    return conv_umma(in_feats, n_in, packed_weights, tiles, n_out, c_in, c_out, out_feats, ep, st);
   }
-  if (!weights) return PCE_ERR_INVALID;
+  if (!weights || !mask || !rowptr || (n_in > 0 && !nbr)) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
 }
-
 
 int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* weights, const void* packed_weights,
                    int32_t c_out, void* out_feats, int32_t dtype, const pce_epilogue* ep, void* stream) {
@@ -98,7 +96,7 @@ int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* we
   const bool aligned = ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
                          reinterpret_cast<uintptr_t>(packed_weights)) & 15) == 0;
   if (packed_weights && aligned && conv_umma_supported(c_in, c_out, dtype))
-    return conv_umma(in_feats, packed_weights, nullptr, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, ep, st);
+    return conv_umma(in_feats, n, packed_weights, nullptr, n, c_in, c_out, out_feats, ep, st);
   if (!weights) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, dtype, ep, true, st);
 }

@@ -1,26 +1,36 @@
 // Fused gather-matmul-scatter on the 5th-generation tensor cores (tcgen05 + tensor
-// memory), fp16 in / fp32 accumulate, output stationary.
+// memory), fp16 in / fp32 accumulate, output stationary, persistent and warp-specialised.
 //
-// One CTA owns 128 consecutive output rows: the accumulator is a 128-lane x C_out-column
-// fp32 tile in tensor memory.  For every kernel offset present in the tile (OR of the
-// rows' indicator bitmasks; absent offsets are skipped) and every 64-channel K block:
-//   * producer warps 0-3 (one thread per output row) gather the neighbour rows with
-//     16-byte cp.async into a 128-byte-swizzled K-major shared-memory tile, zero-filling
-//     rows that lack the offset (four rows per warp instruction, fully coalesced);
-//   * producer thread 0 also pulls the matching pre-packed weight block with one bulk
-//     async copy (cp.async.bulk, completion counted on an mbarrier);
-//   * warp 4 (one elected thread) issues tcgen05.mma (M=128, N=C_out, K=16) over the
-//     block and commits to the stage's "empty" mbarrier, which hands the stage back.
-// After the last block the accumulator is committed, warps 0-3 read it back with
-// tcgen05.ld, apply scale/shift/residual/activation, convert to fp16 and store each
-// output row exactly once.  No atomics, no intermediate buffer in HBM.
+// The kernel reads the map as TILE LISTS (built once per kernel map by pce_tile_lists):
+// output rows are taken in bitmask-sorted order in tiles of 128; for every tile the
+// offsets that at least one of its rows has are listed (`stage_kp`), each with the 128
+// input rows to fetch (`stage_nbr`, -1 = this row lacks the offset).  A stage is one
+// (tile, offset); offsets nobody in the tile has cost nothing (the indicator).
 //
-// Every mbarrier wait is bounded: when a wait runs out the CTA raises an abort flag,
+// One CTA owns a contiguous range of tiles holding about 1/gridDim of the work and
+// streams through that range's stages.  192 threads:
+//   warp  0    producer: per stage and 64-channel K block every lane issues one TMA
+//              tile::gather4 (cp.async.bulk.tensor, four input rows x 128 bytes each, rows
+//              named by index, -1 = out of bounds = zero fill) into a 128-byte-swizzled
+//              K-major tile, and lane 0 stages the pre-packed weight block with one bulk
+//              async copy; all of them complete on the stage's mbarrier.  Stage indices
+//              are prefetched four stages ahead (coalesced 512-byte reads).
+//   warp  1    one lane issues tcgen05.mma (M=128, N=C_out, K=16) and commits to mbarriers.
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator, apply
+//              act(acc*scale + shift + residual), convert to fp16, store each row once.
+// Rings: kStages smem stages (full / empty mbarriers) that run on across tile
+// boundaries, and two accumulators in tensor memory (accfull / accempty), so the gather of
+// tile i+1, the MMAs of tile i and the stores of tile i-1 overlap.
+// No atomics, no intermediate buffer in HBM, bit-identical run to run.
+//
+// Every mbarrier wait is bounded (~1 s): when one expires the CTA raises an abort flag,
 // records PCE_ERR_TIMEOUT in the library's device status word, drains its own copies,
 // frees its tensor memory and returns.
 //
 // Replaces fetch_on_demand_gemm_fp16_tc4_async and the cuBLAS centre GEMM of the
 // reference (ref: backend/spconv.cuh:1567-1730, backend/spconv.cu:273-298,338).
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up at run time
+
 #include "common.cuh"
 
 namespace pce {
@@ -30,9 +40,9 @@ __device__ int g_umma_status = 0;
 namespace umma {
 
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 6;
+constexpr int kStages = 4;
+constexpr int kPrefetch = 4;           // stage indices fetched ahead by the producers
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows x 64 fp16
-constexpr int kMaxWords = 4;       // kernel volume <= 128
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s at 2 GHz
 
 struct Epi {
@@ -43,18 +53,19 @@ struct Epi {
   float slope;
 };
 
+struct Lists {
+  const int* order;      // [n_out] processing order of the output rows, or nullptr (natural)
+  const int* tile_ptr;   // [n_tiles+1] first stage of every tile, or nullptr (dense product)
+  const int* stage_kp;   // [stages] offset of every stage
+  const int* stage_nbr;  // [stages][128] input row per tile row, -1 absent
+};
+
 struct SharedCtl {
-  unsigned long long afull[kMaxStages];
-  unsigned long long bfull[kMaxStages];
-  unsigned long long empty[kMaxStages];
-  unsigned long long tfull[2];
-  unsigned long long tempty[2];
+  unsigned long long full[kStages];
+  unsigned long long empty[kStages];
   unsigned long long accfull[2];
   unsigned long long accempty[2];
   uint32_t tmem_base;
-  uint32_t warp_mask[2][4][kMaxWords];  // per tile-ring slot, per producer warp: OR of its rows' bitmasks
-  int tile_stages[2];
-  int acc_stages[2];
   volatile int abort_flag;
 };
 
@@ -101,20 +112,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, SharedC
   return true;
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+
+// Four rows of the 2-D feature tensor (named by index; out-of-range rows read as zeros),
+// 64 columns from `col`, into 4 x 128 bytes of swizzled shared memory.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* tmap, int col, int4 rows, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
+      "%5, %6}], [%7];" ::"r"(dst),
+      "l"(tmap), "r"(col), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w), "r"(bar)
+      : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -180,20 +191,29 @@ __global__ void k_pack_weights(const __half* __restrict__ w, int kv, int cin, in
   }
 }
 
-// Persistent, warp-specialised kernel.  288 threads:
-//   warps 0-3  producers: one thread per output row of the current tile (gather + weight copy)
-//   warp  4    MMA issuer (one elected lane)
-//   warps 5-8  epilogue: tensor memory -> registers -> scale/shift/residual/activation -> fp16 rows
-// Each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Three rings decouple the roles:
-//   stage ring  (NS slots: afull/bfull/empty)  producers -> MMA, runs on across tile boundaries;
-//   tile ring   (2 slots: tfull/tempty)        producers -> MMA: number of stages of a tile;
-//   acc ring    (2 TMEM accumulators: accfull/accempty)  MMA -> epilogue.
-// So the gather of tile i+1, the MMAs of tile i and the stores of tile i-1 overlap.
-template <int NS>
-__global__ void __launch_bounds__(288, 1)
-    k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, const uint32_t* __restrict__ mask,
-                const int* __restrict__ rowptr, const int* __restrict__ nbr, const int* __restrict__ order, int n_out,
-                int cin, int cout, int kv, __half* __restrict__ out, Epi ep, int tmem_cols) {
+// Work of tiles [0, t): their stages plus one unit per tile for its fixed cost (epilogue).
+__device__ __forceinline__ long long cost_before(const int* tile_ptr, int t) {
+  return (tile_ptr ? static_cast<long long>(__ldg(tile_ptr + t)) : static_cast<long long>(t)) + t;
+}
+
+// First tile whose preceding work reaches `target` (cost_before is strictly increasing).
+__device__ __forceinline__ int tile_at_cost(const int* tile_ptr, int n_tiles, long long target) {
+  int lo = 0, hi = n_tiles;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (cost_before(tile_ptr, mid) >= target)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return tile_ptr ? __ldg(tile_ptr + t) : t; }
+
+__global__ void __launch_bounds__(192, 1)
+    k_conv_umma(const __grid_constant__ CUtensorMap in_map, const __half* __restrict__ wpacked, Lists ls, int n_out,
+                int cin, int cout, __half* __restrict__ out, Epi ep, int tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
@@ -201,33 +221,27 @@ __global__ void __launch_bounds__(288, 1)
   const uint32_t tiles_addr = raw_addr + pad;
   const int b_bytes = cout * 128;
   const int stage_bytes = kABytes + b_bytes;  // both multiples of 1024
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + NS * stage_bytes);
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * stage_bytes);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int words = (kv + 31) >> 5;
   const int kblocks = (cin + 63) >> 6;
   const int n_tiles = (n_out + kTileM - 1) / kTileM;
 
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(smem_u32(&ctl->afull[s]), 128);
-      mbar_init(smem_u32(&ctl->bfull[s]), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&ctl->tfull[s]), 1);
-      mbar_init(smem_u32(&ctl->tempty[s]), 1);
-      mbar_init(smem_u32(&ctl->accfull[s]), 2);  // the MMA thread's own arrive + the tcgen05.commit
+      mbar_init(smem_u32(&ctl->accfull[s]), 1);
       mbar_init(smem_u32(&ctl->accempty[s]), 128);
-      ctl->tile_stages[s] = 0;
-      ctl->acc_stages[s] = 0;
     }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(static_cast<uint32_t>(tmem_cols))
                  : "memory");
@@ -238,158 +252,87 @@ __global__ void __launch_bounds__(288, 1)
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp < 4) {
-    // =========================== producers ===========================
-    int j = 0;               // stages issued so far by this CTA (continuous over tiles)
-    int pending_arrive = 0;  // next stage this thread still has to arrive on
-    const int rsub = lane >> 3;  // row inside a 4-row group
-    const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
-    // row bookkeeping of the NEXT tile is fetched while the current one is gathered
-    int nxt_row = n_out;
-    uint32_t nxt_mask[kMaxWords] = {0, 0, 0, 0};
-    int nxt_cursor = 0;
-    auto fetch_row = [&](int tile) {
-      nxt_row = n_out;
-      for (int w = 0; w < kMaxWords; ++w) nxt_mask[w] = 0;
-      nxt_cursor = 0;
-      const int slot = tile * kTileM + tid;
-      if (tile < n_tiles && slot < n_out) {
-        nxt_row = order ? __ldg(order + slot) : slot;
-        if (mask != nullptr) {
-          for (int w = 0; w < words; ++w) nxt_mask[w] = __ldg(mask + static_cast<size_t>(nxt_row) * words + w);
-          nxt_cursor = __ldg(rowptr + nxt_row);
-        } else {
-          nxt_mask[0] = 1u;  // dense product: the row itself at offset 0
+  // this CTA's contiguous share of the tiles, balanced by work
+  const long long total = cost_before(ls.tile_ptr, n_tiles);
+  const int t0 = tile_at_cost(ls.tile_ptr, n_tiles, total * blockIdx.x / gridDim.x);
+  const int t1 = blockIdx.x + 1 == gridDim.x ? n_tiles
+                                             : tile_at_cost(ls.tile_ptr, n_tiles, total * (blockIdx.x + 1) / gridDim.x);
+
+  if (warp == 0) {
+    // =========================== producer ===========================
+    const int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
+    int4 rowq[kPrefetch];  // this lane's four input rows of the next stages
+    int kpq[kPrefetch];
+    auto load_stage = [&](int g, int4& rows, int& kp) {
+      rows = make_int4(-1, -1, -1, -1);
+      kp = 0;
+      if (g < g1) {
+        if (ls.tile_ptr) {
+          rows = __ldg(reinterpret_cast<const int4*>(ls.stage_nbr + static_cast<size_t>(g) * kTileM) + lane);
+          kp = __ldg(ls.stage_kp + g);
+        } else {  // dense product: stage g is tile g, every row fetches itself at offset 0
+          const int r = g * kTileM + 4 * lane;
+          rows = make_int4(r, r + 1, r + 2, r + 3);  // rows past the end are out of bounds: zeros
         }
       }
     };
-    fetch_row(blockIdx.x);
-    int it = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
-      const int slot2 = it & 1;
-      const int my_row = nxt_row;
-      uint32_t my_mask[kMaxWords];
-      for (int w = 0; w < kMaxWords; ++w) my_mask[w] = nxt_mask[w];
-      int cursor = nxt_cursor;
-      int next_nid = -1;
-      if (my_row < n_out && (my_mask[0] | my_mask[1] | my_mask[2] | my_mask[3]))
-        next_nid = mask != nullptr ? __ldg(nbr + cursor) : my_row;
-      // Each producer warp publishes the OR of its rows' bitmasks in its own cell of the slot;
-      // after the barrier everyone ORs the four cells.  A slot's cells are rewritten two tiles
-      // later, after a barrier that all readers of this tile have passed: no clearing needed.
-      for (int w = 0; w < words; ++w) {
-        const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, my_mask[w]);
-        if (lane == 0) ctl->warp_mask[slot2][warp][w] = m;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ctl->abort_flag) break;  // uniform: every producer reads it after the barrier
-      uint32_t tile_mask[kMaxWords];
-      int n_off = 0;
-      for (int w = 0; w < kMaxWords; ++w) {
-        tile_mask[w] = 0u;
-        if (w < words)
-          tile_mask[w] = ctl->warp_mask[slot2][0][w] | ctl->warp_mask[slot2][1][w] | ctl->warp_mask[slot2][2][w] |
-                         ctl->warp_mask[slot2][3][w];
-        n_off += __popc(tile_mask[w]);
-      }
-      bool ok = true;
-      if (tid == 0) {
-        // the tile-ring slot must have been consumed by the MMA warp (two tiles ago)
-        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->tempty[slot2]), ((it >> 1) - 1) & 1, ctl);
-        if (ok) {
-          ctl->tile_stages[slot2] = n_off * kblocks;
-          mbar_arrive(smem_u32(&ctl->tfull[slot2]));
-        }
-      }
-      fetch_row(tile + gridDim.x);  // loads for the next tile fly during this tile's gather
-      ok = __all_sync(0xFFFFFFFFu, ok);
-      for (int w = 0; w < words && ok; ++w) {
-        uint32_t tm = tile_mask[w];
-        while (tm && ok) {
-          const int bit = __ffs(tm) - 1;
-          tm &= tm - 1;
-          const int kp = w * 32 + bit;
-          int nid = -1;
-          if ((my_mask[w] >> bit) & 1u) {
-            nid = next_nid;
-            ++cursor;
-            uint32_t rest = my_mask[w] & ~((2u << bit) - 1u);
-            bool more = rest != 0;
-            for (int w2 = w + 1; w2 < words; ++w2) more |= my_mask[w2] != 0;
-            next_nid = (more && mask != nullptr) ? __ldg(nbr + cursor) : -1;
-          }
-          for (int kb = 0; kb < kblocks && ok; ++kb, ++j) {
-            const int s = j % NS;
-            const int n = j / NS;
-            if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
-            ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
-            if (!ok) break;
-            const uint32_t a_addr = tiles_addr + s * stage_bytes;
-            if (tid == 0) {
-              const uint32_t bbar = smem_u32(&ctl->bfull[s]);
-              mbar_arrive_expect_tx(bbar, b_bytes);
-              bulk_copy_g2s(a_addr + kABytes, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes,
-                            bbar);
-            }
-            const int kchunks = min(8, (cin - kb * 64) >> 3);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const int r = q * 4 + rsub;  // row inside this warp's 32
-              const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
-              if (chunk < kchunks) {
-                const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-                const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + kb * 64 + chunk * 8 : 0);
-                cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
-              }
-            }
-            cp_async_commit();
-            if (j >= NS - 1) {
-              cp_async_wait<NS - 1>();
-              fence_proxy_async();
-              mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
-              ++pending_arrive;
-            }
-          }
+    for (int q = 0; q < kPrefetch; ++q) load_stage(g0 + q, rowq[q], kpq[q]);
+    int j = 0;  // smem stages issued so far (continuous over tiles)
+    bool ok = true;
+    const uint32_t stage_tx = kABytes + b_bytes;
+    for (int g = g0; g < g1 && ok; ++g) {
+      const int4 rows = rowq[0];
+      const int kp = kpq[0];
+#pragma unroll
+      for (int q = 0; q + 1 < kPrefetch; ++q) {
+        rowq[q] = rowq[q + 1];
+        kpq[q] = kpq[q + 1];
+      }
+      load_stage(g + kPrefetch, rowq[kPrefetch - 1], kpq[kPrefetch - 1]);
+      for (int kb = 0; kb < kblocks; ++kb, ++j) {
+        const int s = j % kStages;
+        const int n = j / kStages;
+        if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        const uint32_t a_addr = tiles_addr + s * stage_bytes;
+        const uint32_t bar = smem_u32(&ctl->full[s]);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar, stage_tx);
+          bulk_copy_g2s(a_addr + kABytes, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes, bar);
+        }
+        tma_gather4(a_addr + lane * 512, &in_map, kb * 64, rows, bar);
+      }
+    }
+    if (!ok && lane == 0) {
+      // aborting: give the copies in flight a bounded chance to land before the CTA leaves
+      for (int u = max(0, j - kStages); u < j; ++u) {
+        const uint32_t bar = smem_u32(&ctl->full[u % kStages]);
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (u / kStages) & 1); ++spin) {
         }
       }
     }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    if (!ctl->abort_flag) {
-      for (; pending_arrive < j; ++pending_arrive) mbar_arrive(smem_u32(&ctl->afull[pending_arrive % NS]));
-    } else if (tid == 0) {
-      // aborting: give this thread's bulk copies a bounded chance to land before the CTA leaves
-      for (int u = max(0, j - NS); u < j; ++u) {
-        const uint32_t bar = smem_u32(&ctl->bfull[u % NS]);
-        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (u / NS) & 1); ++spin) {
-        }
-      }
-    }
-  } else if (warp == 4) {
+  } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
       int j = 0;
-      int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int slot2 = it & 1;
-        const uint32_t par2 = (it >> 1) & 1;
-        ok = mbar_wait(smem_u32(&ctl->tfull[slot2]), par2, ctl);
-        if (!ok) break;
-        const int nst = ctl->tile_stages[slot2];
-        mbar_arrive(smem_u32(&ctl->tempty[slot2]));
+      for (int t = t0; t < t1 && ok; ++t) {
+        const int it = t - t0;
+        const int buf = it & 1;
+        const int nst = (first_stage(ls.tile_ptr, t + 1) - first_stage(ls.tile_ptr, t)) * kblocks;
         // the accumulator must have been drained by the epilogue (two tiles ago)
-        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->accempty[slot2]), (par2 ^ 1), ctl);
+        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->accempty[buf]), ((it >> 1) - 1) & 1, ctl);
         if (!ok) break;
         tc_fence_after();
-        ctl->acc_stages[slot2] = nst;
-        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(slot2 * cout);
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * cout);
         uint32_t accumulate = 0;
         for (int st = 0; st < nst && ok; ++st, ++j) {
-          const int s = j % NS;
-          const uint32_t par = (j / NS) & 1;
-          ok = mbar_wait(smem_u32(&ctl->afull[s]), par, ctl) && mbar_wait(smem_u32(&ctl->bfull[s]), par, ctl);
+          const int s = j % kStages;
+          const uint32_t par = (j / kStages) & 1;
+          ok = mbar_wait(smem_u32(&ctl->full[s]), par, ctl);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = tiles_addr + s * stage_bytes;
@@ -404,42 +347,36 @@ __global__ void __launch_bounds__(288, 1)
           tc_commit(smem_u32(&ctl->empty[s]));
         }
         if (!ok) break;
-        // two arrivals complete the phase: this thread's own (release: publishes acc_stages) and
-        // the commit's, which lands when every MMA of the tile has finished
-        mbar_arrive(smem_u32(&ctl->accfull[slot2]));
         if (nst > 0)
-          tc_commit(smem_u32(&ctl->accfull[slot2]));
+          tc_commit(smem_u32(&ctl->accfull[buf]));  // arrives when every MMA of the tile has finished
         else
-          mbar_arrive(smem_u32(&ctl->accfull[slot2]));  // no MMA was issued: the epilogue writes zeros
+          mbar_arrive(smem_u32(&ctl->accfull[buf]));  // no MMA was issued: the epilogue writes zeros
       }
     }
     __syncwarp();
     tc_fence_before();
   } else {
     // =========================== epilogue ===========================
-    const int et = tid - 160;            // 0..127: accumulator lane == row slot of the tile
-    const int lane_quarter = warp & 3;   // the TMEM lanes this warp may read: 32*(warp%4)..+31
+    const int lane_quarter = warp & 3;  // the TMEM lanes this warp may read: 32*(warp%4)..+31
     const int slot_in_tile = lane_quarter * 32 + lane;
-    (void)et;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
-      const int slot2 = it & 1;
-      const uint32_t par2 = (it >> 1) & 1;
-      const int slot = tile * kTileM + slot_in_tile;
+    for (int t = t0; t < t1; ++t) {
+      const int it = t - t0;
+      const int buf = it & 1;
+      const int slot = t * kTileM + slot_in_tile;
       int my_row = n_out;
-      if (slot < n_out) my_row = order ? __ldg(order + slot) : slot;
-      bool ok = mbar_wait(smem_u32(&ctl->accfull[slot2]), par2, ctl);
+      if (slot < n_out) my_row = ls.order ? __ldg(ls.order + slot) : slot;
+      const bool any = first_stage(ls.tile_ptr, t + 1) > first_stage(ls.tile_ptr, t);
+      bool ok = mbar_wait(smem_u32(&ctl->accfull[buf]), (it >> 1) & 1, ctl);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool any = ctl->acc_stages[slot2] > 0;
       const bool store_row = my_row < n_out;
-      const uint32_t taddr = tmem_base + static_cast<uint32_t>(slot2 * cout) + (static_cast<uint32_t>(lane_quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(buf * cout) + (static_cast<uint32_t>(lane_quarter * 32) << 16);
       __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
       const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
       for (int c0 = 0; c0 < cout; c0 += 16) {
         uint32_t r[16];
-        if (any) {
+        if (any) {  // warp-uniform: the tensor-memory load is warp-collective
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
         } else {
@@ -499,12 +436,12 @@ __global__ void __launch_bounds__(288, 1)
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->accempty[slot2]));  // 128 arrivals hand the accumulator back
+      mbar_arrive(smem_u32(&ctl->accempty[buf]));  // 128 arrivals hand the accumulator back
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(tmem_cols))
@@ -532,26 +469,58 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   return PCE_OK;
 }
 
-int conv_umma(const void* in, const void* wpacked, const uint32_t* mask, const int* rowptr, const int* nbr,
-              const int* order, int n_out, int cin, int cout, int kv, void* out, const pce_epilogue* ep,
-              cudaStream_t st) {
-  if (kv > 32 * umma::kMaxWords) return PCE_ERR_UNSUPPORTED;
+// cuTensorMapEncodeTiled, looked up through the runtime so the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int encode_feature_map(const void* feats, int n_rows, int cin, CUtensorMap* out) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    PCE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (p == nullptr || q != cudaDriverEntryPointSuccess) return PCE_ERR_UNSUPPORTED;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  // [n_rows][cin] fp16, row stride cin*2 bytes; the box is one row of 64 channels (gather4 takes
+  // four such rows by index), written with the 128-byte swizzle tcgen05.mma expects; reads
+  // outside the tensor (absent neighbours, channel tail) return zeros.
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(n_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cin) * 2};
+  const cuuint32_t box[2] = {64, 1};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(feats), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return PCE_ERR_CUDA;
+  }
+  return PCE_OK;
+}
+
+// tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
+int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
+              void* out, const pce_epilogue* ep, cudaStream_t st) {
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
   if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
+  umma::Lists ls{nullptr, nullptr, nullptr, nullptr};
+  if (tiles) ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr};
+  alignas(64) CUtensorMap in_map;
+  PCE_TRY(encode_feature_map(in, n_in > 0 ? n_in : 1, cin, &in_map));
   int tmem_cols = 32;
   while (tmem_cols < 2 * cout) tmem_cols <<= 1;  // two accumulators
-  const size_t stage = static_cast<size_t>(umma::kABytes + cout * 128);
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
-  const int ns = 4;
-  const size_t smem = ns * stage + fixed;
+  const size_t smem = static_cast<size_t>(umma::kStages) * (umma::kABytes + cout * 128) + fixed;
   static int sm_count[64] = {};
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
   if (sm_count[dev] == 0) {
-    const size_t max_smem = static_cast<size_t>(umma::kMaxStages) * (umma::kABytes + 256 * 128) + fixed;
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(max_smem > 232448 ? 232448 : max_smem)));
+    const size_t max_smem = static_cast<size_t>(umma::kStages) * (umma::kABytes + 256 * 128) + fixed;
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(max_smem)));
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -563,9 +532,8 @@ int conv_umma(const void* in, const void* wpacked, const uint32_t* mask, const i
   if (per_sm < 1) per_sm = 1;
   const int n_tiles = div_up(n_out, umma::kTileM);
   const int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
-  umma::k_conv_umma<4><<<grid, 288, smem, st>>>(static_cast<const __half*>(in), static_cast<const __half*>(wpacked),
-                                                mask, rowptr, nbr, order, n_out, cin, cout, kv,
-                                                static_cast<__half*>(out), e, tmem_cols);
+  umma::k_conv_umma<<<grid, 192, smem, st>>>(in_map, static_cast<const __half*>(wpacked), ls, n_out, cin, cout,
+                                             static_cast<__half*>(out), e, tmem_cols);
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }

@@ -392,6 +392,59 @@ __global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int w
   vals[r] = r;
 }
 
+// Tile lists: the map re-laid for 128-row output tiles taken in processing order.
+// One CTA of 128 threads per tile; thread r owns the tile's r-th row.
+//   FILL = false: tile_cnt[t] = number of offsets any row of the tile has.
+//   FILL = true : for the tile's s-th present offset (ascending kp) write stage_kp[base+s] and
+//                 stage_nbr[(base+s)*128 + r] = the row's input at that offset, or -1.
+template <bool FILL>
+__global__ void __launch_bounds__(128)
+    k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
+                 const int* __restrict__ order, int n_rows, int words, int* tile_cnt,
+                 const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
+  __shared__ uint32_t wmask[4][4];
+  const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
+  const int slot = t * 128 + r;
+  int row = -1;
+  if (slot < n_rows) row = order ? __ldg(order + slot) : slot;
+  uint32_t my[4] = {0, 0, 0, 0};
+  if (row >= 0)
+    for (int w = 0; w < words; ++w) my[w] = __ldg(mask + static_cast<size_t>(row) * words + w);
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, my[w]);
+    if (lane == 0) wmask[warp][w] = m;
+  }
+  __syncthreads();
+  uint32_t tm[4];
+  int cnt = 0;
+  for (int w = 0; w < 4; ++w) {
+    tm[w] = wmask[0][w] | wmask[1][w] | wmask[2][w] | wmask[3][w];
+    cnt += __popc(tm[w]);
+  }
+  if (!FILL) {
+    if (r == 0) tile_cnt[t] = cnt;
+    return;
+  }
+  const int base = __ldg(tile_ptr + t);
+  int cursor = row >= 0 ? __ldg(rowptr + row) : 0;
+  int s = 0;
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = tm[w];
+    while (m) {
+      const int bit = __ffs(m) - 1;
+      m &= m - 1;
+      int v = -1;
+      if ((my[w] >> bit) & 1u) v = __ldg(nbr + cursor++);
+      const int g = base + s;
+      if (g < stage_cap) {
+        stage_nbr[static_cast<size_t>(g) * 128 + r] = v;
+        if (r == 0) stage_kp[g] = w * 32 + bit;
+      }
+      ++s;
+    }
+  }
+}
+
 // ---- host helpers ------------------------------------------------------------
 
 static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, cudaStream_t st) {
@@ -666,6 +719,31 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
   char* tmp = ar.take<char>(need);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, keys, skeys, vals, order, n_rows, 0, bits, st));
+  return PCE_OK;
+}
+
+int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, const int32_t* order,
+                         int32_t n_rows, int32_t kv, void* workspace, size_t workspace_bytes, int32_t* tile_ptr,
+                         int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap, void* stream) {
+  if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_tiles = div_up(n_rows, 128);
+  if (n_tiles == 0) {
+    PCE_CUDA(cudaMemsetAsync(tile_ptr, 0, sizeof(int), st));
+    return PCE_OK;
+  }
+  if (!mask || !rowptr || !nbr || !stage_kp || !stage_nbr) return PCE_ERR_INVALID;
+  const int words = (kv + 31) / 32;
+  Arena ar(workspace, workspace_bytes);
+  int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
+  k_tile_lists<false><<<n_tiles, 128, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, cnt, nullptr, nullptr, nullptr, 0);
+  PCE_LAUNCH_CHECK();
+  PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
+  k_tile_lists<true><<<n_tiles, 128, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, nullptr, tile_ptr, stage_kp,
+                                              stage_nbr, stage_cap);
+  PCE_LAUNCH_CHECK();
   return PCE_OK;
 }
 

@@ -105,9 +105,9 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                    kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
-    order = csr.order() if (packed is not None and SORT_ROWS) else None
+    tiles = C.byref(csr.tiles(SORT_ROWS)) if packed is not None else None
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
-                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), _lib.ptr(order), csr.n_rows,
+                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:

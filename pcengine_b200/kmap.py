@@ -38,12 +38,13 @@ def candidates_per_input(ks, stride) -> int:
 class NeighbourCSR:
     """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap]."""
 
-    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src", "kv", "_order")
+    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src", "kv", "_order", "_tiles")
 
     def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None):
         self.mask, self.rowptr, self.nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
         self.kv = kv
         self._order = None
+        self._tiles = {}
 
     def order(self):
         """Output rows sorted by indicator bitmask (int32 [n_rows], built once): the order in which
@@ -56,6 +57,32 @@ class NeighbourCSR:
                                              out.data_ptr(), _lib.stream_ptr(dev)), "pce_csr_sort_rows")
             self._order = out
         return self._order
+
+    def tiles(self, sort_rows: bool = True):
+        """The map as tile lists (a ``_lib.TileLists`` struct of device pointers) for the
+        tensor-core kernel; built once per CSR and per ordering, kept alive with it."""
+        key = bool(sort_rows)
+        hit = self._tiles.get(key)
+        if hit is not None:
+            return hit[0]
+        dev = self.mask.device
+        n_tiles = (self.n_rows + 127) // 128
+        if sort_rows:
+            order = self.order()
+        else:
+            order = torch.arange(self.n_rows, dtype=torch.int32, device=dev)
+        cap = max(1, n_tiles * self.kv)
+        tile_ptr = torch.empty((n_tiles + 1,), dtype=torch.int32, device=dev)
+        stage_kp = torch.empty((cap,), dtype=torch.int32, device=dev)
+        stage_nbr = torch.empty((cap * 128,), dtype=torch.int32, device=dev)
+        ws = _lib.workspace(8 * (n_tiles + 1) + (1 << 20), dev)
+        _lib.check(lib.pce_build_tile_lists(self.mask.data_ptr(), self.rowptr.data_ptr(), self.nbr.data_ptr(),
+                                            order.data_ptr(), self.n_rows, self.kv, ws.data_ptr(), ws.numel(),
+                                            tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(), cap,
+                                            _lib.stream_ptr(dev)), "pce_build_tile_lists")
+        st = _lib.TileLists(order.data_ptr(), tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr())
+        self._tiles[key] = (st, order, tile_ptr, stage_kp, stage_nbr)
+        return st
 
 
 class KernelMap:

@@ -98,3 +98,39 @@ def test_out_of_range_coordinate_reports_status():
     km = pce.KernelMap(bad, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], [70000, 1, 1], True)
     with pytest.raises(RuntimeError):
         km.sizes()
+
+
+@pytest.mark.parametrize("ks,sort_rows", [((3, 3, 3), True), ((3, 3, 3), False), ((5, 5, 5), True), ((2, 2, 2), True)])
+def test_tile_lists_match_the_csr(ks, sort_rows):
+    """Tile lists are the oracle's neighbour CSR re-laid: per 128-row tile (in processing order) one
+    stage per offset present in the tile, with each row's neighbour at that offset or -1."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(14, 56, batch=2)
+    d2 = ko.build_d2(coords, ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    nb = ko.neighbour_csr(d2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    csr.tiles(sort_rows)
+    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[sort_rows]
+    order, tile_ptr = order.cpu().numpy(), tile_ptr.cpu().numpy()
+    stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, 128)
+    n, kv = km.n_out, km.kv
+    assert np.array_equal(np.sort(order), np.arange(n))
+    if not sort_rows:
+        assert np.array_equal(order, np.arange(n))
+    # dense view of the oracle CSR: want[row, kp] = input row or -1
+    want = np.full((n, kv), -1, np.int64)
+    rows = np.repeat(np.arange(n), np.diff(nb["rowptr"]))
+    kps = np.concatenate([np.nonzero([(int(nb["mask"][r, k // 32]) >> (k % 32)) & 1 for k in range(kv)])[0]
+                          for r in range(n)])
+    want[rows, kps] = nb["nbr"]
+    n_tiles = (n + 127) // 128
+    assert tile_ptr[0] == 0 and len(tile_ptr) == n_tiles + 1
+    for t in range(n_tiles):
+        rws = order[t * 128:(t + 1) * 128]
+        present = np.nonzero((want[rws] >= 0).any(axis=0))[0]
+        a, b = tile_ptr[t], tile_ptr[t + 1]
+        assert np.array_equal(stage_kp[a:b], present)
+        got = stage_nbr[a:b, :len(rws)]
+        assert np.array_equal(got, want[rws][:, present].T)
+        assert (stage_nbr[a:b, len(rws):] == -1).all()
