@@ -233,6 +233,10 @@ PCE_API size_t pce_packed_weights_bytes(int32_t kv, int32_t c_in, int32_t c_out)
 PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int32_t c_out, int32_t dtype,
                              void* packed, void* stream);
 
+/* Tuning hook for experiments and tests; what = 0: force the tensor-core kernel's stage-ring
+ * depth (value 4, 6 or 8; 0 restores the automatic choice). */
+PCE_API int pce_tune(int32_t what, int32_t value);
+
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
  * bounded wait expired records PCE_ERR_TIMEOUT.  SYNCHRONISES the device. */
 PCE_API int pce_device_status(int32_t* status_host, int32_t reset);

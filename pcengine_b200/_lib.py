@@ -23,7 +23,7 @@ EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
-    "pce_pack_weights", "pce_device_status", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
+    "pce_pack_weights", "pce_device_status", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
 ]
 
 
@@ -72,6 +72,7 @@ def _load() -> C.CDLL:
     lib.pce_packed_weights_bytes.argtypes = [i32, i32, i32]
     lib.pce_pack_weights.argtypes = [vp, i32, i32, i32, i32, vp, vp]
     lib.pce_device_status.argtypes = [C.POINTER(i32), i32]
+    lib.pce_tune.argtypes = [i32, i32]
     lib.pce_conv_kernel_choice.argtypes = [i32, i32, i32, i32]
     lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
                                     C.POINTER(Epilogue), vp]

@@ -9,6 +9,7 @@ bool conv_umma_supported(int cin, int cout, int dtype);
 size_t umma_packed_bytes(int kv, int cin, int cout);
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
 int umma_status_fetch(int* host_status, bool reset);
+extern int umma_force_stages;
 int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
               void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -54,6 +55,14 @@ int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int32_t c_ou
   if (!weights || !packed || kv < 1) return PCE_ERR_INVALID;
   if (!conv_umma_supported(c_in, c_out, dtype)) return PCE_ERR_UNSUPPORTED;
   return umma_pack_weights(weights, kv, c_in, c_out, packed, static_cast<cudaStream_t>(stream));
+}
+
+int pce_tune(int32_t what, int32_t value) {
+  if (what == 0) {
+    umma_force_stages = value;
+    return PCE_OK;
+  }
+  return PCE_ERR_INVALID;
 }
 
 int pce_device_status(int32_t* status_host, int32_t reset) {
