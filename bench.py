@@ -211,6 +211,78 @@ def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: in
     return rows, int(coords.size(0))
 
 
+def run_scene(args):
+    """``--workload scene``: ONE large indoor scene (20 rooms tiled 5x4, about 1.5 M voxels at 2 cm)
+    split into x-slabs, one per rank, with a kernel-radius halo exchanged by point-to-point messages
+    (NCCL over NVLink) before every layer.  Per layer: time of [halo exchange + convolution] over all
+    ranks (max), voxels/s of the whole scene, algorithmic GB/s and TFLOP/s."""
+    import torch.distributed as dist
+
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    from pcengine_b200 import multigpu as mg
+    from pcengine_b200 import synth
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    xyz = synth.tiled_scene()
+    coords_h = synth.with_batch(xyz)
+    cmax = coords_h[:, 1:].max(0).tolist()
+    n_total = len(coords_h)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    for ks, c in ((3, 64), (3, 256), (5, 64), (5, 256)):
+        radius = (ks - 1) // 2
+        cuts, owned = mg.split_scene(coords_h, world, radius)
+        idx = owned[rank]
+        scene = mg.SlabScene(torch.from_numpy(coords_h[idx]).to(dev), cuts, rank, world, radius).setup()
+        g = torch.Generator().manual_seed(11 + rank)
+        feats = torch.randn(len(idx), c, generator=g).half().to(dev)
+        w = (torch.randn(ks ** 3, c, c, generator=torch.Generator().manual_seed(3)) / (ks ** 3 * c) ** 0.5).half().to(dev)
+        km = pce.KernelMap(scene.local_coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
+        csr = km.csr()
+        pairs = int(csr.rowptr[scene.n_owned].item())  # pairs whose output this rank owns
+        for _ in range(max(args.warmup, 2)):
+            PF.conv_forward(scene.local_feats(feats), w, csr)
+        ts = []
+        for _ in range(max(args.steps, 3)):
+            flush.zero_()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = PF.conv_forward(scene.local_feats(feats), w, csr)
+            b.record()
+            b.synchronize()
+            ts.append(mg.max_over_ranks(a.elapsed_time(b) * 1e-3, dev))
+        t = float(np.median(ts))
+        tot_pairs = pairs
+        halo_rows = int(scene.local_coords.size(0) - scene.n_owned)
+        if world > 1:
+            tp = torch.tensor([pairs, halo_rows], dtype=torch.int64, device=dev)
+            dist.all_reduce(tp)
+            tot_pairs, halo_rows = int(tp[0]), int(tp[1])
+        by = 2 * (n_total * c * 2) + 2 * ks ** 3 * c * c + 4 * tot_pairs
+        fl = 2.0 * tot_pairs * c * c
+        rows.append({"layer": f"subm{ks}_{c}x{c}", "ms": t * 1e3, "voxels_per_s": n_total / t, "pairs": tot_pairs,
+                     "halo_rows_total": halo_rows, "GB/s": by / t / 1e9, "TFLOP/s": fl / t / 1e12,
+                     "hbm_frac_per_gpu": by / t / 1e9 / pk["hbm_gbs"] / world, "tensor_frac_per_gpu": fl / t / 1e12 / pk["tflops"] / world})
+        del km, csr, scene, feats, w, out
+        torch.cuda.empty_cache()
+    if rank == 0:
+        print(json.dumps({"workload": "scene_slabs", "n_gpus": world, "voxels": n_total, "layers": rows,
+                          "note": "x-slabs, kernel-radius halo exchanged before the layer (inside the timed region); "
+                                  "map build outside the timed region"}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_layer(args):
     """``--layer NAME``: only that single layer on ``--scans`` collated scans (a small, short case for
     a profiler capture).  Prints one JSON line with the kernel-only figures."""
@@ -385,10 +457,14 @@ def main():
     ap.add_argument("--layer", type=str, default=None, choices=sorted(LAYERS),
                     help="run one single layer only (kernel-only timing); see --scans")
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
+    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene"],
+                    help="minkunet: batch of 8 LiDAR scans per GPU (default); scene: one 1.5 M-voxel scene in x-slabs")
     ap.add_argument("--lean", action="store_true",
                     help="skip the per-layer table and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
-    if args.layer is not None:
+    if args.workload == "scene":
+        run_scene(args)
+    elif args.layer is not None:
         run_layer(args)
     elif args.impl == "reference":
         run_reference(args)

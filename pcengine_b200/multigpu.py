@@ -1,0 +1,143 @@
+"""Multi-GPU helpers for the two ways the sparse-convolution path shards (the reference has no
+multi-GPU support at all, so nothing here mirrors reference code):
+
+* scan-parallel: independent scans go to different ranks; nothing is exchanged on the data path
+  (``scans_for_rank``, ``max_over_ranks`` for device-side timing);
+* slab-parallel: ONE large scene is cut along x into slabs with balanced voxel counts; every rank
+  owns the outputs of its slab and needs the inputs within the kernel radius of its cut planes.
+  Coordinates of that halo are exchanged once, features before every layer, with neighbour-only
+  point-to-point messages (``torch.distributed`` isend/irecv: NCCL over NVLink between GPUs, gloo in
+  the CPU tests).  Halo rows land in the rank's own memory before any kernel reads them.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def scans_for_rank(n_scans: int, rank: int, world: int) -> List[int]:
+    """Contiguous, balanced share of ``n_scans`` independent scans for ``rank``."""
+    base, extra = divmod(n_scans, world)
+    start = rank * base + min(rank, extra)
+    return list(range(start, start + base + (1 if rank < extra else 0)))
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """Maximum of a host float over all ranks (the step time of a multi-GPU run)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def slab_cuts(x: np.ndarray, world: int, radius: int) -> List[int]:
+    """``world + 1`` cut planes along x (cuts[g] <= x < cuts[g+1] is owned by rank g) that balance the
+    voxel counts; every slab is at least ``radius`` wide so a halo never reaches past a neighbour."""
+    x = np.asarray(x, dtype=np.int64)
+    lo, hi = int(x.min()), int(x.max()) + 1
+    if world == 1:
+        return [lo, hi]
+    hist = np.bincount(x - lo, minlength=hi - lo)
+    cum = np.concatenate([[0], np.cumsum(hist)])
+    cuts = [lo]
+    for g in range(1, world):
+        target = cum[-1] * g / world
+        c = lo + int(np.searchsorted(cum, target))
+        c = max(c, cuts[-1] + max(radius, 1))
+        cuts.append(c)
+    cuts.append(hi)
+    for g in range(world):
+        if cuts[g + 1] - cuts[g] < max(radius, 1):
+            raise ValueError("scene too thin along x for this many slabs and this kernel radius")
+    return cuts
+
+
+class SlabScene:
+    """One rank's view of an x-slab decomposition: owned rows first, then the left and right halo.
+
+    ``coords`` / ``feats`` passed in are the rows this rank OWNS (cuts[rank] <= x < cuts[rank+1]).
+    ``setup`` exchanges halo coordinates with the two neighbours; ``local_feats`` returns the
+    [owned | left halo | right halo] feature matrix after exchanging the boundary rows of ``feats``.
+    A submanifold layer run on (local coords, local feats) gives, in its first ``n_owned`` rows,
+    exactly the rows a single-GPU run produces for these voxels (same neighbours, same kp order).
+    """
+
+    def __init__(self, coords: torch.Tensor, cuts: Sequence[int], rank: int, world: int, radius: int):
+        self.rank, self.world, self.radius = rank, world, radius
+        self.cuts = list(cuts)
+        self.coords = coords
+        self.n_owned = int(coords.size(0))
+        x = coords[:, 1]
+        lo, hi = self.cuts[rank], self.cuts[rank + 1]
+        if self.n_owned and (int(x.min()) < lo or int(x.max()) >= hi):
+            raise ValueError("coords contain rows outside this rank's slab")
+        # rows a neighbour needs from us (our boundary layers)
+        self.send_left = torch.nonzero(x < lo + radius).flatten() if rank > 0 else coords.new_zeros((0,), dtype=torch.long)
+        self.send_right = torch.nonzero(x >= hi - radius).flatten() if rank < world - 1 else coords.new_zeros((0,), dtype=torch.long)
+        self.halo_left = None
+        self.halo_right = None
+        self.local_coords = None
+
+    # -- point-to-point plumbing (neighbour-only) ---------------------------------------------
+    def _exchange(self, to_left: Optional[torch.Tensor], to_right: Optional[torch.Tensor], row_shape, dtype):
+        """Send a row block to each neighbour, receive theirs; returns (from_left, from_right)."""
+        dev = self.coords.device
+        left, right = self.rank - 1, self.rank + 1
+        n_send = torch.tensor([0 if to_left is None else to_left.size(0), 0 if to_right is None else to_right.size(0)],
+                              dtype=torch.int64, device=dev)
+        n_recv = torch.zeros(2, dtype=torch.int64, device=dev)
+        ops = []
+        if left >= 0:
+            ops += [dist.P2POp(dist.isend, n_send[0:1], left), dist.P2POp(dist.irecv, n_recv[0:1], left)]
+        if right < self.world:
+            ops += [dist.P2POp(dist.isend, n_send[1:2], right), dist.P2POp(dist.irecv, n_recv[1:2], right)]
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        counts = n_recv.cpu().tolist()
+        from_left = torch.empty((counts[0],) + tuple(row_shape), dtype=dtype, device=dev)
+        from_right = torch.empty((counts[1],) + tuple(row_shape), dtype=dtype, device=dev)
+        ops = []
+        if left >= 0:
+            if to_left.size(0):
+                ops.append(dist.P2POp(dist.isend, to_left.contiguous(), left))
+            if counts[0]:
+                ops.append(dist.P2POp(dist.irecv, from_left, left))
+        if right < self.world:
+            if to_right.size(0):
+                ops.append(dist.P2POp(dist.isend, to_right.contiguous(), right))
+            if counts[1]:
+                ops.append(dist.P2POp(dist.irecv, from_right, right))
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        return from_left, from_right
+
+    def setup(self):
+        """Exchange the halo coordinates (once per scene)."""
+        if self.world == 1:
+            self.halo_left = self.coords[:0]
+            self.halo_right = self.coords[:0]
+        else:
+            self.halo_left, self.halo_right = self._exchange(self.coords[self.send_left], self.coords[self.send_right],
+                                                             (4,), self.coords.dtype)
+        self.local_coords = torch.cat([self.coords, self.halo_left, self.halo_right], dim=0).contiguous()
+        return self
+
+    def local_feats(self, feats: torch.Tensor) -> torch.Tensor:
+        """[owned | left halo | right halo] features; the halo rows come from the neighbours' ``feats``."""
+        if self.world == 1:
+            return feats
+        fl, fr = self._exchange(feats[self.send_left], feats[self.send_right], (feats.size(1),), feats.dtype)
+        return torch.cat([feats, fl, fr], dim=0).contiguous()
+
+
+def split_scene(coords: np.ndarray, world: int, radius: int):
+    """Host-side split of a whole scene (int32 [N,4]) into per-rank owned row indices + the cuts."""
+    cuts = slab_cuts(coords[:, 1], world, radius)
+    owned = [np.nonzero((coords[:, 1] >= cuts[g]) & (coords[:, 1] < cuts[g + 1]))[0] for g in range(world)]
+    return cuts, owned
