@@ -242,13 +242,14 @@ def run_scene(args):
         idx = owned[rank]
         scene = mg.SlabScene(torch.from_numpy(coords_h[idx]).to(dev), cuts, rank, world, radius).setup()
         g = torch.Generator().manual_seed(11 + rank)
-        feats = torch.randn(len(idx), c, generator=g).half().to(dev)
+        feats = scene.alloc_local(c, torch.float16)
+        feats[: scene.n_owned] = torch.randn(len(idx), c, generator=g).half().to(dev)
         w = (torch.randn(ks ** 3, c, c, generator=torch.Generator().manual_seed(3)) / (ks ** 3 * c) ** 0.5).half().to(dev)
         km = pce.KernelMap(scene.local_coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
         csr = km.csr()
         pairs = int(csr.rowptr[scene.n_owned].item())  # pairs whose output this rank owns
         for _ in range(max(args.warmup, 2)):
-            PF.conv_forward(scene.local_feats(feats), w, csr)
+            PF.conv_forward(scene.exchange_into(feats), w, csr)
         ts = []
         for _ in range(max(args.steps, 3)):
             flush.zero_()
@@ -257,7 +258,7 @@ def run_scene(args):
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            out = PF.conv_forward(scene.local_feats(feats), w, csr)
+            out = PF.conv_forward(scene.exchange_into(feats), w, csr)
             b.record()
             b.synchronize()
             ts.append(mg.max_over_ranks(a.elapsed_time(b) * 1e-3, dev))

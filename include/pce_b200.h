@@ -212,7 +212,7 @@ PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const
  * bitmask (stable radix sort), so rows with the same neighbourhood pattern land in the
  * same 128-row tile and the tile skips every offset none of them has.  Purely a
  * scheduling aid with no reference counterpart.  order[n_rows] receives the permutation;
- * workspace >= 24*n_rows + 8 MiB bytes. */
+ * workspace >= 64*n_rows + 16 MiB bytes. */
 PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace,
                               size_t workspace_bytes, int32_t* order, void* stream);
 

@@ -52,7 +52,7 @@ class NeighbourCSR:
         if self._order is None and self.kv is not None and self.n_rows > 0:
             dev = self.mask.device
             out = torch.empty((self.n_rows,), dtype=torch.int32, device=dev)
-            ws = _lib.workspace(24 * self.n_rows + (8 << 20), dev)
+            ws = _lib.workspace(64 * self.n_rows + (16 << 20), dev)
             _lib.check(lib.pce_csr_sort_rows(self.mask.data_ptr(), self.n_rows, self.kv, ws.data_ptr(), ws.numel(),
                                              out.data_ptr(), _lib.stream_ptr(dev)), "pce_csr_sort_rows")
             self._order = out

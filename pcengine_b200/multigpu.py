@@ -83,34 +83,36 @@ class SlabScene:
         self.local_coords = None
 
     # -- point-to-point plumbing (neighbour-only) ---------------------------------------------
-    def _exchange(self, to_left: Optional[torch.Tensor], to_right: Optional[torch.Tensor], row_shape, dtype):
-        """Send a row block to each neighbour, receive theirs; returns (from_left, from_right)."""
+    def _exchange(self, to_left, to_right, row_shape, dtype, recv_counts=None, out_left=None, out_right=None):
+        """Send a row block to each neighbour, receive theirs; returns (from_left, from_right).
+        Without ``recv_counts`` the sizes are exchanged first (one host synchronisation)."""
         dev = self.coords.device
         left, right = self.rank - 1, self.rank + 1
-        n_send = torch.tensor([0 if to_left is None else to_left.size(0), 0 if to_right is None else to_right.size(0)],
-                              dtype=torch.int64, device=dev)
-        n_recv = torch.zeros(2, dtype=torch.int64, device=dev)
-        ops = []
-        if left >= 0:
-            ops += [dist.P2POp(dist.isend, n_send[0:1], left), dist.P2POp(dist.irecv, n_recv[0:1], left)]
-        if right < self.world:
-            ops += [dist.P2POp(dist.isend, n_send[1:2], right), dist.P2POp(dist.irecv, n_recv[1:2], right)]
-        if ops:
-            for r in dist.batch_isend_irecv(ops):
-                r.wait()
-        counts = n_recv.cpu().tolist()
-        from_left = torch.empty((counts[0],) + tuple(row_shape), dtype=dtype, device=dev)
-        from_right = torch.empty((counts[1],) + tuple(row_shape), dtype=dtype, device=dev)
+        if recv_counts is None:
+            n_send = torch.tensor([0 if to_left is None else to_left.size(0), 0 if to_right is None else to_right.size(0)],
+                                  dtype=torch.int64, device=dev)
+            n_recv = torch.zeros(2, dtype=torch.int64, device=dev)
+            ops = []
+            if left >= 0:
+                ops += [dist.P2POp(dist.isend, n_send[0:1], left), dist.P2POp(dist.irecv, n_recv[0:1], left)]
+            if right < self.world:
+                ops += [dist.P2POp(dist.isend, n_send[1:2], right), dist.P2POp(dist.irecv, n_recv[1:2], right)]
+            if ops:
+                for r in dist.batch_isend_irecv(ops):
+                    r.wait()
+            recv_counts = n_recv.cpu().tolist()
+        from_left = out_left if out_left is not None else torch.empty((recv_counts[0],) + tuple(row_shape), dtype=dtype, device=dev)
+        from_right = out_right if out_right is not None else torch.empty((recv_counts[1],) + tuple(row_shape), dtype=dtype, device=dev)
         ops = []
         if left >= 0:
             if to_left.size(0):
                 ops.append(dist.P2POp(dist.isend, to_left.contiguous(), left))
-            if counts[0]:
+            if recv_counts[0]:
                 ops.append(dist.P2POp(dist.irecv, from_left, left))
         if right < self.world:
             if to_right.size(0):
                 ops.append(dist.P2POp(dist.isend, to_right.contiguous(), right))
-            if counts[1]:
+            if recv_counts[1]:
                 ops.append(dist.P2POp(dist.irecv, from_right, right))
         if ops:
             for r in dist.batch_isend_irecv(ops):
@@ -118,7 +120,7 @@ class SlabScene:
         return from_left, from_right
 
     def setup(self):
-        """Exchange the halo coordinates (once per scene)."""
+        """Exchange the halo coordinates (once per scene); the halo sizes are known from then on."""
         if self.world == 1:
             self.halo_left = self.coords[:0]
             self.halo_right = self.coords[:0]
@@ -126,14 +128,32 @@ class SlabScene:
             self.halo_left, self.halo_right = self._exchange(self.coords[self.send_left], self.coords[self.send_right],
                                                              (4,), self.coords.dtype)
         self.local_coords = torch.cat([self.coords, self.halo_left, self.halo_right], dim=0).contiguous()
+        self.n_local = int(self.local_coords.size(0))
         return self
 
+    def alloc_local(self, channels: int, dtype) -> torch.Tensor:
+        """An [n_local, channels] feature buffer laid out [owned | left halo | right halo].  A layer
+        that writes its output rows into ``buf[:n_owned]`` needs no copy before the next exchange."""
+        return torch.empty((self.n_local, channels), dtype=dtype, device=self.coords.device)
+
+    def exchange_into(self, buf: torch.Tensor) -> torch.Tensor:
+        """Fill the halo rows of ``buf`` (from :meth:`alloc_local`) with the neighbours' boundary rows
+        of their owned part; no size exchange, no host synchronisation, no concatenation."""
+        if self.world == 1:
+            return buf
+        n0, nl = self.n_owned, int(self.halo_left.size(0))
+        owned = buf[:n0]
+        self._exchange(owned[self.send_left], owned[self.send_right], (buf.size(1),), buf.dtype,
+                       recv_counts=[nl, int(self.halo_right.size(0))], out_left=buf[n0:n0 + nl], out_right=buf[n0 + nl:])
+        return buf
+
     def local_feats(self, feats: torch.Tensor) -> torch.Tensor:
-        """[owned | left halo | right halo] features; the halo rows come from the neighbours' ``feats``."""
+        """[owned | left halo | right halo] features from this rank's owned ``feats`` (allocates)."""
         if self.world == 1:
             return feats
-        fl, fr = self._exchange(feats[self.send_left], feats[self.send_right], (feats.size(1),), feats.dtype)
-        return torch.cat([feats, fl, fr], dim=0).contiguous()
+        buf = self.alloc_local(feats.size(1), feats.dtype)
+        buf[: self.n_owned] = feats
+        return self.exchange_into(buf)
 
 
 def split_scene(coords: np.ndarray, world: int, radius: int):
