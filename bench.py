@@ -284,6 +284,54 @@ def run_scene(args):
         dist.destroy_process_group()
 
 
+def run_indoor(args):
+    """``--workload indoor``: the indoor-room sweep.  One 8x8x3 m room voxelised at 2 cm (about 200 k
+    voxels), submanifold 3x3x3 at C_in = C_out in {16, 32, 64, 96, 128, 256}, fp16: the fused
+    output-stationary dataflow (D2) and the explicit gather -> GEMM -> scatter dataflow (D1), kernel-only
+    with an L2 flush between launches, plus what the 'auto' selector picks."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    from pcengine_b200 import synth
+    from pcengine_b200.spconv import _choose_dataflow
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    pk = peaks()
+    xyz, samples = synth.indoor_room(3001, 200000)
+    coords = torch.from_numpy(synth.with_batch(xyz)).to(dev)
+    km = pce.KernelMap(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], xyz.max(0).tolist(), True)
+    csr = km.csr()
+    pairs = int(csr.rowptr[-1].item())
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator().manual_seed(3)
+    rows = []
+    for c in (16, 32, 64, 96, 128, 256):
+        x = torch.randn(km.n_in, c, generator=g).half().to(dev)
+        w = (torch.randn(27, c, c, generator=g) / (27 * c) ** 0.5).half().to(dev)
+        res = {}
+        for name, fn in (("D2", lambda: PF.conv_forward(x, w, csr)), ("D1", lambda: PF.conv_forward_d1(x, w, km))):
+            for _ in range(max(args.warmup, 2)):
+                fn()
+            ts = []
+            for _ in range(max(args.steps, 5)):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                b.synchronize()
+                ts.append(a.elapsed_time(b) * 1e-3)
+            res[name] = float(np.median(ts))
+        by = 2 * (2 * km.n_in * c) + 2 * 27 * c * c + 4 * pairs
+        fl = 2.0 * pairs * c * c
+        pick = _choose_dataflow("auto", c, c)
+        rows.append({"C": c, "D2_us": res["D2"] * 1e6, "D1_us": res["D1"] * 1e6, "auto": pick,
+                     "auto_is_faster": res[pick] <= min(res.values()) * 1.02,
+                     "GB/s": by / res[pick] / 1e9, "TFLOP/s": fl / res[pick] / 1e12,
+                     "hbm_frac": by / res[pick] / 1e9 / pk["hbm_gbs"], "tensor_frac": fl / res[pick] / 1e12 / pk["tflops"]})
+    print(json.dumps({"workload": "indoor_sweep", "voxels": km.n_in, "surface_samples": samples, "pairs": pairs,
+                      "pairs_per_voxel": pairs / km.n_in, "layers": rows}))
+
+
 def run_layer(args):
     """``--layer NAME``: only that single layer on ``--scans`` collated scans (a small, short case for
     a profiler capture).  Prints one JSON line with the kernel-only figures."""
@@ -458,13 +506,15 @@ def main():
     ap.add_argument("--layer", type=str, default=None, choices=sorted(LAYERS),
                     help="run one single layer only (kernel-only timing); see --scans")
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
-    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene"],
+    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor"],
                     help="minkunet: batch of 8 LiDAR scans per GPU (default); scene: one 1.5 M-voxel scene in x-slabs")
     ap.add_argument("--lean", action="store_true",
                     help="skip the per-layer table and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
     if args.workload == "scene":
         run_scene(args)
+    elif args.workload == "indoor":
+        run_indoor(args)
     elif args.layer is not None:
         run_layer(args)
     elif args.impl == "reference":

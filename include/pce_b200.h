@@ -251,11 +251,15 @@ PCE_API int pce_conv_kernel_choice(int32_t c_in, int32_t c_out, int32_t dtype, i
  * Takes the CSR-coded maps of pce_map_build_d1; centre_kp >= 0 adds in @ W[centre_kp]
  * (the reference's cuBLAS beta=1 call, backend/spconv.cu:163-221) inside the
  * scatter pass.  Products are stored in the feature dtype in the buffer and
- * summed in fp32. */
-PCE_API int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
-                            int32_t c_out, const int32_t* qkpos, int32_t qsum, const int32_t* imap_coded,
-                            const int32_t* icsr, const int32_t* omap_coded, const int32_t* ocsr, int32_t n_out,
-                            void* buffer, size_t buffer_bytes, void* out_feats, int32_t dtype, int32_t centre_kp,
+ * summed in fp32.  With packed_weights (pce_pack_weights; may be NULL) and
+ * 1032*(qsum/128)+8 spare bytes behind the two buffer halves the per-offset GEMM
+ * runs on the tensor-core kernel (every 128-row tile of the padded buffer lies
+ * in one offset's segment), otherwise on CUDA cores. */
+PCE_API int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights,
+                            const void* packed_weights, int32_t kv, int32_t c_out, const int32_t* qkpos,
+                            int32_t qsum, const int32_t* imap_coded, const int32_t* icsr,
+                            const int32_t* omap_coded, const int32_t* ocsr, int32_t n_out, void* buffer,
+                            size_t buffer_bytes, void* out_feats, int32_t dtype, int32_t centre_kp,
                             const pce_epilogue* ep, void* stream);
 
 /* Dense rows x matrix with the same epilogue: the 1x1x1 stride-1 shortcut

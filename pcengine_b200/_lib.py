@@ -74,7 +74,7 @@ def _load() -> C.CDLL:
     lib.pce_device_status.argtypes = [C.POINTER(i32), i32]
     lib.pce_tune.argtypes = [i32, i32]
     lib.pce_conv_kernel_choice.argtypes = [i32, i32, i32, i32]
-    lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
+    lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
                                     C.POINTER(Epilogue), vp]
     lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, vp, i32, vp, i32, C.POINTER(Epilogue), vp]
     lib.pce_scale_shift_act.argtypes = [vp, i64, i32, vp, i32, C.POINTER(Epilogue), vp]

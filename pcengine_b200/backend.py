@@ -168,7 +168,9 @@ def conv_fwd_d1_cuda(in_feats, kernel, ksize_code, qsum_nnz, out_feats, kernel_k
     qsum = int(qsum_nnz)
     if buffer.dtype != feats.dtype:
         buffer = buffer.view(torch.uint8).view(feats.dtype) if buffer.is_contiguous() else buffer.to(feats.dtype)
-    _lib.check(lib.pce_conv_fwd_d1(feats.data_ptr(), n_in, c_in, w.data_ptr(), kv, c_out, kernel_qkpos.data_ptr(),
+    from .functional import packed_weights
+    _lib.check(lib.pce_conv_fwd_d1(feats.data_ptr(), n_in, c_in, w.data_ptr(), _lib.ptr(packed_weights(w)), kv, c_out,
+                                   kernel_qkpos.data_ptr(),
                                    qsum, in_map.data_ptr(), in_csr.data_ptr(), out_map.data_ptr(),
                                    out_csr.data_ptr(), n_out, buffer.data_ptr(), buffer.numel() * buffer.element_size(),
                                    out_feats.data_ptr(), _lib.dtype_code(feats.dtype),

@@ -9,6 +9,10 @@
 
 namespace pce {
 
+bool conv_umma_supported(int cin, int cout, int dtype);
+int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
+              void* out, const pce_epilogue* ep, cudaStream_t st);
+
 struct EpiDev {
   const float* scale;
   const float* shift;
@@ -32,7 +36,8 @@ __device__ __forceinline__ __half d1_from_f<__half>(float v) {
 constexpr int kCode = 1186111;
 
 // One warp per input row: copy the row to every buffer slot its CSR entries name
-// (ref: backend/spconv.cuh:48-81 gather_all_input_major_csr_*).
+// (ref: backend/spconv.cuh:48-81 gather_all_input_major_csr_*); 16-byte pieces when the row
+// length allows.
 template <typename T>
 __global__ void k_d1_gather(const T* __restrict__ in, int n_in, int cin, const int* __restrict__ qkpos,
                             const int* __restrict__ icsr, const int* __restrict__ imap, T* __restrict__ buf) {
@@ -41,11 +46,45 @@ __global__ void k_d1_gather(const T* __restrict__ in, int n_in, int cin, const i
   if (warp >= n_in) return;
   const int a = __ldg(icsr + warp), b = __ldg(icsr + warp + 1);
   const T* src = in + static_cast<size_t>(warp) * cin;
+  const int row_bytes = cin * static_cast<int>(sizeof(T));
+  const bool vec = (row_bytes % 16 == 0) && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(buf)) % 16 == 0);
   for (int e = a; e < b; ++e) {
     const int code = __ldg(imap + e);
     const size_t pos = static_cast<size_t>(__ldg(qkpos + code / kCode)) + code % kCode;
     T* dst = buf + pos * cin;
-    for (int c = lane; c < cin; c += 32) dst[c] = src[c];
+    if (vec) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      for (int c = lane; c < row_bytes / 16; c += 32) d4[c] = __ldg(s4 + c);
+    } else {
+      for (int c = lane; c < cin; c += 32) dst[c] = src[c];
+    }
+  }
+}
+
+// Tile lists for the per-offset GEMM over the gather buffer: rows are already dense and every
+// 128-row tile lies inside one offset's padded segment (segments are padded to 128,
+// ref: backend/hash.cuh:478-497), so tile t is one stage with offset = segment(t*128) and the
+// rows fetch themselves.
+__global__ void k_d1_tile_lists(const int* __restrict__ qkpos, int kv, int n_tiles, int* order, int* tile_ptr,
+                                int* stage_kp, int* stage_nbr) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_tiles * 128) {
+    order[i] = i;
+    stage_nbr[i] = i;
+  }
+  if (i <= n_tiles) tile_ptr[i] = i;
+  if (i < n_tiles) {
+    const int row = i * 128;
+    int lo = 0, hi = kv;  // largest kp with qkpos[kp] <= row
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(qkpos + mid) <= row)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    stage_kp[i] = lo;
   }
 }
 
@@ -115,9 +154,10 @@ __global__ void k_d1_scatter(const T* __restrict__ bout, const int* __restrict__
 }
 
 template <typename T>
-static int run_d1(const void* in, int n_in, int cin, const void* w, int kv, int cout, const int* qkpos, int qsum,
-                  const int* imap, const int* icsr, const int* omap, const int* ocsr, int n_out, void* buffer,
-                  void* out, int centre_kp, const EpiDev& ep, cudaStream_t st) {
+static int run_d1(const void* in, int n_in, int cin, const void* w, const void* wpacked, int kv, int cout,
+                  const int* qkpos, int qsum, const int* imap, const int* icsr, const int* omap, const int* ocsr,
+                  int n_out, void* buffer, size_t buffer_bytes, void* out, int centre_kp, const EpiDev& ep, int dtype,
+                  cudaStream_t st) {
   T* bin = static_cast<T*>(buffer);
   T* bout = bin + static_cast<size_t>(qsum) * cin;
   const T* in_t = static_cast<const T*>(in);
@@ -126,12 +166,37 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, int kv, int 
     k_d1_gather<T><<<div_up(static_cast<long long>(n_in) * 32, 256), 256, 0, st>>>(in_t, n_in, cin, qkpos, icsr, imap,
                                                                                     bin);
     PCE_LAUNCH_CHECK();
-    int need = (cout + 3) / 4, g = 1;
-    while (g < need && g < 32) g <<= 1;
-    k_d1_gemm<T><<<div_up(qsum, 256 / g), 256, 0, st>>>(bin, w_t, qkpos, kv, qsum, cin, cout, bout, g);
-    PCE_LAUNCH_CHECK();
+    // The per-offset GEMM: tensor cores when packed weights are given and the scratch for the
+    // tile lists fits behind the two halves of the buffer, else CUDA cores.
+    const int n_tiles = qsum / 128;
+    const size_t used = static_cast<size_t>(qsum) * (cin + cout) * sizeof(T);
+    const size_t lists_at = (used + 255) & ~size_t(255);
+    const size_t lists_bytes = sizeof(int) * (static_cast<size_t>(n_tiles) * 258 + 2);
+    const bool tc = wpacked != nullptr && conv_umma_supported(cin, cout, dtype) && qsum % 128 == 0 &&
+                    lists_at + lists_bytes <= buffer_bytes &&
+                    ((reinterpret_cast<uintptr_t>(buffer) | reinterpret_cast<uintptr_t>(wpacked)) % 16 == 0) &&
+                    (static_cast<size_t>(qsum) * cin * sizeof(T)) % 16 == 0;
+    if (tc) {
+      int* base = reinterpret_cast<int*>(static_cast<char*>(buffer) + lists_at);
+      int* order = base;
+      int* stage_nbr = order + static_cast<size_t>(n_tiles) * 128;
+      int* tile_ptr = stage_nbr + static_cast<size_t>(n_tiles) * 128;
+      int* stage_kp = tile_ptr + n_tiles + 1;
+      k_d1_tile_lists<<<div_up(static_cast<long long>(n_tiles) * 128 + 1, 256), 256, 0, st>>>(qkpos, kv, n_tiles, order,
+                                                                                               tile_ptr, stage_kp, stage_nbr);
+      PCE_LAUNCH_CHECK();
+      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr};
+      PCE_TRY(conv_umma(bin, qsum, wpacked, &tl, qsum, cin, cout, bout, nullptr, st));
+    } else {
+      if (w == nullptr) return PCE_ERR_INVALID;
+      int need = (cout + 3) / 4, g = 1;
+      while (g < need && g < 32) g <<= 1;
+      k_d1_gemm<T><<<div_up(qsum, 256 / g), 256, 0, st>>>(bin, w_t, qkpos, kv, qsum, cin, cout, bout, g);
+      PCE_LAUNCH_CHECK();
+    }
   }
   if (n_out > 0) {
+    if (centre_kp >= 0 && w == nullptr) return PCE_ERR_INVALID;
     const T* wmid = centre_kp >= 0 ? w_t + static_cast<size_t>(centre_kp) * cin * cout : nullptr;
     k_d1_scatter<T><<<div_up(static_cast<long long>(n_out) * cout, 256), 256, 0, st>>>(
         bout, qkpos, ocsr, omap, n_out, cout, in_t, wmid, cin, static_cast<T*>(out), ep);
@@ -144,15 +209,15 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, int kv, int 
 
 using namespace pce;
 
-extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, int32_t kv,
-                               int32_t c_out, const int32_t* qkpos, int32_t qsum, const int32_t* imap_coded,
-                               const int32_t* icsr, const int32_t* omap_coded, const int32_t* ocsr, int32_t n_out,
-                               void* buffer, size_t buffer_bytes, void* out_feats, int32_t dtype, int32_t centre_kp,
-                               const pce_epilogue* ep, void* stream) {
+extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights,
+                               const void* packed_weights, int32_t kv, int32_t c_out, const int32_t* qkpos, int32_t qsum,
+                               const int32_t* imap_coded, const int32_t* icsr, const int32_t* omap_coded,
+                               const int32_t* ocsr, int32_t n_out, void* buffer, size_t buffer_bytes, void* out_feats,
+                               int32_t dtype, int32_t centre_kp, const pce_epilogue* ep, void* stream) {
   if (n_in < 0 || n_out < 0 || c_in < 1 || c_out < 1 || kv < 1 || qsum < 0) return PCE_ERR_INVALID;
   if (dtype != PCE_F32 && dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
   if (n_out == 0) return PCE_OK;
-  if (!weights || !out_feats || !qkpos || !ocsr || !icsr) return PCE_ERR_INVALID;
+  if ((!weights && !packed_weights) || !out_feats || !qkpos || !ocsr || !icsr) return PCE_ERR_INVALID;
   if (qsum > 0 && (!imap_coded || !omap_coded || !buffer || !in_feats)) return PCE_ERR_INVALID;
   if (centre_kp >= kv || (centre_kp >= 0 && n_in != n_out)) return PCE_ERR_INVALID;
   const size_t esize = dtype == PCE_F32 ? 4 : 2;
@@ -161,8 +226,8 @@ extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in,
   if (ep) e = EpiDev{ep->scale, ep->shift, ep->residual, ep->act, ep->slope};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == PCE_F32)
-    return run_d1<float>(in_feats, n_in, c_in, weights, kv, c_out, qkpos, qsum, imap_coded, icsr, omap_coded, ocsr,
-                         n_out, buffer, out_feats, centre_kp, e, st);
-  return run_d1<__half>(in_feats, n_in, c_in, weights, kv, c_out, qkpos, qsum, imap_coded, icsr, omap_coded, ocsr,
-                        n_out, buffer, out_feats, centre_kp, e, st);
+    return run_d1<float>(in_feats, n_in, c_in, weights, nullptr, kv, c_out, qkpos, qsum, imap_coded, icsr, omap_coded,
+                         ocsr, n_out, buffer, buffer_bytes, out_feats, centre_kp, e, dtype, st);
+  return run_d1<__half>(in_feats, n_in, c_in, weights, packed_weights, kv, c_out, qkpos, qsum, imap_coded, icsr,
+                        omap_coded, ocsr, n_out, buffer, buffer_bytes, out_feats, centre_kp, e, dtype, st);
 }

@@ -116,6 +116,45 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
     return out
 
 
+def conv_forward_d1(feats: torch.Tensor, kernel: torch.Tensor, kmap, transposed: bool = False,
+                    epilogue: Optional[FusedEpilogue] = None, buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Explicit gather -> per-offset GEMM -> scatter over a buffer of qsum x (C_in + C_out) elements
+    (the reference's D1 dataflow, script/spconv.py:146-161): ``kmap`` is a KernelMap, whose CSR-coded
+    forms are used; a transposed layer swaps the two sides (script/spconv.py:142-151).  ``buffer`` may
+    be a caller workspace (as ``spTensor.buffer``); it is allocated when missing or too small."""
+    _lib.require_cuda(feats, "feats")
+    if kernel.dim() == 2:
+        kernel = kernel.unsqueeze(0)
+    feats = feats.contiguous()
+    if not kernel.is_contiguous() or kernel.dtype != feats.dtype:
+        kernel = kernel.detach().contiguous().to(feats.dtype)
+    if feats.size(1) != kernel.size(1):
+        raise ValueError("Input feature size and kernel size mismatch")
+    kv, c_in, c_out = kernel.shape
+    imap_c, icsr, omap_c, ocsr = kmap.d1()
+    _, qsum = kmap.sizes()
+    n_in, n_out = kmap.n_in, kmap.n_out
+    if transposed:
+        imap_c, icsr, omap_c, ocsr = omap_c, ocsr, imap_c, icsr
+        n_in, n_out = n_out, n_in
+    if feats.size(0) != n_in:
+        raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({n_in})")
+    esize = feats.element_size()
+    need = qsum * (c_in + c_out) * esize + 1032 * (qsum // 128) + 1024
+    if buffer is None or buffer.numel() * buffer.element_size() < need or not buffer.is_cuda:
+        buffer = torch.empty((need,), dtype=torch.uint8, device=feats.device)
+    out = torch.empty((n_out, c_out), dtype=feats.dtype, device=feats.device)
+    packed = packed_weights(kernel)
+    centre = kmap.mid if (kmap.subm and not transposed) else -1
+    _lib.check(lib.pce_conv_fwd_d1(feats.data_ptr(), n_in, c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
+                                   kmap.qkpos.data_ptr(), qsum, imap_c.data_ptr(), icsr.data_ptr(), omap_c.data_ptr(),
+                                   ocsr.data_ptr(), n_out, buffer.data_ptr(), buffer.numel() * buffer.element_size(),
+                                   out.data_ptr(), _lib.dtype_code(feats.dtype), centre,
+                                   _pack(epilogue, c_out, n_out, feats.dtype), _lib.stream_ptr(feats.device)),
+               "pce_conv_fwd_d1")
+    return out
+
+
 def linear_forward(feats: torch.Tensor, weight: torch.Tensor, epilogue: Optional[FusedEpilogue] = None) -> torch.Tensor:
     """feats [N,C_in] @ weight [C_in,C_out] with the fused epilogue (the 1x1x1 shortcut)."""
     _lib.require_cuda(feats, "feats")

@@ -245,3 +245,33 @@ def test_slab_decomposition_matches_whole_scene(ks, world):
         km = pce.KernelMap(local, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax, True)
         out = PF.conv_forward(feats[torch.from_numpy(rows).cuda()], w, km.csr())
         assert torch.equal(out[: len(owned[g])], full[torch.from_numpy(owned[g]).cuda()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("cin,cout", [(16, 16), (64, 64), (96, 32), (24, 19)])
+def test_explicit_dataflow_d1(dtype, cin, cout):
+    """Tag 'D1' runs gather -> per-offset GEMM (tensor cores for fp16 widths that allow it) -> scatter,
+    for submanifold, strided and transposed layers; same numbers as the oracle, bit-identical run to run."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(33, 60, batch=2)
+    torch.manual_seed(9)
+    feats = torch.randn(len(coords), cin).to(dtype)
+    x = _tensor(pce, coords, feats, tags=("D1", "D1", "end"))
+    conv = pce.conv3d(cin, cout, 3, bias=True).cuda().to(dtype)
+    y = conv(x)
+    km = x.kmaps[(conv.kernel_size_code, x.stride, conv.stride_code)]
+    assert km.dataflow == "D1"
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    ref = co.conv_forward(feats, conv.kernel.detach().cpu(), d2, bias=conv.bias.detach().cpu())
+    tol = 1e-5 if dtype == torch.float32 else 2e-3  # products are rounded to fp16 in the buffer
+    assert co.rel_l2(y.feats.float().cpu(), ref) <= tol
+    assert torch.equal(conv(x).feats, y.feats)
+    down = pce.conv3d(cout, cin, 2, 2).cuda().to(dtype)
+    up = pce.conv3d(cin, cout, 2, 2, transposed=True).cuda().to(dtype)
+    z = down(y)
+    u = up(z)
+    d2s = ko.build_d2(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], cmax_of(coords), False)
+    refz = co.conv_forward(y.feats.cpu(), down.kernel.detach().cpu(), d2s)
+    assert co.rel_l2(z.feats.float().cpu(), refz) <= tol
+    refu = co.conv_forward(z.feats.cpu(), up.kernel.detach().cpu(), d2s, transposed=True)
+    assert co.rel_l2(u.feats.float().cpu(), refu) <= tol
