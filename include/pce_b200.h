@@ -76,17 +76,19 @@ typedef struct pce_epilogue {
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output
- * rows in bitmask-sorted `order`, cut into tiles of 128; tile t owns the stages
- * tile_ptr[t] .. tile_ptr[t+1]-1, one per offset that any of its rows has;
- * stage g applies offset stage_kp[g] and fetches input row stage_nbr[g*128 + r] for
- * the tile's r-th row (-1: that row lacks the offset).  No reference counterpart:
- * it is the CSR-coded map + indicator in the layout a 128-row tensor-memory tile
- * consumes with coalesced reads. */
+ * rows in bitmask-sorted `order`, cut into tiles of tile_rows (128 or 256); tile t
+ * owns the stages tile_ptr[t] .. tile_ptr[t+1]-1, one per offset that any of its rows
+ * has; stage g applies offset stage_kp[g] and fetches input row
+ * stage_nbr[g*tile_rows + r] for the tile's r-th row (-1: that row lacks the offset).
+ * A 256-row tile is two 128-row tensor-memory accumulators fed by one staged weight
+ * block.  No reference counterpart: it is the CSR-coded map + indicator in the layout
+ * the tensor-core kernel consumes with coalesced reads. */
 typedef struct pce_tile_lists {
   const int32_t* order;     /* [n_rows] */
-  const int32_t* tile_ptr;  /* [ceil(n_rows/128) + 1] */
+  const int32_t* tile_ptr;  /* [ceil(n_rows/tile_rows) + 1] */
   const int32_t* stage_kp;  /* [stages] */
-  const int32_t* stage_nbr; /* [stages * 128] */
+  const int32_t* stage_nbr; /* [stages * tile_rows] */
+  int32_t tile_rows;        /* 128 or 256 */
 } pce_tile_lists;
 
 PCE_API const char* pce_strerror(int status);
@@ -217,13 +219,14 @@ PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, 
                               size_t workspace_bytes, int32_t* order, void* stream);
 
 /* Fills the arrays of a pce_tile_lists from the neighbour CSR and a row order (NULL =
- * natural order).  tile_ptr needs ceil(n_rows/128)+1 entries; stage_kp / stage_nbr have
- * room for stage_cap stages (ceil(n_rows/128)*kv always suffices; the stage count ends up
- * in tile_ptr[last]).  kv <= 128.  workspace >= 8*(tiles+1) + 1 MiB bytes. */
+ * natural order) for tiles of tile_rows = 128 or 256 rows.  tile_ptr needs
+ * ceil(n_rows/tile_rows)+1 entries; stage_kp / stage_nbr have room for stage_cap stages
+ * (tiles*kv always suffices; the stage count ends up in tile_ptr[last]).  kv <= 128.
+ * workspace >= 8*(tiles+1) + 1 MiB bytes. */
 PCE_API int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
-                                 const int32_t* order, int32_t n_rows, int32_t kv, void* workspace,
-                                 size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr,
-                                 int32_t stage_cap, void* stream);
+                                 const int32_t* order, int32_t n_rows, int32_t kv, int32_t tile_rows,
+                                 void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                                 int32_t* stage_nbr, int32_t stage_cap, void* stream);
 
 /* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
  * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index
@@ -234,7 +237,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
                              void* packed, void* stream);
 
 /* Tuning hook for experiments and tests; what = 0: force the tensor-core kernel's stage-ring
- * depth (value 4, 6 or 8; 0 restores the automatic choice). */
+ * depth (value 2, 3 or 4; 0 restores the automatic choice); what = 1: sub-tiles per tile (1 or
+ * 2) of the dense product, which has no tile lists to fix it. */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose

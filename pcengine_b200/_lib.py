@@ -33,7 +33,8 @@ class Geom(C.Structure):
 
 
 class TileLists(C.Structure):
-    _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p)]
+    _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p),
+                ("tile_rows", C.c_int32)]
 
 
 class Epilogue(C.Structure):
@@ -66,7 +67,7 @@ def _load() -> C.CDLL:
     lib.pce_csr_from_pairs_workspace_bytes.argtypes = [i32, i32]
     lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, C.POINTER(TileLists), i32, vp, i32,
                                  C.POINTER(Epilogue), i32, vp]
-    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, vp, sz, vp, vp, vp, i32, vp]
+    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
     lib.pce_csr_sort_rows.argtypes = [vp, i32, i32, vp, sz, vp, vp]
     lib.pce_packed_weights_bytes.restype = sz
     lib.pce_packed_weights_bytes.argtypes = [i32, i32, i32]

@@ -10,6 +10,7 @@ size_t umma_packed_bytes(int kv, int cin, int cout);
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
 int umma_status_fetch(int* host_status, bool reset);
 extern int umma_force_stages;
+extern int umma_force_sub;
 int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
               void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -60,6 +61,10 @@ int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int32_t c_ou
 int pce_tune(int32_t what, int32_t value) {
   if (what == 0) {
     umma_force_stages = value;
+    return PCE_OK;
+  }
+  if (what == 1) {
+    umma_force_sub = value;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

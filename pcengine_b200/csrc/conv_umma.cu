@@ -43,7 +43,7 @@ __device__ int g_umma_status = 0;
 namespace umma {
 
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 4;
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows x 64 fp16
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s at 2 GHz
 
@@ -59,7 +59,7 @@ struct Lists {
   const int* order;      // [n_out] processing order of the output rows, or nullptr (natural)
   const int* tile_ptr;   // [n_tiles+1] first stage of every tile, or nullptr (dense product)
   const int* stage_kp;   // [stages] offset of every stage
-  const int* stage_nbr;  // [stages][128] input row per tile row, -1 absent
+  const int* stage_nbr;  // [stages][tile rows] input row per tile row, -1 absent
 };
 
 struct SharedCtl {
@@ -215,9 +215,11 @@ __device__ __forceinline__ int tile_at_cost(const int* tile_ptr, int n_tiles, lo
 __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return tile_ptr ? __ldg(tile_ptr + t) : t; }
 
 // kStages = depth of the smem stage ring (a template parameter because cp.async.wait_group
-// takes an immediate); the launcher picks the deepest ring that fits.
-template <int kStages>
-__global__ void __launch_bounds__(288, 1)
+// takes an immediate).  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
+// has SUB accumulators and every staged weight block feeds SUB MMAs, which halves the weight
+// traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
+template <int kStages, int SUB>
+__global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, int n_out, int cin, int cout,
                 __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
   extern __shared__ uint8_t smem_raw[];
@@ -226,18 +228,21 @@ __global__ void __launch_bounds__(288, 1)
   uint8_t* tiles = smem_raw + pad;  // 1024-byte aligned
   const uint32_t tiles_addr = raw_addr + pad;
   const int b_bytes = cout * 128;
-  const int stage_bytes = kABytes + b_bytes;  // both multiples of 1024
+  constexpr int kRows = kTileM * SUB;          // output rows per tile
+  constexpr int kAStage = kABytes * SUB;       // gathered rows of one stage
+  constexpr int kMmaWarp = 4 * SUB;
+  const int stage_bytes = kAStage + b_bytes;   // both multiples of 1024
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * stage_bytes);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int kblocks = (cin + 63) >> 6;
-  const int n_tiles = (n_out + kTileM - 1) / kTileM;
+  const int n_tiles = (n_out + kRows - 1) / kRows;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&ctl->afull[s]), 128);
+      mbar_init(smem_u32(&ctl->afull[s]), kRows);
       mbar_init(smem_u32(&ctl->bfull[s]), 1);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(288, 1)
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(static_cast<uint32_t>(tmem_cols))
                  : "memory");
@@ -265,7 +270,7 @@ __global__ void __launch_bounds__(288, 1)
   const int t1 = blockIdx.x + 1 == gridDim.x ? n_tiles
                                              : tile_at_cost(ls.tile_ptr, n_tiles, total * (blockIdx.x + 1) / gridDim.x);
 
-  if (warp < 4) {
+  if (warp < kMmaWarp) {
     // =========================== producers ===========================
     const int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
     const int rsub = lane >> 3;  // row inside a 4-row group
@@ -275,10 +280,10 @@ __global__ void __launch_bounds__(288, 1)
       kp = 0;
       if (g < g1) {
         if (ls.tile_ptr) {
-          nid = __ldg(ls.stage_nbr + static_cast<size_t>(g) * kTileM + tid);
+          nid = __ldg(ls.stage_nbr + static_cast<size_t>(g) * kRows + tid);
           kp = __ldg(ls.stage_kp + g);
         } else {  // dense product: stage g is tile g, every row fetches itself at offset 0
-          const int row = g * kTileM + tid;
+          const int row = g * kRows + tid;
           nid = row < n_out ? row : -1;
         }
       }
@@ -297,7 +302,7 @@ __global__ void __launch_bounds__(288, 1)
         if (tid == 0) {
           const uint32_t bbar = smem_u32(&ctl->bfull[s]);
           mbar_arrive_expect_tx(bbar, b_bytes);
-          bulk_copy_g2s(a_addr + kABytes, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes, bbar);
+          bulk_copy_g2s(a_addr + kAStage, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes, bbar);
         }
         const int kchunks = min(8, (cin - kb * 64) >> 3);
 #pragma unroll
@@ -348,7 +353,7 @@ __global__ void __launch_bounds__(288, 1)
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
@@ -362,7 +367,7 @@ __global__ void __launch_bounds__(288, 1)
         if (it >= nacc) ok = mbar_wait(smem_u32(&ctl->accempty[buf]), ((it / nacc) - 1) & 1, ctl);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * cout);
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * SUB * cout);
         uint32_t accumulate = 0;
         for (int st = 0; st < nst && ok; ++st, ++j) {
           const int s = j % kStages;
@@ -371,12 +376,16 @@ __global__ void __launch_bounds__(288, 1)
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = tiles_addr + s * stage_bytes;
-          const uint64_t da = make_desc(a_addr);
-          const uint64_t db = make_desc(a_addr + kABytes);
+          const uint64_t db = make_desc(a_addr + kAStage);
           const int kb = st % kblocks;
           const int ksteps = min(4, (cin - kb * 64) >> 4);
           for (int k = 0; k < ksteps; ++k) {
-            tc_mma_f16(tmem_acc, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc, accumulate);
+#pragma unroll
+            for (int sub = 0; sub < SUB; ++sub) {  // the same weight block feeds every sub-tile
+              const uint64_t da = make_desc(a_addr + sub * kABytes);
+              tc_mma_f16(tmem_acc + static_cast<uint32_t>(sub * cout), da + static_cast<uint64_t>(k * 2),
+                         db + static_cast<uint64_t>(k * 2), idesc, accumulate);
+            }
             accumulate = 1;
           }
           tc_commit(smem_u32(&ctl->empty[s]));
@@ -397,16 +406,24 @@ __global__ void __launch_bounds__(288, 1)
     for (int t = t0; t < t1; ++t) {
       const int it = t - t0;
       const int buf = it % nacc;
-      const int slot = t * kTileM + slot_in_tile;
-      int my_row = n_out;
-      if (slot < n_out) my_row = ls.order ? __ldg(ls.order + slot) : slot;
+      int rows_of[SUB];
+#pragma unroll
+      for (int sub = 0; sub < SUB; ++sub) {
+        const int slot = t * kRows + sub * kTileM + slot_in_tile;
+        rows_of[sub] = n_out;
+        if (slot < n_out) rows_of[sub] = ls.order ? __ldg(ls.order + slot) : slot;
+      }
       const bool any = first_stage(ls.tile_ptr, t + 1) > first_stage(ls.tile_ptr, t);
       bool ok = mbar_wait(smem_u32(&ctl->accfull[buf]), (it / nacc) & 1, ctl);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+#pragma unroll
+      for (int sub = 0; sub < SUB; ++sub) {
+      const int my_row = rows_of[sub];
       const bool store_row = my_row < n_out;
-      const uint32_t taddr = tmem_base + static_cast<uint32_t>(buf * cout) + (static_cast<uint32_t>(lane_quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>((buf * SUB + sub) * cout) +
+                             (static_cast<uint32_t>(lane_quarter * 32) << 16);
       __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
       const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
       for (int c0 = 0; c0 < cout; c0 += 16) {
@@ -470,13 +487,14 @@ __global__ void __launch_bounds__(288, 1)
           *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
         }
       }
+      }  // sub-tiles
       tc_fence_before();
       mbar_arrive(smem_u32(&ctl->accempty[buf]));  // 128 arrivals hand the accumulator back
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(tmem_cols))
@@ -504,8 +522,15 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   return PCE_OK;
 }
 
-// Tuning hook (tests / experiments): 0 = choose, else force 4, 6 or 8 stages.
+// Tuning hooks (tests / experiments): 0 = choose; stages 2..4; sub-tiles 1 or 2.
 int umma_force_stages = 0;
+int umma_force_sub = 0;
+
+template <int NS, int SUB>
+static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
+                        int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols, int nacc) {
+  umma::k_conv_umma<NS, SUB><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, n_out, cin, cout, out, e, tmem_cols, nacc);
+}
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
 int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
@@ -513,25 +538,35 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
   if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
   umma::Lists ls{nullptr, nullptr, nullptr, nullptr};
-  if (tiles) ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr};
-  // Two accumulators (the epilogue of a tile overlaps the next tile's MMAs) unless that would
-  // leave room for only one CTA per SM in tensor memory: then one accumulator and two CTAs.
-  const int nacc = cout > 128 ? 1 : 2;
+  int sub = umma_force_sub == 1 || umma_force_sub == 2 ? umma_force_sub : 1;
+  if (tiles) {
+    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr};
+    if (tiles->tile_rows != 128 && tiles->tile_rows != 256) return PCE_ERR_INVALID;
+    sub = tiles->tile_rows / 128;  // the lists fix the tile height
+  }
+  if (sub * cout > 512) return PCE_ERR_UNSUPPORTED;
+  // Two accumulator sets (the epilogue of a tile overlaps the next tile's MMAs) when two CTAs with
+  // two sets each still fit the 512 tensor-memory columns of an SM, else one set.
+  const int nacc = 4 * sub * cout <= 512 ? 2 : 1;
   int tmem_cols = 32;
-  while (tmem_cols < nacc * cout) tmem_cols <<= 1;
+  while (tmem_cols < nacc * sub * cout) tmem_cols <<= 1;
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
-  const size_t stage = static_cast<size_t>(umma::kABytes + cout * 128);
+  const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
   if (sm_count[dev] == 0) {
     const int cap = 227 * 1024;
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+#define PCE_SET_SMEM(NS, SB) \
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
+    PCE_SET_SMEM(4, 1);
+    PCE_SET_SMEM(3, 1);
+    PCE_SET_SMEM(2, 1);
+    PCE_SET_SMEM(4, 2);
+    PCE_SET_SMEM(3, 2);
+    PCE_SET_SMEM(2, 2);
+#undef PCE_SET_SMEM
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -553,28 +588,25 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
       per_sm = c;
     }
   }
-  if (umma_force_stages >= 2 && umma_force_stages <= 8 && umma_force_stages != 5 && umma_force_stages != 7) {
+  if (umma_force_stages >= 2 && umma_force_stages <= 4) {
     ns = umma_force_stages;
     per_sm = ctas_for(ns);
   }
   if (per_sm < 1) per_sm = 1;
   const size_t smem = ns * stage + fixed;
   if (smem > 227 * 1024) return PCE_ERR_UNSUPPORTED;
-  const int n_tiles = div_up(n_out, umma::kTileM);
+  const int n_tiles = div_up(n_out, umma::kTileM * sub);
   const int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
-  if (ns == 8)
-    umma::k_conv_umma<8><<<grid, 288, smem, st>>>(in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc);
-  else if (ns == 6)
-    umma::k_conv_umma<6><<<grid, 288, smem, st>>>(in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc);
-  else if (ns == 4)
-    umma::k_conv_umma<4><<<grid, 288, smem, st>>>(in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc);
-  else if (ns == 3)
-    umma::k_conv_umma<3><<<grid, 288, smem, st>>>(in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc);
-  else
-    umma::k_conv_umma<2><<<grid, 288, smem, st>>>(in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc);
+#define PCE_GO(NS, SB) launch_umma<NS, SB>(grid, smem, st, in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc)
+  if (sub == 1) {
+    if (ns == 4) PCE_GO(4, 1); else if (ns == 3) PCE_GO(3, 1); else PCE_GO(2, 1);
+  } else {
+    if (ns == 4) PCE_GO(4, 2); else if (ns == 3) PCE_GO(3, 2); else PCE_GO(2, 2);
+  }
+#undef PCE_GO
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }

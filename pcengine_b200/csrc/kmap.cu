@@ -190,6 +190,11 @@ __global__ void k_decode_keys(const unsigned long long* __restrict__ keys, int n
 // Input-major query: one thread per (input row, offset).  Writes the dense
 // indicator table map[kp][in] (= the reference's D2 `map`), optionally the
 // transposed table map_out[kp][out], and per-offset hit counts.
+// MIRROR (submanifold maps with odd kernel sizes): only the offsets below the centre are
+// probed (gridDim.y = mid); a hit "input i feeds output j through kp" is also the hit
+// "input j feeds output i through kv-1-kp", so each probe fills two entries and the rows
+// kp >= mid, preset to -1 by the caller, receive only their hits.
+template <bool MIRROR>
 __global__ void k_query(const int4* __restrict__ in_coords, int n_in, GeomDev g, const Slot* __restrict__ table,
                         unsigned tmask, int* __restrict__ map, int* __restrict__ map_out, int n_out,
                         int* knnz, int* status) {
@@ -204,9 +209,35 @@ __global__ void k_query(const int4* __restrict__ in_coords, int n_in, GeomDev g,
     }
   }
   if (i < n_in) map[static_cast<size_t>(kp) * n_in + i] = res;
-  if (res >= 0 && map_out != nullptr) map_out[static_cast<size_t>(kp) * n_out + res] = i;
+  if (MIRROR) {
+    if (res >= 0) map[static_cast<size_t>(g.kv - 1 - kp) * n_in + res] = i;
+  } else {
+    if (res >= 0 && map_out != nullptr) map_out[static_cast<size_t>(kp) * n_out + res] = i;
+  }
   int cnt = __syncthreads_count(res >= 0);
-  if (threadIdx.x == 0 && cnt) atomicAdd(&knnz[kp], cnt);
+  if (threadIdx.x == 0 && cnt) {
+    atomicAdd(&knnz[kp], cnt);
+    if (MIRROR) atomicAdd(&knnz[g.kv - 1 - kp], cnt);
+  }
+}
+
+// Launches the query for all offsets; n_in, n_out > 0.
+static int run_query(const int32_t* in_coords, int n_in, const GeomDev& gd, const Slot* table, unsigned tsize, int* map,
+                     int* map_out, int n_out, int* knnz, int* st_word, cudaStream_t st) {
+  const bool odd = (gd.ks[0] & 1) && (gd.ks[1] & 1) && (gd.ks[2] & 1);
+  if (gd.subm && odd && gd.kv > 1 && map_out == nullptr && n_in == n_out) {
+    PCE_CUDA(cudaMemsetAsync(map + static_cast<size_t>(gd.mid) * n_in, 0xFF,
+                             sizeof(int) * static_cast<size_t>(gd.kv - gd.mid) * n_in, st));
+    dim3 grid(div_up(n_in, 256), gd.mid);
+    k_query<true><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                        nullptr, n_out, knnz, st_word);
+  } else {
+    dim3 grid(div_up(n_in, 256), gd.kv);
+    k_query<false><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                         map_out, n_out, knnz, st_word);
+  }
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
 }
 
 // kpos / qkpos (segments padded to 128), kv+1 entries each
@@ -392,19 +423,20 @@ __global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int w
   vals[r] = r;
 }
 
-// Tile lists: the map re-laid for 128-row output tiles taken in processing order.
-// One CTA of 128 threads per tile; thread r owns the tile's r-th row.
+// Tile lists: the map re-laid for output tiles of blockDim.x (128 or 256) rows taken in
+// processing order.  One CTA per tile; thread r owns the tile's r-th row.
 //   FILL = false: tile_cnt[t] = number of offsets any row of the tile has.
 //   FILL = true : for the tile's s-th present offset (ascending kp) write stage_kp[base+s] and
-//                 stage_nbr[(base+s)*128 + r] = the row's input at that offset, or -1.
+//                 stage_nbr[(base+s)*rows + r] = the row's input at that offset, or -1.
 template <bool FILL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
     k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
                  const int* __restrict__ order, int n_rows, int words, int* tile_cnt,
                  const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
-  __shared__ uint32_t wmask[4][4];
+  __shared__ uint32_t wmask[8][4];
   const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
-  const int slot = t * 128 + r;
+  const int rows = blockDim.x, nwarps = blockDim.x >> 5;
+  const int slot = t * rows + r;
   int row = -1;
   if (slot < n_rows) row = order ? __ldg(order + slot) : slot;
   uint32_t my[4] = {0, 0, 0, 0};
@@ -418,7 +450,8 @@ __global__ void __launch_bounds__(128)
   uint32_t tm[4];
   int cnt = 0;
   for (int w = 0; w < 4; ++w) {
-    tm[w] = wmask[0][w] | wmask[1][w] | wmask[2][w] | wmask[3][w];
+    tm[w] = 0;
+    for (int q = 0; q < nwarps; ++q) tm[w] |= wmask[q][w];
     cnt += __popc(tm[w]);
   }
   if (!FILL) {
@@ -437,7 +470,7 @@ __global__ void __launch_bounds__(128)
       if ((my[w] >> bit) & 1u) v = __ldg(nbr + cursor++);
       const int g = base + s;
       if (g < stage_cap) {
-        stage_nbr[static_cast<size_t>(g) * 128 + r] = v;
+        stage_nbr[static_cast<size_t>(g) * rows + r] = v;
         if (r == 0) stage_kp[g] = w * 32 + bit;
       }
       ++s;
@@ -538,10 +571,7 @@ int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32_t* out_
     k_insert_rows<<<div_up(n_out, 256), 256, 0, st>>>(reinterpret_cast<const int4*>(out_coords), n_out, table,
                                                       tsize - 1, st_word);
     PCE_LAUNCH_CHECK();
-    dim3 grid(div_up(n_in, 256), gd.kv);
-    k_query<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
-                                  map_out, n_out, knnz, st_word);
-    PCE_LAUNCH_CHECK();
+    PCE_TRY(run_query(in_coords, n_in, gd, table, tsize, map, map_out, n_out, knnz, st_word, st));
   } else if (n_in > 0) {
     PCE_CUDA(cudaMemsetAsync(map, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_in, st));
   }
@@ -603,10 +633,7 @@ int pce_map_build_d2_noalloc(const int32_t* in_coords, int32_t n_in, const int32
     k_insert_rows<<<div_up(n_out, 256), 256, 0, st>>>(reinterpret_cast<const int4*>(out_coords), n_out, table,
                                                       tsize - 1, st_word);
     PCE_LAUNCH_CHECK();
-    dim3 grid(div_up(n_in, 256), gd.kv);
-    k_query<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
-                                  map_out, n_out, knnz, st_word);
-    PCE_LAUNCH_CHECK();
+    PCE_TRY(run_query(in_coords, n_in, gd, table, tsize, map, map_out, n_out, knnz, st_word, st));
   } else if (n_in > 0) {
     PCE_CUDA(cudaMemsetAsync(map, 0xFF, sizeof(int) * static_cast<size_t>(gd.kv) * n_in, st));
   }
@@ -723,11 +750,12 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
 }
 
 int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, const int32_t* order,
-                         int32_t n_rows, int32_t kv, void* workspace, size_t workspace_bytes, int32_t* tile_ptr,
-                         int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap, void* stream) {
+                         int32_t n_rows, int32_t kv, int32_t tile_rows, void* workspace, size_t workspace_bytes,
+                         int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap, void* stream) {
   if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
+  if (tile_rows != 128 && tile_rows != 256) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int n_tiles = div_up(n_rows, 128);
+  const int n_tiles = div_up(n_rows, tile_rows);
   if (n_tiles == 0) {
     PCE_CUDA(cudaMemsetAsync(tile_ptr, 0, sizeof(int), st));
     return PCE_OK;
@@ -738,10 +766,10 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
   int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
-  k_tile_lists<false><<<n_tiles, 128, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, cnt, nullptr, nullptr, nullptr, 0);
+  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, cnt, nullptr, nullptr, nullptr, 0);
   PCE_LAUNCH_CHECK();
   PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
-  k_tile_lists<true><<<n_tiles, 128, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, nullptr, tile_ptr, stage_kp,
+  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, nullptr, tile_ptr, stage_kp,
                                               stage_nbr, stage_cap);
   PCE_LAUNCH_CHECK();
   return PCE_OK;

@@ -19,6 +19,8 @@ _KERNEL_NAME = {_lib.KERNEL_SIMT: "conv_simt", _lib.KERNEL_UMMA: "conv_umma"}
 PROFILE = None
 # Form the tensor-core kernel's tiles in bitmask-sorted row order (scheduling only; results are unchanged).
 SORT_ROWS = True
+# Rows per tile of the tensor-core kernel: 128, 256, or None for the automatic choice.
+TILE_ROWS = None
 
 
 class FusedEpilogue:
@@ -74,6 +76,64 @@ def packed_weights(kernel: torch.Tensor, as_linear: bool = False) -> Optional[to
     return out
 
 
+def _ceil16(c: int) -> int:
+    return (int(c) + 15) // 16 * 16
+
+
+def _padded_kernel(kernel: torch.Tensor, cin_p: int, cout_p: int) -> torch.Tensor:
+    """``kernel`` [(kv,)C_in,C_out] zero-padded to [(kv,)cin_p,cout_p]; cached on the tensor like
+    the packed layout, so static weights are padded once."""
+    tag = (kernel._version, kernel.data_ptr(), tuple(kernel.shape), cin_p, cout_p)
+    hit = getattr(kernel, "_pce_padded", None)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    c_in, c_out = kernel.shape[-2:]
+    out = torch.nn.functional.pad(kernel.detach(), (0, cout_p - c_out, 0, cin_p - c_in)).contiguous()
+    try:
+        kernel._pce_padded = (tag, out)
+    except AttributeError:
+        pass
+    return out
+
+
+def _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice):
+    """fp16 layers whose channel counts are not multiples of 16 (a 4-channel stem, a 19-class head)
+    still run on the tensor-core kernel: input channels, weights and the per-channel epilogue
+    constants are zero-padded to the next multiple of 16 and the caller drops the extra output
+    columns.  The padded products are exact zeros, so the result is the unpadded one.  Returns
+    (feats, kernel, epilogue, padded) with ``padded`` False when nothing changed."""
+    kv, c_in, c_out = ((1,) + tuple(kernel.shape)) if kernel.dim() == 2 else kernel.shape
+    cin_p, cout_p = _ceil16(c_in), _ceil16(c_out)
+    if feats.dtype != torch.float16 or kernel_choice == "simt" or (cin_p == c_in and cout_p == c_out) \
+            or cout_p > 256 or kv > 128:
+        return feats, kernel, epilogue, False
+    if cout_p != c_out and epilogue is not None and epilogue.residual is not None:
+        return feats, kernel, epilogue, False
+    kernel = _padded_kernel(kernel, cin_p, cout_p)
+    if cin_p != c_in:
+        feats = torch.nn.functional.pad(feats, (0, cin_p - c_in))
+    if cout_p != c_out and epilogue is not None:
+        def widen(t):
+            return None if t is None else torch.nn.functional.pad(t, (0, cout_p - c_out))
+        epilogue = FusedEpilogue(widen(epilogue.scale), widen(epilogue.shift), None, epilogue.act, epilogue.slope)
+    return feats, kernel, epilogue, True
+
+
+_SM_COUNT = {}
+
+
+def _auto_tile_rows(n_rows: int, c_out: int, device) -> int:
+    """Rows per tile of the tensor-core kernel.  256-row tiles stage every weight block once for two
+    accumulators; measured on LiDAR layers they win (C=96: 174 -> 141 us on 486k rows) only while
+    every CTA still gets several tiles, and lose on narrow grids and on C_out = 256, where the wider
+    stage leaves room for one CTA per SM only."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNT.get(idx)
+    if sms is None:
+        sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return 256 if (c_out <= 128 and n_rows >= 6 * 256 * sms) else 128
+
+
 def device_status(reset: bool = True) -> int:
     """The library's device status word (0 = ok); synchronises the device."""
     v = C.c_int32(0)
@@ -95,6 +155,8 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         raise ValueError("Input feature size and kernel size mismatch")
     if feats.size(0) != csr.n_src:
         raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({csr.n_src})")
+    c_out_true = kernel.size(2)
+    feats, kernel, epilogue, padded = _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice)
     kv, c_in, c_out = kernel.shape
     out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
     packed = packed_weights(kernel) if kernel_choice != "simt" else None
@@ -105,7 +167,9 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                    kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
-    tiles = C.byref(csr.tiles(SORT_ROWS)) if packed is not None else None
+    tiles = None
+    if packed is not None:
+        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device)))
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
@@ -113,7 +177,7 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
     if rec is not None:
         rec["end"].record()
         PROFILE.append(rec)
-    return out
+    return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
 
 
 def conv_forward_d1(feats: torch.Tensor, kernel: torch.Tensor, kmap, transposed: bool = False,
@@ -163,6 +227,8 @@ def linear_forward(feats: torch.Tensor, weight: torch.Tensor, epilogue: Optional
         weight = weight.detach().contiguous().to(feats.dtype)
     if feats.size(1) != weight.size(0):
         raise ValueError("Input feature size and kernel size mismatch")
+    c_out_true = weight.size(1)
+    feats, weight, epilogue, padded = _pad_for_tensor_cores(feats, weight, epilogue, "auto")
     n, c_in = feats.shape
     c_out = weight.size(1)
     out = torch.empty((n, c_out), dtype=feats.dtype, device=feats.device)
@@ -170,7 +236,7 @@ def linear_forward(feats: torch.Tensor, weight: torch.Tensor, epilogue: Optional
     _lib.check(lib.pce_linear_fwd(feats.data_ptr(), n, c_in, weight.data_ptr(), _lib.ptr(packed), c_out, out.data_ptr(),
                                   _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, n, feats.dtype),
                                   _lib.stream_ptr(feats.device)), "pce_linear_fwd")
-    return out
+    return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
 
 
 def scale_shift_act(feats: torch.Tensor, epilogue: FusedEpilogue) -> torch.Tensor:

@@ -35,6 +35,10 @@ def candidates_per_input(ks, stride) -> int:
     return n
 
 
+# Rows per tile of the tile lists (128 or 256) when the caller does not say.
+TILE_ROWS = 128
+
+
 class NeighbourCSR:
     """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap]."""
 
@@ -58,15 +62,16 @@ class NeighbourCSR:
             self._order = out
         return self._order
 
-    def tiles(self, sort_rows: bool = True):
+    def tiles(self, sort_rows: bool = True, tile_rows: int | None = None):
         """The map as tile lists (a ``_lib.TileLists`` struct of device pointers) for the
-        tensor-core kernel; built once per CSR and per ordering, kept alive with it."""
-        key = bool(sort_rows)
+        tensor-core kernel; built once per CSR, ordering and tile height, kept alive with it."""
+        tile_rows = int(tile_rows or TILE_ROWS)
+        key = (bool(sort_rows), tile_rows)
         hit = self._tiles.get(key)
         if hit is not None:
             return hit[0]
         dev = self.mask.device
-        n_tiles = (self.n_rows + 127) // 128
+        n_tiles = (self.n_rows + tile_rows - 1) // tile_rows
         if sort_rows:
             order = self.order()
         else:
@@ -74,13 +79,14 @@ class NeighbourCSR:
         cap = max(1, n_tiles * self.kv)
         tile_ptr = torch.empty((n_tiles + 1,), dtype=torch.int32, device=dev)
         stage_kp = torch.empty((cap,), dtype=torch.int32, device=dev)
-        stage_nbr = torch.empty((cap * 128,), dtype=torch.int32, device=dev)
+        stage_nbr = torch.empty((cap * tile_rows,), dtype=torch.int32, device=dev)
         ws = _lib.workspace(8 * (n_tiles + 1) + (1 << 20), dev)
         _lib.check(lib.pce_build_tile_lists(self.mask.data_ptr(), self.rowptr.data_ptr(), self.nbr.data_ptr(),
-                                            order.data_ptr(), self.n_rows, self.kv, ws.data_ptr(), ws.numel(),
+                                            order.data_ptr(), self.n_rows, self.kv, tile_rows, ws.data_ptr(), ws.numel(),
                                             tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(), cap,
                                             _lib.stream_ptr(dev)), "pce_build_tile_lists")
-        st = _lib.TileLists(order.data_ptr(), tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr())
+        st = _lib.TileLists(order.data_ptr(), tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(),
+                            tile_rows)
         self._tiles[key] = (st, order, tile_ptr, stage_kp, stage_nbr)
         return st
 

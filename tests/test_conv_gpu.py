@@ -209,6 +209,68 @@ def test_row_order_is_only_scheduling():
     assert PF.device_status() == 0
 
 
+@pytest.mark.parametrize("cin,cout,ks", [(64, 64, 3), (96, 128, 3), (256, 256, 3), (32, 48, 5), (128, 32, 2)])
+def test_tile_height_is_only_scheduling(cin, cout, ks):
+    """256-row tiles (two accumulators per staged weight block) give the same features as 128-row
+    tiles, bit for bit: every output row still sums its offsets in ascending order in fp32."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(11, 72, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    g = torch.Generator().manual_seed(cin * 7 + cout)
+    x = torch.randn(len(coords), cin, generator=g).half().cuda()
+    w = (torch.randn(ks ** 3, cin, cout, generator=g) / 30).half().cuda()
+    ep = PF.FusedEpilogue(scale=torch.rand(cout, generator=g).cuda() + 0.5, shift=torch.randn(cout, generator=g).cuda(),
+                          act="relu")
+    try:
+        PF.TILE_ROWS = 128
+        a = PF.conv_forward(x, w, csr, ep)
+        PF.TILE_ROWS = 256
+        b = PF.conv_forward(x, w, csr, ep)
+    finally:
+        PF.TILE_ROWS = None
+    assert (128 in [k[1] for k in csr._tiles]) and (256 in [k[1] for k in csr._tiles])
+    assert torch.equal(a, b)
+    d2 = ko.build_d2(coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    want = co.conv_forward(x.float().cpu(), w.float().cpu(), d2)
+    want = torch.relu(want * ep.scale.cpu() + ep.shift.cpu())
+    assert co.rel_l2(b.float().cpu(), want) <= 1e-3  # fp16 features, fp32 accumulation
+    assert PF.device_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout", [(4, 32), (24, 19), (3, 5)])
+def test_ragged_channels_run_on_tensor_cores(cin, cout):
+    """fp16 layers whose widths are not multiples of 16 are zero-padded onto the tensor-core kernel;
+    the result has the unpadded shape, is contiguous and agrees with the CUDA-core kernel."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(5, 64, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(len(coords), cin, generator=g).half().cuda()
+    w = (torch.randn(27, cin, cout, generator=g) / (27 * cin) ** 0.5).half().cuda()
+    ep = PF.FusedEpilogue(scale=(torch.rand(cout, generator=g) + 0.5).cuda(), shift=torch.randn(cout, generator=g).cuda(),
+                          act="leaky", slope=0.1)
+    PF.PROFILE = []
+    try:
+        a = PF.conv_forward(x, w, km.csr(), ep)
+        kernels = [r["kernel"] for r in PF.PROFILE]
+    finally:
+        PF.PROFILE = None
+    assert kernels == ["conv_umma"]
+    b = PF.conv_forward(x, w, km.csr(), ep, "simt")
+    assert a.shape == (len(coords), cout) and a.is_contiguous()
+    assert co.rel_l2(a.float().cpu(), b.float().cpu()) <= 1e-3
+    # the padded weights are cached on the tensor and refreshed when it changes in place
+    with torch.no_grad():
+        w.mul_(2.0)
+    c = PF.conv_forward(x, w, km.csr(), ep)
+    d = PF.conv_forward(x, w, km.csr(), ep, "simt")
+    assert co.rel_l2(c.float().cpu(), d.float().cpu()) <= 1e-3
+    assert PF.device_status() == 0
+
+
 def test_dense_product_on_tensor_cores():
     """1x1x1 layers with tensor-core friendly widths run the tcgen05 kernel in identity mode."""
     import pcengine_b200 as pce

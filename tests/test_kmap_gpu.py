@@ -100,20 +100,21 @@ def test_out_of_range_coordinate_reports_status():
         km.sizes()
 
 
-@pytest.mark.parametrize("ks,sort_rows", [((3, 3, 3), True), ((3, 3, 3), False), ((5, 5, 5), True), ((2, 2, 2), True)])
-def test_tile_lists_match_the_csr(ks, sort_rows):
-    """Tile lists are the oracle's neighbour CSR re-laid: per 128-row tile (in processing order) one
-    stage per offset present in the tile, with each row's neighbour at that offset or -1."""
+@pytest.mark.parametrize("ks,sort_rows,tile_rows", [((3, 3, 3), True, 128), ((3, 3, 3), False, 128), ((5, 5, 5), True, 128),
+                                                    ((2, 2, 2), True, 128), ((3, 3, 3), True, 256), ((5, 5, 5), False, 256)])
+def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows):
+    """Tile lists are the oracle's neighbour CSR re-laid: per tile of 128 or 256 rows (in processing
+    order) one stage per offset present in the tile, with each row's neighbour at that offset or -1."""
     import pcengine_b200 as pce
     coords = surface_cloud(14, 56, batch=2)
     d2 = ko.build_d2(coords, ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     nb = ko.neighbour_csr(d2)
     km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     csr = km.csr()
-    csr.tiles(sort_rows)
-    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[sort_rows]
+    csr.tiles(sort_rows, tile_rows)
+    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows)]
     order, tile_ptr = order.cpu().numpy(), tile_ptr.cpu().numpy()
-    stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, 128)
+    stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, tile_rows)
     n, kv = km.n_out, km.kv
     assert np.array_equal(np.sort(order), np.arange(n))
     if not sort_rows:
@@ -124,10 +125,10 @@ def test_tile_lists_match_the_csr(ks, sort_rows):
     kps = np.concatenate([np.nonzero([(int(nb["mask"][r, k // 32]) >> (k % 32)) & 1 for k in range(kv)])[0]
                           for r in range(n)])
     want[rows, kps] = nb["nbr"]
-    n_tiles = (n + 127) // 128
+    n_tiles = (n + tile_rows - 1) // tile_rows
     assert tile_ptr[0] == 0 and len(tile_ptr) == n_tiles + 1
     for t in range(n_tiles):
-        rws = order[t * 128:(t + 1) * 128]
+        rws = order[t * tile_rows:(t + 1) * tile_rows]
         present = np.nonzero((want[rws] >= 0).any(axis=0))[0]
         a, b = tile_ptr[t], tile_ptr[t + 1]
         assert np.array_equal(stage_kp[a:b], present)
