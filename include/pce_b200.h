@@ -277,6 +277,78 @@ PCE_API int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const 
 PCE_API int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dtype,
                         const pce_epilogue* ep, void* stream);
 
+/* ------------------------------------------------------ kernel-map planner -- */
+
+/* The reference builds a kernel map inside the first convolution that needs it and keeps
+ * it in the tensor's `kmaps` dictionary (ref: script/spconv.py:338-427).  A map depends on
+ * coordinates only, and building one is ~30 short launches plus, for a strided layer, a
+ * size read back to the host, so built lazily the maps leave the GPU waiting for the
+ * host.  A plan lists the maps of a network in first-use order; pce_plan_begin hands the
+ * input coordinates to a host thread of the library, which queues all maps (with the
+ * same entry points as above, so bit-identical) on a CUDA stream of its own while the
+ * caller queues feature kernels; pce_pass_map gives the caller map i once its kernels are
+ * queued and makes the caller's stream wait for them. */
+
+#define PCE_PLAN_MAX_USES 8
+
+typedef struct pce_plan_map_spec {
+  int32_t ks[3], stride[3], pad[3];
+  int32_t in_level;    /* coordinate level the map reads: 0 = the input, k = created by the
+                        * k-th non-submanifold spec before this one */
+  int32_t submanifold; /* 1: outputs = inputs; 0: the output coordinates form a new level */
+  int32_t want_fwd;    /* neighbour CSR of the layer itself (rows = the map's outputs) */
+  int32_t want_tr;     /* neighbour CSR of the matching transposed layer (rows = the map's inputs) */
+  /* output widths of the layers that use each CSR on the tensor-core kernel, 0-terminated;
+   * they select the tile heights (pce_tile_rows_for) whose tile lists are prepared */
+  int32_t c_out_fwd[PCE_PLAN_MAX_USES];
+  int32_t c_out_tr[PCE_PLAN_MAX_USES];
+} pce_plan_map_spec;
+
+typedef struct pce_planned_csr {
+  const uint32_t* mask;
+  const int32_t* rowptr;
+  const int32_t* nbr;
+  int32_t n_rows, n_src, nbr_cap;
+  pce_tile_lists tiles128, tiles256; /* tile_rows == 0: not prepared */
+} pce_planned_csr;
+
+typedef struct pce_planned_map {
+  int32_t n_in, n_out, kv, symmetric;
+  int32_t cmax_out[3];
+  const int32_t* in_coords;  /* [n_in,4] */
+  const int32_t* out_coords; /* [n_out,4]; == in_coords for a submanifold map */
+  const int32_t* map;        /* [kv*n_in] as pce_map_build_d2 */
+  const int32_t* map_out;    /* [kv*n_out] or NULL when symmetric */
+  const int32_t *knnz, *kpos, *qkpos, *status;
+  int32_t has_fwd, has_tr;
+  pce_planned_csr fwd, tr;
+} pce_planned_map;
+
+typedef struct pce_plan pce_plan; /* specs + planning thread + stream + recycled storage */
+typedef struct pce_pass pce_pass; /* the maps of one network pass; device memory owned by it */
+
+/* Rows per tile (128 or 256) the engine uses for a layer of n_rows outputs and c_out
+ * channels on a GPU with sm_count SMs: 256-row tiles stage every weight block once for two
+ * accumulators and pay off only while every CTA still gets several tiles. */
+PCE_API int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_out, int32_t sm_count);
+
+/* Binds to the current device; starts the planning thread. */
+PCE_API int pce_plan_create(const pce_plan_map_spec* specs, int32_t n_specs, pce_plan** plan);
+/* Joins the thread and frees recycled storage; passes not yet released are leaked. */
+PCE_API void pce_plan_destroy(pce_plan* plan);
+/* Starts building the maps for coords [n,4] (device memory that stays valid for the pass);
+ * cmin / cmax are the coordinate bounds of the input level.  Work queued on `stream` before
+ * this call precedes the planner's kernels.  Returns at once. */
+PCE_API int pce_plan_begin(pce_plan* plan, const int32_t* coords, int32_t n, const int32_t* cmin,
+                           const int32_t* cmax, void* stream, pce_pass** pass);
+/* Blocks the host until map `index` is queued (30 s limit: PCE_ERR_TIMEOUT), makes `stream`
+ * wait for its kernels and returns its arrays, valid until the pass is released. */
+PCE_API int pce_pass_map(pce_pass* pass, int32_t index, void* stream, pce_planned_map* out);
+/* Gives the pass's storage back to the plan for reuse (waits for the planning thread to be
+ * done with it).  Kernels already queued that read the maps stay valid as long as the next
+ * pce_plan_begin is issued on the stream they run on. */
+PCE_API int pce_pass_release(pce_pass* pass);
+
 #ifdef __cplusplus
 }
 #endif

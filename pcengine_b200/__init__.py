@@ -9,6 +9,7 @@ from .batchnorm import BatchNorm, bn_scale_shift
 from .functional import FusedEpilogue
 from .kmap import KernelMap
 from .minkunet import MinkUNet, randomize_batchnorm
+from .planner import MapPlan
 from .spconv import conv3d, conv_func
 from .sptensor import SparseTensor, spTensor
 from .utils import (cat, conv_info_decoder, conv_info_encoder, fapply, init_layer_scheduler, output_stride_compute,

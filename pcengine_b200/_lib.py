@@ -24,6 +24,7 @@ EXPORTS = [
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
     "pce_pack_weights", "pce_device_status", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
+    "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release",
 ]
 
 
@@ -35,6 +36,28 @@ class Geom(C.Structure):
 class TileLists(C.Structure):
     _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p),
                 ("tile_rows", C.c_int32)]
+
+
+PLAN_MAX_USES = 8
+
+
+class PlanMapSpec(C.Structure):
+    _fields_ = [("ks", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("pad", C.c_int32 * 3), ("in_level", C.c_int32),
+                ("submanifold", C.c_int32), ("want_fwd", C.c_int32), ("want_tr", C.c_int32),
+                ("c_out_fwd", C.c_int32 * PLAN_MAX_USES), ("c_out_tr", C.c_int32 * PLAN_MAX_USES)]
+
+
+class PlannedCSR(C.Structure):
+    _fields_ = [("mask", C.c_void_p), ("rowptr", C.c_void_p), ("nbr", C.c_void_p), ("n_rows", C.c_int32),
+                ("n_src", C.c_int32), ("nbr_cap", C.c_int32), ("tiles128", TileLists), ("tiles256", TileLists)]
+
+
+class PlannedMap(C.Structure):
+    _fields_ = [("n_in", C.c_int32), ("n_out", C.c_int32), ("kv", C.c_int32), ("symmetric", C.c_int32),
+                ("cmax_out", C.c_int32 * 3), ("in_coords", C.c_void_p), ("out_coords", C.c_void_p), ("map", C.c_void_p),
+                ("map_out", C.c_void_p), ("knnz", C.c_void_p), ("kpos", C.c_void_p), ("qkpos", C.c_void_p),
+                ("status", C.c_void_p), ("has_fwd", C.c_int32), ("has_tr", C.c_int32), ("fwd", PlannedCSR),
+                ("tr", PlannedCSR)]
 
 
 class Epilogue(C.Structure):
@@ -79,6 +102,14 @@ def _load() -> C.CDLL:
                                     C.POINTER(Epilogue), vp]
     lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, vp, i32, vp, i32, C.POINTER(Epilogue), vp]
     lib.pce_scale_shift_act.argtypes = [vp, i64, i32, vp, i32, C.POINTER(Epilogue), vp]
+    lib.pce_tile_rows_for.restype = i32
+    lib.pce_tile_rows_for.argtypes = [i32, i32, i32]
+    lib.pce_plan_create.argtypes = [C.POINTER(PlanMapSpec), i32, C.POINTER(vp)]
+    lib.pce_plan_destroy.restype = None
+    lib.pce_plan_destroy.argtypes = [vp]
+    lib.pce_plan_begin.argtypes = [vp, vp, i32, C.POINTER(i32), C.POINTER(i32), vp, C.POINTER(vp)]
+    lib.pce_pass_map.argtypes = [vp, i32, vp, C.POINTER(PlannedMap)]
+    lib.pce_pass_release.argtypes = [vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("pce_version", "pce_last_cuda_error"):

@@ -414,6 +414,16 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
         if (slot < n_out) rows_of[sub] = ls.order ? __ldg(ls.order + slot) : slot;
       }
       const bool any = first_stage(ls.tile_ptr, t + 1) > first_stage(ls.tile_ptr, t);
+      if (ep.residual) {
+        // the rows are known before the accumulator is: pull the residual rows into L2 while waiting
+#pragma unroll
+        for (int sub = 0; sub < SUB; ++sub) {
+          if (rows_of[sub] < n_out) {
+            const char* rp = reinterpret_cast<const char*>(ep.residual + static_cast<size_t>(rows_of[sub]) * cout);
+            for (int off = 0; off < cout * 2; off += 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + off));
+          }
+        }
+      }
       bool ok = mbar_wait(smem_u32(&ctl->accfull[buf]), (it / nacc) & 1, ctl);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -427,6 +437,11 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
       __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
       const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
       for (int c0 = 0; c0 < cout; c0 += 16) {
+        uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+        if (rrow) {  // issued ahead of the tensor-memory load, consumed after it
+          ra = *reinterpret_cast<const uint4*>(rrow + c0);
+          rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
+        }
         uint32_t r[16];
         if (any) {  // warp-uniform: the tensor-memory load is warp-collective
           tmem_ld16(taddr + c0, r);
@@ -459,8 +474,6 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
           }
         }
         if (rrow) {
-          const uint4 ra = *reinterpret_cast<const uint4*>(rrow + c0);
-          const uint4 rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
           const __half2* ha = reinterpret_cast<const __half2*>(&ra);
           const __half2* hb = reinterpret_cast<const __half2*>(&rb);
 #pragma unroll

@@ -111,7 +111,6 @@ class KernelMap:
         if subm:
             self.out_coords = in_coords
             self.n_out = self.n_in
-            ws = _lib.workspace(lib.pce_map_workspace_bytes(self.n_in, kv, self.n_in), dev)
         else:
             cap = max(1, self.n_in * candidates_per_input(ks, stride))
             ws = _lib.workspace(lib.pce_map_workspace_bytes(self.n_in, kv, cap), dev)
@@ -122,10 +121,29 @@ class KernelMap:
                        "pce_downsample_coords")
             self.n_out = int(n_out.value)
             self.out_coords = oc[: self.n_out]
-        self.map = torch.empty((kv * self.n_in,), dtype=torch.int32, device=dev)
+        self._built = False
+        self.ready = None  # CUDA event recorded after an off-stream build; consumers wait on it
+        self._csr: dict = {}
+        self._pairs = None
+        self._d1 = None
+        self._sizes = None
+        self.dataflow = "D2"
         # A submanifold map with odd kernel sizes is its own transpose under kp -> kv-1-kp, so
         # the output-major table is read out of `map`; otherwise it is written separately.
         self.symmetric = self.subm and all(k % 2 == 1 for k in ks)
+        self.build()
+
+    def build(self) -> "KernelMap":
+        """Hash the output coordinates, query every (input, offset) and scan the per-offset counts
+        (idempotent), on PyTorch's current stream."""
+        if self._built:
+            return self
+        dev, kv, in_coords = self.device, self.kv, self.in_coords
+        st = _lib.stream_ptr(dev)
+        ws = _lib.workspace(lib.pce_map_workspace_bytes(self.n_in, kv, self.n_out), dev)
+        self.map = torch.empty((kv * self.n_in,), dtype=torch.int32, device=dev)
+        # A submanifold map with odd kernel sizes is its own transpose under kp -> kv-1-kp, so
+        # the output-major table is read out of `map`; otherwise it is written separately.
         self.map_out = None if self.symmetric else torch.empty((kv * max(self.n_out, 1),), dtype=torch.int32, device=dev)
         self.knnz = torch.empty((kv,), dtype=torch.int32, device=dev)
         self.kpos = torch.empty((kv + 1,), dtype=torch.int32, device=dev)
@@ -135,17 +153,20 @@ class KernelMap:
                                         C.byref(self.geom), ws.data_ptr(), ws.numel(), _lib.ptr(self.map),
                                         self.knnz.data_ptr(), self.kpos.data_ptr(), self.qkpos.data_ptr(),
                                         _lib.ptr(self.map_out), self.status.data_ptr(), st), "pce_map_build_d2")
-        self._csr: dict = {}
-        self._pairs = None
-        self._d1 = None
-        self._sizes = None
-        self.dataflow = "D2"
+        self._built = True
+        return self
+
+    def wait(self) -> None:
+        """Make PyTorch's current stream wait for a build that ran on another stream."""
+        if self.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready)
 
     # -- sizes that live on the device -------------------------------------
     def sizes(self):
         """(pairs, qsum) read back once (one synchronisation), also validates the status word.
         The reference reads qkpos[-1] the same way (script/spconv.py:376,421)."""
         if self._sizes is None:
+            self.build().wait()
             host = torch.stack([self.kpos[-1], self.qkpos[-1], self.status[0]]).cpu()
             if int(host[2]) != 0:
                 _lib.check(int(host[2]), "kernel map build")
@@ -157,6 +178,7 @@ class KernelMap:
         key = bool(transposed)
         if key in self._csr:
             return self._csr[key]
+        self.build()
         dev, kv = self.device, self.kv
         st = _lib.stream_ptr(dev)
         ident = self.mid if self.subm else -1

@@ -20,6 +20,7 @@ from torch import nn
 from .activation import ReLU
 from .batchnorm import BatchNorm, bn_scale_shift
 from .functional import FusedEpilogue
+from .planner import MapPlan
 from .spconv import conv3d
 from .sptensor import spTensor
 from .utils import cat
@@ -114,7 +115,28 @@ class MinkUNet(nn.Module):
                                           ResidualBlock(cs[5 + i], cs[5 + i])))
         self.classifier = conv3d(cs[8], num_classes, 1, 1, bias=True)
 
+    def layer_plan(self) -> list:
+        """The convolutions in forward order as (kernel_size, stride, transposed, C_in, C_out), one
+        entry per distinct use of a kernel map (what :class:`MapPlan` takes)."""
+        cs = self.widths
+        plan = [(3, 1, False, cs[0], cs[0])]
+        for i in range(4):
+            plan += [(2, 2, False, cs[i], cs[i]), (3, 1, False, cs[i], cs[i + 1])]
+        for i in range(4):
+            plan += [(2, 2, True, cs[4 + i], cs[5 + i]), (3, 1, False, cs[5 + i], cs[5 + i])]
+        return plan
+
+    # Hand the kernel maps of a pass to the library's planning thread (eval mode, CUDA) instead of
+    # building each one inside the layer that first needs it.
+    plan_ahead = True
+
     def forward(self, x: spTensor) -> spTensor:
+        if self.plan_ahead and not self.training and x.feats.is_cuda:
+            plans = self.__dict__.setdefault("_map_plans", {})
+            plan = plans.get(x.feats.dtype)
+            if plan is None:
+                plan = plans[x.feats.dtype] = MapPlan(self.layer_plan(), x.stride, x.feats.dtype)
+            plan.begin(x)
         feats: List[spTensor] = [self.stem(x)]
         for i in range(4):
             feats.append(self.enc[i](self.down[i](feats[-1])))

@@ -111,15 +111,47 @@ def _choose_dataflow(tag: str, in_channel: int, out_channel: int) -> str:
 
 
 def _run_conv(feats, w, kmap, transposed, ep, buffer):
+    kmap.wait()
     if kmap.dataflow == "D1":
         return PF.conv_forward_d1(feats, w, kmap, transposed, ep, buffer)
     return PF.conv_forward(feats, w, kmap.csr(transposed=transposed), ep)
+
+
+def _map_for(input, in_channel, out_channel, kernel_size_code, stride_code, padding_code):
+    """The kernel map of a non-transposed layer applied to ``input``: fetched from ``input.kmaps`` or
+    built and registered there (script/spconv.py:338-427).  Returns (map, output stride code,
+    output coords_max, output coords_min)."""
+    output_stride = output_stride_compute(stride_code, input.stride, 0)
+    key = (kernel_size_code, input.stride, stride_code)
+    kmap = input.kmaps.get(key)
+    if kmap is None and input.planner is not None:
+        kmap = input.planner.fetch(input, key, output_stride)
+    subm = stride_code == _ONES
+    coords_max = [input.coords_max[i] for i in range(3)]
+    coords_min = [input.coords_min[i] for i in range(3)]
+    ks = conv_info_decoder(kernel_size_code)
+    stride = conv_info_decoder(stride_code)
+    padding = conv_info_decoder(padding_code)
+    if not subm:
+        coords_max = [(input.coords_max[i] + 2 * padding[i] - (ks[i] - 1)) // stride[i] for i in range(3)]
+    if kmap is None:
+        tag = input.init_tag[0] if len(input.init_tag) else "end"
+        if tag not in _TAGS:
+            raise NotImplementedError(f"no dataflow tag left for a new kernel map (init_tag[0] = {tag!r})")
+        kmap = KernelMap(input.coords, ks, stride, padding, coords_min, coords_max, subm)
+        kmap.dataflow = _choose_dataflow(tag, in_channel, out_channel)
+        input.kmaps[key] = kmap
+        input.cbook[output_stride] = kmap.out_coords
+        if not (tag == "auto" and len(input.init_tag) == 1):
+            input.init_tag = input.init_tag[1:]
+    return kmap, output_stride, coords_max, coords_min
 
 
 def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_code, padding_code, bias, transposed,
               tensorcore, epilogue: Optional[FusedEpilogue] = None):
     """Run one sparse convolution on ``input`` and return the output ``spTensor``."""
     ep = _with_bias(epilogue, bias)
+    planner = getattr(input, "planner", None)
     w = kernel  # the Parameter itself: the packed tensor-core layout is cached on it
 
     if kernel_size_code == _ONES and stride_code == _ONES:
@@ -131,6 +163,8 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
     elif transposed:
         output_stride = output_stride_compute(stride_code, input.stride, 1)
         kmap = input.kmaps.get((kernel_size_code, output_stride, stride_code))
+        if kmap is None and planner is not None:
+            kmap = planner.fetch(input, (kernel_size_code, output_stride, stride_code), None)
         if kmap is None:
             raise RuntimeError("transposed conv3d needs the kernel map of its matching strided conv3d "
                                "(same kernel size and stride) built earlier on this tensor's network")
@@ -143,27 +177,8 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
                           coords_min=input.coords_min)
 
     else:
-        output_stride = output_stride_compute(stride_code, input.stride, 0)
-        key = (kernel_size_code, input.stride, stride_code)
-        kmap = input.kmaps.get(key)
-        subm = stride_code == _ONES
-        coords_max = [input.coords_max[i] for i in range(3)]
-        coords_min = [input.coords_min[i] for i in range(3)]
-        ks = conv_info_decoder(kernel_size_code)
-        stride = conv_info_decoder(stride_code)
-        padding = conv_info_decoder(padding_code)
-        if not subm:
-            coords_max = [(input.coords_max[i] + 2 * padding[i] - (ks[i] - 1)) // stride[i] for i in range(3)]
-        if kmap is None:
-            tag = input.init_tag[0] if len(input.init_tag) else "end"
-            if tag not in _TAGS:
-                raise NotImplementedError(f"no dataflow tag left for a new kernel map (init_tag[0] = {tag!r})")
-            kmap = KernelMap(input.coords, ks, stride, padding, coords_min, coords_max, subm)
-            kmap.dataflow = _choose_dataflow(tag, in_channel, out_channel)
-            input.kmaps[key] = kmap
-            input.cbook[output_stride] = kmap.out_coords
-            if not (tag == "auto" and len(input.init_tag) == 1):
-                input.init_tag = input.init_tag[1:]
+        kmap, output_stride, coords_max, coords_min = _map_for(input, in_channel, out_channel, kernel_size_code,
+                                                               stride_code, padding_code)
         out_feats = _run_conv(input.feats, w, kmap, False, ep, input.buffer)
         output = spTensor(feats=out_feats, coords=kmap.out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=coords_max,
@@ -171,4 +186,5 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
 
     output.kmaps = input.kmaps
     output.cbook = input.cbook
+    output.planner = planner
     return output

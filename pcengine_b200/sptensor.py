@@ -22,6 +22,7 @@ class spTensor:
         self.buffer = buffer
         self.kmaps: Dict = {}
         self.cbook: Dict = {}
+        self.planner = None  # pending kernel-map builds of a planned network (spconv.plan_kernel_maps)
         self.init_tag = ["end"] if init_tag is None else init_tag
         self.coords_min = [0, 0, 0] if coords_min is None else coords_min
         if coords_max is None:
@@ -80,6 +81,7 @@ class spTensor:
                        coords_min=self.coords_min)
         out.cbook = self.cbook
         out.kmaps = self.kmaps
+        out.planner = self.planner
         return out
 
     def __add__(self, other):

@@ -49,3 +49,92 @@ def test_fused_and_module_paths_agree():
             block._fused = lambda x: False
             plain = block(tensor()).feats
         assert co.rel_l2(fused.cpu(), plain.cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_planned_maps_equal_lazy_maps(dtype):
+    """The planning thread leaves the same maps in the tensor (coordinates, map table, offsets, CSR,
+    tile lists) and the same logits, bit for bit, as building each map at the layer that first needs
+    it; repeated passes recycle the planner's storage."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(44, 72, batch=3)
+    torch.manual_seed(11)
+    feats = torch.randn(len(coords), 4).to(dtype)
+    model = pce.MinkUNet(4, 19, cr=0.5)
+    pce.randomize_batchnorm(model, 5)
+    model = model.to(dtype).eval().cuda()
+
+    def run(plan_ahead):
+        model.plan_ahead = plan_ahead
+        x = pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords),
+                         init_tag=["auto"])
+        with torch.no_grad():
+            y = model(x)
+        torch.cuda.synchronize()
+        return y
+    lazy, planned = run(False), run(True)
+    for _ in range(3):
+        planned = run(True)
+    assert type(next(iter(planned.kmaps.values()))).__name__ == "PlannedKernelMap"
+    assert torch.equal(lazy.feats, planned.feats)
+    assert sorted(lazy.kmaps) == sorted(planned.kmaps) and len(planned.kmaps) == 9
+    for key, a in lazy.kmaps.items():
+        b = planned.kmaps[key]
+        assert (a.n_in, a.n_out, a.kv, a.symmetric) == (b.n_in, b.n_out, b.kv, b.symmetric)
+        assert torch.equal(a.out_coords, b.out_coords) and torch.equal(a.map, b.map.tensor())
+        assert torch.equal(a.kpos, b.kpos.tensor()) and torch.equal(a.qkpos, b.qkpos.tensor())
+        assert a.sizes() == b.sizes()
+        for tr, ca in a._csr.items():
+            cb = b._csr[tr]
+            p = int(ca.rowptr[-1])
+            assert torch.equal(ca.mask, cb.mask.tensor()) and torch.equal(ca.rowptr, cb.rowptr.tensor())
+            assert torch.equal(ca.nbr[:p], cb.nbr.tensor()[:p])
+            assert sorted(ca._tiles) == sorted(cb._tiles)
+            for tk, ta in ca._tiles.items():
+                tb = cb._tiles[tk]
+                stages = int(ta[2][-1])
+                assert torch.equal(ta[1], tb[1].tensor()) and torch.equal(ta[2], tb[2].tensor())
+                assert torch.equal(ta[3][:stages], tb[3].tensor()[:stages])
+                assert torch.equal(ta[4][:stages * tk[1]], tb[4].tensor()[:stages * tk[1]])
+
+
+def test_map_plan_api():
+    """MapPlan on a hand-written layer list: maps not in the plan are still built lazily, a tensor the
+    plan does not fit stays on the lazy path, and the reference forms derive from a planned map."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(45, 48)
+    cm = cmax_of(coords)
+
+    def tensor():
+        return pce.spTensor(torch.randn(len(coords), 16, generator=torch.Generator().manual_seed(3)).half().cuda(),
+                            torch.from_numpy(coords).cuda(), None, [0, 0, 0], cm, init_tag=["auto"])
+    plan = pce.MapPlan([(3, 1, False, 16, 32), (2, 2, False, 32, 32), (3, 1, False, 32, 64), (2, 2, True, 64, 32)])
+    with pytest.raises(RuntimeError):
+        pce.MapPlan([(2, 2, True, 64, 32)])
+    conv = pce.conv3d(16, 32, 3).cuda().half()
+    down = pce.conv3d(32, 32, 2, 2).cuda().half()
+    five = pce.conv3d(32, 32, 5).cuda().half()
+    up = pce.conv3d(32, 16, 2, 2, transposed=True).cuda().half()
+    outs = []
+    for planned in (False, True):
+        x = tensor()
+        assert plan.begin(x) if planned else True
+        a = conv(x)
+        b = down(a)
+        c = five(b)          # 5x5x5 at the coarse level is not in the plan
+        d = up(c)
+        outs.append((a.feats, b.feats, c.feats, d.feats, b.coords, d.coords))
+        if planned:
+            km = x.kmaps[(conv.kernel_size_code, x.stride, conv.stride_code)]
+            lazy_km = pce.KernelMap(x.coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cm, True)
+            for got, want in zip(km.pairs(), lazy_km.pairs()):
+                assert torch.equal(got, want)
+            for got, want in zip(km.d1(), lazy_km.d1()):
+                assert torch.equal(got, want)
+    for u, v in zip(*outs):
+        assert torch.equal(u, v)
+    x = tensor()
+    x.stride = pce.conv_info_encoder([2, 2, 2])
+    assert plan.begin(x) is False and x.planner is None
+    plan.close()
+    assert plan.begin(tensor()) is False
