@@ -386,13 +386,17 @@ def run_ours(args):
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
     logits_pin = torch.empty((len(coords_h), NUM_CLASSES), dtype=torch.float16).pin_memory()
 
-    def step(c, f):
+    def step(c, f, ready=None):
         x = pce.spTensor(f, c, None, [0, 0, 0], cmax, batchsize=SCANS_PER_GPU, init_tag=pce.MinkUNet.tags())
+        x.coords_ready = ready  # lets the map planner start as soon as the coordinates exist
         with torch.no_grad():
             return model(x).feats
 
+    resident = torch.cuda.Event()  # the device-resident inputs exist from here on
+    resident.record()
+
     for _ in range(max(args.warmup, 3)):
-        step(coords_d, feats_d)
+        step(coords_d, feats_d, resident)
     # ---- device-resident timing ------------------------------------------------------------
     sampler = ClockSampler(local)
     if rank == 0:
@@ -403,7 +407,7 @@ def run_ours(args):
     e0.record()
     for _ in range(args.steps):
         flush.zero_()
-        step(coords_d, feats_d)
+        step(coords_d, feats_d, resident)
     e1.record()
     barrier()
     dt = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
@@ -416,7 +420,7 @@ def run_ours(args):
     p0.record()
     for _ in range(args.steps):
         flush.zero_()
-        step(coords_d, feats_d)
+        step(coords_d, feats_d, resident)
     p1.record()
     barrier()
     dt_prof = p0.elapsed_time(p1) * 1e-3
@@ -477,7 +481,7 @@ def run_ours(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "minkunet_lidar_batch8", "scans_per_gpu": SCANS_PER_GPU, "voxels_per_gpu": int(len(coords_h)),
                    "voxels_per_scan": sizes, "in_channels": IN_CHANNELS, "classes": NUM_CLASSES,
-                   "widths": "32-32-64-128-256-256-128-96-96", "map_build": "inside the timed step",
+                   "widths": "32-32-64-128-256-256-128-96-96", "map_build": "inside the timed step (planner threads, own streams)",
                    "l2": "192 MiB memset between steps, inside the timed region", "accumulate": "fp32"},
         "e2e": {"value": total_scans / dt_e2e, "unit": UNIT,
                 "h2d_bytes_per_step": int(coords_pin.numel() * 4 + feats_pin.numel() * 2),

@@ -238,7 +238,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
 
 /* Tuning hook for experiments and tests; what = 0: force the tensor-core kernel's stage-ring
  * depth (value 2, 3 or 4; 0 restores the automatic choice); what = 1: sub-tiles per tile (1 or
- * 2) of the dense product, which has no tile lists to fix it. */
+ * 2) of the dense product, which has no tile lists to fix it; what = 2: accumulator sets in
+ * tensor memory (1 or 2). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
@@ -287,7 +288,9 @@ PCE_API int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, in
  * input coordinates to a host thread of the library, which queues all maps (with the
  * same entry points as above, so bit-identical) on a CUDA stream of its own while the
  * caller queues feature kernels; pce_pass_map gives the caller map i once its kernels are
- * queued and makes the caller's stream wait for them. */
+ * queued and makes the caller's stream wait for them.  Unlike the calls above, the planner
+ * owns its device memory: cudaMalloc'ed arenas that grow to the largest pass seen and are
+ * recycled from pass to pass, freed by pce_plan_destroy. */
 
 #define PCE_PLAN_MAX_USES 8
 
@@ -329,7 +332,8 @@ typedef struct pce_pass pce_pass; /* the maps of one network pass; device memory
 
 /* Rows per tile (128 or 256) the engine uses for a layer of n_rows outputs and c_out
  * channels on a GPU with sm_count SMs: 256-row tiles stage every weight block once for two
- * accumulators and pay off only while every CTA still gets several tiles. */
+ * accumulators but halve the tiles in flight; they pay off only for narrow outputs on maps
+ * large enough to give every CTA several tiles. */
 PCE_API int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_out, int32_t sm_count);
 
 /* Binds to the current device; starts the planning thread. */
@@ -338,16 +342,19 @@ PCE_API int pce_plan_create(const pce_plan_map_spec* specs, int32_t n_specs, pce
 PCE_API void pce_plan_destroy(pce_plan* plan);
 /* Starts building the maps for coords [n,4] (device memory that stays valid for the pass);
  * cmin / cmax are the coordinate bounds of the input level.  Work queued on `stream` before
- * this call precedes the planner's kernels.  Returns at once. */
+ * this call (the producer of the coordinates) precedes the planner's kernels; nothing else
+ * orders the planner against the caller, so with the coordinates produced on a stream of
+ * their own the maps of the next pass are built while the current one computes.  Returns
+ * at once. */
 PCE_API int pce_plan_begin(pce_plan* plan, const int32_t* coords, int32_t n, const int32_t* cmin,
                            const int32_t* cmax, void* stream, pce_pass** pass);
 /* Blocks the host until map `index` is queued (30 s limit: PCE_ERR_TIMEOUT), makes `stream`
  * wait for its kernels and returns its arrays, valid until the pass is released. */
 PCE_API int pce_pass_map(pce_pass* pass, int32_t index, void* stream, pce_planned_map* out);
-/* Gives the pass's storage back to the plan for reuse (waits for the planning thread to be
- * done with it).  Kernels already queued that read the maps stay valid as long as the next
- * pce_plan_begin is issued on the stream they run on. */
-PCE_API int pce_pass_release(pce_pass* pass);
+/* Gives the pass's storage back to the plan for reuse (waits for the planning threads to be
+ * done with it).  `stream` is the stream the kernels that read the maps were queued on: the
+ * pass that recycles the storage waits for everything queued there up to this call. */
+PCE_API int pce_pass_release(pce_pass* pass, void* stream);
 
 #ifdef __cplusplus
 }

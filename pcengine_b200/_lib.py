@@ -109,7 +109,7 @@ def _load() -> C.CDLL:
     lib.pce_plan_destroy.argtypes = [vp]
     lib.pce_plan_begin.argtypes = [vp, vp, i32, C.POINTER(i32), C.POINTER(i32), vp, C.POINTER(vp)]
     lib.pce_pass_map.argtypes = [vp, i32, vp, C.POINTER(PlannedMap)]
-    lib.pce_pass_release.argtypes = [vp]
+    lib.pce_pass_release.argtypes = [vp, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("pce_version", "pce_last_cuda_error"):

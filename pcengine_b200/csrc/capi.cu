@@ -11,6 +11,7 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
 int umma_status_fetch(int* host_status, bool reset);
 extern int umma_force_stages;
 extern int umma_force_sub;
+extern int umma_force_nacc;
 int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
               void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -65,6 +66,10 @@ int pce_tune(int32_t what, int32_t value) {
   }
   if (what == 1) {
     umma_force_sub = value;
+    return PCE_OK;
+  }
+  if (what == 2) {
+    umma_force_nacc = value;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

@@ -124,11 +124,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// Makes the mbarrier receive one (already counted) arrival once every cp.async this thread has
+// issued so far has landed: the thread itself does not wait.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -288,8 +289,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
         }
       }
     };
-    int j = 0;               // smem stages issued so far (continuous over tiles)
-    int pending_arrive = 0;  // next smem stage this thread still has to arrive on
+    int j = 0;  // smem stages issued so far (continuous over tiles)
     bool ok = true;
     auto run_stage = [&](int nid, int kp) {
       for (int kb = 0; kb < kblocks; ++kb, ++j) {
@@ -315,13 +315,9 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
-        cp_async_commit();
-        if (j >= kStages - 1) {
-          cp_async_wait<kStages - 1>();
-          fence_proxy_async();
-          mbar_arrive(smem_u32(&ctl->afull[pending_arrive % kStages]));
-          ++pending_arrive;
-        }
+        // the stage's "rows landed" barrier fires by itself when this thread's copies are done, so a
+        // stage becomes usable as soon as its data is there, whatever this thread waits for next
+        cp_async_arrive_noinc(smem_u32(&ctl->afull[s]));
       }
     };
     // Four index registers, each reloaded right after its stage has been issued and not
@@ -341,11 +337,8 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
       if (g + 3 < g1 && ok) run_stage(nid3, kp3);
       load_stage(g + 7, nid3, kp3);
     }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    if (ok) {
-      for (; pending_arrive < j; ++pending_arrive) mbar_arrive(smem_u32(&ctl->afull[pending_arrive % kStages]));
-    } else if (tid == 0) {
+    cp_async_wait_all();
+    if (!ok && tid == 0) {
       // aborting: give this thread's bulk copies a bounded chance to land before the CTA leaves
       for (int u = max(0, j - kStages); u < j; ++u) {
         const uint32_t bar = smem_u32(&ctl->bfull[u % kStages]);
@@ -374,6 +367,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
           const uint32_t par = (j / kStages) & 1;
           ok = mbar_wait(smem_u32(&ctl->afull[s]), par, ctl) && mbar_wait(smem_u32(&ctl->bfull[s]), par, ctl);
           if (!ok) break;
+          fence_proxy_async();  // the gathered rows were written through the generic proxy
           tc_fence_after();
           const uint32_t a_addr = tiles_addr + s * stage_bytes;
           const uint64_t db = make_desc(a_addr + kAStage);
@@ -535,9 +529,10 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   return PCE_OK;
 }
 
-// Tuning hooks (tests / experiments): 0 = choose; stages 2..4; sub-tiles 1 or 2.
+// Tuning hooks (tests / experiments): 0 = choose; stages 2..4; sub-tiles 1 or 2; accumulator sets 1 or 2.
 int umma_force_stages = 0;
 int umma_force_sub = 0;
+int umma_force_nacc = 0;
 
 template <int NS, int SUB>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
@@ -558,11 +553,6 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
     sub = tiles->tile_rows / 128;  // the lists fix the tile height
   }
   if (sub * cout > 512) return PCE_ERR_UNSUPPORTED;
-  // Two accumulator sets (the epilogue of a tile overlaps the next tile's MMAs) when two CTAs with
-  // two sets each still fit the 512 tensor-memory columns of an SM, else one set.
-  const int nacc = 4 * sub * cout <= 512 ? 2 : 1;
-  int tmem_cols = 32;
-  while (tmem_cols < nacc * sub * cout) tmem_cols <<= 1;
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
   const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
@@ -584,27 +574,42 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
   }
-  // Two resident CTAs per SM hide each other's per-tile latencies better than a deeper ring in
-  // one CTA does (measured: C=128 280 -> 190 us, C=256 612 -> 403 us on 486k voxels).
-  auto ctas_for = [&](int n) {
+  // Configuration = (ring depth, accumulator sets).  What the kernel needs most is row gathers in
+  // flight, i.e. stages resident per SM = resident CTAs x ring depth; the CTAs per SM are bounded by
+  // shared memory, by the 512 tensor-memory columns and by the register file.  Measured on LiDAR
+  // layers (486k / 297k / 149k rows): at an equal stage count more CTAs win (C=96: 3 CTAs x 2 stages
+  // with one accumulator set 146 us, 2 x 3 with two sets 159 us; C=128: 115 vs 122 us), and at equal
+  // CTAs two accumulator sets win (the epilogue of a tile then overlaps the next tile's MMAs).
+  const int threads = 32 * (4 * sub + 5);
+  const int by_regs = 65536 / (threads * 72);  // 70 registers per thread, allocated in units of 8
+  auto tmem_for = [&](int sets) {
+    int cols = 32;
+    while (cols < sets * sub * cout) cols <<= 1;
+    return cols;
+  };
+  auto ctas_for = [&](int n, int sets) {
+    if (sets * sub * cout > 512) return 0;
     int c = static_cast<int>((227 * 1024) / (n * stage + fixed + 1024));
-    if (c > 512 / tmem_cols) c = 512 / tmem_cols;
+    if (c > 512 / tmem_for(sets)) c = 512 / tmem_for(sets);
+    if (c > by_regs) c = by_regs;
     return c > 4 ? 4 : c;
   };
-  // prefer two resident CTAs, then the most stages per SM, then the deeper ring
-  int ns = 4, per_sm = ctas_for(4);
-  for (int n = 3; n >= 2; --n) {
-    const int c = ctas_for(n);
-    const int two_new = c >= 2, two_old = per_sm >= 2;
-    if (two_new > two_old || (two_new == two_old && c * n > per_sm * ns)) {
-      ns = n;
-      per_sm = c;
+  int ns = 2, nacc = 1, per_sm = 0;
+  for (int n = 4; n >= 2; --n) {
+    for (int sets = 2; sets >= 1; --sets) {
+      const int c = ctas_for(n, sets);
+      const bool better = c * n > per_sm * ns || (c * n == per_sm * ns && c > per_sm);
+      if (c > 0 && (per_sm == 0 || better)) {
+        ns = n;
+        nacc = sets;
+        per_sm = c;
+      }
     }
   }
-  if (umma_force_stages >= 2 && umma_force_stages <= 4) {
-    ns = umma_force_stages;
-    per_sm = ctas_for(ns);
-  }
+  if (umma_force_stages >= 2 && umma_force_stages <= 4) ns = umma_force_stages;
+  if ((umma_force_nacc == 1 || umma_force_nacc == 2) && umma_force_nacc * sub * cout <= 512) nacc = umma_force_nacc;
+  per_sm = ctas_for(ns, nacc);
+  const int tmem_cols = tmem_for(nacc);
   if (per_sm < 1) per_sm = 1;
   const size_t smem = ns * stage + fixed;
   if (smem > 227 * 1024) return PCE_ERR_UNSUPPORTED;

@@ -21,9 +21,11 @@
 //
 // Memory: a pass owns a device arena (bump allocation over cudaMalloc'ed chunks, recycled with
 // the pass object); transient workspaces come from one grow-only scratch buffer per lane, which
-// is safe because a lane's kernels all run on its one stream.  pce_plan_begin records an event
-// on the caller's stream and every lane's stream waits for it, so a recycled arena is never
-// written before the previous pass's readers have finished.
+// is safe because a lane's kernels all run on its one stream.  Ordering against the caller:
+// pce_plan_begin records an event on the stream that produced the coordinates and every lane
+// waits for it; pce_pass_release records an event on the stream that read the maps and the
+// lanes of the pass that recycles the arena wait for that one.  Nothing else ties the planner
+// to the feature stream, so the maps of pass i+1 are built while pass i still computes.
 #include <condition_variable>
 #include <chrono>
 #include <deque>
@@ -103,6 +105,8 @@ struct pce_pass {
   DeviceArena arena;
   int32_t cmin[3] = {0, 0, 0};
   cudaEvent_t start = nullptr;
+  cudaEvent_t released = nullptr;          // recorded at release on the stream that read the maps
+  bool has_released = false;
   std::vector<LevelState> levels;          // [0] = the input
   std::vector<cudaEvent_t> ready;          // one per map
   std::vector<pce_planned_map> maps;
@@ -140,7 +144,8 @@ struct pce_plan {
   PlanLane lanes[kLanes];
   std::mutex m;
   std::condition_variable cv;
-  std::vector<pce_pass*> idle;  // recycled passes (arena + events)
+  std::deque<pce_pass*> idle;  // released passes (arena + events), oldest first
+  int n_passes = 0;            // pass objects created so far
   bool stop = false;
 };
 
@@ -160,8 +165,11 @@ static int scratch_for(PlanLane* l, size_t bytes, void** out) {
   return PCE_OK;
 }
 
+// 256-row tiles share every staged weight block between two accumulators, but they halve the number
+// of tiles in flight per SM; measured on 486k-row LiDAR layers they win only for narrow outputs
+// (C=32: 72 -> 67 us) and lose from C=96 up (146 -> 168 us), and they need several tiles per CTA.
 static int tile_rows_policy(int n_rows, int c_out, int sm_count) {
-  return (c_out <= 128 && static_cast<long long>(n_rows) >= 6ll * 256 * sm_count) ? 256 : 128;
+  return (c_out <= 32 && static_cast<long long>(n_rows) >= 6ll * 256 * sm_count) ? 256 : 128;
 }
 
 static void fill_geom(const pce_plan_map_spec& sp, const int32_t* cmin, const int32_t* cmax_out, pce_geom* g) {
@@ -224,6 +232,7 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
 // Lane 0: the output coordinates of every strided spec, in order.
 static int run_coords_lane(pce_plan* p, PlanLane* l, pce_pass* ps) {
   PCE_CUDA(cudaStreamWaitEvent(l->stream, ps->start, 0));
+  if (ps->has_released) PCE_CUDA(cudaStreamWaitEvent(l->stream, ps->released, 0));
   for (size_t i = 0; i < p->specs.size(); ++i) {
     const pce_plan_map_spec& sp = p->specs[i];
     if (sp.submanifold) continue;
@@ -337,6 +346,7 @@ static int build_map(pce_plan* p, PlanLane* l, pce_pass* ps, int i) {
 // Map lanes: take the next map in first-use order until none is left.
 static int run_map_lane(pce_plan* p, PlanLane* l, pce_pass* ps) {
   PCE_CUDA(cudaStreamWaitEvent(l->stream, ps->start, 0));
+  if (ps->has_released) PCE_CUDA(cudaStreamWaitEvent(l->stream, ps->released, 0));
   for (;;) {
     int i;
     {
@@ -382,6 +392,7 @@ int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_out, int32_t sm_count) {
 static void free_pass(pce_pass* ps) {
   ps->arena.release();
   if (ps->start) cudaEventDestroy(ps->start);
+  if (ps->released) cudaEventDestroy(ps->released);
   for (cudaEvent_t ev : ps->ready)
     if (ev) cudaEventDestroy(ev);
   for (LevelState& lv : ps->levels)
@@ -448,19 +459,34 @@ int pce_plan_begin(pce_plan* p, const int32_t* coords, int32_t n, const int32_t*
   int dev = -1;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev != p->device) return PCE_ERR_INVALID;
+  // Storage to build into: the oldest released pass whose readers have finished; if they have not,
+  // a new pass (up to kMaxPasses), so that the maps of this pass are built while the previous
+  // pass still computes; beyond that the oldest one, whose readers the lanes then wait for.
+  constexpr int kMaxPasses = 3;
   pce_pass* ps = nullptr;
   {
     std::lock_guard<std::mutex> lk(p->m);
     if (p->stop) return PCE_ERR_INVALID;
     if (!p->idle.empty()) {
-      ps = p->idle.back();
-      p->idle.pop_back();
+      pce_pass* oldest = p->idle.front();
+      bool drained = true;
+      if (oldest->has_released) {
+        const cudaError_t q = cudaEventQuery(oldest->released);
+        drained = q == cudaSuccess;
+        if (q == cudaErrorNotReady) (void)cudaGetLastError();  // "not ready" is an answer, not a failure
+      }
+      if (drained || p->n_passes >= kMaxPasses) {
+        ps = oldest;
+        p->idle.pop_front();
+      }
     }
+    if (!ps) ++p->n_passes;
   }
   if (!ps) {
     ps = new pce_pass();
     ps->plan = p;
     cudaError_t e = cudaEventCreateWithFlags(&ps->start, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ps->released, cudaEventDisableTiming);
     ps->ready.assign(p->specs.size(), nullptr);
     ps->levels.assign(p->n_levels, LevelState{});
     for (size_t i = 0; i < p->specs.size() && e == cudaSuccess; ++i)
@@ -491,8 +517,8 @@ int pce_plan_begin(pce_plan* p, const int32_t* coords, int32_t n, const int32_t*
   ps->lanes_done = 0;
   ps->error = PCE_OK;
   ps->finished = false;
-  // everything queued on the caller's stream so far (the coordinates' producer, the previous
-  // pass's readers of a recycled arena) precedes the planner's first kernel
+  // everything queued on `stream` so far (the coordinates' producer) precedes the planner's
+  // first kernel
   cudaError_t e = cudaEventRecord(ps->start, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     std::lock_guard<std::mutex> lk(p->m);
@@ -524,12 +550,16 @@ int pce_pass_map(pce_pass* ps, int32_t index, void* stream, pce_planned_map* out
   return PCE_OK;
 }
 
-int pce_pass_release(pce_pass* ps) {
+int pce_pass_release(pce_pass* ps, void* stream) {
   if (!ps) return PCE_ERR_INVALID;
   pce_plan* p = ps->plan;
+  // the readers of the maps were queued on `stream`: whoever recycles the storage waits for them
+  const cudaError_t e = cudaEventRecord(ps->released, static_cast<cudaStream_t>(stream));
   std::unique_lock<std::mutex> lk(p->m);
   const bool done = p->cv.wait_for(lk, std::chrono::seconds(30), [&] { return ps->finished; });
   if (!done) return PCE_ERR_TIMEOUT;  // the pass stays with the planner; its storage is not recycled
+  if (e != cudaSuccess) return cuda_fail(e);  // not recycled either: its readers are unknown
+  ps->has_released = true;
   p->idle.push_back(ps);
   return PCE_OK;
 }

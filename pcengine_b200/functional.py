@@ -123,10 +123,8 @@ _SM_COUNT = {}
 
 
 def _auto_tile_rows(n_rows: int, c_out: int, device) -> int:
-    """Rows per tile of the tensor-core kernel (pce_tile_rows_for).  256-row tiles stage every weight
-    block once for two accumulators; measured on LiDAR layers they win (C=96: 174 -> 141 us on 486k
-    rows) only while every CTA still gets several tiles, and lose on narrow grids and on C_out = 256,
-    where the wider stage leaves room for one CTA per SM only."""
+    """Rows per tile of the tensor-core kernel (pce_tile_rows_for): 256-row tiles, which stage every
+    weight block once for two accumulators, for narrow outputs on large maps, else 128."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     sms = _SM_COUNT.get(idx)
     if sms is None:

@@ -76,13 +76,17 @@ class _DevArray:
 class _PassHandle:
     """Owns a ``pce_pass``; releases it to the plan when the last user goes away."""
 
-    def __init__(self, plan, handle):
-        self.plan, self.handle = plan, handle
+    def __init__(self, plan, handle, device):
+        self.plan, self.handle, self.device = plan, handle, device
 
     def __del__(self):
         h, self.handle = self.handle, None
         if h and self.plan.handle:
-            lib.pce_pass_release(h)
+            try:  # the maps were read on the stream current now (the one the network ran on)
+                stream = _lib.stream_ptr(self.device)
+            except Exception:
+                stream = None
+            lib.pce_pass_release(h, stream)
 
 
 class PlannedKernelMap(KernelMap):
@@ -206,6 +210,7 @@ class MapPlan:
             raise ValueError("MapPlan: no layer needs a kernel map")
         self.n_levels = len(level_of) - 1
         self.handles: Dict[int, int] = {}
+        self.gates: Dict = {}  # per device: a stream that carries nothing but coordinate-ready events
         self.handle = True  # cleared when the plan is closed
 
     def _c_specs(self):
@@ -236,9 +241,12 @@ class MapPlan:
 
     def begin(self, x) -> bool:
         """Start building the maps for the pass whose input tensor is ``x`` and attach the pass to
-        it; conv_func picks the maps up from there.  Returns False (and leaves ``x`` on the lazy
-        path) when the tensor does not fit the plan: other stride, maps already present, an
-        override of the tile policy in force, or an empty tensor."""
+        it; conv_func picks the maps up from there.  The planner waits for the producer of the
+        coordinates only: everything queued so far on the current stream, or, when the tensor
+        carries a CUDA event in ``x.coords_ready``, just that event, which lets the maps of the
+        next pass be built while the current pass still computes.  Returns False (and leaves ``x``
+        on the lazy path) when the tensor does not fit the plan: other stride, maps already
+        present, an override of the tile policy in force, or an empty tensor."""
         coords = x.coords
         if (not self.handle or not coords.is_cuda or coords.size(0) == 0 or x.stride != self.in_stride or x.kmaps
                 or PF.TILE_ROWS is not None or not PF.SORT_ROWS or coords.dtype != torch.int32
@@ -250,9 +258,17 @@ class MapPlan:
         cmax = (C.c_int32 * 3)(*[int(v) for v in x.coords_max])
         out = C.c_void_p()
         with torch.cuda.device(dev):
-            _lib.check(lib.pce_plan_begin(h, coords.data_ptr(), coords.size(0), cmin, cmax, _lib.stream_ptr(dev),
-                                          C.byref(out)), "pce_plan_begin")
-        x.planner = PlannedPass(self, _PassHandle(self, out.value), x)
+            stream = _lib.stream_ptr(dev)
+            ready = getattr(x, "coords_ready", None)
+            if ready is not None:
+                gate = self.gates.get(dev)
+                if gate is None:
+                    gate = self.gates[dev] = torch.cuda.Stream(dev)
+                gate.wait_event(ready)
+                stream = gate.cuda_stream
+            _lib.check(lib.pce_plan_begin(h, coords.data_ptr(), coords.size(0), cmin, cmax, stream, C.byref(out)),
+                       "pce_plan_begin")
+        x.planner = PlannedPass(self, _PassHandle(self, out.value, dev), x)
         return True
 
     def close(self) -> None:

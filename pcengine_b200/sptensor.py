@@ -22,7 +22,8 @@ class spTensor:
         self.buffer = buffer
         self.kmaps: Dict = {}
         self.cbook: Dict = {}
-        self.planner = None  # pending kernel-map builds of a planned network (spconv.plan_kernel_maps)
+        self.planner = None       # the planner pass that builds this network pass's kernel maps (planner.MapPlan)
+        self.coords_ready = None  # optional CUDA event after which `coords` is valid (read by MapPlan.begin)
         self.init_tag = ["end"] if init_tag is None else init_tag
         self.coords_min = [0, 0, 0] if coords_min is None else coords_min
         if coords_max is None:
