@@ -155,10 +155,11 @@ def run_reference(args):
 
 # ----------------------------------------------------------------------------- GPU arm
 LAYERS = {  # name: (map kind, kv, c_in, c_out)
-    "subm3_32x32": ("subm", 27, 32, 32), "subm3_64x64": ("subm", 27, 64, 64), "subm3_128x128": ("subm", 27, 128, 128),
+    "subm3_32x32": ("subm", 27, 32, 32), "subm3_64x64": ("subm", 27, 64, 64), "subm3_96x96": ("subm", 27, 96, 96),
+    "subm3_128x128": ("subm", 27, 128, 128),
     "subm3_256x256": ("subm", 27, 256, 256), "down2s2_32x64": ("down", 8, 32, 64), "up2s2_64x32": ("up", 8, 64, 32),
 }
-DEFAULT_LAYERS = ["subm3_32x32", "subm3_64x64", "subm3_128x128", "down2s2_32x64", "up2s2_64x32"]
+DEFAULT_LAYERS = ["subm3_32x32", "subm3_64x64", "subm3_96x96", "subm3_128x128", "down2s2_32x64", "up2s2_64x32"]
 
 
 def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: int = 3):
