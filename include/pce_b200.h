@@ -66,13 +66,27 @@ typedef struct pce_geom {
  * output row: y = act(acc * scale[c] + shift[c] + residual[row][c]).
  * Replaces the separate passes of ref: script/batchnorm.py:7-11,
  * script/activation.py:6-15, the bias add at script/spconv.py:325,453 and the
- * residual add of script/sptensor.py:80-91.  Any pointer may be NULL. */
+ * residual add of script/sptensor.py:80-91.  Any pointer may be NULL.
+ *
+ * extra_*: a second operand that joins the accumulation itself,
+ *   acc[row] += extra_feats[row] @ W2,   W2 [extra_c, c_out] given in the packed layout
+ * (pce_pack_weights with kv = 1).  It is multiplied by `scale` like the rest of the
+ * accumulator, so a block that wants y = act(bn2(conv2(x)) + bn_s(shortcut(x0))) folds both
+ * BatchNorm scales into the two weight tensors and passes only the summed shifts; the
+ * plain residual of a block is the case W2 = identity.  Compared with `residual`, the rows
+ * travel through the kernel's gather pipeline instead of being read in its epilogue, and a
+ * 1x1x1 shortcut convolution costs no launch and no round trip of its output through
+ * memory.  Tensor-core kernel only (fp16, extra_c a multiple of 16, tile lists built with
+ * identity_stage = 1); other calls return PCE_ERR_UNSUPPORTED when it is set. */
 typedef struct pce_epilogue {
   const float* scale;   /* [c_out] */
   const float* shift;   /* [c_out] */
   const void* residual; /* [n_out, c_out], same dtype as the features */
   int32_t act;
   float slope;
+  const void* extra_feats;          /* [n_out, extra_c] fp16 */
+  const void* extra_packed_weights; /* pce_packed_weights_bytes(1, extra_c, c_out) bytes */
+  int32_t extra_c;
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output
@@ -81,7 +95,9 @@ typedef struct pce_epilogue {
  * has; stage g applies offset stage_kp[g] and fetches input row
  * stage_nbr[g*tile_rows + r] for the tile's r-th row (-1: that row lacks the offset).
  * A 256-row tile is two 128-row tensor-memory accumulators fed by one staged weight
- * block.  No reference counterpart: it is the CSR-coded map + indicator in the layout
+ * block.  With identity_stage = 1 every tile ends with one more stage, stage_kp = -1, whose
+ * entry for a row is the row itself: where pce_epilogue.extra_feats joins the accumulation
+ * (a launch without a second operand skips it).  No reference counterpart: it is the CSR-coded map + indicator in the layout
  * the tensor-core kernel consumes with coalesced reads. */
 typedef struct pce_tile_lists {
   const int32_t* order;     /* [n_rows] */
@@ -89,6 +105,7 @@ typedef struct pce_tile_lists {
   const int32_t* stage_kp;  /* [stages] */
   const int32_t* stage_nbr; /* [stages * tile_rows] */
   int32_t tile_rows;        /* 128 or 256 */
+  int32_t identity_stage;   /* 0 or 1 */
 } pce_tile_lists;
 
 PCE_API const char* pce_strerror(int status);
@@ -221,12 +238,14 @@ PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, 
 /* Fills the arrays of a pce_tile_lists from the neighbour CSR and a row order (NULL =
  * natural order) for tiles of tile_rows = 128 or 256 rows.  tile_ptr needs
  * ceil(n_rows/tile_rows)+1 entries; stage_kp / stage_nbr have room for stage_cap stages
- * (tiles*kv always suffices; the stage count ends up in tile_ptr[last]).  kv <= 128.
+ * (tiles*(kv + identity_stage) always suffices; the stage count ends up in tile_ptr[last]).
+ * kv <= 128.
  * workspace >= 8*(tiles+1) + 1 MiB bytes. */
 PCE_API int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
                                  const int32_t* order, int32_t n_rows, int32_t kv, int32_t tile_rows,
-                                 void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
-                                 int32_t* stage_nbr, int32_t stage_cap, void* stream);
+                                 int32_t identity_stage, void* workspace, size_t workspace_bytes,
+                                 int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap,
+                                 void* stream);
 
 /* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
  * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index
@@ -312,7 +331,8 @@ typedef struct pce_planned_csr {
   const int32_t* rowptr;
   const int32_t* nbr;
   int32_t n_rows, n_src, nbr_cap;
-  pce_tile_lists tiles128, tiles256; /* tile_rows == 0: not prepared */
+  pce_tile_lists tiles128, tiles256; /* tile_rows == 0: not prepared; the forward lists of a
+                                      * submanifold map carry the identity stage */
 } pce_planned_csr;
 
 typedef struct pce_planned_map {

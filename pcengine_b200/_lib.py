@@ -35,7 +35,7 @@ class Geom(C.Structure):
 
 class TileLists(C.Structure):
     _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p),
-                ("tile_rows", C.c_int32)]
+                ("tile_rows", C.c_int32), ("identity_stage", C.c_int32)]
 
 
 PLAN_MAX_USES = 8
@@ -62,7 +62,8 @@ class PlannedMap(C.Structure):
 
 class Epilogue(C.Structure):
     _fields_ = [("scale", C.c_void_p), ("shift", C.c_void_p), ("residual", C.c_void_p),
-                ("act", C.c_int32), ("slope", C.c_float)]
+                ("act", C.c_int32), ("slope", C.c_float), ("extra_feats", C.c_void_p),
+                ("extra_packed_weights", C.c_void_p), ("extra_c", C.c_int32)]
 
 
 def _load() -> C.CDLL:
@@ -90,7 +91,7 @@ def _load() -> C.CDLL:
     lib.pce_csr_from_pairs_workspace_bytes.argtypes = [i32, i32]
     lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, C.POINTER(TileLists), i32, vp, i32,
                                  C.POINTER(Epilogue), i32, vp]
-    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
+    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
     lib.pce_csr_sort_rows.argtypes = [vp, i32, i32, vp, sz, vp, vp]
     lib.pce_packed_weights_bytes.restype = sz
     lib.pce_packed_weights_bytes.argtypes = [i32, i32, i32]

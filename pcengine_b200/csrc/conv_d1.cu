@@ -185,7 +185,7 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, const void* 
       k_d1_tile_lists<<<div_up(static_cast<long long>(n_tiles) * 128 + 1, 256), 256, 0, st>>>(qkpos, kv, n_tiles, order,
                                                                                                tile_ptr, stage_kp, stage_nbr);
       PCE_LAUNCH_CHECK();
-      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128};
+      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128, 0};
       PCE_TRY(conv_umma(bin, qsum, wpacked, &tl, qsum, cin, cout, bout, nullptr, st));
     } else {
       if (w == nullptr) return PCE_ERR_INVALID;
@@ -220,6 +220,7 @@ extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in,
   if ((!weights && !packed_weights) || !out_feats || !qkpos || !ocsr || !icsr) return PCE_ERR_INVALID;
   if (qsum > 0 && (!imap_coded || !omap_coded || !buffer || !in_feats)) return PCE_ERR_INVALID;
   if (centre_kp >= kv || (centre_kp >= 0 && n_in != n_out)) return PCE_ERR_INVALID;
+  if (ep && ep->extra_feats) return PCE_ERR_UNSUPPORTED;
   const size_t esize = dtype == PCE_F32 ? 4 : 2;
   if (static_cast<size_t>(qsum) * (c_in + c_out) * esize > buffer_bytes) return PCE_ERR_WORKSPACE;
   EpiDev e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};

@@ -60,6 +60,15 @@ struct Lists {
   const int* tile_ptr;   // [n_tiles+1] first stage of every tile, or nullptr (dense product)
   const int* stage_kp;   // [stages] offset of every stage
   const int* stage_nbr;  // [stages][tile rows] input row per tile row, -1 absent
+  int identity;          // every tile's last stage is the identity stage (stage_kp = -1)
+};
+
+// Second operand: out[row] += in2[row] @ w2, joined to the accumulation at the identity stage.
+// The residual of a block (w2 = identity matrix) and its 1x1x1 shortcut convolution take this path.
+struct Second {
+  const __half* in2;  // [n_out][cin2], nullptr: none
+  const __half* w2;   // packed like the weights of one offset: kblocks2 images of cout x 128 B
+  int cin2;
 };
 
 struct SharedCtl {
@@ -221,8 +230,8 @@ __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return 
 // traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
 template <int kStages, int SUB>
 __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
-    k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, int n_out, int cin, int cout,
-                __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
+    k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, Second sec, int n_out, int cin,
+                int cout, __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
@@ -239,7 +248,13 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int kblocks = (cin + 63) >> 6;
+  const int kblocks2 = sec.in2 ? (sec.cin2 + 63) >> 6 : 0;  // ring stages of the identity stage
   const int n_tiles = (n_out + kRows - 1) / kRows;
+  // ring stages of tile t: its listed offsets times the K blocks, the identity stage counted with
+  // the second operand's K blocks (none when this launch has no second operand)
+  auto tile_main_stages = [&](int t) {
+    return (first_stage(ls.tile_ptr, t + 1) - first_stage(ls.tile_ptr, t) - (ls.identity ? 1 : 0)) * kblocks;
+  };
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -292,7 +307,11 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
     int j = 0;  // smem stages issued so far (continuous over tiles)
     bool ok = true;
     auto run_stage = [&](int nid, int kp) {
-      for (int kb = 0; kb < kblocks; ++kb, ++j) {
+      const bool second = kp < 0;  // the identity stage
+      const __half* src_base = second ? sec.in2 : in;
+      const int width = second ? sec.cin2 : cin;
+      const int nkb = second ? kblocks2 : kblocks;  // 0: listed, but this launch has no second operand
+      for (int kb = 0; kb < nkb; ++kb, ++j) {
         const int s = j % kStages;
         const int n = j / kStages;
         if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
@@ -302,16 +321,18 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
         if (tid == 0) {
           const uint32_t bbar = smem_u32(&ctl->bfull[s]);
           mbar_arrive_expect_tx(bbar, b_bytes);
-          bulk_copy_g2s(a_addr + kAStage, wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64, b_bytes, bbar);
+          const __half* wsrc = second ? sec.w2 + static_cast<size_t>(kb) * cout * 64
+                                      : wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64;
+          bulk_copy_g2s(a_addr + kAStage, wsrc, b_bytes, bbar);
         }
-        const int kchunks = min(8, (cin - kb * 64) >> 3);
+        const int kchunks = min(8, (width - kb * 64) >> 3);
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           const int r = q * 4 + rsub;  // row inside this warp's 32
           const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
           if (chunk < kchunks) {
             const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-            const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + kb * 64 + chunk * 8 : 0);
+            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * width + kb * 64 + chunk * 8 : 0);
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
@@ -355,7 +376,8 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
       for (int t = t0; t < t1 && ok; ++t) {
         const int it = t - t0;
         const int buf = it % nacc;
-        const int nst = (first_stage(ls.tile_ptr, t + 1) - first_stage(ls.tile_ptr, t)) * kblocks;
+        const int nst_main = tile_main_stages(t);
+        const int nst = nst_main + (ls.identity ? kblocks2 : 0);
         // the accumulator must have been drained by the epilogue (two tiles ago)
         if (it >= nacc) ok = mbar_wait(smem_u32(&ctl->accempty[buf]), ((it / nacc) - 1) & 1, ctl);
         if (!ok) break;
@@ -371,8 +393,9 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
           tc_fence_after();
           const uint32_t a_addr = tiles_addr + s * stage_bytes;
           const uint64_t db = make_desc(a_addr + kAStage);
-          const int kb = st % kblocks;
-          const int ksteps = min(4, (cin - kb * 64) >> 4);
+          const bool second = st >= nst_main;
+          const int kb = second ? st - nst_main : st % kblocks;
+          const int ksteps = min(4, ((second ? sec.cin2 : cin) - kb * 64) >> 4);
           for (int k = 0; k < ksteps; ++k) {
 #pragma unroll
             for (int sub = 0; sub < SUB; ++sub) {  // the same weight block feeds every sub-tile
@@ -407,7 +430,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
         rows_of[sub] = n_out;
         if (slot < n_out) rows_of[sub] = ls.order ? __ldg(ls.order + slot) : slot;
       }
-      const bool any = first_stage(ls.tile_ptr, t + 1) > first_stage(ls.tile_ptr, t);
+      const bool any = tile_main_stages(t) + (ls.identity ? kblocks2 : 0) > 0;
       if (ep.residual) {
         // the rows are known before the accumulator is: pull the residual rows into L2 while waiting
 #pragma unroll
@@ -536,8 +559,10 @@ int umma_force_nacc = 0;
 
 template <int NS, int SUB>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
-                        int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols, int nacc) {
-  umma::k_conv_umma<NS, SUB><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, n_out, cin, cout, out, e, tmem_cols, nacc);
+                        const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols,
+                        int nacc) {
+  umma::k_conv_umma<NS, SUB><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
+                                                                      nacc);
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
@@ -545,14 +570,21 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
               void* out, const pce_epilogue* ep, cudaStream_t st) {
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
   if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
-  umma::Lists ls{nullptr, nullptr, nullptr, nullptr};
+  umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0};
+  umma::Second sec{nullptr, nullptr, 0};
   int sub = umma_force_sub == 1 || umma_force_sub == 2 ? umma_force_sub : 1;
   if (tiles) {
-    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr};
+    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr, tiles->identity_stage ? 1 : 0};
     if (tiles->tile_rows != 128 && tiles->tile_rows != 256) return PCE_ERR_INVALID;
     sub = tiles->tile_rows / 128;  // the lists fix the tile height
   }
   if (sub * cout > 512) return PCE_ERR_UNSUPPORTED;
+  if (ep && ep->extra_feats) {
+    // the second operand rides on the identity stage of the tile lists
+    if (!ls.identity || !ep->extra_packed_weights || ep->extra_c < 16 || ep->extra_c % 16) return PCE_ERR_UNSUPPORTED;
+    sec = umma::Second{static_cast<const __half*>(ep->extra_feats), static_cast<const __half*>(ep->extra_packed_weights),
+                       ep->extra_c};
+  }
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
   const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
@@ -618,7 +650,7 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
-#define PCE_GO(NS, SB) launch_umma<NS, SB>(grid, smem, st, in_h, w_h, ls, n_out, cin, cout, out_h, e, tmem_cols, nacc)
+#define PCE_GO(NS, SB) launch_umma<NS, SB>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc)
   if (sub == 1) {
     if (ns == 4) PCE_GO(4, 1); else if (ns == 3) PCE_GO(3, 1); else PCE_GO(2, 1);
   } else {

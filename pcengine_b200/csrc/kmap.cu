@@ -425,13 +425,15 @@ __global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int w
 
 // Tile lists: the map re-laid for output tiles of blockDim.x (128 or 256) rows taken in
 // processing order.  One CTA per tile; thread r owns the tile's r-th row.
-//   FILL = false: tile_cnt[t] = number of offsets any row of the tile has.
+//   FILL = false: tile_cnt[t] = number of offsets any row of the tile has (+1 with `identity`).
 //   FILL = true : for the tile's s-th present offset (ascending kp) write stage_kp[base+s] and
 //                 stage_nbr[(base+s)*rows + r] = the row's input at that offset, or -1.
+//   identity: every tile ends with one more stage, stage_kp = -1, whose entry for a row is the row
+//   itself: the place where a second operand indexed like the output joins the accumulation.
 template <bool FILL>
 __global__ void __launch_bounds__(256)
     k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
-                 const int* __restrict__ order, int n_rows, int words, int* tile_cnt,
+                 const int* __restrict__ order, int n_rows, int words, int identity, int* tile_cnt,
                  const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
   __shared__ uint32_t wmask[8][4];
   const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
@@ -455,7 +457,7 @@ __global__ void __launch_bounds__(256)
     cnt += __popc(tm[w]);
   }
   if (!FILL) {
-    if (r == 0) tile_cnt[t] = cnt;
+    if (r == 0) tile_cnt[t] = cnt + (identity ? 1 : 0);
     return;
   }
   const int base = __ldg(tile_ptr + t);
@@ -474,6 +476,13 @@ __global__ void __launch_bounds__(256)
         if (r == 0) stage_kp[g] = w * 32 + bit;
       }
       ++s;
+    }
+  }
+  if (identity) {
+    const int g = base + s;
+    if (g < stage_cap) {
+      stage_nbr[static_cast<size_t>(g) * rows + r] = row;
+      if (r == 0) stage_kp[g] = -1;
     }
   }
 }
@@ -750,8 +759,9 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
 }
 
 int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, const int32_t* order,
-                         int32_t n_rows, int32_t kv, int32_t tile_rows, void* workspace, size_t workspace_bytes,
-                         int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap, void* stream) {
+                         int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, void* workspace,
+                         size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr,
+                         int32_t stage_cap, void* stream) {
   if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
   if (tile_rows != 128 && tile_rows != 256) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -766,10 +776,10 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
   int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
-  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, cnt, nullptr, nullptr, nullptr, 0);
+  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, cnt, nullptr, nullptr, nullptr, 0);
   PCE_LAUNCH_CHECK();
   PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
-  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, nullptr, tile_ptr, stage_kp,
+  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, nullptr, tile_ptr, stage_kp,
                                               stage_nbr, stage_cap);
   PCE_LAUNCH_CHECK();
   return PCE_OK;

@@ -24,12 +24,19 @@ TILE_ROWS = None
 
 
 class FusedEpilogue:
-    """y = act(acc*scale + shift + residual); scale/shift are fp32 [C_out] CUDA tensors."""
+    """y = act(acc*scale + shift + residual); scale/shift are fp32 [C_out] CUDA tensors.
 
-    __slots__ = ("scale", "shift", "residual", "act", "slope")
+    ``extra_feats`` [N_out, C2] with ``extra_weight`` [C2, C_out] is a second operand that joins the
+    accumulator itself, acc[row] += extra_feats[row] @ extra_weight (tensor-core kernel only, see
+    :func:`supports_second_operand`): a block's residual (identity weight) or its 1x1x1 shortcut
+    convolution, gathered by the kernel's pipeline instead of read in its epilogue."""
 
-    def __init__(self, scale=None, shift=None, residual=None, act=None, slope=0.01):
+    __slots__ = ("scale", "shift", "residual", "act", "slope", "extra_feats", "extra_weight")
+
+    def __init__(self, scale=None, shift=None, residual=None, act=None, slope=0.01, extra_feats=None,
+                 extra_weight=None):
         self.scale, self.shift, self.residual, self.act, self.slope = scale, shift, residual, act, slope
+        self.extra_feats, self.extra_weight = extra_feats, extra_weight
 
     def pack(self, c_out: int, n_out: int, dtype) -> _lib.Epilogue:
         e = _lib.Epilogue()
@@ -46,7 +53,23 @@ class FusedEpilogue:
             e.residual = r.data_ptr()
         e.act = _ACT[self.act]
         e.slope = float(self.slope)
+        if self.extra_feats is not None:
+            x2, w2 = self.extra_feats, self.extra_weight
+            if w2 is None or w2.dim() != 2 or w2.size(1) != c_out or w2.size(0) != x2.size(1):
+                raise ValueError("extra_weight must be [C2, C_out] for extra_feats [N_out, C2]")
+            if x2.dtype != dtype or w2.dtype != dtype or tuple(x2.shape) != (n_out, w2.size(0)) or not x2.is_contiguous():
+                raise ValueError("extra_feats must be contiguous [N_out, C2] in the features' dtype")
+            packed = packed_weights(w2, as_linear=True) if w2.is_contiguous() else None
+            if packed is None:
+                raise NotImplementedError("the second operand needs fp16 and channel counts that are multiples of 16")
+            e.extra_feats, e.extra_packed_weights, e.extra_c = x2.data_ptr(), packed.data_ptr(), w2.size(0)
         return e
+
+
+def supports_second_operand(dtype, c_in: int, c_out: int, c2: int) -> bool:
+    """Whether a convolution with these widths can take ``FusedEpilogue.extra_feats``."""
+    return (dtype == torch.float16 and c_in % 16 == 0 and c_out % 16 == 0 and c2 % 16 == 0 and 16 <= c_out <= 256
+            and c2 >= 16)
 
 
 def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype):
@@ -154,6 +177,10 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
     if feats.size(0) != csr.n_src:
         raise ValueError(f"feature rows ({feats.size(0)}) do not match the kernel map ({csr.n_src})")
     c_out_true = kernel.size(2)
+    second = epilogue is not None and epilogue.extra_feats is not None
+    if second and (kernel_choice == "simt" or kernel.size(0) > 128
+                   or not supports_second_operand(feats.dtype, kernel.size(1), c_out_true, epilogue.extra_feats.size(1))):
+        raise NotImplementedError("a second operand (FusedEpilogue.extra_feats) needs the tensor-core kernel")
     feats, kernel, epilogue, padded = _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice)
     kv, c_in, c_out = kernel.shape
     out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
@@ -167,7 +194,7 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         rec["start"].record()
     tiles = None
     if packed is not None:
-        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device)))
+        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device), second))
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),

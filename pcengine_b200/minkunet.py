@@ -19,9 +19,9 @@ from torch import nn
 
 from .activation import ReLU
 from .batchnorm import BatchNorm, bn_scale_shift
-from .functional import FusedEpilogue
+from .functional import FusedEpilogue, supports_second_operand
 from .planner import MapPlan
-from .spconv import conv3d
+from .spconv import conv3d, conv_func
 from .sptensor import spTensor
 from .utils import cat
 
@@ -46,6 +46,14 @@ class _Fusable(nn.Module):
             self._folded[name] = bn_scale_shift(bn)
         return self._folded[name]
 
+    def _fold_weight(self, name: str, weight: torch.Tensor, scale: torch.Tensor, dtype):
+        """``weight`` [..., C_out] times the per-channel BatchNorm scale, in ``dtype`` (cached like
+        the folded constants; the tensor-core layout is cached on the result)."""
+        key = (name, dtype)
+        if key not in self._folded:
+            self._folded[key] = (weight.detach().float() * scale).to(dtype).contiguous()
+        return self._folded[key]
+
     def _fused(self, x: spTensor) -> bool:
         return (not self.training) and x.feats.is_cuda
 
@@ -65,6 +73,9 @@ class ConvBNReLU(_Fusable):
 
 
 class ResidualBlock(_Fusable):
+    # fold the shortcut into conv2's launch when the tensor-core kernel can take it
+    one_kernel_tail = True
+
     def __init__(self, cin, cout, ks=3):
         super().__init__()
         self.conv1 = conv3d(cin, cout, ks, 1)
@@ -79,10 +90,38 @@ class ResidualBlock(_Fusable):
             self.short_conv = None
             self.short_bn = None
 
+    def _one_kernel_tail(self, x: spTensor, y: spTensor) -> spTensor:
+        """relu(bn2(conv2(y)) + shortcut(x)) as ONE convolution launch: both BatchNorm scales are
+        folded into the weights, and the shortcut (its 1x1x1 convolution, or the identity) enters the
+        accumulator as the second operand of conv2."""
+        c2, dtype = self.conv2, x.feats.dtype
+        s2, t2 = self._fold("bn2", self.bn2)
+        w_main = self._fold_weight("conv2", c2.kernel, s2, dtype)
+        if self.short_conv is not None:
+            ss, ts = self._fold("short_bn", self.short_bn)
+            w_extra = self._fold_weight("short", self.short_conv.kernel, ss, dtype)
+            if "shift_sum" not in self._folded:
+                self._folded["shift_sum"] = (t2 + ts).contiguous()
+            shift = self._folded["shift_sum"]
+        else:
+            key = ("eye", dtype)
+            if key not in self._folded:
+                self._folded[key] = torch.eye(c2.out_channels, dtype=dtype, device=x.feats.device)
+            w_extra, shift = self._folded[key], t2
+        ep = FusedEpilogue(shift=shift, act="relu", extra_feats=x.feats.contiguous(), extra_weight=w_extra)
+        return conv_func(input=y, in_channel=c2.in_channels, out_channel=c2.out_channels, kernel=w_main,
+                         kernel_size_code=c2.kernel_size_code, stride_code=c2.stride_code, padding_code=c2.padding_code,
+                         bias=None, transposed=False, tensorcore=c2.tensorcore, epilogue=ep)
+
     def forward(self, x: spTensor) -> spTensor:
         if self._fused(x):
             s1, t1 = self._fold("bn1", self.bn1)
             y = self.conv1(x, epilogue=FusedEpilogue(scale=s1, shift=t1, act="relu"))
+            if (self.one_kernel_tail and self.conv2.bias is None and self.conv2.kernel_volume <= 128
+                    and (self.short_conv is None or self.short_conv.bias is None)
+                    and supports_second_operand(x.feats.dtype, self.conv2.in_channels, self.conv2.out_channels,
+                                                x.feats.size(1))):
+                return self._one_kernel_tail(x, y)
             if self.short_conv is not None:
                 ss, ts = self._fold("short_bn", self.short_bn)
                 sc = self.short_conv(x, epilogue=FusedEpilogue(scale=ss, shift=ts)).feats

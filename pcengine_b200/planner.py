@@ -125,13 +125,14 @@ class PlannedKernelMap(KernelMap):
                                _DevArray(c.nbr, (c.nbr_cap,), device, keep), int(c.n_rows), int(c.n_src), kv)
             for t in (c.tiles128, c.tiles256):
                 if t.tile_rows:
-                    lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows)
+                    lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows, t.identity_stage)
                     n_tiles = (csr.n_rows + t.tile_rows - 1) // t.tile_rows
                     csr._order = _DevArray(t.order, (csr.n_rows,), device, keep)
-                    csr._tiles[(True, int(t.tile_rows))] = (
+                    stages = n_tiles * (kv + int(t.identity_stage))
+                    csr._tiles[(True, int(t.tile_rows), bool(t.identity_stage))] = (
                         lists, csr._order, _DevArray(t.tile_ptr, (n_tiles + 1,), device, keep),
-                        _DevArray(t.stage_kp, (n_tiles * kv,), device, keep),
-                        _DevArray(t.stage_nbr, (n_tiles * kv * t.tile_rows,), device, keep))
+                        _DevArray(t.stage_kp, (stages,), device, keep),
+                        _DevArray(t.stage_nbr, (stages * t.tile_rows,), device, keep))
             self._csr[transposed] = csr
 
 

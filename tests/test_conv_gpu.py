@@ -271,6 +271,69 @@ def test_ragged_channels_run_on_tensor_cores(cin, cout):
     assert PF.device_status() == 0
 
 
+@pytest.mark.parametrize("cin,cout,c2,ks,tile_rows", [(64, 64, 64, 3, 128), (96, 96, 128, 3, 128), (32, 32, 32, 3, 256),
+                                                       (128, 256, 384, 3, 128), (48, 80, 16, 5, 128)])
+def test_second_operand_joins_the_accumulator(cin, cout, c2, ks, tile_rows):
+    """FusedEpilogue.extra_feats: out = act((conv(x) + x2 @ w2) * scale + shift), against the oracle's
+    convolution plus a dense product, and bit-identical between the two tile heights' code paths and
+    to itself run to run."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(21, 64, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    g = torch.Generator().manual_seed(cin + 3 * cout + c2)
+    n = len(coords)
+    x = torch.randn(n, cin, generator=g).half()
+    w = (torch.randn(ks ** 3, cin, cout, generator=g) / (ks ** 3 * cin) ** 0.5).half()
+    x2 = torch.randn(n, c2, generator=g).half()
+    w2 = (torch.randn(c2, cout, generator=g) / c2 ** 0.5).half()
+    scale, shift = torch.rand(cout, generator=g) + 0.5, torch.randn(cout, generator=g)
+    ep = PF.FusedEpilogue(scale=scale.cuda(), shift=shift.cuda(), act="relu", extra_feats=x2.cuda(), extra_weight=w2.cuda())
+    plain = PF.FusedEpilogue(scale=scale.cuda(), shift=shift.cuda(), act="relu")
+    try:
+        PF.TILE_ROWS = tile_rows
+        a = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        b = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        c = PF.conv_forward(x.cuda(), w.cuda(), csr, plain)  # served by the lists that have the identity stage
+    finally:
+        PF.TILE_ROWS = None
+    assert torch.equal(a, b)
+    d2 = ko.build_d2(coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    want = torch.relu((co.conv_forward(x.float(), w.float(), d2) + x2.float() @ w2.float()) * scale + shift)
+    assert co.rel_l2(a.float().cpu(), want) <= 1e-3  # fp16 operands, fp32 accumulation
+    # the lists with the identity stage also served the launch without a second operand
+    assert any(k[2] for k in csr._tiles) and not any(not k[2] for k in csr._tiles)
+    assert co.rel_l2(c.float().cpu(), torch.relu(co.conv_forward(x.float(), w.float(), d2) * scale + shift)) <= 1e-3
+    with pytest.raises(NotImplementedError):
+        PF.conv_forward(x.cuda(), w.cuda(), csr, ep, "simt")
+    with pytest.raises(NotImplementedError):
+        PF.conv_forward(x.float().cuda(), w.float().cuda(), csr,
+                        PF.FusedEpilogue(extra_feats=x2.float().cuda(), extra_weight=w2.float().cuda()))
+    assert PF.device_status() == 0
+
+
+def test_residual_block_as_one_launch():
+    """A ResidualBlock whose shortcut rides in conv2's launch (BatchNorm scales folded into fp16
+    weights) agrees with the block run as conv2 + shortcut + residual epilogue."""
+    import pcengine_b200 as pce
+    from pcengine_b200.minkunet import ResidualBlock
+    coords = surface_cloud(23, 56, batch=2)
+    for cin, cout in ((32, 64), (64, 64)):
+        torch.manual_seed(cin)
+        block = ResidualBlock(cin, cout)
+        pce.randomize_batchnorm(block, 9)
+        block = block.half().cuda().eval()
+        feats = torch.randn(len(coords), cin).half().cuda()
+        outs = []
+        for one in (True, False):
+            block.one_kernel_tail = one
+            x = pce.spTensor(feats, torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), init_tag=["auto"])
+            with torch.no_grad():
+                outs.append(block(x).feats.float().cpu())
+        assert co.rel_l2(outs[0], outs[1]) <= 2e-3
+
+
 def test_dense_product_on_tensor_cores():
     """1x1x1 layers with tensor-core friendly widths run the tcgen05 kernel in identity mode."""
     import pcengine_b200 as pce

@@ -100,19 +100,21 @@ def test_out_of_range_coordinate_reports_status():
         km.sizes()
 
 
-@pytest.mark.parametrize("ks,sort_rows,tile_rows", [((3, 3, 3), True, 128), ((3, 3, 3), False, 128), ((5, 5, 5), True, 128),
-                                                    ((2, 2, 2), True, 128), ((3, 3, 3), True, 256), ((5, 5, 5), False, 256)])
-def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows):
+@pytest.mark.parametrize("ks,sort_rows,tile_rows,identity", [
+    ((3, 3, 3), True, 128, False), ((3, 3, 3), False, 128, False), ((5, 5, 5), True, 128, False), ((2, 2, 2), True, 128, False),
+    ((3, 3, 3), True, 256, False), ((5, 5, 5), False, 256, False), ((3, 3, 3), True, 128, True), ((3, 3, 3), True, 256, True)])
+def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity):
     """Tile lists are the oracle's neighbour CSR re-laid: per tile of 128 or 256 rows (in processing
-    order) one stage per offset present in the tile, with each row's neighbour at that offset or -1."""
+    order) one stage per offset present in the tile, with each row's neighbour at that offset or -1;
+    with ``identity`` one more stage (offset -1) in which every row names itself."""
     import pcengine_b200 as pce
     coords = surface_cloud(14, 56, batch=2)
     d2 = ko.build_d2(coords, ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     nb = ko.neighbour_csr(d2)
     km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     csr = km.csr()
-    csr.tiles(sort_rows, tile_rows)
-    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows)]
+    csr.tiles(sort_rows, tile_rows, identity)
+    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows, identity)]
     order, tile_ptr = order.cpu().numpy(), tile_ptr.cpu().numpy()
     stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, tile_rows)
     n, kv = km.n_out, km.kv
@@ -131,6 +133,10 @@ def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows):
         rws = order[t * tile_rows:(t + 1) * tile_rows]
         present = np.nonzero((want[rws] >= 0).any(axis=0))[0]
         a, b = tile_ptr[t], tile_ptr[t + 1]
+        if identity:
+            b -= 1
+            assert stage_kp[b] == -1 and np.array_equal(stage_nbr[b, :len(rws)], rws)
+            assert (stage_nbr[b, len(rws):] == -1).all()
         assert np.array_equal(stage_kp[a:b], present)
         got = stage_nbr[a:b, :len(rws)]
         assert np.array_equal(got, want[rws][:, present].T)
