@@ -396,6 +396,9 @@ def run_ours(args):
     resident = torch.cuda.Event()  # the device-resident inputs exist from here on
     resident.record()
 
+    for _ in range(2):  # set-up, not warm-up: packs the weights, lets the planner create its storage
+        step(coords_d, feats_d, resident)
+        torch.cuda.synchronize()
     for _ in range(max(args.warmup, 3)):
         step(coords_d, feats_d, resident)
     # ---- device-resident timing ------------------------------------------------------------
@@ -427,15 +430,37 @@ def run_ours(args):
     dt_prof = p0.elapsed_time(p1) * 1e-3
     prof, PF.PROFILE = PF.PROFILE, None
     # ---- end to end: pinned host -> device, forward, logits -> pinned host -----------------
+    # A serving loop with two batches in flight: batch i's inputs are copied on an input stream (the
+    # map planner starts on their arrival), its logits are copied back on the compute stream, and the
+    # host waits for batch i-1's logits once batch i is queued.  Every step moves its own inputs and
+    # its own result; input and result buffers are double.
+    main = torch.cuda.current_stream(dev)
+    s_in = torch.cuda.Stream(dev)
+    c_buf = [torch.empty_like(coords_d) for _ in range(2)]
+    f_buf = [torch.empty_like(feats_d) for _ in range(2)]
+    l_pin = [logits_pin, torch.empty_like(logits_pin).pin_memory()]
+    ev_in = [torch.cuda.Event() for _ in range(2)]     # inputs of the batch are on the device
+    ev_done = [torch.cuda.Event() for _ in range(2)]   # the batch no longer reads its input buffers
+    ev_out = [torch.cuda.Event() for _ in range(2)]    # its logits are on the host
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        c = coords_pin.to(dev, non_blocking=True)
-        f = feats_pin.to(dev, non_blocking=True)
+    for i in range(args.steps):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_done[b])
+            c_buf[b].copy_(coords_pin, non_blocking=True)
+            f_buf[b].copy_(feats_pin, non_blocking=True)
+            ev_in[b].record(s_in)
+        main.wait_event(ev_in[b])
         flush.zero_()
-        out = step(c, f)
-        logits_pin.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        out = step(c_buf[b], f_buf[b], ev_in[b])
+        ev_done[b].record(main)
+        l_pin[b].copy_(out, non_blocking=True)
+        ev_out[b].record(main)
+        if i >= 1:
+            ev_out[b ^ 1].synchronize()
+    ev_out[(args.steps - 1) & 1].synchronize()
     dt_e2e = max_over_ranks(time.perf_counter() - t0)
     clocks = sampler.stop() if rank == 0 else None
     # ---- roofline of the dominant convolution kernel ---------------------------------------
@@ -483,6 +508,7 @@ def run_ours(args):
         "config": {"workload": "minkunet_lidar_batch8", "scans_per_gpu": SCANS_PER_GPU, "voxels_per_gpu": int(len(coords_h)),
                    "voxels_per_scan": sizes, "in_channels": IN_CHANNELS, "classes": NUM_CLASSES,
                    "widths": "32-32-64-128-256-256-128-96-96", "map_build": "inside the timed step (planner threads, own streams)",
+                   "e2e_loop": "two batches in flight: H2D on an input stream, host waits for the previous batch's logits",
                    "l2": "192 MiB memset between steps, inside the timed region", "accumulate": "fp32"},
         "e2e": {"value": total_scans / dt_e2e, "unit": UNIT,
                 "h2d_bytes_per_step": int(coords_pin.numel() * 4 + feats_pin.numel() * 2),
