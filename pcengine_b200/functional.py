@@ -133,11 +133,11 @@ def _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice):
     if cout_p != c_out and epilogue is not None and epilogue.residual is not None:
         return feats, kernel, epilogue, False
     kernel = _padded_kernel(kernel, cin_p, cout_p)
-    if cin_p != c_in:
-        feats = torch.nn.functional.pad(feats, (0, cin_p - c_in))
+    if cin_p != c_in:  # (torch.nn.functional.pad costs 0.3 ms of host time here; cat does not)
+        feats = torch.cat([feats, feats.new_zeros((feats.size(0), cin_p - c_in))], dim=1)
     if cout_p != c_out and epilogue is not None:
         def widen(t):
-            return None if t is None else torch.nn.functional.pad(t, (0, cout_p - c_out))
+            return None if t is None else torch.cat([t, t.new_zeros((cout_p - c_out,))])
         epilogue = FusedEpilogue(widen(epilogue.scale), widen(epilogue.shift), None, epilogue.act, epilogue.slope)
     return feats, kernel, epilogue, True
 
