@@ -10,6 +10,9 @@
 // power-of-two table at load <= 0.5; every probe loop is bounded by the table
 // size and reports PCE_ERR_TABLE_FULL through the status word instead of
 // spinning.
+#include <sched.h>
+
+#include <chrono>
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
@@ -489,6 +492,34 @@ __global__ void __launch_bounds__(256)
 
 // ---- host helpers ------------------------------------------------------------
 
+// Waits for everything queued on `st` without burning a core: polls an event, yielding the
+// processor between polls, for a short while (the usual case: a few microseconds of work ahead),
+// then sleeps on it.  cudaStreamSynchronize spins, and the size read-back of a strided layer can
+// wait for milliseconds behind other work; with one process per GPU and several planner threads
+// per process, spinning starves the threads that queue the kernels being waited for.
+static int wait_for_stream(cudaStream_t st) {
+  static thread_local cudaEvent_t ev[64] = {};
+  int dev = 0;
+  PCE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    PCE_CUDA(cudaStreamSynchronize(st));
+    return PCE_OK;
+  }
+  if (!ev[dev]) PCE_CUDA(cudaEventCreateWithFlags(&ev[dev], cudaEventBlockingSync | cudaEventDisableTiming));
+  PCE_CUDA(cudaEventRecord(ev[dev], st));
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    const cudaError_t q = cudaEventQuery(ev[dev]);
+    if (q == cudaSuccess) return PCE_OK;
+    if (q != cudaErrorNotReady) return cuda_fail(q);
+    (void)cudaGetLastError();  // "not ready" is an answer, not a failure
+    if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(200)) break;
+    sched_yield();
+  }
+  PCE_CUDA(cudaEventSynchronize(ev[dev]));
+  return PCE_OK;
+}
+
 static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, cudaStream_t st) {
   size_t need = 0;
   PCE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, in, out, static_cast<int>(n), st));
@@ -539,9 +570,14 @@ int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom
   k_candidates<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, ukeys,
                                      out_cap, ctr, ctr + 1);
   PCE_LAUNCH_CHECK();
-  int host[2] = {0, 0};
-  PCE_CUDA(cudaMemcpyAsync(host, ctr, sizeof(host), cudaMemcpyDeviceToHost, st));
-  PCE_CUDA(cudaStreamSynchronize(st));
+  // read back through pinned memory: a copy to pageable memory would make the copy call itself wait
+  // (spinning) for the stream, a pinned one returns at once and the wait below sleeps
+  static thread_local int* pinned = nullptr;
+  if (!pinned) PCE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&pinned), 64, cudaHostAllocDefault));
+  int* host = pinned;
+  host[0] = host[1] = 0;
+  PCE_CUDA(cudaMemcpyAsync(host, ctr, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+  PCE_TRY(wait_for_stream(st));
   if (host[1] != 0) return host[1];
   int n_out = host[0];
   if (n_out > out_cap) return PCE_ERR_CAPACITY;
