@@ -152,10 +152,30 @@ __global__ void k_insert_rows(const int4* __restrict__ coords, int n, Slot* tabl
   atomicMax(&table[s].val, i);  // slots start at -1; duplicate rows keep the largest index
 }
 
+// Sort key of an output coordinate: (b, x - lo, y - lo, z - lo) in as few bits as the output bounds
+// need (z lowest), so that the radix sort of the unique keys runs over ~30 bits instead of 64.
+struct KeyBits {
+  int sh_y, sh_x, sh_b;  // shifts of the y, x and batch fields
+};
+
+static KeyBits key_bits_for(const GeomDev& g) {
+  auto bits = [](long long extent) {
+    int b = 1;
+    while (b < 16 && (1ll << b) < extent) ++b;
+    return b;
+  };
+  KeyBits k;
+  k.sh_y = bits(static_cast<long long>(g.hi[2]) - g.lo[2] + 1);
+  k.sh_x = k.sh_y + bits(static_cast<long long>(g.hi[1]) - g.lo[1] + 1);
+  k.sh_b = k.sh_x + bits(static_cast<long long>(g.hi[0]) - g.lo[0] + 1);
+  return k;
+}
+
 // Strided output coordinates, step 1: every valid candidate is inserted into a
-// set; first-time keys are appended to ukeys (unordered).
-__global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev g, Slot* table, unsigned tmask,
-                             unsigned long long* ukeys, int ucap, int* counter, int* status) {
+// set; the sort keys of first-time members are appended to ukeys (unordered).
+__global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev g, KeyBits kb, Slot* table,
+                             unsigned tmask, unsigned long long* ukeys, int ucap, int* counter, int* status,
+                             int* max_batch) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int kp = blockIdx.y;
   if (i >= n_in) return;
@@ -175,19 +195,25 @@ __global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev 
   }
   if (fresh) {
     int pos = atomicAdd(counter, 1);
-    if (pos < ucap)
-      ukeys[pos] = key;
+    if (pos < ucap)  // candidate() keeps q inside [lo, hi], so every field fits its bits
+      ukeys[pos] = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
+                   (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
+                   (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
+                   static_cast<unsigned long long>(qz - g.lo[2]);
     else
       atomicMax(status, PCE_ERR_CAPACITY);
+    atomicMax(max_batch, c.x);
   }
 }
 
-__global__ void k_decode_keys(const unsigned long long* __restrict__ keys, int n, int4* coords) {
+__global__ void k_decode_keys(const unsigned long long* __restrict__ keys, int n, GeomDev g, KeyBits kb, int4* coords) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  int b, x, y, z;
-  unpack_key(keys[i], b, x, y, z);
-  coords[i] = make_int4(b, x, y, z);
+  const unsigned long long k = keys[i];
+  const int z = static_cast<int>(k & ((1ull << kb.sh_y) - 1)) + g.lo[2];
+  const int y = static_cast<int>((k >> kb.sh_y) & ((1ull << (kb.sh_x - kb.sh_y)) - 1)) + g.lo[1];
+  const int x = static_cast<int>((k >> kb.sh_x) & ((1ull << (kb.sh_b - kb.sh_x)) - 1)) + g.lo[0];
+  coords[i] = make_int4(static_cast<int>(k >> kb.sh_b), x, y, z);
 }
 
 // Input-major query: one thread per (input row, offset).  Writes the dense
@@ -565,30 +591,33 @@ int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom
   int* ctr = ar.take<int>(64);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * tsize, st));
-  PCE_CUDA(cudaMemsetAsync(ctr, 0, 2 * sizeof(int), st));
+  PCE_CUDA(cudaMemsetAsync(ctr, 0, 3 * sizeof(int), st));
+  const KeyBits kb = key_bits_for(gd);
   dim3 grid(div_up(n_in, 256), gd.kv);
-  k_candidates<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, ukeys,
-                                     out_cap, ctr, ctr + 1);
+  k_candidates<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, kb, table, tsize - 1, ukeys,
+                                     out_cap, ctr, ctr + 1, ctr + 2);
   PCE_LAUNCH_CHECK();
   // read back through pinned memory: a copy to pageable memory would make the copy call itself wait
   // (spinning) for the stream, a pinned one returns at once and the wait below sleeps
   static thread_local int* pinned = nullptr;
   if (!pinned) PCE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&pinned), 64, cudaHostAllocDefault));
   int* host = pinned;
-  host[0] = host[1] = 0;
-  PCE_CUDA(cudaMemcpyAsync(host, ctr, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+  host[0] = host[1] = host[2] = 0;
+  PCE_CUDA(cudaMemcpyAsync(host, ctr, 3 * sizeof(int), cudaMemcpyDeviceToHost, st));
   PCE_TRY(wait_for_stream(st));
   if (host[1] != 0) return host[1];
   int n_out = host[0];
   if (n_out > out_cap) return PCE_ERR_CAPACITY;
   *n_out_host = n_out;
   if (n_out == 0) return PCE_OK;
+  int end_bit = kb.sh_b + 1;  // the batch field ends at its highest index seen
+  while (end_bit < 64 && (host[2] >> (end_bit - kb.sh_b)) != 0) ++end_bit;
   size_t need = 0;
-  PCE_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, need, ukeys, skeys, n_out, 0, 64, st));
+  PCE_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, need, ukeys, skeys, n_out, 0, end_bit, st));
   char* tmp = ar.take<char>(need);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
-  PCE_CUDA(cub::DeviceRadixSort::SortKeys(tmp, need, ukeys, skeys, n_out, 0, 64, st));
-  k_decode_keys<<<div_up(n_out, 256), 256, 0, st>>>(skeys, n_out, reinterpret_cast<int4*>(out_coords));
+  PCE_CUDA(cub::DeviceRadixSort::SortKeys(tmp, need, ukeys, skeys, n_out, 0, end_bit, st));
+  k_decode_keys<<<div_up(n_out, 256), 256, 0, st>>>(skeys, n_out, gd, kb, reinterpret_cast<int4*>(out_coords));
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }

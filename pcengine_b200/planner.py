@@ -76,17 +76,15 @@ class _DevArray:
 class _PassHandle:
     """Owns a ``pce_pass``; releases it to the plan when the last user goes away."""
 
-    def __init__(self, plan, handle, device):
+    def __init__(self, plan, handle, device, stream):
         self.plan, self.handle, self.device = plan, handle, device
+        self.stream = stream  # the stream the maps are read on: the one of the latest fetch
 
     def __del__(self):
         h, self.handle = self.handle, None
         if h and self.plan.handle:
-            try:  # the maps were read on the stream current now (the one the network ran on)
-                stream = _lib.stream_ptr(self.device)
-            except Exception:
-                stream = None
-            lib.pce_pass_release(h, stream)
+            # a failure (say, the stream no longer exists) leaves the pass unrecycled, which is safe
+            lib.pce_pass_release(h, self.stream)
 
 
 class PlannedKernelMap(KernelMap):
@@ -154,7 +152,9 @@ class PlannedPass:
             return None
         spec = self.plan.specs[idx]
         out = _lib.PlannedMap()
-        _lib.check(lib.pce_pass_map(self._handle.handle, idx, _lib.stream_ptr(self.device), C.byref(out)), "pce_pass_map")
+        stream = _lib.stream_ptr(self.device)
+        _lib.check(lib.pce_pass_map(self._handle.handle, idx, stream, C.byref(out)), "pce_pass_map")
+        self._handle.stream = stream
         in_coords = self.level_coords[spec["in_level"]]
         if in_coords is None:
             in_coords = _DevArray(out.in_coords, (out.n_in, 4), self.device, self._handle).tensor()
@@ -269,7 +269,7 @@ class MapPlan:
                 stream = gate.cuda_stream
             _lib.check(lib.pce_plan_begin(h, coords.data_ptr(), coords.size(0), cmin, cmax, stream, C.byref(out)),
                        "pce_plan_begin")
-        x.planner = PlannedPass(self, _PassHandle(self, out.value, dev), x)
+        x.planner = PlannedPass(self, _PassHandle(self, out.value, dev, _lib.stream_ptr(dev)), x)
         return True
 
     def close(self) -> None:

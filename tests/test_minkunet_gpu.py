@@ -139,3 +139,36 @@ def test_map_plan_api():
     assert plan.begin(x) is False and x.planner is None
     plan.close()
     assert plan.begin(tensor()) is False
+
+
+def test_planned_pass_on_a_side_stream():
+    """The network run on a stream of its own, with the coordinates produced on yet another one
+    (``coords_ready``), gives the logits of the plain run; storage released from that stream is
+    recycled safely over repeated passes."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(46, 64, batch=2)
+    torch.manual_seed(12)
+    feats = torch.randn(len(coords), 4).half().cuda()
+    model = pce.MinkUNet(4, 19, cr=0.5)
+    pce.randomize_batchnorm(model, 6)
+    model = model.half().eval().cuda()
+    cm = cmax_of(coords)
+    coords_pin = torch.from_numpy(coords).pin_memory()
+    with torch.no_grad():
+        want = model(pce.spTensor(feats, coords_pin.cuda(), None, [0, 0, 0], cm, init_tag=["auto"])).feats.clone()
+    torch.cuda.synchronize()
+    work, copy = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(6):
+        with torch.cuda.stream(copy):
+            c = coords_pin.to("cuda", non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(copy)
+        work.wait_event(ready)
+        with torch.cuda.stream(work), torch.no_grad():
+            x = pce.spTensor(feats, c, None, [0, 0, 0], cm, init_tag=["auto"])
+            x.coords_ready = ready
+            got = model(x).feats
+            c.record_stream(work)
+        del x
+    work.synchronize()
+    assert torch.equal(got, want)
