@@ -227,11 +227,12 @@ PCE_API int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const
                          void* out_feats, int32_t dtype, const pce_epilogue* ep, int32_t kernel_choice,
                          void* stream);
 
-/* Processing order for the tensor-core kernel: output rows sorted by their indicator
- * bitmask (stable radix sort), so rows with the same neighbourhood pattern land in the
- * same 128-row tile and the tile skips every offset none of them has.  Purely a
- * scheduling aid with no reference counterpart.  order[n_rows] receives the permutation;
- * workspace >= 64*n_rows + 16 MiB bytes. */
+/* Processing order for the tensor-core kernel: output rows sorted (stable radix sort) by
+ * their indicator bitmask with the bits permuted by rarity, the rarest offset most
+ * significant, so rows with the same neighbourhood pattern land in the same tile, rows
+ * with a rare offset land next to each other, and a tile skips every offset none of its
+ * rows has.  Purely a scheduling aid with no reference counterpart.  order[n_rows]
+ * receives the permutation; kv <= 128; workspace >= 64*n_rows + 16 MiB bytes. */
 PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace,
                               size_t workspace_bytes, int32_t* order, void* stream);
 

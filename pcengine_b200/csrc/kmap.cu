@@ -433,23 +433,75 @@ __global__ void k_pairs_rows(const int* __restrict__ skeys, const int* __restric
   if (j < cap) nbr[j] = v;
 }
 
-// Sort key of an output row: its indicator bitmask (one word), or the words folded into
-// 64 bits for larger kernels.  Only used to group similar rows, never for correctness.
-__global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int words, unsigned long long* keys,
-                            int* vals) {
-  int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= n_rows) return;
-  unsigned long long k = mask[static_cast<size_t>(r) * words];
-  if (words > 1) {
-    unsigned long long hi = mask[static_cast<size_t>(r) * words + 1];
-    for (int w = 2; w < words; ++w) {
-      const unsigned m = mask[static_cast<size_t>(r) * words + w];
-      hi ^= (static_cast<unsigned long long>(m) << (8 * (w - 1))) | (m >> (32 - 8 * (w - 1)));
+// Row order for the tile lists.  Rows that share offsets should share tiles, and a tile pays one
+// stage for every offset ANY of its rows has, so the expensive offsets are the rare ones: a tile
+// that contains a single row with a rare offset pays a stage that is 1/128 full.  The sort key is
+// therefore the indicator bitmask with its bits permuted by rarity, the rarest offset in the most
+// significant position: rows with a rare offset end up next to each other and the tiles in between
+// do not pay for it.  Measured stages per 128-row tile against the plain bitmask as key: 3x3x3
+// LiDAR levels 3-7 % fewer, 5x5x5 indoor 16.0 instead of 23.5 (19.0 for the unpermuted full mask).
+// Only used to group similar rows, never for correctness.
+
+// counts[k] = rows that have offset k.
+__global__ void k_offset_counts(const uint32_t* __restrict__ mask, int n_rows, int words, int* counts) {
+  __shared__ int local[128];
+  if (threadIdx.x < 128) local[threadIdx.x] = 0;
+  __syncthreads();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  for (int w = 0; w < words; ++w) {
+    const uint32_t m = r < n_rows ? __ldg(mask + static_cast<size_t>(r) * words + w) : 0u;
+    const uint32_t any = __reduce_or_sync(0xFFFFFFFFu, m);
+    for (uint32_t rest = any; rest; rest &= rest - 1) {
+      const int bit = __ffs(rest) - 1;
+      const int c = __popc(__ballot_sync(0xFFFFFFFFu, (m >> bit) & 1u));
+      if (lane == 0) atomicAdd(&local[w * 32 + bit], c);
     }
-    k |= hi << 32;
   }
-  keys[r] = k;
+  __syncthreads();
+  if (threadIdx.x < 128 && local[threadIdx.x]) atomicAdd(&counts[threadIdx.x], local[threadIdx.x]);
+}
+
+// keys = the bitmask with offset k moved to bit kv-1-rank(k), rank 0 = rarest (ties by index);
+// lo holds positions 0..63, hi positions 64..127 (kv > 64 only).
+__global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int words, int kv,
+                            const int* __restrict__ counts, unsigned long long* lo, unsigned long long* hi,
+                            int* vals) {
+  __shared__ int pos[128];
+  if (threadIdx.x < 128) {
+    const int k = threadIdx.x;
+    int rank = 0;
+    if (k < kv) {
+      const int ck = counts[k];
+      for (int j = 0; j < kv; ++j) {
+        const int cj = counts[j];
+        rank += (cj < ck || (cj == ck && j < k)) ? 1 : 0;
+      }
+    }
+    pos[k] = kv - 1 - rank;
+  }
+  __syncthreads();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  unsigned long long klo = 0, khi = 0;
+  for (int w = 0; w < words; ++w) {
+    for (uint32_t m = mask[static_cast<size_t>(r) * words + w]; m; m &= m - 1) {
+      const int p = pos[w * 32 + __ffs(m) - 1];
+      if (p < 64)
+        klo |= 1ull << p;
+      else
+        khi |= 1ull << (p - 64);
+    }
+  }
+  lo[r] = klo;
+  if (hi) hi[r] = khi;
   vals[r] = r;
+}
+
+__global__ void k_gather_u64(const unsigned long long* __restrict__ src, const int* __restrict__ idx, int n,
+                             unsigned long long* dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[idx[i]];
 }
 
 // Tile lists: the map re-laid for output tiles of blockDim.x (128 or 256) rows taken in
@@ -802,24 +854,42 @@ int pce_csr_from_dense(const int32_t* table, int32_t kv, int32_t n_rows, int32_t
 
 int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* workspace, size_t workspace_bytes,
                       int32_t* order, void* stream) {
-  if (n_rows < 0 || kv < 1) return PCE_ERR_INVALID;
+  if (n_rows < 0 || kv < 1 || kv > 128) return PCE_ERR_INVALID;
   if (n_rows == 0) return PCE_OK;
   if (!mask || !order) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int words = (kv + 31) / 32;
+  const bool two = kv > 64;  // the key needs a second 64-bit word
   Arena ar(workspace, workspace_bytes);
-  unsigned long long* keys = ar.take<unsigned long long>(n_rows);
-  unsigned long long* skeys = ar.take<unsigned long long>(n_rows);
+  unsigned long long* lo = ar.take<unsigned long long>(n_rows);
+  unsigned long long* sorted = ar.take<unsigned long long>(n_rows);
+  unsigned long long* hi = two ? ar.take<unsigned long long>(n_rows) : nullptr;
+  unsigned long long* hi_by_lo = two ? ar.take<unsigned long long>(n_rows) : nullptr;
   int* vals = ar.take<int>(n_rows);
+  int* by_lo = two ? ar.take<int>(n_rows) : order;
+  int* counts = ar.take<int>(128);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
-  k_mask_keys<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, keys, vals);
+  PCE_CUDA(cudaMemsetAsync(counts, 0, 128 * sizeof(int), st));
+  k_offset_counts<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, counts);
   PCE_LAUNCH_CHECK();
-  const int bits = words == 1 ? (kv < 32 ? kv : 32) : 64;
-  size_t need = 0;
-  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, keys, skeys, vals, order, n_rows, 0, bits, st));
+  k_mask_keys<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, kv, counts, lo, hi, vals);
+  PCE_LAUNCH_CHECK();
+  // least significant word first; the radix sort is stable, so the second pass keeps its order
+  const int lo_bits = kv < 64 ? kv : 64;
+  size_t need = 0, need_hi = 0;
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, lo, sorted, vals, by_lo, n_rows, 0, lo_bits, st));
+  if (two) {
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need_hi, hi_by_lo, sorted, by_lo, order, n_rows, 0, kv - 64, st));
+    if (need_hi > need) need = need_hi;
+  }
   char* tmp = ar.take<char>(need);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
-  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, keys, skeys, vals, order, n_rows, 0, bits, st));
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, lo, sorted, vals, by_lo, n_rows, 0, lo_bits, st));
+  if (two) {
+    k_gather_u64<<<div_up(n_rows, 256), 256, 0, st>>>(hi, by_lo, n_rows, hi_by_lo);
+    PCE_LAUNCH_CHECK();
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, hi_by_lo, sorted, by_lo, order, n_rows, 0, kv - 64, st));
+  }
   return PCE_OK;
 }
 

@@ -141,3 +141,31 @@ def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity):
         got = stage_nbr[a:b, :len(rws)]
         assert np.array_equal(got, want[rws][:, present].T)
         assert (stage_nbr[a:b, len(rws):] == -1).all()
+
+
+@pytest.mark.parametrize("ks", [(3, 3, 3), (5, 5, 5), (4, 4, 4), (2, 2, 2)])
+def test_row_order_groups_equal_masks_and_rare_offsets(ks):
+    """The processing order is a permutation in which rows with the same indicator bitmask are
+    contiguous, and the rows that have the rarest offset form one contiguous run at the end (that
+    offset is the most significant bit of the sort key), for one-, two- and four-word masks."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(17, 48, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    order = csr.order().cpu().numpy()
+    n, kv = km.n_out, km.kv
+    assert np.array_equal(np.sort(order), np.arange(n))
+    mask = csr.mask.cpu().numpy().view(np.uint32)
+    bits = np.zeros((n, kv), dtype=bool)
+    for k in range(kv):
+        bits[:, k] = (mask[:, k // 32] >> (k % 32)) & 1
+    sorted_bits = bits[order]
+    changes = np.count_nonzero((sorted_bits[1:] != sorted_bits[:-1]).any(axis=1))
+    assert changes == len(np.unique(bits, axis=0)) - 1
+    counts = bits.sum(0)
+    present = np.nonzero(counts)[0]
+    rarest = present[np.argmin(counts[present])]  # ties: lowest index, as the kernel ranks them
+    has = sorted_bits[:, rarest]
+    absent_rank = [k for k in range(kv) if counts[k] < counts[rarest]]  # offsets no row has rank above it
+    if not absent_rank or all(counts[k] == 0 for k in absent_rank):
+        assert has[-int(counts[rarest]):].all() and not has[:-int(counts[rarest])].any()
