@@ -466,21 +466,41 @@ def run_ours(args):
     # ---- roofline of the dominant convolution kernel ---------------------------------------
     by_kernel = {}
     by_shape = {}
+    t_min_convs = 0.0
     for rec in prof:
         t = rec["start"].elapsed_time(rec["end"]) * 1e-3
         pairs = int(rec["rowptr"][-1].item())
         e = rec["esize"]
         byt = e * (rec["n_in"] * rec["cin"] + rec["n_out"] * rec["cout"]) + e * rec["kv"] * rec["cin"] * rec["cout"] + 4 * pairs
+        flops = 2.0 * pairs * rec["cin"] * rec["cout"]
+        if rec["extra_c"]:  # second operand: its rows and weights are read, one more product per row
+            byt += e * rec["extra_c"] * (rec["n_out"] + rec["cout"])
+            flops += 2.0 * rec["n_out"] * rec["extra_c"] * rec["cout"]
+        if rec["residual"]:
+            byt += e * rec["n_out"] * rec["cout"]
+        t_min_convs += max(byt / (pk["hbm_gbs"] * 1e9), flops / (pk["tflops"] * 1e12))
         k = by_kernel.setdefault(rec["kernel"], dict(t=0.0, bytes=0.0, flops=0.0, n=0))
         k["t"] += t
         k["bytes"] += byt
-        k["flops"] += 2.0 * pairs * rec["cin"] * rec["cout"]
+        k["flops"] += flops
         k["n"] += 1
         sh = by_shape.setdefault((rec["kernel"], rec["n_out"], rec["kv"], rec["cin"], rec["cout"]), [0, 0.0, 0.0, 0.0])
         sh[0] += 1
         sh[1] += t
         sh[2] += byt
-        sh[3] += 2.0 * pairs * rec["cin"] * rec["cout"]
+        sh[3] += flops
+    # Lower bound of a step: every convolution at the better of its two roofs plus every kernel map at
+    # the copy bandwidth over its algorithmic bytes (coordinates in, table payload, 12 B per lookup,
+    # neighbour table out, output coordinates of a strided map).
+    t_min = t_min_convs / max(args.steps, 1)
+    x_last = pce.spTensor(feats_d, coords_d, None, [0, 0, 0], cmax, batchsize=SCANS_PER_GPU, init_tag=pce.MinkUNet.tags())
+    with torch.no_grad():
+        maps = model(x_last).kmaps
+    for km in maps.values():
+        lookups = km.n_out * (km.kv - (1 if km.subm else 0))
+        map_bytes = 28 * km.n_in + 12 * lookups + 4 * km.n_out * km.kv + (0 if km.subm else 16 * km.n_out)
+        t_min += map_bytes / (pk["hbm_gbs"] * 1e9)
+    del maps, x_last
     roof = None
     if by_kernel:
         name, k = max(by_kernel.items(), key=lambda kv: kv[1]["t"])
@@ -515,6 +535,10 @@ def run_ours(args):
                 "d2h_bytes_per_step": int(logits_pin.numel() * 2), "ms_per_step": dt_e2e / args.steps * 1e3},
         "gpu_launches": launches,
         "roofline": roof,
+        "network_roofline": {"t_min_ms": t_min * 1e3, "t_measured_ms": dt / args.steps * 1e3,
+                             "frac": t_min / (dt / args.steps),
+                             "note": "sum over the step's convolutions of max(bytes/copy bandwidth, flops/GEMM peak) "
+                                     "plus its kernel maps' algorithmic bytes / copy bandwidth, over the measured step"},
         "kernels": {k: {"launches": v["n"], "ms": v["t"] * 1e3} for k, v in by_kernel.items()},
         "conv_shapes": [{"kernel": k[0], "n_out": k[1], "kv": k[2], "cin": k[3], "cout": k[4], "launches": v[0],
                          "us_per_launch": v[1] / v[0] * 1e6, "GB/s": v[2] / v[1] / 1e9, "TFLOP/s": v[3] / v[1] / 1e12}

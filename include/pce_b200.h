@@ -117,6 +117,22 @@ PCE_API int pce_last_cuda_error(void);
  * primitives such as radix sort / scan passes and memsets are not counted). */
 PCE_API uint64_t pce_kernel_launches(void);
 
+/* ---------------------------------------------------------- voxelisation -- */
+
+/* floor(points / voxel) and one row per occupied voxel: the device form of
+ * sparse_quantize (ref: script/utils.py:34-55, NumPy on the host), the step before the
+ * kernel maps.  points float32 [n,3] (device), voxel_host 3 floats (host).  The division
+ * is done in double precision as NumPy does it; out_coords [<= n, 4] = (batch, x, y, z)
+ * in ascending (x,y,z) order (the order of the reference's ravel hash); out_index[u]
+ * (optional) = the first point of voxel u, out_inverse[i] (optional) = the voxel of point
+ * i.  SYNCHRONISES `stream` once to return *n_unique_host.  A voxel coordinate outside
+ * the packable range gives PCE_ERR_RANGE. */
+PCE_API size_t pce_quantize_workspace_bytes(int32_t n);
+PCE_API int pce_quantize_unique(const float* points, int32_t n, const float* voxel_host, int32_t batch,
+                                void* workspace, size_t workspace_bytes, int32_t* out_coords,
+                                int32_t* out_index, int32_t* out_inverse, int32_t* n_unique_host,
+                                void* stream);
+
 /* ------------------------------------------------------------------ maps -- */
 
 /* Scratch bytes needed by the map-building calls below for n_in inputs. */

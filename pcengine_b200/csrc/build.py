@@ -14,7 +14,7 @@ import sys
 CSRC = os.path.dirname(os.path.abspath(__file__))
 HERE = os.path.dirname(CSRC)
 LIB = os.path.join(HERE, "libpce_b200.so")
-SOURCES = ["capi.cu", "kmap.cu", "conv_simt.cu", "conv_d1.cu", "conv_umma.cu", "planner.cu"]
+SOURCES = ["capi.cu", "kmap.cu", "conv_simt.cu", "conv_d1.cu", "conv_umma.cu", "planner.cu", "quantize.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -588,6 +588,7 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
   const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
+  static int regs_per_thread[2] = {72, 72};  // per sub-tile count, allocation units of 8; read back at set-up
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
@@ -602,6 +603,11 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
     PCE_SET_SMEM(3, 2);
     PCE_SET_SMEM(2, 2);
 #undef PCE_SET_SMEM
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[0] = (fa.numRegs + 7) / 8 * 8;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[1] = (fa.numRegs + 7) / 8 * 8;
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -613,7 +619,7 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   // with one accumulator set 146 us, 2 x 3 with two sets 159 us; C=128: 115 vs 122 us), and at equal
   // CTAs two accumulator sets win (the epilogue of a tile then overlaps the next tile's MMAs).
   const int threads = 32 * (4 * sub + 5);
-  const int by_regs = 65536 / (threads * 72);  // 70 registers per thread, allocated in units of 8
+  const int by_regs = 65536 / (threads * regs_per_thread[sub - 1]);
   auto tmem_for = [&](int sets) {
     int cols = 32;
     while (cols < sets * sub * cout) cols <<= 1;

@@ -190,6 +190,8 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         which = _lib.KERNEL_UMMA if packed is not None else _lib.KERNEL_SIMT
         rec = dict(kernel=_KERNEL_NAME.get(which, "none"), n_in=feats.size(0), n_out=csr.n_rows, cin=c_in, cout=c_out,
                    kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
+                   extra_c=epilogue.extra_feats.size(1) if second else 0,
+                   residual=epilogue is not None and epilogue.residual is not None,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
     tiles = None

@@ -54,10 +54,14 @@ def ravel_hash(x: np.ndarray) -> np.ndarray:
 
 def sparse_quantize(coords, voxel_size: Union[float, Tuple[float, ...]] = 1, *, return_index: bool = False,
                     return_inverse: bool = False):
-    """floor(coords / voxel) and keep one point per voxel (script/utils.py:34-55)."""
+    """floor(coords / voxel) and keep one point per voxel (script/utils.py:34-55).  A CUDA tensor of
+    points is voxelised on the device (pce_quantize_unique) and CUDA tensors come back: int32 [M,3]
+    voxels in the same order as the host path, int64 ``indices`` / ``inverse``."""
     if isinstance(voxel_size, (float, int)):
         voxel_size = tuple(repeat(voxel_size, 3))
     assert isinstance(voxel_size, tuple) and len(voxel_size) == 3
+    if isinstance(coords, torch.Tensor) and coords.is_cuda:
+        return _sparse_quantize_cuda(coords, voxel_size, return_index, return_inverse)
     coords = np.floor(coords / np.array(voxel_size)).astype(np.int32)
     _, indices, inverse = np.unique(ravel_hash(coords), return_index=True, return_inverse=True)
     outputs = [coords[indices]]
@@ -65,6 +69,34 @@ def sparse_quantize(coords, voxel_size: Union[float, Tuple[float, ...]] = 1, *, 
         outputs.append(indices)
     if return_inverse:
         outputs.append(inverse)
+    return outputs[0] if len(outputs) == 1 else outputs
+
+
+def _sparse_quantize_cuda(points: torch.Tensor, voxel_size, return_index: bool, return_inverse: bool):
+    import ctypes as C
+
+    from . import _lib
+    from ._lib import lib
+    if points.dim() != 2 or points.size(1) != 3:
+        raise ValueError("points must be [N,3]")
+    if points.dtype == torch.float64:
+        raise NotImplementedError("device voxelisation takes float32 points (the host path handles float64)")
+    pts = points.detach().to(torch.float32).contiguous()
+    n, dev = pts.size(0), pts.device
+    out = torch.empty((max(n, 1), 4), dtype=torch.int32, device=dev)
+    index = torch.empty((max(n, 1),), dtype=torch.int32, device=dev) if return_index else None
+    inverse = torch.empty((max(n, 1),), dtype=torch.int32, device=dev) if return_inverse else None
+    ws = _lib.workspace(lib.pce_quantize_workspace_bytes(n), dev)
+    voxel = (C.c_float * 3)(*[float(v) for v in voxel_size])
+    m = C.c_int32(0)
+    _lib.check(lib.pce_quantize_unique(pts.data_ptr(), n, voxel, 0, ws.data_ptr(), ws.numel(), out.data_ptr(),
+                                       _lib.ptr(index), _lib.ptr(inverse), C.byref(m), _lib.stream_ptr(dev)),
+               "pce_quantize_unique")
+    outputs = [out[: m.value, 1:].contiguous()]
+    if return_index:
+        outputs.append(index[: m.value].long())
+    if return_inverse:
+        outputs.append(inverse[:n].long())
     return outputs[0] if len(outputs) == 1 else outputs
 
 

@@ -169,3 +169,37 @@ def test_row_order_groups_equal_masks_and_rare_offsets(ks):
     absent_rank = [k for k in range(kv) if counts[k] < counts[rarest]]  # offsets no row has rank above it
     if not absent_rank or all(counts[k] == 0 for k in absent_rank):
         assert has[-int(counts[rarest]):].all() and not has[:-int(counts[rarest])].any()
+
+
+@pytest.mark.parametrize("n,voxel", [(50000, 0.05), (20000, (0.1, 0.05, 0.2)), (1, 0.5), (3000, 1)])
+def test_device_voxelisation_matches_the_host_path(n, voxel):
+    """sparse_quantize on a CUDA tensor returns what the NumPy path returns: the same voxels in the
+    same order, the first point of every voxel, and the point-to-voxel map (negative coordinates,
+    many points per voxel, anisotropic voxels)."""
+    import pcengine_b200 as pce
+    rng = np.random.default_rng(n)
+    pts = (rng.normal(0, 3.0, (n, 3)) + rng.integers(-2, 3, (n, 3))).astype(np.float32)
+    pts[: n // 4] = pts[n // 4: 2 * (n // 4)]  # exact duplicates
+    want_c, want_i, want_v = pce.sparse_quantize(pts, voxel, return_index=True, return_inverse=True)
+    got_c, got_i, got_v = pce.sparse_quantize(torch.from_numpy(pts).cuda(), voxel, return_index=True, return_inverse=True)
+    assert got_c.dtype == torch.int32 and got_c.is_cuda and got_c.is_contiguous()
+    assert np.array_equal(got_c.cpu().numpy(), want_c)
+    assert np.array_equal(got_i.cpu().numpy(), want_i)
+    assert np.array_equal(got_v.cpu().numpy(), want_v)
+    only = pce.sparse_quantize(torch.from_numpy(pts).cuda(), voxel)
+    assert torch.equal(only, got_c)
+    # the voxels feed a kernel map directly
+    coords = torch.cat([torch.zeros((got_c.size(0), 1), dtype=torch.int32, device="cuda"), got_c - got_c.min(0).values], dim=1)
+    km = pce.KernelMap(coords.contiguous(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0],
+                       coords[:, 1:].max(0).values.tolist(), True)
+    assert km.sizes()[0] >= 0
+
+
+def test_device_voxelisation_edge_cases():
+    import pcengine_b200 as pce
+    empty = pce.sparse_quantize(torch.empty((0, 3), device="cuda"), 0.1, return_inverse=True)
+    assert empty[0].shape == (0, 3) and empty[1].shape == (0,)
+    with pytest.raises(RuntimeError):  # 1e9 / 0.01 does not fit the packable coordinate range
+        pce.sparse_quantize(torch.tensor([[1e9, 0.0, 0.0]], device="cuda"), 0.01)
+    with pytest.raises(NotImplementedError):
+        pce.sparse_quantize(torch.zeros((4, 3), dtype=torch.float64, device="cuda"), 0.1)
