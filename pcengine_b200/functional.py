@@ -189,7 +189,7 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
     if PROFILE is not None:
         which = _lib.KERNEL_UMMA if packed is not None else _lib.KERNEL_SIMT
         rec = dict(kernel=_KERNEL_NAME.get(which, "none"), n_in=feats.size(0), n_out=csr.n_rows, cin=c_in, cout=c_out,
-                   kv=kv, esize=feats.element_size(), rowptr=csr.rowptr,
+                   kv=kv, esize=feats.element_size(),
                    extra_c=epilogue.extra_feats.size(1) if second else 0,
                    residual=epilogue is not None and epilogue.residual is not None,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
@@ -203,6 +203,7 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
         rec["end"].record()
+        rec["pairs"] = csr.rowptr[-1:].clone()  # a copy: the record must not keep the map's storage alive
         PROFILE.append(rec)
     return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
 
