@@ -382,7 +382,8 @@ PCE_API void pce_plan_destroy(pce_plan* plan);
  * this call (the producer of the coordinates) precedes the planner's kernels; nothing else
  * orders the planner against the caller, so with the coordinates produced on a stream of
  * their own the maps of the next pass are built while the current one computes.  Returns
- * at once. */
+ * at once.  Up to three passes are created freely and at most eight exist; with eight
+ * passes unreleased the call returns PCE_ERR_CAPACITY. */
 PCE_API int pce_plan_begin(pce_plan* plan, const int32_t* coords, int32_t n, const int32_t* cmin,
                            const int32_t* cmax, void* stream, pce_pass** pass);
 /* Blocks the host until map `index` is queued (30 s limit: PCE_ERR_TIMEOUT), makes `stream`

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libpce_b200.so")
 
 PCE_OK = 0
 PCE_ERR_INVALID = 1
+PCE_ERR_CAPACITY = 8
 PCE_F32, PCE_F16 = 0, 1
 ACT_NONE, ACT_RELU, ACT_LEAKY = 0, 1, 2
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_UMMA = 0, 1, 2

@@ -463,7 +463,10 @@ int pce_plan_begin(pce_plan* p, const int32_t* coords, int32_t n, const int32_t*
   // Storage to build into: the oldest released pass whose readers have finished; if they have not,
   // a new pass (up to kMaxPasses), so that the maps of this pass are built while the previous
   // pass still computes; beyond that the oldest one, whose readers the lanes then wait for.
+  // A caller that keeps the maps of many passes alive gets at most kHardPasses arenas; the next
+  // begin then fails with PCE_ERR_CAPACITY (the caller builds that pass's maps lazily instead).
   constexpr int kMaxPasses = 3;
+  constexpr int kHardPasses = 8;
   pce_pass* ps = nullptr;
   {
     std::lock_guard<std::mutex> lk(p->m);
@@ -481,7 +484,10 @@ int pce_plan_begin(pce_plan* p, const int32_t* coords, int32_t n, const int32_t*
         p->idle.pop_front();
       }
     }
-    if (!ps) ++p->n_passes;
+    if (!ps) {
+      if (p->n_passes >= kHardPasses) return PCE_ERR_CAPACITY;
+      ++p->n_passes;
+    }
   }
   if (!ps) {
     ps = new pce_pass();

@@ -246,8 +246,9 @@ class MapPlan:
         coordinates only: everything queued so far on the current stream, or, when the tensor
         carries a CUDA event in ``x.coords_ready``, just that event, which lets the maps of the
         next pass be built while the current pass still computes.  Returns False (and leaves ``x``
-        on the lazy path) when the tensor does not fit the plan: other stride, maps already
-        present, an override of the tile policy in force, or an empty tensor."""
+        on the lazy path) when the tensor does not fit the plan (other stride, maps already
+        present, an override of the tile policy in force, an empty tensor) or when eight earlier
+        passes of this plan are still referenced (their maps kept alive by the caller)."""
         coords = x.coords
         if (not self.handle or not coords.is_cuda or coords.size(0) == 0 or x.stride != self.in_stride or x.kmaps
                 or PF.TILE_ROWS is not None or not PF.SORT_ROWS or coords.dtype != torch.int32
@@ -267,8 +268,10 @@ class MapPlan:
                     gate = self.gates[dev] = torch.cuda.Stream(dev)
                 gate.wait_event(ready)
                 stream = gate.cuda_stream
-            _lib.check(lib.pce_plan_begin(h, coords.data_ptr(), coords.size(0), cmin, cmax, stream, C.byref(out)),
-                       "pce_plan_begin")
+            status = lib.pce_plan_begin(h, coords.data_ptr(), coords.size(0), cmin, cmax, stream, C.byref(out))
+            if status == _lib.PCE_ERR_CAPACITY:  # too many passes are still referenced: this one builds lazily
+                return False
+            _lib.check(status, "pce_plan_begin")
         x.planner = PlannedPass(self, _PassHandle(self, out.value, dev, _lib.stream_ptr(dev)), x)
         return True
 

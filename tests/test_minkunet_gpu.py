@@ -172,3 +172,29 @@ def test_planned_pass_on_a_side_stream():
         del x
     work.synchronize()
     assert torch.equal(got, want)
+
+
+def test_many_live_passes_fall_back_to_lazy_maps():
+    """Keeping the outputs (and with them the planner storage) of more passes than the planner holds
+    arenas for makes further passes build their maps lazily; every result stays the same."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(47, 40)
+    torch.manual_seed(13)
+    feats = torch.randn(len(coords), 4).half().cuda()
+    model = pce.MinkUNet(4, 19, cr=0.25)
+    pce.randomize_batchnorm(model, 7)
+    model = model.half().eval().cuda()
+    kept = []
+    for _ in range(11):
+        x = pce.spTensor(feats, torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), init_tag=["auto"])
+        with torch.no_grad():
+            kept.append(model(x))
+    kinds = [type(next(iter(y.kmaps.values()))).__name__ for y in kept]
+    assert kinds[:8] == ["PlannedKernelMap"] * 8 and kinds[8:] == ["KernelMap"] * 3
+    for y in kept[1:]:
+        assert torch.equal(y.feats, kept[0].feats)
+    del kept, y
+    x = pce.spTensor(feats, torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), init_tag=["auto"])
+    with torch.no_grad():
+        again = model(x)
+    assert type(next(iter(again.kmaps.values()))).__name__ == "PlannedKernelMap"  # storage came back
