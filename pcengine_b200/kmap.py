@@ -127,7 +127,6 @@ class KernelMap:
             self.n_out = int(n_out.value)
             self.out_coords = oc[: self.n_out]
         self._built = False
-        self.ready = None  # CUDA event recorded after an off-stream build; consumers wait on it
         self._csr: dict = {}
         self._pairs = None
         self._d1 = None
@@ -161,17 +160,12 @@ class KernelMap:
         self._built = True
         return self
 
-    def wait(self) -> None:
-        """Make PyTorch's current stream wait for a build that ran on another stream."""
-        if self.ready is not None:
-            torch.cuda.current_stream(self.device).wait_event(self.ready)
-
     # -- sizes that live on the device -------------------------------------
     def sizes(self):
         """(pairs, qsum) read back once (one synchronisation), also validates the status word.
         The reference reads qkpos[-1] the same way (script/spconv.py:376,421)."""
         if self._sizes is None:
-            self.build().wait()
+            self.build()
             host = torch.stack([self.kpos[-1], self.qkpos[-1], self.status[0]]).cpu()
             if int(host[2]) != 0:
                 _lib.check(int(host[2]), "kernel map build")

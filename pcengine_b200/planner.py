@@ -110,7 +110,6 @@ class PlannedKernelMap(KernelMap):
         self.qkpos = _DevArray(out.qkpos, (kv + 1,), device, keep)
         self.status = _DevArray(out.status, (1,), device, keep)
         self._built = True
-        self.ready = None
         self._csr = {}
         self._pairs = self._d1 = self._sizes = None
         self.dataflow = "D2"

@@ -111,7 +111,6 @@ def _choose_dataflow(tag: str, in_channel: int, out_channel: int) -> str:
 
 
 def _run_conv(feats, w, kmap, transposed, ep, buffer):
-    kmap.wait()
     if kmap.dataflow == "D1":
         return PF.conv_forward_d1(feats, w, kmap, transposed, ep, buffer)
     return PF.conv_forward(feats, w, kmap.csr(transposed=transposed), ep)
