@@ -202,7 +202,7 @@ __global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev 
                    static_cast<unsigned long long>(qz - g.lo[2]);
     else
       atomicMax(status, PCE_ERR_CAPACITY);
-    atomicMax(max_batch, c.x);
+    if (c.x > *reinterpret_cast<volatile int*>(max_batch)) atomicMax(max_batch, c.x);  // rarely taken: one hot address
   }
 }
 
