@@ -87,6 +87,15 @@ typedef struct pce_epilogue {
   const void* extra_feats;          /* [n_out, extra_c] fp16 */
   const void* extra_packed_weights; /* pce_packed_weights_bytes(1, extra_c, c_out) bytes */
   int32_t extra_c;
+  /* Halo push (slab-parallel scenes): output row r is stored a second time to
+   * push_base[s] + push_slot[s][r] * c_out elements for s = 0, 1 where push_slot[s][r] >= 0.
+   * push_base[s] is the feature buffer of a neighbouring GPU mapped into this process
+   * (peer memory); the stores are plain 16-byte peer stores from the convolution's
+   * epilogue, so the boundary rows cross NVLink while the interior is still computed and
+   * no separate exchange step reads them back.  The caller orders the neighbour's reads
+   * after this launch (a barrier between the GPUs).  Tensor-core kernel only. */
+  const int32_t* push_slot[2]; /* [n_out] each, or NULL */
+  void* push_base[2];
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output

@@ -102,7 +102,8 @@ int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* w
       return PCE_ERR_INVALID;
     return conv_umma(in_feats, n_in, packed_weights, tiles, n_out, c_in, c_out, out_feats, ep, st);
   }
-  if (ep && ep->extra_feats) return PCE_ERR_UNSUPPORTED;  // the second operand needs the tensor-core kernel
+  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1]))
+    return PCE_ERR_UNSUPPORTED;  // the second operand and the halo push need the tensor-core kernel
   if (!weights || !mask || !rowptr || (n_in > 0 && !nbr)) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
 }
@@ -112,7 +113,7 @@ int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* we
   if (n < 0 || c_in < 1 || c_out < 1) return PCE_ERR_INVALID;
   if (n == 0) return PCE_OK;
   if (!in_feats || !out_feats || (!weights && !packed_weights)) return PCE_ERR_INVALID;
-  if (ep && ep->extra_feats) return PCE_ERR_UNSUPPORTED;
+  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1])) return PCE_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool aligned = ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
                          reinterpret_cast<uintptr_t>(packed_weights)) & 15) == 0;

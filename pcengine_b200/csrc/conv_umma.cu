@@ -53,6 +53,10 @@ struct Epi {
   const __half* residual;
   int act;
   float slope;
+  // halo push: output row r is also stored to push_base[s] + push_slot[s][r] * cout (slot >= 0), memory
+  // of a neighbouring GPU mapped into this process (plain peer stores over NVLink)
+  const int* push_slot[2];
+  __half* push_base[2];
 };
 
 struct Lists {
@@ -228,7 +232,7 @@ __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return 
 // takes an immediate).  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
 // has SUB accumulators and every staged weight block feeds SUB MMAs, which halves the weight
 // traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
-template <int kStages, int SUB>
+template <int kStages, int SUB, bool PUSH>
 __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, Second sec, int n_out, int cin,
                 int cout, __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
@@ -452,6 +456,14 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
       const uint32_t taddr = tmem_base + static_cast<uint32_t>((buf * SUB + sub) * cout) +
                              (static_cast<uint32_t>(lane_quarter * 32) << 16);
       __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
+      __half* prow[2] = {nullptr, nullptr};
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (PUSH && ep.push_slot[s] && store_row) {
+          const int slot = __ldg(ep.push_slot[s] + my_row);
+          if (slot >= 0) prow[s] = ep.push_base[s] + static_cast<size_t>(slot) * cout;
+        }
+      }
       const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
       for (int c0 = 0; c0 < cout; c0 += 16) {
         uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
@@ -516,6 +528,13 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
           *reinterpret_cast<uint4*>(orow + c0) = oa;
           *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
         }
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (PUSH && prow[s]) {
+            *reinterpret_cast<uint4*>(prow[s] + c0) = oa;
+            *reinterpret_cast<uint4*>(prow[s] + c0 + 8) = ob;
+          }
+        }
       }
       }  // sub-tiles
       tc_fence_before();
@@ -557,19 +576,27 @@ int umma_force_stages = 0;
 int umma_force_sub = 0;
 int umma_force_nacc = 0;
 
-template <int NS, int SUB>
+template <int NS, int SUB, bool PUSH>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
                         const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols,
                         int nacc) {
-  umma::k_conv_umma<NS, SUB><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
+  umma::k_conv_umma<NS, SUB, PUSH><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
                                                                       nacc);
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
 int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
               void* out, const pce_epilogue* ep, cudaStream_t st) {
-  umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};
-  if (ep) e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope};
+  umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}};
+  if (ep) {
+    e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope,
+                  {ep->push_slot[0], ep->push_slot[1]},
+                  {static_cast<__half*>(ep->push_base[0]), static_cast<__half*>(ep->push_base[1])}};
+    for (int s = 0; s < 2; ++s) {
+      if (e.push_slot[s] && (!e.push_base[s] || (reinterpret_cast<uintptr_t>(e.push_base[s]) & 15))) return PCE_ERR_INVALID;
+      if (!e.push_slot[s]) e.push_base[s] = nullptr;
+    }
+  }
   umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0};
   umma::Second sec{nullptr, nullptr, 0};
   int sub = umma_force_sub == 1 || umma_force_sub == 2 ? umma_force_sub : 1;
@@ -588,14 +615,15 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
   const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
-  static int regs_per_thread[2] = {72, 72};  // per sub-tile count, allocation units of 8; read back at set-up
+  static int regs_per_thread[2][2] = {{72, 72}, {80, 80}};  // [push][sub-1], allocation units of 8; read back at set-up
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
   if (sm_count[dev] == 0) {
     const int cap = 227 * 1024;
 #define PCE_SET_SMEM(NS, SB) \
-  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); \
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
     PCE_SET_SMEM(4, 1);
     PCE_SET_SMEM(3, 1);
     PCE_SET_SMEM(2, 1);
@@ -604,10 +632,14 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
     PCE_SET_SMEM(2, 2);
 #undef PCE_SET_SMEM
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[0] = (fa.numRegs + 7) / 8 * 8;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[1] = (fa.numRegs + 7) / 8 * 8;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1, false>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[0][0] = (fa.numRegs + 7) / 8 * 8;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2, false>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[0][1] = (fa.numRegs + 7) / 8 * 8;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1, true>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[1][0] = (fa.numRegs + 7) / 8 * 8;
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2, true>) == cudaSuccess && fa.numRegs > 0)
+      regs_per_thread[1][1] = (fa.numRegs + 7) / 8 * 8;
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -619,7 +651,7 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   // with one accumulator set 146 us, 2 x 3 with two sets 159 us; C=128: 115 vs 122 us), and at equal
   // CTAs two accumulator sets win (the epilogue of a tile then overlaps the next tile's MMAs).
   const int threads = 32 * (4 * sub + 5);
-  const int by_regs = 65536 / (threads * regs_per_thread[sub - 1]);
+  const int by_regs = 65536 / (threads * regs_per_thread[(e.push_slot[0] || e.push_slot[1]) ? 1 : 0][sub - 1]);
   auto tmem_for = [&](int sets) {
     int cols = 32;
     while (cols < sets * sub * cout) cols <<= 1;
@@ -656,7 +688,14 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
-#define PCE_GO(NS, SB) launch_umma<NS, SB>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc)
+  const bool push = e.push_slot[0] || e.push_slot[1];  // (its variant needs more registers: fewer CTAs fit)
+#define PCE_GO(NS, SB)                                                                                              \
+  do {                                                                                                              \
+    if (push)                                                                                                       \
+      launch_umma<NS, SB, true>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);   \
+    else                                                                                                            \
+      launch_umma<NS, SB, false>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);  \
+  } while (0)
   if (sub == 1) {
     if (ns == 4) PCE_GO(4, 1); else if (ns == 3) PCE_GO(3, 1); else PCE_GO(2, 1);
   } else {

@@ -29,14 +29,19 @@ class FusedEpilogue:
     ``extra_feats`` [N_out, C2] with ``extra_weight`` [C2, C_out] is a second operand that joins the
     accumulator itself, acc[row] += extra_feats[row] @ extra_weight (tensor-core kernel only, see
     :func:`supports_second_operand`): a block's residual (identity weight) or its 1x1x1 shortcut
-    convolution, gathered by the kernel's pipeline instead of read in its epilogue."""
+    convolution, gathered by the kernel's pipeline instead of read in its epilogue.
 
-    __slots__ = ("scale", "shift", "residual", "act", "slope", "extra_feats", "extra_weight")
+    ``push_slots`` / ``push_bases``: the halo push of a slab-parallel scene (see
+    ``multigpu.SlabScene.push_epilogue``): output row r is also stored to peer memory
+    ``push_bases[s] + push_slots[s][r] * C_out`` for the slots that are >= 0."""
+
+    __slots__ = ("scale", "shift", "residual", "act", "slope", "extra_feats", "extra_weight", "push_slots", "push_bases")
 
     def __init__(self, scale=None, shift=None, residual=None, act=None, slope=0.01, extra_feats=None,
-                 extra_weight=None):
+                 extra_weight=None, push_slots=None, push_bases=None):
         self.scale, self.shift, self.residual, self.act, self.slope = scale, shift, residual, act, slope
         self.extra_feats, self.extra_weight = extra_feats, extra_weight
+        self.push_slots, self.push_bases = push_slots, push_bases
 
     def pack(self, c_out: int, n_out: int, dtype) -> _lib.Epilogue:
         e = _lib.Epilogue()
@@ -63,6 +68,13 @@ class FusedEpilogue:
             if packed is None:
                 raise NotImplementedError("the second operand needs fp16 and channel counts that are multiples of 16")
             e.extra_feats, e.extra_packed_weights, e.extra_c = x2.data_ptr(), packed.data_ptr(), w2.size(0)
+        if self.push_slots is not None:
+            for s, (slots, base) in enumerate(zip(self.push_slots, self.push_bases)):
+                if slots is None or not base:
+                    continue
+                if slots.dtype != torch.int32 or slots.numel() != n_out or not slots.is_contiguous() or not slots.is_cuda:
+                    raise ValueError("push_slots must be contiguous int32 CUDA tensors with one entry per output row")
+                e.push_slot[s], e.push_base[s] = slots.data_ptr(), int(base)
         return e
 
 
@@ -163,8 +175,9 @@ def device_status(reset: bool = True) -> int:
 
 
 def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, epilogue: Optional[FusedEpilogue] = None,
-                 kernel_choice: str = "auto") -> torch.Tensor:
-    """Fused gather-matmul-scatter over a neighbour CSR; returns [csr.n_rows, C_out]."""
+                 kernel_choice: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused gather-matmul-scatter over a neighbour CSR; returns [csr.n_rows, C_out] (written into
+    ``out`` when given: a contiguous tensor of that shape and the features' dtype)."""
     _lib.require_cuda(feats, "feats")
     _lib.require_cuda(kernel, "kernel")
     if kernel.dim() == 2:
@@ -183,7 +196,12 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         raise NotImplementedError("a second operand (FusedEpilogue.extra_feats) needs the tensor-core kernel")
     feats, kernel, epilogue, padded = _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice)
     kv, c_in, c_out = kernel.shape
-    out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    if out is None or padded:
+        if out is not None:
+            raise ValueError("`out` cannot be used with channel counts that need padding")
+        out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    elif tuple(out.shape) != (csr.n_rows, c_out) or out.dtype != feats.dtype or not out.is_contiguous():
+        raise ValueError("`out` must be a contiguous [n_rows, C_out] tensor in the features' dtype")
     packed = packed_weights(kernel) if kernel_choice != "simt" else None
     rec = None
     if PROFILE is not None:

@@ -50,6 +50,13 @@ class NeighbourCSR:
         self._order = None
         self._tiles = {}
 
+    def restrict(self, n_rows: int) -> "NeighbourCSR":
+        """The CSR of the first ``n_rows`` output rows only (same inputs, shared storage): what a
+        slab of a scene uses to compute its owned rows and not the halo's."""
+        if not 0 <= n_rows <= self.n_rows:
+            raise ValueError("restrict: n_rows out of range")
+        return NeighbourCSR(self.mask[:max(n_rows, 1)], self.rowptr[: n_rows + 1], self.nbr, n_rows, self.n_src, self.kv)
+
     def order(self):
         """Output rows sorted by indicator bitmask (int32 [n_rows], built once): the order in which
         the tensor-core kernel forms its 128-row tiles."""

@@ -5,9 +5,11 @@ multi-GPU support at all, so nothing here mirrors reference code):
   (``scans_for_rank``, ``max_over_ranks`` for device-side timing);
 * slab-parallel: ONE large scene is cut along x into slabs with balanced voxel counts; every rank
   owns the outputs of its slab and needs the inputs within the kernel radius of its cut planes.
-  Coordinates of that halo are exchanged once, features before every layer, with neighbour-only
-  point-to-point messages (``torch.distributed`` isend/irecv: NCCL over NVLink between GPUs, gloo in
-  the CPU tests).  Halo rows land in the rank's own memory before any kernel reads them.
+  Coordinates of that halo are exchanged once, features before every layer, either with
+  neighbour-only point-to-point messages (``torch.distributed`` isend/irecv: NCCL over NVLink between
+  GPUs, gloo in the CPU tests) or, between GPUs, by the convolution kernel itself storing its boundary
+  rows into the neighbours' halo rows (``PeerPush``).  Halo rows land in the rank's own memory before
+  any kernel reads them.
 """
 from __future__ import annotations
 
@@ -154,6 +156,69 @@ class SlabScene:
         buf = self.alloc_local(feats.size(1), feats.dtype)
         buf[: self.n_owned] = feats
         return self.exchange_into(buf)
+
+
+class PeerPush:
+    """Halo exchange of a :class:`SlabScene` done by the convolution itself.
+
+    Every rank keeps two feature buffers [n_local, C] in symmetric memory (each rank's buffers are
+    mapped into its neighbours' address spaces).  A layer reads buffer ``src`` and writes its owned
+    output rows into its own buffer ``dst`` AND, from the convolution kernel's epilogue with plain
+    peer stores over NVLink, the boundary rows into the halo rows of the neighbours' ``dst`` buffers
+    (:meth:`epilogue`).  One barrier between the GPUs (:meth:`barrier`) then makes every ``dst``
+    complete; with the two buffers used alternately that barrier also orders the next layer's
+    writes after this layer's reads.  Compared with sending the boundary rows after the layer
+    (``SlabScene.exchange_into``) there is no gather of the boundary rows, no message and no copy
+    into the halo: the rows cross the link while the interior tiles are still being computed.
+
+    The kernels only ever LOAD local memory; remote memory is written, never read, and no multicast
+    is involved."""
+
+    def __init__(self, scene: "SlabScene", channels: int, dtype=torch.float16, group=None):
+        import torch.distributed._symmetric_memory as symm
+        if scene.local_coords is None:
+            raise RuntimeError("SlabScene.setup() must run first")
+        self.scene, self.channels = scene, channels
+        dev = scene.coords.device
+        group = group if group is not None else dist.group.WORLD
+        nl, nr = int(scene.halo_left.size(0)), int(scene.halo_right.size(0))
+        mine = torch.tensor([scene.n_owned, nl, nr, scene.n_local], dtype=torch.int64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(scene.world)]
+        dist.all_gather(every, mine, group=group)
+        every = [t.cpu().tolist() for t in every]
+        rows = max(e[3] for e in every)
+        self.buffers = [symm.empty((rows, channels), dtype=dtype, device=dev) for _ in range(2)]
+        self.handles = [symm.rendezvous(t, group) for t in self.buffers]
+        # where my boundary rows live in the neighbours' buffers
+        n0 = scene.n_owned
+        self.slots = [torch.full((n0,), -1, dtype=torch.int32, device=dev) for _ in range(2)]
+        if scene.rank > 0:  # my left boundary = the left neighbour's RIGHT halo
+            e = every[scene.rank - 1]
+            self.slots[0][scene.send_left] = (e[0] + e[1] + torch.arange(scene.send_left.numel(), device=dev)).to(torch.int32)
+        if scene.rank < scene.world - 1:  # my right boundary = the right neighbour's LEFT halo
+            e = every[scene.rank + 1]
+            self.slots[1][scene.send_right] = (e[0] + torch.arange(scene.send_right.numel(), device=dev)).to(torch.int32)
+
+    def local(self, k: int) -> torch.Tensor:
+        """Buffer ``k`` as this rank's [n_local, C] feature matrix ([owned | left halo | right halo])."""
+        return self.buffers[k][: self.scene.n_local]
+
+    def owned(self, k: int) -> torch.Tensor:
+        return self.buffers[k][: self.scene.n_owned]
+
+    def epilogue(self, k: int, **kwargs):
+        """A FusedEpilogue (plus any of its usual fields) that also stores the boundary rows into the
+        neighbours' buffer ``k``."""
+        from .functional import FusedEpilogue
+        r, w = self.scene.rank, self.scene.world
+        ptrs = self.handles[k].buffer_ptrs
+        bases = (int(ptrs[r - 1]) if r > 0 else 0, int(ptrs[r + 1]) if r < w - 1 else 0)
+        return FusedEpilogue(push_slots=(self.slots[0] if bases[0] else None, self.slots[1] if bases[1] else None),
+                             push_bases=bases, **kwargs)
+
+    def barrier(self, k: int) -> None:
+        """All ranks have finished the layer that wrote buffer ``k`` (queued on the current stream)."""
+        self.handles[k].barrier(channel=0)
 
 
 def split_scene(coords: np.ndarray, world: int, radius: int):
