@@ -627,7 +627,8 @@ size_t pce_map_workspace_bytes(int32_t n_in, int32_t kv, int32_t n_out_cap) {
 int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom* g, void* workspace,
                           size_t workspace_bytes, int32_t* out_coords, int32_t out_cap, int32_t* n_out_host,
                           void* stream) {
-  if (!in_coords || !g || !out_coords || !n_out_host || n_in < 0 || out_cap < 0) return PCE_ERR_INVALID;
+  if (!g || !n_out_host || n_in < 0 || out_cap < 0) return PCE_ERR_INVALID;
+  if (n_in > 0 && (!in_coords || !out_coords)) return PCE_ERR_INVALID;
   for (int i = 0; i < 3; ++i)
     if (g->ks[i] < 1 || g->stride[i] < 1) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

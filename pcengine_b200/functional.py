@@ -202,6 +202,8 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
     elif tuple(out.shape) != (csr.n_rows, c_out) or out.dtype != feats.dtype or not out.is_contiguous():
         raise ValueError("`out` must be a contiguous [n_rows, C_out] tensor in the features' dtype")
+    if csr.n_rows == 0:  # nothing to compute: an empty tensor stays empty
+        return out[:, :c_out_true] if padded else out
     packed = packed_weights(kernel) if kernel_choice != "simt" else None
     rec = None
     if PROFILE is not None:

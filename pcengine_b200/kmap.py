@@ -60,7 +60,9 @@ class NeighbourCSR:
     def order(self):
         """Output rows sorted by indicator bitmask (int32 [n_rows], built once): the order in which
         the tensor-core kernel forms its 128-row tiles."""
-        if self._order is None and self.kv is not None and self.n_rows > 0:
+        if self._order is None and self.n_rows == 0:
+            self._order = torch.empty((0,), dtype=torch.int32, device=self.mask.device)
+        if self._order is None and self.kv is not None:
             dev = self.mask.device
             out = torch.empty((self.n_rows,), dtype=torch.int32, device=dev)
             ws = _lib.workspace(64 * self.n_rows + (16 << 20), dev)

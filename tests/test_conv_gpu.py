@@ -401,3 +401,50 @@ def test_explicit_dataflow_d1(dtype, cin, cout):
     assert co.rel_l2(z.feats.float().cpu(), refz) <= tol
     refu = co.conv_forward(z.feats.cpu(), up.kernel.detach().cpu(), d2s, transposed=True)
     assert co.rel_l2(u.feats.float().cpu(), refu) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_empty_and_tiny_tensors(dtype):
+    """Zero voxels, one voxel and voxels without neighbours go through the same operators: an empty
+    tensor stays empty with the right width, a lone voxel only sees the centre weight."""
+    import pcengine_b200 as pce
+    conv = pce.conv3d(16, 32, 3).cuda().to(dtype)
+    down = pce.conv3d(32, 32, 2, 2).cuda().to(dtype)
+    up = pce.conv3d(32, 16, 2, 2, transposed=True).cuda().to(dtype)
+    for coords in (np.zeros((0, 4), np.int32), np.array([[0, 5, 5, 5]], np.int32),
+                   np.array([[0, 0, 0, 0], [0, 9, 9, 9], [1, 0, 0, 0], [1, 20, 3, 7]], np.int32)):
+        n = len(coords)
+        feats = torch.randn(n, 16).to(dtype)
+        x = pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], [31, 31, 31], init_tag=["auto"])
+        y = conv(x)
+        assert y.feats.shape == (n, 32)
+        z = down(y)
+        u = up(z)
+        assert u.feats.shape == (n, 16) and z.feats.shape[1] == 32
+        if n:
+            want = feats.float() @ conv.kernel.detach().float().cpu()[13]  # isolated voxels: the centre offset only
+            assert co.rel_l2(y.feats.float().cpu(), want) <= TOL[dtype]
+            d2 = ko.build_d2(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], [31, 31, 31], False)
+            assert np.array_equal(z.coords.cpu().numpy(), d2["out_coords"])
+
+
+def test_negative_coordinates_and_large_batch_index():
+    """Coordinates below zero (with matching bounds) and a batch index in the hundreds pack into the
+    64-bit keys like any other; maps and features match the oracle."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    rng = np.random.default_rng(8)
+    xyz = rng.integers(-12, 13, (4000, 3))
+    coords = np.unique(np.concatenate([rng.choice([0, 7, 300], (4000, 1)), xyz], axis=1), axis=0).astype(np.int32)
+    cmin, cmax = [-12, -12, -12], [12, 12, 12]
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), cmin, cmax, True)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), cmin, cmax, True)
+    assert np.array_equal(km.map.cpu().numpy(), d2["map"].reshape(-1))
+    feats = torch.randn(len(coords), 32).half()
+    w = (torch.randn(27, 32, 32) / 30).half()
+    out = PF.conv_forward(feats.cuda(), w.cuda(), km.csr())
+    assert co.rel_l2(out.float().cpu(), co.conv_forward(feats, w, d2)) <= 1e-3
+    ds = ko.build_d2(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), cmin, cmax, False)  # derives the output bound
+    kd = pce.KernelMap(torch.from_numpy(coords).cuda(), (2, 2, 2), (2, 2, 2), (0, 0, 0), cmin, ds["cmax_out"], False)
+    assert np.array_equal(kd.out_coords.cpu().numpy(), ds["out_coords"])
+    assert np.array_equal(kd.map.cpu().numpy(), ds["map"].reshape(-1))

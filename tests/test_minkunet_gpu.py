@@ -198,3 +198,23 @@ def test_many_live_passes_fall_back_to_lazy_maps():
     with torch.no_grad():
         again = model(x)
     assert type(next(iter(again.kmaps.values()))).__name__ == "PlannedKernelMap"  # storage came back
+
+
+@pytest.mark.parametrize("n", [0, 1, 5])
+def test_network_on_nearly_nothing(n):
+    """The whole network (planner path included) on zero, one and five voxels: shapes hold and the
+    planned run equals the lazy one."""
+    import pcengine_b200 as pce
+    coords = np.array([[0, 3, 3, 3], [0, 3, 3, 4], [0, 20, 20, 20], [1, 3, 3, 3], [1, 40, 2, 9]], np.int32)[:n].reshape(-1, 4)
+    torch.manual_seed(14)
+    feats = torch.randn(n, 4).half().cuda()
+    model = pce.MinkUNet(4, 19, cr=0.25)
+    pce.randomize_batchnorm(model, 8)
+    model = model.half().eval().cuda()
+    outs = []
+    for plan in (True, False):
+        model.plan_ahead = plan
+        x = pce.spTensor(feats, torch.from_numpy(coords).cuda(), None, [0, 0, 0], [63, 63, 63], init_tag=["auto"])
+        with torch.no_grad():
+            outs.append(model(x).feats)
+    assert outs[0].shape == (n, 19) and torch.equal(outs[0], outs[1])
