@@ -1,31 +1,37 @@
 // Fused gather-matmul-scatter on the 5th-generation tensor cores (tcgen05 + tensor
 // memory), fp16 in / fp32 accumulate, output stationary, persistent and warp-specialised.
 //
-// The kernel reads the map as TILE LISTS (built once per kernel map by pce_tile_lists):
-// output rows are taken in bitmask-sorted order in tiles of 128; for every tile the
-// offsets that at least one of its rows has are listed (`stage_kp`), each with the 128
-// input rows to fetch (`stage_nbr`, -1 = this row lacks the offset).  A stage is one
-// (tile, offset); offsets nobody in the tile has cost nothing (the indicator).
+// The kernel reads the map as TILE LISTS (built once per kernel map by pce_build_tile_lists):
+// output rows are taken in sorted order (pce_csr_sort_rows) in tiles of 128 or 256; for every
+// tile the offsets that at least one of its rows has are listed (`stage_kp`), each with the
+// input row to fetch per tile row (`stage_nbr`, -1 = this row lacks the offset).  A stage is one
+// (tile, offset); offsets nobody in the tile has cost nothing (the indicator).  Lists built with
+// the identity stage end every tile with a stage in which each row names itself: there a second
+// operand (a residual block's shortcut) joins the accumulation.
 //
 // One CTA owns a contiguous range of tiles holding about 1/gridDim of the work and
-// streams through that range's stages.  288 threads:
-//   warps 0-3  producers, one thread per tile row: per stage and 64-channel K block they
+// streams through that range's stages.  Threads (SUB = 128-row sub-tiles per tile):
+//   4*SUB producer warps, one thread per tile row: per stage and 64-channel K block they
 //              gather the input rows with 16-byte cp.async (4 rows per warp instruction,
-//              full 128-byte lines, zero-fill for -1) into a 128-byte-swizzled K-major tile;
-//              thread 0 also stages the pre-packed weight block with one bulk async copy
+//              full 128-byte lines, zero-fill for -1) into a 128-byte-swizzled K-major tile and
+//              attach the stage's barrier to the copies (cp.async.mbarrier.arrive.noinc): the
+//              barrier fires when the data has landed, the thread does not wait for it.
+//              Thread 0 also stages the pre-packed weight block with one bulk async copy
 //              (cp.async.bulk, the TMA engine).  Stage indices are read four stages ahead
-//              (coalesced 512-byte reads) into registers that are never moved, so the
-//              loads stay in flight until the stage that uses them.
+//              (coalesced reads) into registers that are never moved, so the loads stay in
+//              flight until the stage that uses them.
 //              Measured on B200 (random 128-byte rows, L2 resident): cp.async sustains more
 //              than 100 GB/s per SM, while TMA tile::gather4 and per-row bulk copies cost
 //              about 43 ns per operation per issuing warp (11 GB/s per SM per warp), so the
 //              row gather stays on cp.async and only the dense weight block uses TMA.
-//   warp  4    one lane issues tcgen05.mma (M=128, N=C_out, K=16) and commits to mbarriers.
-//   warps 5-8  epilogue: tcgen05.ld the finished accumulator, apply
-//              act(acc*scale + shift + residual), convert to fp16, store each row once.
+//   one MMA warp: one lane issues tcgen05.mma (M=128, N=C_out, K=16; one per sub-tile on the
+//              same weight descriptor) and commits to mbarriers.
+//   4 epilogue warps: tcgen05.ld the finished accumulator, apply
+//              act(acc*scale + shift + residual), convert to fp16, store each row once (and, in
+//              the PUSH variant, boundary rows a second time into a neighbouring GPU's halo).
 // Rings: kStages smem stages (afull / bfull / empty mbarriers) that run on across tile
-// boundaries, and two accumulators in tensor memory (accfull / accempty), so the gather of
-// tile i+1, the MMAs of tile i and the stores of tile i-1 overlap.
+// boundaries, and one or two accumulator sets in tensor memory (accfull / accempty); with two,
+// the gather of tile i+1, the MMAs of tile i and the stores of tile i-1 overlap.
 // No atomics, no intermediate buffer in HBM, bit-identical run to run.
 //
 // Every mbarrier wait is bounded (~1 s): when one expires the CTA raises an abort flag,
@@ -228,8 +234,7 @@ __device__ __forceinline__ int tile_at_cost(const int* tile_ptr, int n_tiles, lo
 
 __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return tile_ptr ? __ldg(tile_ptr + t) : t; }
 
-// kStages = depth of the smem stage ring (a template parameter because cp.async.wait_group
-// takes an immediate).  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
+// kStages = depth of the smem stage ring.  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
 // has SUB accumulators and every staged weight block feeds SUB MMAs, which halves the weight
 // traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
 template <int kStages, int SUB, bool PUSH>
