@@ -106,7 +106,12 @@ typedef struct pce_epilogue {
  * A 256-row tile is two 128-row tensor-memory accumulators fed by one staged weight
  * block.  With identity_stage = 1 every tile ends with one more stage, stage_kp = -1, whose
  * entry for a row is the row itself: where pce_epilogue.extra_feats joins the accumulation
- * (a launch without a second operand skips it).  No reference counterpart: it is the CSR-coded map + indicator in the layout
+ * (a launch without a second operand skips it).  With slots = 2 or 4 a stage holds that
+ * many of the tile's offsets (stage_kp[g*slots + q], stage_nbr[(g*slots + q)*tile_rows + r],
+ * unused slots kp = -2): a layer with 32 or 16 input channels fills only half or a quarter
+ * of the kernel's 64-channel K block, so its offsets are taken two or four at a time and the
+ * tile needs half or a quarter of the stages.  pce_conv_fwd takes slots = 64 / c_in for
+ * c_in = 32 or 16, else 1.  No reference counterpart: it is the CSR-coded map + indicator in the layout
  * the tensor-core kernel consumes with coalesced reads. */
 typedef struct pce_tile_lists {
   const int32_t* order;     /* [n_rows] */
@@ -115,6 +120,7 @@ typedef struct pce_tile_lists {
   const int32_t* stage_nbr; /* [stages * tile_rows] */
   int32_t tile_rows;        /* 128 or 256 */
   int32_t identity_stage;   /* 0 or 1 */
+  int32_t slots;            /* offsets per stage: 1, 2 or 4 */
 } pce_tile_lists;
 
 PCE_API const char* pce_strerror(int status);
@@ -263,15 +269,15 @@ PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, 
 
 /* Fills the arrays of a pce_tile_lists from the neighbour CSR and a row order (NULL =
  * natural order) for tiles of tile_rows = 128 or 256 rows.  tile_ptr needs
- * ceil(n_rows/tile_rows)+1 entries; stage_kp / stage_nbr have room for stage_cap stages
- * (tiles*(kv + identity_stage) always suffices; the stage count ends up in tile_ptr[last]).
- * kv <= 128.
+ * ceil(n_rows/tile_rows)+1 entries; stage_kp / stage_nbr have room for stage_cap stages of
+ * `slots` entries each (tiles*(ceil(kv/slots) + identity_stage) always suffices; the stage
+ * count ends up in tile_ptr[last]).  kv <= 128.
  * workspace >= 8*(tiles+1) + 1 MiB bytes. */
 PCE_API int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr,
                                  const int32_t* order, int32_t n_rows, int32_t kv, int32_t tile_rows,
-                                 int32_t identity_stage, void* workspace, size_t workspace_bytes,
-                                 int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr, int32_t stage_cap,
-                                 void* stream);
+                                 int32_t identity_stage, int32_t slots, void* workspace,
+                                 size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                                 int32_t* stage_nbr, int32_t stage_cap, void* stream);
 
 /* Weight re-layout for the tensor-core kernel: per (offset, 64-channel K block) a
  * c_out x 128-byte K-major image with 16-byte chunks XOR-swizzled by the row index
@@ -346,10 +352,13 @@ typedef struct pce_plan_map_spec {
   int32_t submanifold; /* 1: outputs = inputs; 0: the output coordinates form a new level */
   int32_t want_fwd;    /* neighbour CSR of the layer itself (rows = the map's outputs) */
   int32_t want_tr;     /* neighbour CSR of the matching transposed layer (rows = the map's inputs) */
-  /* output widths of the layers that use each CSR on the tensor-core kernel, 0-terminated;
-   * they select the tile heights (pce_tile_rows_for) whose tile lists are prepared */
+  /* widths of the layers that use each CSR on the tensor-core kernel, c_out 0-terminated;
+   * c_out selects the tile height (pce_tile_rows_for) and c_in the offsets per stage (64/c_in
+   * for 16 or 32 input channels, else 1) of the tile lists that are prepared */
   int32_t c_out_fwd[PCE_PLAN_MAX_USES];
   int32_t c_out_tr[PCE_PLAN_MAX_USES];
+  int32_t c_in_fwd[PCE_PLAN_MAX_USES];
+  int32_t c_in_tr[PCE_PLAN_MAX_USES];
 } pce_plan_map_spec;
 
 typedef struct pce_planned_csr {
@@ -357,8 +366,10 @@ typedef struct pce_planned_csr {
   const int32_t* rowptr;
   const int32_t* nbr;
   int32_t n_rows, n_src, nbr_cap;
-  pce_tile_lists tiles128, tiles256; /* tile_rows == 0: not prepared; the forward lists of a
-                                      * submanifold map carry the identity stage */
+  int32_t n_lists;
+  pce_tile_lists lists[PCE_PLAN_MAX_USES]; /* distinct (tile_rows, slots) among the uses; the
+                                            * forward lists of a submanifold map carry the
+                                            * identity stage */
 } pce_planned_csr;
 
 typedef struct pce_planned_map {

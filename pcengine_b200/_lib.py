@@ -36,7 +36,7 @@ class Geom(C.Structure):
 
 class TileLists(C.Structure):
     _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p),
-                ("tile_rows", C.c_int32), ("identity_stage", C.c_int32)]
+                ("tile_rows", C.c_int32), ("identity_stage", C.c_int32), ("slots", C.c_int32)]
 
 
 PLAN_MAX_USES = 8
@@ -45,12 +45,14 @@ PLAN_MAX_USES = 8
 class PlanMapSpec(C.Structure):
     _fields_ = [("ks", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("pad", C.c_int32 * 3), ("in_level", C.c_int32),
                 ("submanifold", C.c_int32), ("want_fwd", C.c_int32), ("want_tr", C.c_int32),
-                ("c_out_fwd", C.c_int32 * PLAN_MAX_USES), ("c_out_tr", C.c_int32 * PLAN_MAX_USES)]
+                ("c_out_fwd", C.c_int32 * PLAN_MAX_USES), ("c_out_tr", C.c_int32 * PLAN_MAX_USES),
+                ("c_in_fwd", C.c_int32 * PLAN_MAX_USES), ("c_in_tr", C.c_int32 * PLAN_MAX_USES)]
 
 
 class PlannedCSR(C.Structure):
     _fields_ = [("mask", C.c_void_p), ("rowptr", C.c_void_p), ("nbr", C.c_void_p), ("n_rows", C.c_int32),
-                ("n_src", C.c_int32), ("nbr_cap", C.c_int32), ("tiles128", TileLists), ("tiles256", TileLists)]
+                ("n_src", C.c_int32), ("nbr_cap", C.c_int32), ("n_lists", C.c_int32),
+                ("lists", TileLists * PLAN_MAX_USES)]
 
 
 class PlannedMap(C.Structure):
@@ -93,7 +95,7 @@ def _load() -> C.CDLL:
     lib.pce_csr_from_pairs_workspace_bytes.argtypes = [i32, i32]
     lib.pce_conv_fwd.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, C.POINTER(TileLists), i32, vp, i32,
                                  C.POINTER(Epilogue), i32, vp]
-    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
+    lib.pce_build_tile_lists.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, sz, vp, vp, vp, i32, vp]
     lib.pce_csr_sort_rows.argtypes = [vp, i32, i32, vp, sz, vp, vp]
     lib.pce_packed_weights_bytes.restype = sz
     lib.pce_packed_weights_bytes.argtypes = [i32, i32, i32]

@@ -12,8 +12,8 @@ int umma_status_fetch(int* host_status, bool reset);
 extern int umma_force_stages;
 extern int umma_force_sub;
 extern int umma_force_nacc;
-int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
-              void* out, const pce_epilogue* ep, cudaStream_t st);
+int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+              int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
 
 using namespace pce;
@@ -100,7 +100,7 @@ int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* w
     if ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
          reinterpret_cast<uintptr_t>(packed_weights)) & 15)
       return PCE_ERR_INVALID;
-    return conv_umma(in_feats, n_in, packed_weights, tiles, n_out, c_in, c_out, out_feats, ep, st);
+    return conv_umma(in_feats, n_in, packed_weights, kv, tiles, n_out, c_in, c_out, out_feats, ep, st);
   }
   if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1]))
     return PCE_ERR_UNSUPPORTED;  // the second operand and the halo push need the tensor-core kernel
@@ -118,7 +118,7 @@ int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* we
   const bool aligned = ((reinterpret_cast<uintptr_t>(in_feats) | reinterpret_cast<uintptr_t>(out_feats) |
                          reinterpret_cast<uintptr_t>(packed_weights)) & 15) == 0;
   if (packed_weights && aligned && conv_umma_supported(c_in, c_out, dtype))
-    return conv_umma(in_feats, n, packed_weights, nullptr, n, c_in, c_out, out_feats, ep, st);
+    return conv_umma(in_feats, n, packed_weights, 1, nullptr, n, c_in, c_out, out_feats, ep, st);
   if (!weights) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, dtype, ep, true, st);
 }

@@ -10,8 +10,8 @@
 namespace pce {
 
 bool conv_umma_supported(int cin, int cout, int dtype);
-int conv_umma(const void* in, int n_in, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
-              void* out, const pce_epilogue* ep, cudaStream_t st);
+int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+              int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 
 struct EpiDev {
   const float* scale;
@@ -185,8 +185,8 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, const void* 
       k_d1_tile_lists<<<div_up(static_cast<long long>(n_tiles) * 128 + 1, 256), 256, 0, st>>>(qkpos, kv, n_tiles, order,
                                                                                                tile_ptr, stage_kp, stage_nbr);
       PCE_LAUNCH_CHECK();
-      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128, 0};
-      PCE_TRY(conv_umma(bin, qsum, wpacked, &tl, qsum, cin, cout, bout, nullptr, st));
+      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128, 0, 1};
+      PCE_TRY(conv_umma(bin, qsum, wpacked, kv, &tl, qsum, cin, cout, bout, nullptr, st));
     } else {
       if (w == nullptr) return PCE_ERR_INVALID;
       int need = (cout + 3) / 4, g = 1;

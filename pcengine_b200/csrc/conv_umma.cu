@@ -71,6 +71,7 @@ struct Lists {
   const int* stage_kp;   // [stages] offset of every stage
   const int* stage_nbr;  // [stages][tile rows] input row per tile row, -1 absent
   int identity;          // every tile's last stage is the identity stage (stage_kp = -1)
+  const __half* wslots;  // SLOTS > 1: weights as [kv][cout][cin] (one 16-byte chunk row per output channel)
 };
 
 // Second operand: out[row] += in2[row] @ w2, joined to the accumulation at the identity stage.
@@ -214,6 +215,19 @@ __global__ void k_pack_weights(const __half* __restrict__ w, int kv, int cin, in
   }
 }
 
+// Weights [kv][cin][cout] -> [kv][cout][cin]: per offset and output channel the cin input-channel values in a row.
+__global__ void k_pack_weight_slots(const __half* __restrict__ w, int kv, int cin, int cout, __half* __restrict__ out) {
+  const long long total = static_cast<long long>(kv) * cout * cin;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int ci = static_cast<int>(i % cin);
+    const long long t = i / cin;
+    const int co = static_cast<int>(t % cout);
+    const int kp = static_cast<int>(t / cout);
+    out[i] = w[(static_cast<size_t>(kp) * cin + ci) * cout + co];
+  }
+}
+
 // Work of tiles [0, t): their stages plus one unit per tile for its fixed cost (epilogue).
 __device__ __forceinline__ long long cost_before(const int* tile_ptr, int t) {
   return (tile_ptr ? static_cast<long long>(__ldg(tile_ptr + t)) : static_cast<long long>(t)) + t;
@@ -237,8 +251,12 @@ __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return 
 // kStages = depth of the smem stage ring.  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
 // has SUB accumulators and every staged weight block feeds SUB MMAs, which halves the weight
 // traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
-template <int kStages, int SUB, bool PUSH>
-__global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
+// SLOTS = offsets per stage (1, 2, 4): with 32 or 16 input channels an offset fills half or a quarter
+// of the 64-channel K block, so SLOTS offsets of a tile share one ring stage: every row gathers one
+// neighbour per slot into its part of the 128-byte row, and the producers assemble the stage's weight
+// block from the per-offset images with cp.async (covered by the same barrier as the rows).
+template <int kStages, int SUB, bool PUSH, int SLOTS>
+__global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, Second sec, int n_out, int cin,
                 int cout, __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
   extern __shared__ uint8_t smem_raw[];
@@ -300,6 +318,9 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
     const int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
     const int rsub = lane >> 3;  // row inside a 4-row group
     const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
+    int j = 0;  // smem stages issued so far (continuous over tiles)
+    bool ok = true;
+    if constexpr (SLOTS == 1) {
     auto load_stage = [&](int g, int& nid, int& kp) {
       nid = -1;
       kp = 0;
@@ -313,8 +334,6 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
         }
       }
     };
-    int j = 0;  // smem stages issued so far (continuous over tiles)
-    bool ok = true;
     auto run_stage = [&](int nid, int kp) {
       const bool second = kp < 0;  // the identity stage
       const __half* src_base = second ? sec.in2 : in;
@@ -367,6 +386,90 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
       if (g + 3 < g1 && ok) run_stage(nid3, kp3);
       load_stage(g + 7, nid3, kp3);
     }
+    } else {
+    // ---- several offsets per stage (cin = 64 / SLOTS channels each) ----
+    constexpr int kSlotChunks = 8 / SLOTS;  // 16-byte chunks of one slot inside the 128-byte row
+    const int my_slot = chunk / kSlotChunks, my_cc = chunk % kSlotChunks;
+    auto load_stage = [&](int g, int (&nid)[SLOTS], int (&kp)[SLOTS]) {
+#pragma unroll
+      for (int q = 0; q < SLOTS; ++q) {
+        nid[q] = -1;
+        kp[q] = -2;
+        if (g < g1) {
+          nid[q] = __ldg(ls.stage_nbr + (static_cast<size_t>(g) * SLOTS + q) * kRows + tid);
+          kp[q] = __ldg(ls.stage_kp + static_cast<size_t>(g) * SLOTS + q);
+        }
+      }
+    };
+    auto run_stage = [&](const int (&nid)[SLOTS], const int (&kp)[SLOTS]) {
+      const bool second = kp[0] == -1;  // the identity stage: slot 0 only, the second operand's width
+      const int nkb = second ? kblocks2 : 1;
+      for (int kb = 0; kb < nkb; ++kb, ++j) {
+        const int s = j % kStages;
+        const int n = j / kStages;
+        if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) return;
+        const uint32_t a_addr = tiles_addr + s * stage_bytes;
+        const uint32_t b_addr = a_addr + kAStage;
+        if (second) {
+          if (tid == 0) {
+            const uint32_t bbar = smem_u32(&ctl->bfull[s]);
+            mbar_arrive_expect_tx(bbar, b_bytes);
+            bulk_copy_g2s(b_addr, sec.w2 + static_cast<size_t>(kb) * cout * 64, b_bytes, bbar);
+          }
+          const int kchunks = min(8, (sec.cin2 - kb * 64) >> 3);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int r = q * 4 + rsub;
+            const int src_row = __shfl_sync(0xFFFFFFFFu, nid[0], r);
+            if (chunk < kchunks) {
+              const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
+              const __half* src = sec.in2 + (src_row >= 0 ? static_cast<size_t>(src_row) * sec.cin2 + kb * 64 + chunk * 8 : 0);
+              cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+            }
+          }
+        } else {
+          if (tid == 0) mbar_arrive(smem_u32(&ctl->bfull[s]));  // the weights below ride on afull; keep bfull's phase in step
+          // weight block: per slot the offset's [cout][cin] image, chunk by chunk into the swizzled
+          // K-major block; unused slots are zero-filled so that the MMA can always run all K steps
+          const int per_slot = cout * kSlotChunks;
+          for (int c = tid; c < per_slot * SLOTS; c += kRows) {
+            const int q = c / per_slot, e = c - q * per_slot;
+            const int co = e / kSlotChunks, cc = e % kSlotChunks;
+            const int kq = kp[q];
+            const uint32_t dst = b_addr + co * 128 + (((q * kSlotChunks + cc) ^ (co & 7)) << 4);
+            const __half* src = ls.wslots + (kq >= 0 ? (static_cast<size_t>(kq) * cout + co) * cin + cc * 8 : 0);
+            cp_async16(dst, src, kq >= 0 ? 16u : 0u);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int r = q * 4 + rsub;
+            int src_row = -1;
+#pragma unroll
+            for (int u = 0; u < SLOTS; ++u) {
+              const int v = __shfl_sync(0xFFFFFFFFu, nid[u], r);
+              if (u == my_slot) src_row = v;
+            }
+            const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
+            const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + my_cc * 8 : 0);
+            cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+          }
+        }
+        cp_async_arrive_noinc(smem_u32(&ctl->afull[s]));
+      }
+    };
+    // two stages of indices in flight (SLOTS entries each)
+    int nidA[SLOTS], kpA[SLOTS], nidB[SLOTS], kpB[SLOTS];
+    load_stage(g0, nidA, kpA);
+    load_stage(g0 + 1, nidB, kpB);
+    for (int g = g0; g < g1 && ok; g += 2) {
+      run_stage(nidA, kpA);
+      load_stage(g + 2, nidA, kpA);
+      if (g + 1 < g1 && ok) run_stage(nidB, kpB);
+      load_stage(g + 3, nidB, kpB);
+    }
+    }
     cp_async_wait_all();
     if (!ok && tid == 0) {
       // aborting: give this thread's bulk copies a bounded chance to land before the CTA leaves
@@ -404,7 +507,8 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), 1)
           const uint64_t db = make_desc(a_addr + kAStage);
           const bool second = st >= nst_main;
           const int kb = second ? st - nst_main : st % kblocks;
-          const int ksteps = min(4, ((second ? sec.cin2 : cin) - kb * 64) >> 4);
+          // with several offsets per stage the whole 64-channel block is always filled (unused slots with zeros)
+          const int ksteps = (SLOTS > 1 && !second) ? 4 : min(4, ((second ? sec.cin2 : cin) - kb * 64) >> 4);
           for (int k = 0; k < ksteps; ++k) {
 #pragma unroll
             for (int sub = 0; sub < SUB; ++sub) {  // the same weight block feeds every sub-tile
@@ -562,8 +666,11 @@ bool conv_umma_supported(int cin, int cout, int dtype) {
   return dtype == PCE_F16 && cin >= 16 && cin % 16 == 0 && cout >= 16 && cout % 16 == 0 && cout <= 256;
 }
 
+// Per-offset blocks, and for 16 or 32 input channels also the per-offset [cout][cin] images from which
+// stages that hold several offsets assemble their weight block.
 size_t umma_packed_bytes(int kv, int cin, int cout) {
-  return static_cast<size_t>(kv) * ((cin + 63) / 64) * cout * 128;
+  const size_t blocks = static_cast<size_t>(kv) * ((cin + 63) / 64) * cout * 128;
+  return blocks + ((cin == 16 || cin == 32) ? static_cast<size_t>(kv) * cout * cin * 2 : 0);
 }
 
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st) {
@@ -573,6 +680,12 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   umma::k_pack_weights<<<grid, 256, 0, st>>>(static_cast<const __half*>(w), kv, cin, cout, kblocks,
                                              static_cast<__half*>(packed));
   PCE_LAUNCH_CHECK();
+  if (cin == 16 || cin == 32) {
+    const long long n = static_cast<long long>(kv) * cout * cin;
+    umma::k_pack_weight_slots<<<static_cast<int>(std::min<long long>((n + 255) / 256, 148ll * 8)), 256, 0, st>>>(
+        static_cast<const __half*>(w), kv, cin, cout, static_cast<__half*>(packed) + total);
+    PCE_LAUNCH_CHECK();
+  }
   return PCE_OK;
 }
 
@@ -581,17 +694,17 @@ int umma_force_stages = 0;
 int umma_force_sub = 0;
 int umma_force_nacc = 0;
 
-template <int NS, int SUB, bool PUSH>
+template <int NS, int SUB, bool PUSH, int SLOTS>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
                         const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols,
                         int nacc) {
-  umma::k_conv_umma<NS, SUB, PUSH><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
+  umma::k_conv_umma<NS, SUB, PUSH, SLOTS><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
                                                                       nacc);
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
-int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_lists* tiles, int n_out, int cin, int cout,
-              void* out, const pce_epilogue* ep, cudaStream_t st) {
+int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+              int cout, void* out, const pce_epilogue* ep, cudaStream_t st) {
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}};
   if (ep) {
     e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope,
@@ -602,11 +715,19 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
       if (!e.push_slot[s]) e.push_base[s] = nullptr;
     }
   }
-  umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0};
+  umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0, nullptr};
+  int slots = 1;
   umma::Second sec{nullptr, nullptr, 0};
   int sub = umma_force_sub == 1 || umma_force_sub == 2 ? umma_force_sub : 1;
   if (tiles) {
-    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr, tiles->identity_stage ? 1 : 0};
+    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr, tiles->identity_stage ? 1 : 0, nullptr};
+    slots = tiles->slots > 1 ? tiles->slots : 1;
+    if (slots != 1) {
+      // several offsets per stage: the lists must match the layer's width, and the packed weights carry
+      // the per-offset [cout][cin] images behind the per-offset blocks
+      if ((slots != 2 && slots != 4) || cin * slots != 64) return PCE_ERR_INVALID;
+      ls.wslots = static_cast<const __half*>(wpacked) + static_cast<size_t>(kv) * cout * 64;
+    }
     if (tiles->tile_rows != 128 && tiles->tile_rows != 256) return PCE_ERR_INVALID;
     sub = tiles->tile_rows / 128;  // the lists fix the tile height
   }
@@ -620,15 +741,19 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
   const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
-  static int regs_per_thread[2][2] = {{72, 72}, {80, 80}};  // [push][sub-1], allocation units of 8; read back at set-up
+  // registers per thread by kernel variant (plain, push, 2 slots, 4 slots) and sub-tile count, in
+  // allocation units of 8; read back from the compiled kernels at set-up
+  static int regs_per_thread[4][2] = {{72, 72}, {80, 80}, {80, 80}, {96, 88}};
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
   if (sm_count[dev] == 0) {
     const int cap = 227 * 1024;
 #define PCE_SET_SMEM(NS, SB) \
-  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); \
-  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); \
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));  \
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); \
+  PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
     PCE_SET_SMEM(4, 1);
     PCE_SET_SMEM(3, 1);
     PCE_SET_SMEM(2, 1);
@@ -637,14 +762,17 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
     PCE_SET_SMEM(2, 2);
 #undef PCE_SET_SMEM
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1, false>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[0][0] = (fa.numRegs + 7) / 8 * 8;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2, false>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[0][1] = (fa.numRegs + 7) / 8 * 8;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 1, true>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[1][0] = (fa.numRegs + 7) / 8 * 8;
-    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<2, 2, true>) == cudaSuccess && fa.numRegs > 0)
-      regs_per_thread[1][1] = (fa.numRegs + 7) / 8 * 8;
+#define PCE_REGS(V, SB, KERNEL) \
+  if (cudaFuncGetAttributes(&fa, KERNEL) == cudaSuccess && fa.numRegs > 0) regs_per_thread[V][SB - 1] = (fa.numRegs + 7) / 8 * 8
+    PCE_REGS(0, 1, (umma::k_conv_umma<2, 1, false, 1>));
+    PCE_REGS(0, 2, (umma::k_conv_umma<2, 2, false, 1>));
+    PCE_REGS(1, 1, (umma::k_conv_umma<2, 1, true, 1>));
+    PCE_REGS(1, 2, (umma::k_conv_umma<2, 2, true, 1>));
+    PCE_REGS(2, 1, (umma::k_conv_umma<2, 1, false, 2>));
+    PCE_REGS(2, 2, (umma::k_conv_umma<2, 2, false, 2>));
+    PCE_REGS(3, 1, (umma::k_conv_umma<2, 1, false, 4>));
+    PCE_REGS(3, 2, (umma::k_conv_umma<2, 2, false, 4>));
+#undef PCE_REGS
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -656,7 +784,10 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   // with one accumulator set 146 us, 2 x 3 with two sets 159 us; C=128: 115 vs 122 us), and at equal
   // CTAs two accumulator sets win (the epilogue of a tile then overlaps the next tile's MMAs).
   const int threads = 32 * (4 * sub + 5);
-  const int by_regs = 65536 / (threads * regs_per_thread[(e.push_slot[0] || e.push_slot[1]) ? 1 : 0][sub - 1]);
+  const bool push = e.push_slot[0] || e.push_slot[1];
+  if (push && slots != 1) return PCE_ERR_UNSUPPORTED;  // the halo push has no several-offsets-per-stage variant
+  const int variant = push ? 1 : (slots == 2 ? 2 : (slots == 4 ? 3 : 0));
+  const int by_regs = 65536 / (threads * regs_per_thread[variant][sub - 1]);
   auto tmem_for = [&](int sets) {
     int cols = 32;
     while (cols < sets * sub * cout) cols <<= 1;
@@ -693,13 +824,16 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, const pce_tile_
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
-  const bool push = e.push_slot[0] || e.push_slot[1];  // (its variant needs more registers: fewer CTAs fit)
 #define PCE_GO(NS, SB)                                                                                              \
   do {                                                                                                              \
-    if (push)                                                                                                       \
-      launch_umma<NS, SB, true>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);   \
-    else                                                                                                            \
-      launch_umma<NS, SB, false>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);  \
+    if (push)                                                                                                         \
+      launch_umma<NS, SB, true, 1>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);  \
+    else if (slots == 2)                                                                                              \
+      launch_umma<NS, SB, false, 2>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc); \
+    else if (slots == 4)                                                                                              \
+      launch_umma<NS, SB, false, 4>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc); \
+    else                                                                                                              \
+      launch_umma<NS, SB, false, 1>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc); \
   } while (0)
   if (sub == 1) {
     if (ns == 4) PCE_GO(4, 1); else if (ns == 3) PCE_GO(3, 1); else PCE_GO(2, 1);

@@ -511,10 +511,13 @@ __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const i
 //                 stage_nbr[(base+s)*rows + r] = the row's input at that offset, or -1.
 //   identity: every tile ends with one more stage, stage_kp = -1, whose entry for a row is the row
 //   itself: the place where a second operand indexed like the output joins the accumulation.
+//   slots (1, 2 or 4): offsets per stage.  A layer with 32 (16) input channels fills only half (a
+//   quarter) of the kernel's 64-channel K block, so 2 (4) of a tile's offsets share one stage:
+//   stage_kp[g*slots + q] and stage_nbr[(g*slots + q)*rows + r]; unused slots hold kp = -2, nbr = -1.
 template <bool FILL>
 __global__ void __launch_bounds__(256)
     k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
-                 const int* __restrict__ order, int n_rows, int words, int identity, int* tile_cnt,
+                 const int* __restrict__ order, int n_rows, int words, int identity, int slots, int* tile_cnt,
                  const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
   __shared__ uint32_t wmask[8][4];
   const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
@@ -538,7 +541,7 @@ __global__ void __launch_bounds__(256)
     cnt += __popc(tm[w]);
   }
   if (!FILL) {
-    if (r == 0) tile_cnt[t] = cnt + (identity ? 1 : 0);
+    if (r == 0) tile_cnt[t] = (cnt + slots - 1) / slots + (identity ? 1 : 0);
     return;
   }
   const int base = __ldg(tile_ptr + t);
@@ -551,19 +554,31 @@ __global__ void __launch_bounds__(256)
       m &= m - 1;
       int v = -1;
       if ((my[w] >> bit) & 1u) v = __ldg(nbr + cursor++);
-      const int g = base + s;
+      const int g = base + s / slots;
       if (g < stage_cap) {
-        stage_nbr[static_cast<size_t>(g) * rows + r] = v;
-        if (r == 0) stage_kp[g] = w * 32 + bit;
+        const size_t e = static_cast<size_t>(g) * slots + s % slots;
+        stage_nbr[e * rows + r] = v;
+        if (r == 0) stage_kp[e] = w * 32 + bit;
       }
       ++s;
     }
   }
-  if (identity) {
-    const int g = base + s;
+  for (; s % slots; ++s) {  // unused slots of the last stage
+    const int g = base + s / slots;
     if (g < stage_cap) {
-      stage_nbr[static_cast<size_t>(g) * rows + r] = row;
-      if (r == 0) stage_kp[g] = -1;
+      const size_t e = static_cast<size_t>(g) * slots + s % slots;
+      stage_nbr[e * rows + r] = -1;
+      if (r == 0) stage_kp[e] = -2;
+    }
+  }
+  if (identity) {
+    const int g = base + s / slots;
+    if (g < stage_cap) {
+      for (int q = 0; q < slots; ++q) {
+        const size_t e = static_cast<size_t>(g) * slots + q;
+        stage_nbr[e * rows + r] = q == 0 ? row : -1;
+        if (r == 0) stage_kp[e] = q == 0 ? -1 : -2;
+      }
     }
   }
 }
@@ -895,11 +910,12 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
 }
 
 int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, const int32_t* order,
-                         int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, void* workspace,
-                         size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp, int32_t* stage_nbr,
-                         int32_t stage_cap, void* stream) {
+                         int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, int32_t slots,
+                         void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                         int32_t* stage_nbr, int32_t stage_cap, void* stream) {
   if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
   if (tile_rows != 128 && tile_rows != 256) return PCE_ERR_INVALID;
+  if (slots != 1 && slots != 2 && slots != 4) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_tiles = div_up(n_rows, tile_rows);
   if (n_tiles == 0) {
@@ -912,11 +928,12 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
   int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
-  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, cnt, nullptr, nullptr, nullptr, 0);
+  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
+                                                     cnt, nullptr, nullptr, nullptr, 0);
   PCE_LAUNCH_CHECK();
   PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
-  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, nullptr, tile_ptr, stage_kp,
-                                              stage_nbr, stage_cap);
+  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
+                                                    nullptr, tile_ptr, stage_kp, stage_nbr, stage_cap);
   PCE_LAUNCH_CHECK();
   return PCE_OK;
 }

@@ -185,7 +185,8 @@ static void fill_geom(const pce_plan_map_spec& sp, const int32_t* cmin, const in
 
 // One direction of a map: neighbour CSR, row order and the requested tile lists.
 static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* table, int kv, int n_rows, int n_src, int reverse,
-                     int ident, size_t nbr_cap, const int32_t* c_outs, int identity_stage, pce_planned_csr* out) {
+                     int ident, size_t nbr_cap, const int32_t* c_outs, const int32_t* c_ins, int identity_stage,
+                     pce_planned_csr* out) {
   cudaStream_t st = l->stream;
   const int words = (kv + 31) / 32;
   uint32_t* mask = ps->take_n<uint32_t>(static_cast<size_t>(n_rows > 0 ? n_rows : 1) * words);
@@ -202,29 +203,37 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
   out->n_rows = n_rows;
   out->n_src = n_src;
   out->nbr_cap = static_cast<int32_t>(nbr_cap);
-  out->tiles128 = pce_tile_lists{nullptr, nullptr, nullptr, nullptr, 0, 0};
-  out->tiles256 = pce_tile_lists{nullptr, nullptr, nullptr, nullptr, 0, 0};
-  bool want[2] = {false, false};
-  for (int u = 0; u < PCE_PLAN_MAX_USES && c_outs[u] > 0; ++u)
-    want[tile_rows_policy(n_rows, c_outs[u], p->sm_count) == 256 ? 1 : 0] = true;
-  if ((!want[0] && !want[1]) || kv > 128 || n_rows == 0) return PCE_OK;
+  out->n_lists = 0;
+  // the distinct (tile height, offsets per stage) among the uses
+  int want_rows[PCE_PLAN_MAX_USES], want_slots[PCE_PLAN_MAX_USES], n_want = 0;
+  for (int u = 0; u < PCE_PLAN_MAX_USES && c_outs[u] > 0; ++u) {
+    const int rows = tile_rows_policy(n_rows, c_outs[u], p->sm_count);
+    const int slots = c_ins[u] == 32 ? 2 : (c_ins[u] == 16 ? 4 : 1);
+    bool seen = false;
+    for (int v = 0; v < n_want; ++v) seen = seen || (want_rows[v] == rows && want_slots[v] == slots);
+    if (!seen) {
+      want_rows[n_want] = rows;
+      want_slots[n_want] = slots;
+      ++n_want;
+    }
+  }
+  if (n_want == 0 || kv > 128 || n_rows == 0) return PCE_OK;
   int32_t* order = ps->take_n<int32_t>(n_rows);
   if (!order) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
   PCE_TRY(scratch_for(l, 64 * static_cast<size_t>(n_rows) + (16u << 20), &ws));
   PCE_TRY(pce_csr_sort_rows(mask, n_rows, kv, ws, l->scratch_cap, order, st));
-  for (int h = 0; h < 2; ++h) {
-    if (!want[h]) continue;
-    const int rows = h ? 256 : 128;
+  for (int h = 0; h < n_want; ++h) {
+    const int rows = want_rows[h], slots = want_slots[h];
     const int n_tiles = div_up(n_rows, rows);
-    const size_t cap = static_cast<size_t>(n_tiles) * (kv + (identity_stage ? 1 : 0));
+    const size_t cap = static_cast<size_t>(n_tiles) * ((kv + slots - 1) / slots + (identity_stage ? 1 : 0));
     int32_t* tile_ptr = ps->take_n<int32_t>(static_cast<size_t>(n_tiles) + 1);
-    int32_t* stage_kp = ps->take_n<int32_t>(cap);
-    int32_t* stage_nbr = ps->take_n<int32_t>(cap * rows);
+    int32_t* stage_kp = ps->take_n<int32_t>(cap * slots);
+    int32_t* stage_nbr = ps->take_n<int32_t>(cap * slots * rows);
     if (!tile_ptr || !stage_kp || !stage_nbr) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
     PCE_TRY(scratch_for(l, 8 * (static_cast<size_t>(n_tiles) + 1) + (1u << 20), &ws));
-    PCE_TRY(pce_build_tile_lists(mask, rowptr, nbr, order, n_rows, kv, rows, identity_stage, ws, l->scratch_cap, tile_ptr,
-                                 stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
-    (h ? out->tiles256 : out->tiles128) = pce_tile_lists{order, tile_ptr, stage_kp, stage_nbr, rows, identity_stage};
+    PCE_TRY(pce_build_tile_lists(mask, rowptr, nbr, order, n_rows, kv, rows, identity_stage, slots, ws, l->scratch_cap,
+                                 tile_ptr, stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
+    out->lists[out->n_lists++] = pce_tile_lists{order, tile_ptr, stage_kp, stage_nbr, rows, identity_stage, slots};
   }
   return PCE_OK;
 }
@@ -327,12 +336,12 @@ static int build_map(pce_plan* p, PlanLane* l, pce_pass* ps, int i) {
     // output-major table: the map itself read with kp reversed when symmetric, else map_out
     // residual blocks live on submanifold maps: their lists carry the identity stage
     PCE_TRY(build_csr(p, l, ps, symmetric ? map : map_out, kv, n_out, n_in, symmetric ? 1 : 0, ident, cap_nbr,
-                      sp.c_out_fwd, sp.submanifold ? 1 : 0, &out.fwd));
+                      sp.c_out_fwd, sp.c_in_fwd, sp.submanifold ? 1 : 0, &out.fwd));
     out.has_fwd = 1;
   }
   if (sp.want_tr) {
     // roles swapped: the input-major table is the output-major one of the transposed layer
-    PCE_TRY(build_csr(p, l, ps, map, kv, n_in, n_out, 0, ident, cap_nbr, sp.c_out_tr, 0, &out.tr));
+    PCE_TRY(build_csr(p, l, ps, map, kv, n_in, n_out, 0, ident, cap_nbr, sp.c_out_tr, sp.c_in_tr, 0, &out.tr));
     out.has_tr = 1;
   }
   PCE_CUDA(cudaEventRecord(ps->ready[i], st));

@@ -21,6 +21,8 @@ PROFILE = None
 SORT_ROWS = True
 # Rows per tile of the tensor-core kernel: 128, 256, or None for the automatic choice.
 TILE_ROWS = None
+# Take the offsets of layers with 16 / 32 input channels four / two per stage (scheduling only).
+PACK_OFFSETS = True
 
 
 class FusedEpilogue:
@@ -76,6 +78,14 @@ class FusedEpilogue:
                     raise ValueError("push_slots must be contiguous int32 CUDA tensors with one entry per output row")
                 e.push_slot[s], e.push_base[s] = slots.data_ptr(), int(base)
         return e
+
+
+def stage_slots(c_in: int) -> int:
+    """Offsets per stage of the tile lists a layer with ``c_in`` (padded) input channels uses: a
+    16- or 32-channel offset fills a quarter or half of the kernel's 64-channel K block."""
+    if not PACK_OFFSETS:
+        return 1
+    return 4 if c_in == 16 else (2 if c_in == 32 else 1)
 
 
 def supports_second_operand(dtype, c_in: int, c_out: int, c2: int) -> bool:
@@ -216,7 +226,8 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         rec["start"].record()
     tiles = None
     if packed is not None:
-        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device), second))
+        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device), second,
+                                  stage_slots(c_in)))
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),

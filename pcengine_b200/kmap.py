@@ -71,16 +71,17 @@ class NeighbourCSR:
             self._order = out
         return self._order
 
-    def tiles(self, sort_rows: bool = True, tile_rows: int | None = None, identity: bool = False):
+    def tiles(self, sort_rows: bool = True, tile_rows: int | None = None, identity: bool = False, slots: int = 1):
         """The map as tile lists (a ``_lib.TileLists`` struct of device pointers) for the
         tensor-core kernel; built once per CSR, ordering, tile height and ``identity`` (every tile
-        ends with the stage where a second operand joins), kept alive with it.  A request without
-        ``identity`` is also served by lists that have the stage: the kernel skips it."""
+        ends with the stage where a second operand joins) and ``slots`` (offsets per stage: 64 / C_in
+        for layers with 16 or 32 input channels), kept alive with it.  A request without ``identity``
+        is also served by lists that have the stage: the kernel skips it."""
         tile_rows = int(tile_rows or TILE_ROWS)
-        key = (bool(sort_rows), tile_rows, bool(identity))
+        key = (bool(sort_rows), tile_rows, bool(identity), int(slots))
         hit = self._tiles.get(key)
         if hit is None and not identity:
-            hit = self._tiles.get((bool(sort_rows), tile_rows, True))
+            hit = self._tiles.get((bool(sort_rows), tile_rows, True, int(slots)))
         if hit is not None:
             return hit[0]
         dev = self.mask.device
@@ -89,18 +90,19 @@ class NeighbourCSR:
             order = self.order()
         else:
             order = torch.arange(self.n_rows, dtype=torch.int32, device=dev)
-        cap = max(1, n_tiles * (self.kv + (1 if identity else 0)))
+        cap = max(1, n_tiles * ((self.kv + slots - 1) // slots + (1 if identity else 0)))
         tile_ptr = torch.empty((n_tiles + 1,), dtype=torch.int32, device=dev)
-        stage_kp = torch.empty((cap,), dtype=torch.int32, device=dev)
-        stage_nbr = torch.empty((cap * tile_rows,), dtype=torch.int32, device=dev)
+        stage_kp = torch.empty((cap * slots,), dtype=torch.int32, device=dev)
+        stage_nbr = torch.empty((cap * slots * tile_rows,), dtype=torch.int32, device=dev)
         ws = _lib.workspace(8 * (n_tiles + 1) + (1 << 20), dev)
         _lib.check(lib.pce_build_tile_lists(self.mask.data_ptr(), self.rowptr.data_ptr(), self.nbr.data_ptr(),
-                                            order.data_ptr(), self.n_rows, self.kv, tile_rows, 1 if identity else 0, ws.data_ptr(),
+                                            order.data_ptr(), self.n_rows, self.kv, tile_rows, 1 if identity else 0, int(slots),
+                                            ws.data_ptr(),
                                             ws.numel(),
                                             tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(), cap,
                                             _lib.stream_ptr(dev)), "pce_build_tile_lists")
         st = _lib.TileLists(order.data_ptr(), tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(),
-                            tile_rows, 1 if identity else 0)
+                            tile_rows, 1 if identity else 0, int(slots))
         self._tiles[key] = (st, order, tile_ptr, stage_kp, stage_nbr)
         return st
 

@@ -139,6 +139,7 @@ class MinkUNet(nn.Module):
         super().__init__()
         cs = [int(cr * c) for c in (32, 32, 64, 128, 256, 256, 128, 96, 96)]
         self.widths = cs
+        self.in_channels = in_channels
         self.stem = nn.Sequential(ConvBNReLU(in_channels, cs[0], 3), ConvBNReLU(cs[0], cs[0], 3))
         self.down = nn.ModuleList()
         self.enc = nn.ModuleList()
@@ -158,11 +159,13 @@ class MinkUNet(nn.Module):
         """The convolutions in forward order as (kernel_size, stride, transposed, C_in, C_out), one
         entry per distinct use of a kernel map (what :class:`MapPlan` takes)."""
         cs = self.widths
-        plan = [(3, 1, False, cs[0], cs[0])]
+        skips = [cs[3], cs[2], cs[1], cs[0]]
+        plan = [(3, 1, False, self.in_channels, cs[0]), (3, 1, False, cs[0], cs[0])]
         for i in range(4):
-            plan += [(2, 2, False, cs[i], cs[i]), (3, 1, False, cs[i], cs[i + 1])]
+            plan += [(2, 2, False, cs[i], cs[i]), (3, 1, False, cs[i], cs[i + 1]), (3, 1, False, cs[i + 1], cs[i + 1])]
         for i in range(4):
-            plan += [(2, 2, True, cs[4 + i], cs[5 + i]), (3, 1, False, cs[5 + i], cs[5 + i])]
+            plan += [(2, 2, True, cs[4 + i], cs[5 + i]), (3, 1, False, cs[5 + i] + skips[i], cs[5 + i]),
+                     (3, 1, False, cs[5 + i], cs[5 + i])]
         return plan
 
     # Hand the kernel maps of a pass to the library's planning thread (eval mode, CUDA) instead of

@@ -120,16 +120,17 @@ class PlannedKernelMap(KernelMap):
             csr = NeighbourCSR(_DevArray(c.mask, (max(c.n_rows, 1), words), device, keep),
                                _DevArray(c.rowptr, (c.n_rows + 1,), device, keep),
                                _DevArray(c.nbr, (c.nbr_cap,), device, keep), int(c.n_rows), int(c.n_src), kv)
-            for t in (c.tiles128, c.tiles256):
-                if t.tile_rows:
-                    lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows, t.identity_stage)
-                    n_tiles = (csr.n_rows + t.tile_rows - 1) // t.tile_rows
-                    csr._order = _DevArray(t.order, (csr.n_rows,), device, keep)
-                    stages = n_tiles * (kv + int(t.identity_stage))
-                    csr._tiles[(True, int(t.tile_rows), bool(t.identity_stage))] = (
-                        lists, csr._order, _DevArray(t.tile_ptr, (n_tiles + 1,), device, keep),
-                        _DevArray(t.stage_kp, (stages,), device, keep),
-                        _DevArray(t.stage_nbr, (stages * t.tile_rows,), device, keep))
+            for i in range(c.n_lists):
+                t = c.lists[i]
+                slots = max(int(t.slots), 1)
+                lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows, t.identity_stage, slots)
+                n_tiles = (csr.n_rows + t.tile_rows - 1) // t.tile_rows
+                csr._order = _DevArray(t.order, (csr.n_rows,), device, keep)
+                entries = n_tiles * ((kv + slots - 1) // slots + int(t.identity_stage)) * slots
+                csr._tiles[(True, int(t.tile_rows), bool(t.identity_stage), slots)] = (
+                    lists, csr._order, _DevArray(t.tile_ptr, (n_tiles + 1,), device, keep),
+                    _DevArray(t.stage_kp, (entries,), device, keep),
+                    _DevArray(t.stage_nbr, (entries * t.tile_rows,), device, keep))
             self._csr[transposed] = csr
 
 
@@ -202,9 +203,9 @@ class MapPlan:
                 self.specs.append(spec)
             spec = self.specs[self.index[key]]
             uses = spec["tr" if transposed else "fwd"]
-            wide = PF._ceil16(c_out)
-            if wide not in uses and len(uses) < _lib.PLAN_MAX_USES - 1:
-                uses.append(wide)
+            use = (PF._ceil16(c_out), PF._ceil16(c_in))
+            if use not in uses and len(uses) < _lib.PLAN_MAX_USES - 1:
+                uses.append(use)
             cur = out_stride
         if not self.specs:
             raise ValueError("MapPlan: no layer needs a kernel map")
@@ -222,10 +223,10 @@ class MapPlan:
             c.in_level, c.submanifold = s["in_level"], 1 if s["subm"] else 0
             c.want_fwd, c.want_tr = (1 if s["fwd"] else 0), (1 if s["tr"] else 0)
             for name in ("fwd", "tr"):
-                dst = c.c_out_fwd if name == "fwd" else c.c_out_tr
-                widths = [w for w in s[name] if tensor_cores and w <= 256]
-                for i, w in enumerate(widths):
-                    dst[i] = w
+                dst_out, dst_in = (c.c_out_fwd, c.c_in_fwd) if name == "fwd" else (c.c_out_tr, c.c_in_tr)
+                widths = [u for u in s[name] if tensor_cores and u[0] <= 256]
+                for i, (w_out, w_in) in enumerate(widths):
+                    dst_out[i], dst_in[i] = w_out, (w_in if PF.PACK_OFFSETS else 0)
         return arr
 
     def _handle_for(self, device) -> int:

@@ -88,14 +88,16 @@ def test_map_plan_specs_of_the_unet():
     assert [s["subm"] for s in plan.specs] == [True, False, True, False, True, False, True, False, True]
     assert [s["in_level"] for s in plan.specs] == [0, 0, 1, 1, 2, 2, 3, 3, 4]
     assert [s["out_level"] for s in plan.specs] == [0, 1, 1, 2, 2, 3, 3, 4, 4]
-    assert plan.specs[0]["fwd"] == [32, 96] and plan.specs[0]["tr"] == []
-    assert plan.specs[1]["fwd"] == [32] and plan.specs[1]["tr"] == [96]
-    assert plan.specs[8]["fwd"] == [256]
+    # uses are (C_out, C_in) rounded up to the tensor-core granule: the 4-channel stem reads 16
+    assert plan.specs[0]["fwd"] == [(32, 16), (32, 32), (96, 128), (96, 96)] and plan.specs[0]["tr"] == []
+    assert plan.specs[1]["fwd"] == [(32, 32)] and plan.specs[1]["tr"] == [(96, 96)]
+    assert plan.specs[8]["fwd"] == [(256, 128), (256, 256)]
     c = plan._c_specs()
     assert c[1].want_fwd == 1 and c[1].want_tr == 1 and list(c[1].c_out_tr)[:2] == [96, 0]
+    assert list(c[0].c_in_fwd)[:4] == [16, 32, 128, 96]
     assert list(c[0].ks) == [3, 3, 3] and list(c[1].stride) == [2, 2, 2] and c[3].in_level == 1
     ragged = pce.MapPlan([(3, 1, False, 4, 19)], dtype=torch.float32)
-    assert ragged.specs[0]["fwd"] == [32] and list(ragged._c_specs()[0].c_out_fwd)[:1] == [0]  # no tile lists for fp32
+    assert ragged.specs[0]["fwd"] == [(32, 16)] and list(ragged._c_specs()[0].c_out_fwd)[:1] == [0]  # no tile lists for fp32
     import pytest
     with pytest.raises(ValueError):
         pce.MapPlan([(1, 1, False, 8, 8)])

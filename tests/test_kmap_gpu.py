@@ -100,23 +100,27 @@ def test_out_of_range_coordinate_reports_status():
         km.sizes()
 
 
-@pytest.mark.parametrize("ks,sort_rows,tile_rows,identity", [
-    ((3, 3, 3), True, 128, False), ((3, 3, 3), False, 128, False), ((5, 5, 5), True, 128, False), ((2, 2, 2), True, 128, False),
-    ((3, 3, 3), True, 256, False), ((5, 5, 5), False, 256, False), ((3, 3, 3), True, 128, True), ((3, 3, 3), True, 256, True)])
-def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity):
+@pytest.mark.parametrize("ks,sort_rows,tile_rows,identity,slots", [
+    ((3, 3, 3), True, 128, False, 1), ((3, 3, 3), False, 128, False, 1), ((5, 5, 5), True, 128, False, 1),
+    ((2, 2, 2), True, 128, False, 1), ((3, 3, 3), True, 256, False, 1), ((5, 5, 5), False, 256, False, 1),
+    ((3, 3, 3), True, 128, True, 1), ((3, 3, 3), True, 256, True, 1), ((3, 3, 3), True, 128, False, 2),
+    ((3, 3, 3), True, 128, True, 4), ((5, 5, 5), True, 256, True, 2), ((2, 2, 2), False, 128, False, 4)])
+def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity, slots):
     """Tile lists are the oracle's neighbour CSR re-laid: per tile of 128 or 256 rows (in processing
     order) one stage per offset present in the tile, with each row's neighbour at that offset or -1;
-    with ``identity`` one more stage (offset -1) in which every row names itself."""
+    with ``identity`` one more stage (offset -1) in which every row names itself; with ``slots`` > 1 the
+    tile's offsets are taken ``slots`` per stage (unused slots: offset -2, rows -1)."""
     import pcengine_b200 as pce
     coords = surface_cloud(14, 56, batch=2)
     d2 = ko.build_d2(coords, ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     nb = ko.neighbour_csr(d2)
     km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     csr = km.csr()
-    csr.tiles(sort_rows, tile_rows, identity)
-    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows, identity)]
+    csr.tiles(sort_rows, tile_rows, identity, slots)
+    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows, identity, slots)]
     order, tile_ptr = order.cpu().numpy(), tile_ptr.cpu().numpy()
     stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, tile_rows)
+    stage_kp3, stage_nbr3 = stage_kp.reshape(-1, slots), stage_nbr.reshape(-1, slots, tile_rows)
     n, kv = km.n_out, km.kv
     assert np.array_equal(np.sort(order), np.arange(n))
     if not sort_rows:
@@ -135,12 +139,15 @@ def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity):
         a, b = tile_ptr[t], tile_ptr[t + 1]
         if identity:
             b -= 1
-            assert stage_kp[b] == -1 and np.array_equal(stage_nbr[b, :len(rws)], rws)
-            assert (stage_nbr[b, len(rws):] == -1).all()
-        assert np.array_equal(stage_kp[a:b], present)
-        got = stage_nbr[a:b, :len(rws)]
-        assert np.array_equal(got, want[rws][:, present].T)
-        assert (stage_nbr[a:b, len(rws):] == -1).all()
+            assert stage_kp3[b, 0] == -1 and (stage_kp3[b, 1:] == -2).all()
+            assert np.array_equal(stage_nbr3[b, 0, :len(rws)], rws) and (stage_nbr3[b, 0, len(rws):] == -1).all()
+            assert (stage_nbr3[b, 1:] == -1).all()
+        assert b - a == (len(present) + slots - 1) // slots
+        kps = stage_kp3[a:b].reshape(-1)
+        nbrs = stage_nbr3[a:b].reshape(-1, tile_rows)
+        assert np.array_equal(kps[:len(present)], present) and (kps[len(present):] == -2).all()
+        assert np.array_equal(nbrs[:len(present), :len(rws)], want[rws][:, present].T)
+        assert (nbrs[:len(present), len(rws):] == -1).all() and (nbrs[len(present):] == -1).all()
 
 
 @pytest.mark.parametrize("ks", [(3, 3, 3), (5, 5, 5), (4, 4, 4), (2, 2, 2)])
