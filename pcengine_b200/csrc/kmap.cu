@@ -178,31 +178,48 @@ __global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev 
                              int* max_batch) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int kp = blockIdx.y;
-  if (i >= n_in) return;
-  int4 c = __ldg(coords + i);
-  int qx, qy, qz;
-  if (!candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) return;
-  if (!packable(c.x, qx, qy, qz)) {
-    atomicMax(status, PCE_ERR_RANGE);
-    return;
-  }
-  unsigned long long key = pack_key(c.x, qx, qy, qz);
-  bool fresh;
-  unsigned s = table_claim(table, tmask, key, fresh);
-  if (s == 0xFFFFFFFFu) {
-    atomicMax(status, PCE_ERR_TABLE_FULL);
-    return;
-  }
-  if (fresh) {
-    int pos = atomicAdd(counter, 1);
-    if (pos < ucap)  // candidate() keeps q inside [lo, hi], so every field fits its bits
-      ukeys[pos] = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
+  bool fresh = false;
+  unsigned long long sort_key = 0;
+  int batch = 0;
+  if (i < n_in) {
+    int4 c = __ldg(coords + i);
+    int qx, qy, qz;
+    if (candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) {
+      if (!packable(c.x, qx, qy, qz)) {
+        atomicMax(status, PCE_ERR_RANGE);
+      } else {
+        unsigned s = table_claim(table, tmask, pack_key(c.x, qx, qy, qz), fresh);
+        if (s == 0xFFFFFFFFu) {
+          atomicMax(status, PCE_ERR_TABLE_FULL);
+          fresh = false;
+        }
+        // candidate() keeps q inside [lo, hi], so every field fits its bits
+        sort_key = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
                    (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
                    (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
                    static_cast<unsigned long long>(qz - g.lo[2]);
+        batch = c.x;
+      }
+    }
+  }
+  // one append per warp, not per key: the counter is a single address
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned m = __ballot_sync(0xFFFFFFFFu, fresh);
+  if (m == 0) return;
+  const int leader = __ffs(m) - 1;
+  int base = 0;
+  const int wmax = __reduce_max_sync(0xFFFFFFFFu, fresh ? batch : 0);
+  if (static_cast<int>(lane) == leader) {
+    base = atomicAdd(counter, __popc(m));
+    if (wmax > *reinterpret_cast<volatile int*>(max_batch)) atomicMax(max_batch, wmax);
+  }
+  base = __shfl_sync(0xFFFFFFFFu, base, leader);
+  if (fresh) {
+    const int pos = base + __popc(m & ((1u << lane) - 1));
+    if (pos < ucap)
+      ukeys[pos] = sort_key;
     else
       atomicMax(status, PCE_ERR_CAPACITY);
-    if (c.x > *reinterpret_cast<volatile int*>(max_batch)) atomicMax(max_batch, c.x);  // rarely taken: one hot address
   }
 }
 
