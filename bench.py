@@ -419,6 +419,13 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if world > 1 and args.pin:
+        # one share of the host cores per rank: the rank's main thread and the planner's threads stay
+        # off the other ranks' cores
+        cores = sorted(os.sched_getaffinity(0))
+        share = len(cores) // world
+        if share >= 2:
+            os.sched_setaffinity(0, cores[local * share:(local + 1) * share])
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -427,12 +434,16 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x: float) -> float:
+    per_rank = {}
+
+    def max_over_ranks(x: float, name: str) -> float:
         if world == 1:
             return x
         t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        every = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        per_rank[name] = [round(float(v.item()) / args.steps * 1e3, 3) for v in every]
+        return max(float(v.item()) for v in every)
 
     pk = peaks()
     coords_h, feats_h, sizes = make_batch(rank)
@@ -475,7 +486,7 @@ def run_ours(args):
         step(coords_d, feats_d, resident)
     e1.record()
     barrier()
-    dt = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+    dt = max_over_ranks(e0.elapsed_time(e1) * 1e-3, "ms_per_step")
     launches = int(_lib.lib.pce_kernel_launches() - launches0)
     # ---- the same K steps again with a CUDA-event pair around every convolution launch ------
     # (kept out of the loop above: ~80 extra event records per step perturb the headline time)
@@ -529,7 +540,7 @@ def run_ours(args):
     barrier()
     t0 = time.perf_counter()
     serve(args.steps)
-    dt_e2e = max_over_ranks(time.perf_counter() - t0)
+    dt_e2e = max_over_ranks(time.perf_counter() - t0, "e2e_ms_per_step")
     clocks = sampler.stop() if rank == 0 else None
     # ---- roofline of the dominant convolution kernel ---------------------------------------
     by_kernel = {}
@@ -615,6 +626,8 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "clocks": clocks,
     }
+    if world > 1:
+        line["per_rank"] = {**per_rank, "host_cores": len(os.sched_getaffinity(0)), "pinned": bool(args.pin)}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -631,6 +644,8 @@ def main():
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
     ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor"],
                     help="minkunet: batch of 8 LiDAR scans per GPU (default); scene: one 1.5 M-voxel scene in x-slabs")
+    ap.add_argument("--pin", action="store_true",
+                    help="multi-rank runs: give each rank its own share of the host cores")
     ap.add_argument("--lean", action="store_true",
                     help="skip the per-layer table and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
