@@ -96,6 +96,13 @@ typedef struct pce_epilogue {
    * after this launch (a barrier between the GPUs).  Tensor-core kernel only. */
   const int32_t* push_slot[2]; /* [n_out] each, or NULL */
   void* push_base[2];
+  /* Row pitches in elements, 0 = dense (c_in / c_out).  A layer may read its input from, and write
+   * its output into, a column range of a wider row-major matrix (in_feats / out_feats then point at
+   * the first column of the range): the output of an up-sampling layer and the skip features land
+   * side by side in one buffer without a concatenation pass.  Tensor-core kernel only; a pitch must
+   * be a multiple of 8 elements and the pointers 16-byte aligned. */
+  int32_t in_ld;
+  int32_t out_ld;
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output

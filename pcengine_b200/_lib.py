@@ -67,7 +67,8 @@ class Epilogue(C.Structure):
     _fields_ = [("scale", C.c_void_p), ("shift", C.c_void_p), ("residual", C.c_void_p),
                 ("act", C.c_int32), ("slope", C.c_float), ("extra_feats", C.c_void_p),
                 ("extra_packed_weights", C.c_void_p), ("extra_c", C.c_int32),
-                ("push_slot", C.c_void_p * 2), ("push_base", C.c_void_p * 2)]
+                ("push_slot", C.c_void_p * 2), ("push_base", C.c_void_p * 2),
+                ("in_ld", C.c_int32), ("out_ld", C.c_int32)]
 
 
 def _load() -> C.CDLL:

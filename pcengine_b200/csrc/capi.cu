@@ -102,8 +102,9 @@ int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* w
       return PCE_ERR_INVALID;
     return conv_umma(in_feats, n_in, packed_weights, kv, tiles, n_out, c_in, c_out, out_feats, ep, st);
   }
-  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1]))
-    return PCE_ERR_UNSUPPORTED;  // the second operand and the halo push need the tensor-core kernel
+  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1] || (ep->in_ld > 0 && ep->in_ld != c_in) ||
+             (ep->out_ld > 0 && ep->out_ld != c_out)))
+    return PCE_ERR_UNSUPPORTED;  // the second operand, the halo push and row pitches need the tensor-core kernel
   if (!weights || !mask || !rowptr || (n_in > 0 && !nbr)) return PCE_ERR_INVALID;
   return conv_simt(in_feats, weights, mask, rowptr, nbr, n_out, c_in, c_out, kv, out_feats, dtype, ep, false, st);
 }
@@ -120,6 +121,7 @@ int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const void* we
   if (packed_weights && aligned && conv_umma_supported(c_in, c_out, dtype))
     return conv_umma(in_feats, n, packed_weights, 1, nullptr, n, c_in, c_out, out_feats, ep, st);
   if (!weights) return PCE_ERR_INVALID;
+  if (ep && ((ep->in_ld > 0 && ep->in_ld != c_in) || (ep->out_ld > 0 && ep->out_ld != c_out))) return PCE_ERR_UNSUPPORTED;
   return conv_simt(in_feats, weights, nullptr, nullptr, nullptr, n, c_in, c_out, 1, out_feats, dtype, ep, true, st);
 }
 

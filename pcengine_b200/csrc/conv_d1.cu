@@ -220,7 +220,9 @@ extern "C" int pce_conv_fwd_d1(const void* in_feats, int32_t n_in, int32_t c_in,
   if ((!weights && !packed_weights) || !out_feats || !qkpos || !ocsr || !icsr) return PCE_ERR_INVALID;
   if (qsum > 0 && (!imap_coded || !omap_coded || !buffer || !in_feats)) return PCE_ERR_INVALID;
   if (centre_kp >= kv || (centre_kp >= 0 && n_in != n_out)) return PCE_ERR_INVALID;
-  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1])) return PCE_ERR_UNSUPPORTED;
+  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1] || (ep->in_ld > 0 && ep->in_ld != c_in) ||
+             (ep->out_ld > 0 && ep->out_ld != c_out)))
+    return PCE_ERR_UNSUPPORTED;
   const size_t esize = dtype == PCE_F32 ? 4 : 2;
   if (static_cast<size_t>(qsum) * (c_in + c_out) * esize > buffer_bytes) return PCE_ERR_WORKSPACE;
   EpiDev e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f};

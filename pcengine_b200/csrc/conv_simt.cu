@@ -239,7 +239,9 @@ int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dt
   if (n < 0 || c < 1) return PCE_ERR_INVALID;
   if (n == 0) return PCE_OK;
   if (!x || !y) return PCE_ERR_INVALID;
-  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1])) return PCE_ERR_UNSUPPORTED;
+  if (ep && (ep->extra_feats || ep->push_slot[0] || ep->push_slot[1] || (ep->in_ld > 0 && ep->in_ld != c) ||
+             (ep->out_ld > 0 && ep->out_ld != c)))
+    return PCE_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   EpiDev e = to_dev(ep);
   long long total = static_cast<long long>(n) * c;

@@ -63,6 +63,10 @@ struct Epi {
   // of a neighbouring GPU mapped into this process (plain peer stores over NVLink)
   const int* push_slot[2];
   __half* push_base[2];
+  // row pitch of the input and the output features in elements (the channel count when dense): a layer
+  // may read and write a column range of a wider row-major matrix
+  int ld_in;
+  int ld_out;
 };
 
 struct Lists {
@@ -349,6 +353,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
       const bool second = kp < 0;  // the identity stage
       const __half* src_base = second ? sec.in2 : in;
       const int width = second ? sec.cin2 : cin;
+      const int pitch = second ? sec.cin2 : ep.ld_in;
       const int nkb = second ? kblocks2 : kblocks;  // 0: listed, but this launch has no second operand
       for (int kb = 0; kb < nkb; ++kb, ++j) {
         const int s = j % kStages;
@@ -371,7 +376,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
           const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
           if (chunk < kchunks) {
             const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * width + kb * 64 + chunk * 8 : 0);
+            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * pitch + kb * 64 + chunk * 8 : 0);
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
@@ -463,7 +468,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
               if (u == my_slot) src_row = v;
             }
             const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-            const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * cin + my_cc * 8 : 0);
+            const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * ep.ld_in + my_cc * 8 : 0);
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
@@ -575,7 +580,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
       const bool store_row = my_row < n_out;
       const uint32_t taddr = tmem_base + static_cast<uint32_t>((buf * SUB + sub) * cout) +
                              (static_cast<uint32_t>(lane_quarter * 32) << 16);
-      __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * cout;
+      __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * ep.ld_out;
       __half* prow[2] = {nullptr, nullptr};
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
@@ -716,11 +721,14 @@ static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
 int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st) {
-  umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}};
+  umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}, cin, cout};
   if (ep) {
     e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope,
                   {ep->push_slot[0], ep->push_slot[1]},
-                  {static_cast<__half*>(ep->push_base[0]), static_cast<__half*>(ep->push_base[1])}};
+                  {static_cast<__half*>(ep->push_base[0]), static_cast<__half*>(ep->push_base[1])},
+                  ep->in_ld > 0 ? ep->in_ld : cin, ep->out_ld > 0 ? ep->out_ld : cout};
+    // rows stay 16-byte aligned: the pitch is a multiple of 8 halves and covers the channels
+    if (e.ld_in < cin || e.ld_out < cout || (e.ld_in & 7) || (e.ld_out & 7)) return PCE_ERR_INVALID;
     for (int s = 0; s < 2; ++s) {
       if (e.push_slot[s] && (!e.push_base[s] || (reinterpret_cast<uintptr_t>(e.push_base[s]) & 15))) return PCE_ERR_INVALID;
       if (!e.push_slot[s]) e.push_base[s] = nullptr;

@@ -94,8 +94,19 @@ def supports_second_operand(dtype, c_in: int, c_out: int, c2: int) -> bool:
             and c2 >= 16)
 
 
-def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype):
-    return C.byref(ep.pack(c_out, n_out, dtype)) if ep is not None else None
+def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype, in_ld: int = 0, out_ld: int = 0):
+    if ep is None and not in_ld and not out_ld:
+        return None
+    e = ep.pack(c_out, n_out, dtype) if ep is not None else _lib.Epilogue()
+    e.in_ld, e.out_ld = in_ld, out_ld
+    return C.byref(e)
+
+
+def _row_pitched(t: torch.Tensor) -> bool:
+    """A [N, C] fp16 matrix the tensor-core kernel can address in place: rows contiguous, at a pitch
+    that is a multiple of 8 elements, 16-byte aligned (a column range of a wider matrix qualifies)."""
+    return (t.dim() == 2 and t.dtype == torch.float16 and t.stride(1) == 1 and t.stride(0) >= t.size(1)
+            and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0)
 
 
 def packed_weights(kernel: torch.Tensor, as_linear: bool = False) -> Optional[torch.Tensor]:
@@ -187,12 +198,15 @@ def device_status(reset: bool = True) -> int:
 def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, epilogue: Optional[FusedEpilogue] = None,
                  kernel_choice: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fused gather-matmul-scatter over a neighbour CSR; returns [csr.n_rows, C_out] (written into
-    ``out`` when given: a contiguous tensor of that shape and the features' dtype)."""
+    ``out`` when given: a tensor of that shape and the features' dtype).  On the tensor-core path
+    ``feats`` and ``out`` may be column ranges of wider row-major matrices (see :func:`_row_pitched`);
+    they are then read and written in place."""
     _lib.require_cuda(feats, "feats")
     _lib.require_cuda(kernel, "kernel")
     if kernel.dim() == 2:
         kernel = kernel.unsqueeze(0)
-    feats = feats.contiguous()
+    if not _row_pitched(feats):
+        feats = feats.contiguous()
     if not kernel.is_contiguous() or kernel.dtype != feats.dtype:
         kernel = kernel.detach().contiguous().to(feats.dtype)
     if feats.size(1) != kernel.size(1):
@@ -206,15 +220,20 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         raise NotImplementedError("a second operand (FusedEpilogue.extra_feats) needs the tensor-core kernel")
     feats, kernel, epilogue, padded = _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice)
     kv, c_in, c_out = kernel.shape
-    if out is None or padded:
-        if out is not None:
-            raise ValueError("`out` cannot be used with channel counts that need padding")
-        out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
-    elif tuple(out.shape) != (csr.n_rows, c_out) or out.dtype != feats.dtype or not out.is_contiguous():
-        raise ValueError("`out` must be a contiguous [n_rows, C_out] tensor in the features' dtype")
-    if csr.n_rows == 0:  # nothing to compute: an empty tensor stays empty
-        return out[:, :c_out_true] if padded else out
     packed = packed_weights(kernel) if kernel_choice != "simt" else None
+    if packed is None:
+        feats = feats.contiguous()  # row pitches are the tensor-core kernel's
+    given = None
+    if out is not None and (tuple(out.shape) != (csr.n_rows, c_out_true) or out.dtype != feats.dtype):
+        raise ValueError("`out` must be a [n_rows, C_out] tensor in the features' dtype")
+    if out is not None and (padded or (not out.is_contiguous() and (packed is None or not _row_pitched(out)))):
+        given, out = out, None  # computed into a tensor of this function's own, then copied
+    if out is None:
+        out = torch.empty((csr.n_rows, c_out), dtype=feats.dtype, device=feats.device)
+    if csr.n_rows == 0:  # nothing to compute: an empty tensor stays empty
+        return given if given is not None else (out[:, :c_out_true] if padded else out)
+    in_ld = 0 if feats.is_contiguous() else feats.stride(0)
+    out_ld = 0 if out.is_contiguous() else out.stride(0)
     rec = None
     if PROFILE is not None:
         which = _lib.KERNEL_UMMA if packed is not None else _lib.KERNEL_SIMT
@@ -230,12 +249,16 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                                   stage_slots(c_in)))
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
-                                out.data_ptr(), _lib.dtype_code(feats.dtype), _pack(epilogue, c_out, csr.n_rows, feats.dtype),
+                                out.data_ptr(), _lib.dtype_code(feats.dtype),
+                                _pack(epilogue, c_out, csr.n_rows, feats.dtype, in_ld, out_ld),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
         rec["end"].record()
         rec["pairs"] = csr.rowptr[-1:].clone()  # a copy: the record must not keep the map's storage alive
         PROFILE.append(rec)
+    if given is not None:
+        given.copy_(out[:, :c_out_true])
+        return given
     return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
 
 

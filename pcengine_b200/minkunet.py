@@ -12,7 +12,7 @@ modules run.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 from torch import nn
@@ -65,10 +65,11 @@ class ConvBNReLU(_Fusable):
         self.bn = BatchNorm(cout)
         self.relu = ReLU(True)
 
-    def forward(self, x: spTensor) -> spTensor:
+    def forward(self, x: spTensor, out: Optional[torch.Tensor] = None) -> spTensor:
+        """``out`` (fused path only): the tensor the output features are written into."""
         if self._fused(x):
             s, t = self._fold("bn", self.bn)
-            return self.conv(x, epilogue=FusedEpilogue(scale=s, shift=t, act="relu"))
+            return self.conv(x, epilogue=FusedEpilogue(scale=s, shift=t, act="relu"), out=out)
         return self.relu(self.bn(self.conv(x)))
 
 
@@ -90,7 +91,7 @@ class ResidualBlock(_Fusable):
             self.short_conv = None
             self.short_bn = None
 
-    def _one_kernel_tail(self, x: spTensor, y: spTensor) -> spTensor:
+    def _one_kernel_tail(self, x: spTensor, y: spTensor, out: Optional[torch.Tensor] = None) -> spTensor:
         """relu(bn2(conv2(y)) + shortcut(x)) as ONE convolution launch: both BatchNorm scales are
         folded into the weights, and the shortcut (its 1x1x1 convolution, or the identity) enters the
         accumulator as the second operand of conv2."""
@@ -111,9 +112,10 @@ class ResidualBlock(_Fusable):
         ep = FusedEpilogue(shift=shift, act="relu", extra_feats=x.feats.contiguous(), extra_weight=w_extra)
         return conv_func(input=y, in_channel=c2.in_channels, out_channel=c2.out_channels, kernel=w_main,
                          kernel_size_code=c2.kernel_size_code, stride_code=c2.stride_code, padding_code=c2.padding_code,
-                         bias=None, transposed=False, tensorcore=c2.tensorcore, epilogue=ep)
+                         bias=None, transposed=False, tensorcore=c2.tensorcore, epilogue=ep, out=out)
 
-    def forward(self, x: spTensor) -> spTensor:
+    def forward(self, x: spTensor, out: Optional[torch.Tensor] = None) -> spTensor:
+        """``out`` (fused path only): the tensor the block's output features are written into."""
         if self._fused(x):
             s1, t1 = self._fold("bn1", self.bn1)
             y = self.conv1(x, epilogue=FusedEpilogue(scale=s1, shift=t1, act="relu"))
@@ -121,14 +123,14 @@ class ResidualBlock(_Fusable):
                     and (self.short_conv is None or self.short_conv.bias is None)
                     and supports_second_operand(x.feats.dtype, self.conv2.in_channels, self.conv2.out_channels,
                                                 x.feats.size(1))):
-                return self._one_kernel_tail(x, y)
+                return self._one_kernel_tail(x, y, out)
             if self.short_conv is not None:
                 ss, ts = self._fold("short_bn", self.short_bn)
                 sc = self.short_conv(x, epilogue=FusedEpilogue(scale=ss, shift=ts)).feats
             else:
                 sc = x.feats.contiguous()
             s2, t2 = self._fold("bn2", self.bn2)
-            return self.conv2(y, epilogue=FusedEpilogue(scale=s2, shift=t2, residual=sc, act="relu"))
+            return self.conv2(y, epilogue=FusedEpilogue(scale=s2, shift=t2, residual=sc, act="relu"), out=out)
         y = self.bn2(self.conv2(self.relu(self.bn1(self.conv1(x)))))
         sc = x if self.short_conv is None else self.short_bn(self.short_conv(x))
         return self.relu(y + sc)
@@ -179,6 +181,8 @@ class MinkUNet(nn.Module):
             if plan is None:
                 plan = plans[x.feats.dtype] = MapPlan(self.layer_plan(), x.stride, x.feats.dtype)
             plan.begin(x)
+        if self.shared_skip_buffers and not self.training and x.feats.is_cuda and x.feats.dtype == torch.float16:
+            return self._forward_shared(x)
         feats: List[spTensor] = [self.stem(x)]
         for i in range(4):
             feats.append(self.enc[i](self.down[i](feats[-1])))
@@ -186,6 +190,34 @@ class MinkUNet(nn.Module):
         for i in range(4):
             y = self.up[i](y)
             y = self.dec[i](cat([y, feats[3 - i]]))
+        return self.classifier(y)
+
+    # Inference in fp16: every decoder stage's input [up-sampled | skip] is ONE matrix that the
+    # encoder's skip layer and the up-sampling layer write their column ranges of, instead of a
+    # concatenation pass over both.
+    shared_skip_buffers = True
+
+    def _forward_shared(self, x: spTensor) -> spTensor:
+        cs = self.widths
+        joined: List[torch.Tensor] = []   # per encoder level: [rows, C_up + C_skip]
+
+        def skip_view(rows: int, level: int) -> torch.Tensor:
+            c_up, c_skip = cs[8 - level], cs[level]
+            buf = torch.empty((rows, c_up + c_skip), dtype=x.feats.dtype, device=x.feats.device)
+            joined.append(buf)
+            return buf[:, c_up:]
+
+        h = self.stem[0](x)
+        y = self.stem[1](h, out=skip_view(h.feats.size(0), 0))
+        for i in range(4):
+            d = self.down[i](y)
+            h = self.enc[i][0](d)
+            y = self.enc[i][1](h, out=skip_view(h.feats.size(0), i + 1) if i < 3 else None)
+        for i in range(4):
+            level = 3 - i
+            c_up = cs[5 + i]
+            u = self.up[i](y, out=joined[level][:, :c_up])
+            y = self.dec[i](u._like(joined[level]))
         return self.classifier(y)
 
     @staticmethod

@@ -78,11 +78,14 @@ class conv3d(nn.Module):
         if self.bias is not None:
             self.bias.data.uniform_(-bound, bound)
 
-    def forward(self, input: spTensor, epilogue: Optional[FusedEpilogue] = None) -> spTensor:
+    def forward(self, input: spTensor, epilogue: Optional[FusedEpilogue] = None,
+                out: Optional[torch.Tensor] = None) -> spTensor:
+        """``out``: where the output features go, e.g. a column range of a wider matrix that a later
+        layer reads whole (the result's ``feats`` is then that tensor)."""
         return conv_func(input=input, in_channel=self.in_channels, out_channel=self.out_channels, kernel=self.kernel,
                          kernel_size_code=self.kernel_size_code, stride_code=self.stride_code,
                          padding_code=self.padding_code, bias=self.bias, transposed=self.transposed,
-                         tensorcore=self.tensorcore, epilogue=epilogue)
+                         tensorcore=self.tensorcore, epilogue=epilogue, out=out)
 
 
 def _with_bias(epilogue: Optional[FusedEpilogue], bias) -> Optional[FusedEpilogue]:
@@ -110,10 +113,14 @@ def _choose_dataflow(tag: str, in_channel: int, out_channel: int) -> str:
     return "D2"
 
 
-def _run_conv(feats, w, kmap, transposed, ep, buffer):
+def _run_conv(feats, w, kmap, transposed, ep, buffer, out=None):
     if kmap.dataflow == "D1":
-        return PF.conv_forward_d1(feats, w, kmap, transposed, ep, buffer)
-    return PF.conv_forward(feats, w, kmap.csr(transposed=transposed), ep)
+        res = PF.conv_forward_d1(feats, w, kmap, transposed, ep, buffer)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    return PF.conv_forward(feats, w, kmap.csr(transposed=transposed), ep, out=out)
 
 
 def _map_for(input, in_channel, out_channel, kernel_size_code, stride_code, padding_code):
@@ -147,14 +154,18 @@ def _map_for(input, in_channel, out_channel, kernel_size_code, stride_code, padd
 
 
 def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_code, padding_code, bias, transposed,
-              tensorcore, epilogue: Optional[FusedEpilogue] = None):
-    """Run one sparse convolution on ``input`` and return the output ``spTensor``."""
+              tensorcore, epilogue: Optional[FusedEpilogue] = None, out: Optional[torch.Tensor] = None):
+    """Run one sparse convolution on ``input`` and return the output ``spTensor`` (its features written
+    into ``out`` when given)."""
     ep = _with_bias(epilogue, bias)
     planner = getattr(input, "planner", None)
     w = kernel  # the Parameter itself: the packed tensor-core layout is cached on it
 
     if kernel_size_code == _ONES and stride_code == _ONES:
         out_feats = PF.linear_forward(input.feats, w if w.dim() == 2 else w[0], ep)
+        if out is not None:
+            out.copy_(out_feats)
+            out_feats = out
         output = spTensor(coords=input.coords, feats=out_feats, buffer=input.buffer, batchsize=input.batchsize,
                           stride=input.stride, init_tag=input.init_tag, coords_max=input.coords_max,
                           coords_min=input.coords_min)
@@ -170,7 +181,7 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
         # the reference reads cbook[output_stride] and fails when no layer registered that
         # stride (script/spconv.py:309); the map itself remembers its fine side.
         out_coords = input.cbook.get(output_stride, kmap.in_coords)
-        out_feats = _run_conv(input.feats, w, kmap, True, ep, input.buffer)
+        out_feats = _run_conv(input.feats, w, kmap, True, ep, input.buffer, out)
         output = spTensor(feats=out_feats, coords=out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=input.coords_max,
                           coords_min=input.coords_min)
@@ -178,7 +189,7 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
     else:
         kmap, output_stride, coords_max, coords_min = _map_for(input, in_channel, out_channel, kernel_size_code,
                                                                stride_code, padding_code)
-        out_feats = _run_conv(input.feats, w, kmap, False, ep, input.buffer)
+        out_feats = _run_conv(input.feats, w, kmap, False, ep, input.buffer, out)
         output = spTensor(feats=out_feats, coords=kmap.out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=coords_max,
                           coords_min=coords_min)

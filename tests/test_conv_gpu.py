@@ -313,6 +313,44 @@ def test_second_operand_joins_the_accumulator(cin, cout, c2, ks, tile_rows):
                         PF.FusedEpilogue(extra_feats=x2.float().cuda(), extra_weight=w2.float().cuda()))
     assert PF.device_status() == 0
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("cin,cout,ks", [(64, 64, 3), (32, 96, 3), (16, 32, 3), (96, 96, 2), (128, 256, 3)])
+def test_column_ranges_of_wider_matrices(cin, cout, ks):
+    """Row pitches: the input read from, and the output written into, a column range of a wider
+    row-major matrix give the bits of the dense call, and the columns beside the range stay untouched."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(33, 64, batch=2)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    g = torch.Generator().manual_seed(7 * cin + cout)
+    n = len(coords)
+    x = torch.randn(n, cin, generator=g).half().cuda()
+    w = (torch.randn(ks ** 3, cin, cout, generator=g) / (ks ** 3 * cin) ** 0.5).half().cuda()
+    ep = PF.FusedEpilogue(scale=(torch.rand(cout, generator=g) + 0.5).cuda(), shift=torch.randn(cout, generator=g).cuda(),
+                          act="relu")
+    want = PF.conv_forward(x, w, csr, ep)
+    wide_in = torch.full((n, cin + 40), 7.0, dtype=torch.float16, device="cuda")
+    wide_in[:, 8:8 + cin] = x
+    wide_out = torch.full((n, cout + 24), -3.0, dtype=torch.float16, device="cuda")
+    got = PF.conv_forward(wide_in[:, 8:8 + cin], w, csr, ep, out=wide_out[:, 16:16 + cout])
+    assert got.data_ptr() == wide_out[:, 16:].data_ptr()  # written in place, no copy
+    assert torch.equal(got, want)
+    assert bool((wide_out[:, :16] == -3.0).all()) and bool((wide_out[:, 16 + cout:] == -3.0).all())
+    # a range the kernel cannot address in place (odd column offset) goes through a copy, same values
+    odd_out = torch.zeros((n, cout + 3), dtype=torch.float16, device="cuda")
+    got = PF.conv_forward(wide_in[:, 8:8 + cin], w, csr, ep, out=odd_out[:, 3:])
+    assert torch.equal(got, want) and torch.equal(odd_out[:, 3:], want)
+    # the CUDA-core path takes the same arguments
+    ref32 = PF.conv_forward(x.float(), w.float(), csr, ep, "simt")
+    out32 = torch.zeros((n, cout + 8), dtype=torch.float32, device="cuda")
+    PF.conv_forward(wide_in[:, 8:8 + cin].float(), w.float(), csr, ep, "simt", out=out32[:, 8:])
+    assert torch.equal(out32[:, 8:], ref32)
+    with pytest.raises(ValueError):
+        PF.conv_forward(x, w, csr, ep, out=torch.empty((n, cout + 1), dtype=torch.float16, device="cuda"))
+    assert PF.device_status() == 0
+
+
 
 def test_residual_block_as_one_launch():
     """A ResidualBlock whose shortcut rides in conv2's launch (BatchNorm scales folded into fp16

@@ -218,3 +218,30 @@ def test_network_on_nearly_nothing(n):
         with torch.no_grad():
             outs.append(model(x).feats)
     assert outs[0].shape == (n, 19) and torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("cr", [1.0, 0.5, 0.3])
+def test_shared_skip_buffers_equal_concatenation(cr):
+    """fp16 inference writes every decoder input [up-sampled | skip] as one matrix (the skip layer and the
+    up-sampling layer each write their column range); the logits are the bits of the path that
+    concatenates.  cr = 0.3 gives widths the kernel cannot address in place (copies take over)."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(41, 72, batch=3)
+    torch.manual_seed(11)
+    feats = torch.randn(len(coords), 4).half()
+    model = pce.MinkUNet(4, 19, cr=cr)
+    pce.randomize_batchnorm(model, 5)
+    model = model.half().eval().cuda()
+
+    def run():
+        x = pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), batchsize=3,
+                         init_tag=pce.MinkUNet.tags())
+        with torch.no_grad():
+            return model(x).feats
+    assert model.shared_skip_buffers
+    shared = run()
+    model.shared_skip_buffers = False
+    joined = run()
+    assert torch.equal(shared, joined)
+    assert PF.device_status() == 0
