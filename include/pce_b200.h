@@ -297,7 +297,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
 /* Tuning hook for experiments and tests; what = 0: force the tensor-core kernel's stage-ring
  * depth (value 2, 3 or 4; 0 restores the automatic choice); what = 1: sub-tiles per tile (1 or
  * 2) of the dense product, which has no tile lists to fix it; what = 2: accumulator sets in
- * tensor memory (1 or 2). */
+ * tensor memory (1 or 2); what = 3: programmatic dependent launch of the tensor-core kernel (its
+ * set-up overlaps the tail of the kernel before it in the stream; 1 = on, the default, 0 = off). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose

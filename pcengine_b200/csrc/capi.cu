@@ -12,6 +12,7 @@ int umma_status_fetch(int* host_status, bool reset);
 extern int umma_force_stages;
 extern int umma_force_sub;
 extern int umma_force_nacc;
+extern int umma_overlap_launches;
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -70,6 +71,10 @@ int pce_tune(int32_t what, int32_t value) {
   }
   if (what == 2) {
     umma_force_nacc = value;
+    return PCE_OK;
+  }
+  if (what == 3) {
+    umma_overlap_launches = value ? 1 : 0;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

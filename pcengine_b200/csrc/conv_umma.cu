@@ -307,6 +307,16 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(static_cast<uint32_t>(tmem_cols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Launched with programmatic stream serialisation: everything above ran while the kernel before
+  // this one in the stream was still finishing; nothing below (the lists, the features, the output
+  // buffer) may be touched before that kernel has completed and its writes are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (warp < 2) {
     // this CTA's contiguous share of the tiles, balanced by work: warp 0 finds its first tile,
     // warp 1 the next CTA's first tile
@@ -314,12 +324,6 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     const unsigned b = blockIdx.x + warp;
     const int t = b >= gridDim.x ? n_tiles : warp_tile_at_cost(ls.tile_ptr, n_tiles, total * b / gridDim.x, lane);
     if (lane == 0) ctl->range[warp] = t;
-  }
-  if (warp == kMmaWarp) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
-                 "r"(static_cast<uint32_t>(tmem_cols))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -574,6 +578,9 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+      // last tile of this CTA: once every CTA is here (or gone), the next kernel of the stream may be
+      // set up on the SMs; it waits for this grid's completion before it touches memory
+      if (t == t1 - 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
       for (int sub = 0; sub < SUB; ++sub) {
       const int my_row = rows_of[sub];
@@ -709,13 +716,25 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
 int umma_force_stages = 0;
 int umma_force_sub = 0;
 int umma_force_nacc = 0;
+// Programmatic dependent launch: the kernel's set-up (barriers, tensor-memory allocation) overlaps the
+// tail of the kernel before it in the stream.
+int umma_overlap_launches = 1;
 
 template <int NS, int SUB, bool PUSH, int SLOTS>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
                         const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols,
                         int nacc) {
-  umma::k_conv_umma<NS, SUB, PUSH, SLOTS><<<grid, 32 * (4 * SUB + 5), smem, st>>>(in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
-                                                                      nacc);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(32 * (4 * SUB + 5));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = umma_overlap_launches ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, umma::k_conv_umma<NS, SUB, PUSH, SLOTS>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, nacc);
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
