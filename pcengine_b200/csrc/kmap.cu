@@ -173,54 +173,75 @@ static KeyBits key_bits_for(const GeomDev& g) {
 
 // Strided output coordinates, step 1: every valid candidate is inserted into a
 // set; the sort keys of first-time members are appended to ukeys (unordered).
+// One thread per input coordinate walks the kernel offsets and keeps the new keys it finds in a small
+// register buffer; a warp appends its buffers with ONE atomic on the shared counter (when a lane's buffer
+// is full, and at the end): the counter is a single address, and an atomic per key, or per warp and
+// offset, serialises the kernel on it.
 __global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev g, KeyBits kb, Slot* table,
                              unsigned tmask, unsigned long long* ukeys, int ucap, int* counter, int* status,
                              int* max_batch) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  int kp = blockIdx.y;
-  bool fresh = false;
-  unsigned long long sort_key = 0;
-  int batch = 0;
-  if (i < n_in) {
-    int4 c = __ldg(coords + i);
+  constexpr int kHold = 4;
+  constexpr unsigned kFull = 0xFFFFFFFFu;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned lane = threadIdx.x & 31;
+  const bool live = i < n_in;
+  const int4 c = live ? __ldg(coords + i) : make_int4(0, 0, 0, 0);
+  unsigned long long held[kHold];
+  int n_held = 0;
+  bool any_fresh = false;
+  auto flush = [&]() {
+    int incl = n_held;  // inclusive prefix of the lanes' counts
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(kFull, incl, d);
+      if (lane >= static_cast<unsigned>(d)) incl += v;
+    }
+    const int total = __shfl_sync(kFull, incl, 31);
+    if (total == 0) return;
+    int base = 0;
+    if (lane == 31) base = atomicAdd(counter, total);
+    base = __shfl_sync(kFull, base, 31) + incl - n_held;
+#pragma unroll
+    for (int u = 0; u < kHold; ++u) {
+      if (u < n_held) {
+        if (base + u < ucap)
+          ukeys[base + u] = held[u];
+        else
+          atomicMax(status, PCE_ERR_CAPACITY);
+      }
+    }
+    n_held = 0;
+  };
+  for (int kp = 0; kp < g.kv; ++kp) {
     int qx, qy, qz;
-    if (candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) {
+    if (live && candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) {
       if (!packable(c.x, qx, qy, qz)) {
         atomicMax(status, PCE_ERR_RANGE);
       } else {
-        unsigned s = table_claim(table, tmask, pack_key(c.x, qx, qy, qz), fresh);
+        bool fresh = false;
+        const unsigned s = table_claim(table, tmask, pack_key(c.x, qx, qy, qz), fresh);
         if (s == 0xFFFFFFFFu) {
           atomicMax(status, PCE_ERR_TABLE_FULL);
-          fresh = false;
+        } else if (fresh) {
+          // candidate() keeps q inside [lo, hi], so every field fits its bits
+          const unsigned long long key = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
+                                         (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
+                                         (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
+                                         static_cast<unsigned long long>(qz - g.lo[2]);
+#pragma unroll
+          for (int u = 0; u < kHold; ++u)
+            if (u == n_held) held[u] = key;
+          ++n_held;
+          any_fresh = true;
         }
-        // candidate() keeps q inside [lo, hi], so every field fits its bits
-        sort_key = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
-                   (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
-                   (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
-                   static_cast<unsigned long long>(qz - g.lo[2]);
-        batch = c.x;
       }
     }
+    if (__any_sync(kFull, n_held == kHold)) flush();
   }
-  // one append per warp, not per key: the counter is a single address
-  const unsigned lane = threadIdx.x & 31;
-  const unsigned m = __ballot_sync(0xFFFFFFFFu, fresh);
-  if (m == 0) return;
-  const int leader = __ffs(m) - 1;
-  int base = 0;
-  const int wmax = __reduce_max_sync(0xFFFFFFFFu, fresh ? batch : 0);
-  if (static_cast<int>(lane) == leader) {
-    base = atomicAdd(counter, __popc(m));
-    if (wmax > *reinterpret_cast<volatile int*>(max_batch)) atomicMax(max_batch, wmax);
-  }
-  base = __shfl_sync(0xFFFFFFFFu, base, leader);
-  if (fresh) {
-    const int pos = base + __popc(m & ((1u << lane) - 1));
-    if (pos < ucap)
-      ukeys[pos] = sort_key;
-    else
-      atomicMax(status, PCE_ERR_CAPACITY);
-  }
+  flush();
+  // the largest batch index among the new keys (it sizes the sort key): one atomic per warp at most
+  const int wmax = __reduce_max_sync(kFull, any_fresh ? c.x : 0);
+  if (lane == 0 && wmax > *reinterpret_cast<volatile int*>(max_batch)) atomicMax(max_batch, wmax);
 }
 
 __global__ void k_decode_keys(const unsigned long long* __restrict__ keys, int n, GeomDev g, KeyBits kb, int4* coords) {
@@ -678,7 +699,7 @@ int pce_downsample_coords(const int32_t* in_coords, int32_t n_in, const pce_geom
   PCE_CUDA(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * tsize, st));
   PCE_CUDA(cudaMemsetAsync(ctr, 0, 3 * sizeof(int), st));
   const KeyBits kb = key_bits_for(gd);
-  dim3 grid(div_up(n_in, 256), gd.kv);
+  const int grid = div_up(n_in, 256);
   k_candidates<<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, kb, table, tsize - 1, ukeys,
                                      out_cap, ctr, ctr + 1, ctr + 2);
   PCE_LAUNCH_CHECK();
