@@ -200,6 +200,12 @@ LAYERS = {  # name: (map kind, kv, c_in, c_out)
 DEFAULT_LAYERS = ["subm3_32x32", "subm3_64x64", "subm3_96x96", "subm3_128x128", "down2s2_32x64", "up2s2_64x32"]
 
 
+def _host_lead():
+    """Keeps the GPU busy for ~0.25 ms so that the host has queued the timed launch (and its event
+    pair) before the GPU gets to it: a kernel-only time then holds no launch latency of an idle GPU."""
+    torch.cuda._sleep(500000)
+
+
 def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: int = 3):
     """Single LiDAR-shaped layers on ``scans`` collated scans (seeds 2000..): kernel-only time per layer
     with an L2 flush between launches; algorithmic bytes / flops per launch against the measured peaks."""
@@ -234,6 +240,7 @@ def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: in
             PF.conv_forward(x, w, csr)
         ts = []
         for _ in range(iters):
+            _host_lead()
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -375,6 +382,7 @@ def run_indoor(args):
                 fn()
             ts = []
             for _ in range(max(args.steps, 5)):
+                _host_lead()
                 flush.zero_()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
