@@ -51,3 +51,32 @@ def test_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(base, f)).read()
                 assert "oracle" not in src, os.path.join(base, f)
+
+
+def test_ctypes_mirrors_match_the_header_layout(tmp_path):
+    """The header compiled as plain C: size of every struct and offset of its last field equal the
+    ctypes mirrors' (a field added on one side only would shift everything behind it)."""
+    import subprocess
+
+    from pcengine_b200 import _lib
+    pairs = [("pce_geom", _lib.Geom), ("pce_tile_lists", _lib.TileLists), ("pce_epilogue", _lib.Epilogue),
+             ("pce_plan_map_spec", _lib.PlanMapSpec), ("pce_planned_csr", _lib.PlannedCSR),
+             ("pce_planned_map", _lib.PlannedMap)]
+    lines = []
+    for cname, mirror in pairs:
+        last = mirror._fields_[-1][0]
+        lines.append(f'printf("{cname} %zu %zu\\n", sizeof({cname}), offsetof({cname}, {last}));')
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "pce_b200.h"\nint main(void) {\n'
+                   + "\n".join(lines) + "\nreturn 0; }\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    seen = {}
+    for line in out:
+        if line:
+            name, size, off = line.split()
+            seen[name] = (int(size), int(off))
+    for cname, mirror in pairs:
+        last = mirror._fields_[-1][0]
+        assert seen[cname] == (ctypes.sizeof(mirror), getattr(mirror, last).offset), cname

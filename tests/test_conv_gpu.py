@@ -314,6 +314,38 @@ def test_second_operand_joins_the_accumulator(cin, cout, c2, ks, tile_rows):
     assert PF.device_status() == 0
 
 @pytest.mark.gpu
+def test_overlapped_launches_keep_the_stream_order():
+    """Programmatic dependent launch (a convolution's set-up overlaps the previous kernel's tail): a chain
+    of layers in which every launch reads what the launch before it wrote gives the same bits with the
+    overlap on and off, run after run."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import _lib
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(9, 96, batch=4)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    csr = km.csr()
+    g = torch.Generator().manual_seed(99)
+    widths = [32, 64, 96, 64, 128, 32, 16, 64]
+    x0 = torch.randn(len(coords), widths[0], generator=g).half().cuda()
+    ws = [(torch.randn(27, a, b, generator=g) / (27 * a) ** 0.5).half().cuda() for a, b in zip(widths[:-1], widths[1:])]
+
+    def chain():
+        x = x0
+        for w in ws:
+            x = PF.conv_forward(x, w, csr, PF.FusedEpilogue(act="relu"))
+        return x
+    try:
+        _lib.lib.pce_tune(3, 0)
+        want = chain()
+        _lib.lib.pce_tune(3, 1)
+        for _ in range(5):
+            assert torch.equal(chain(), want)
+    finally:
+        _lib.lib.pce_tune(3, 1)
+    assert PF.device_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cin,cout,ks", [(64, 64, 3), (32, 96, 3), (16, 32, 3), (96, 96, 2), (128, 256, 3)])
 def test_column_ranges_of_wider_matrices(cin, cout, ks):
     """Row pitches: the input read from, and the output written into, a column range of a wider
