@@ -128,6 +128,11 @@ typedef struct pce_tile_lists {
   int32_t tile_rows;        /* 128 or 256 */
   int32_t identity_stage;   /* 0 or 1 */
   int32_t slots;            /* offsets per stage: 1, 2 or 4 */
+  int32_t settled;          /* non-zero: the lists were complete before the kernel that precedes this
+                             * launch in its stream was launched (planner lists, lists kept from an
+                             * earlier call).  The tensor-core kernel is launched so that its set-up
+                             * overlaps that kernel's tail, and may then read the lists that early
+                             * too; 0 is always safe. */
 } pce_tile_lists;
 
 PCE_API const char* pce_strerror(int status);
@@ -298,7 +303,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * depth (value 2, 3 or 4; 0 restores the automatic choice); what = 1: sub-tiles per tile (1 or
  * 2) of the dense product, which has no tile lists to fix it; what = 2: accumulator sets in
  * tensor memory (1 or 2); what = 3: programmatic dependent launch of the tensor-core kernel (its
- * set-up overlaps the tail of the kernel before it in the stream; 1 = on, the default, 0 = off). */
+ * set-up overlaps the tail of the kernel before it in the stream; 1 = on, the default, 0 = off,
+ * 2 = on, but tile lists are never read before that kernel has finished). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose

@@ -36,7 +36,8 @@ class Geom(C.Structure):
 
 class TileLists(C.Structure):
     _fields_ = [("order", C.c_void_p), ("tile_ptr", C.c_void_p), ("stage_kp", C.c_void_p), ("stage_nbr", C.c_void_p),
-                ("tile_rows", C.c_int32), ("identity_stage", C.c_int32), ("slots", C.c_int32)]
+                ("tile_rows", C.c_int32), ("identity_stage", C.c_int32), ("slots", C.c_int32),
+                ("settled", C.c_int32)]
 
 
 PLAN_MAX_USES = 8

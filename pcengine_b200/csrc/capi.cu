@@ -74,7 +74,7 @@ int pce_tune(int32_t what, int32_t value) {
     return PCE_OK;
   }
   if (what == 3) {
-    umma_overlap_launches = value ? 1 : 0;
+    umma_overlap_launches = value < 0 || value > 2 ? 1 : value;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

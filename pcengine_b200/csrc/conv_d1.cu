@@ -185,7 +185,7 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, const void* 
       k_d1_tile_lists<<<div_up(static_cast<long long>(n_tiles) * 128 + 1, 256), 256, 0, st>>>(qkpos, kv, n_tiles, order,
                                                                                                tile_ptr, stage_kp, stage_nbr);
       PCE_LAUNCH_CHECK();
-      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128, 0, 1};
+      pce_tile_lists tl{order, tile_ptr, stage_kp, stage_nbr, 128, 0, 1, 0};
       PCE_TRY(conv_umma(bin, qsum, wpacked, kv, &tl, qsum, cin, cout, bout, nullptr, st));
     } else {
       if (w == nullptr) return PCE_ERR_INVALID;

@@ -76,6 +76,7 @@ struct Lists {
   const int* stage_nbr;  // [stages][tile rows] input row per tile row, -1 absent
   int identity;          // every tile's last stage is the identity stage (stage_kp = -1)
   const __half* wslots;  // SLOTS > 1: weights as [kv][cout][cin] (one 16-byte chunk row per output channel)
+  int settled;           // the lists were complete before the previous kernel of the stream was launched
 };
 
 // Second operand: out[row] += in2[row] @ w2, joined to the accumulation at the identity stage.
@@ -314,9 +315,11 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // Launched with programmatic stream serialisation: everything above ran while the kernel before
-  // this one in the stream was still finishing; nothing below (the lists, the features, the output
-  // buffer) may be touched before that kernel has completed and its writes are visible.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // this one in the stream was still finishing; the features and the output buffer may not be touched
+  // before that kernel has completed and its writes are visible.  The tile lists may, when they are
+  // older than that kernel (ls.settled): the search for this CTA's tiles and the first index loads
+  // then overlap its tail as well.
+  if (!ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (warp < 2) {
     // this CTA's contiguous share of the tiles, balanced by work: warp 0 finds its first tile,
     // warp 1 the next CTA's first tile
@@ -396,6 +399,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     load_stage(g0 + 1, nid1, kp1);
     load_stage(g0 + 2, nid2, kp2);
     load_stage(g0 + 3, nid3, kp3);
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int g = g0; g < g1 && ok; g += 4) {
       run_stage(nid0, kp0);
       load_stage(g + 4, nid0, kp0);
@@ -483,6 +487,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     int nidA[SLOTS], kpA[SLOTS], nidB[SLOTS], kpB[SLOTS];
     load_stage(g0, nidA, kpA);
     load_stage(g0 + 1, nidB, kpB);
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int g = g0; g < g1 && ok; g += 2) {
       run_stage(nidA, kpA);
       load_stage(g + 2, nidA, kpA);
@@ -501,6 +506,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
       int j = 0;
@@ -553,6 +559,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     // =========================== epilogue ===========================
     const int lane_quarter = warp & 3;  // the TMEM lanes this warp may read: 32*(warp%4)..+31
     const int slot_in_tile = lane_quarter * 32 + lane;
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int t = t0; t < t1; ++t) {
       const int it = t - t0;
       const int buf = it % nacc;
@@ -716,8 +723,9 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
 int umma_force_stages = 0;
 int umma_force_sub = 0;
 int umma_force_nacc = 0;
-// Programmatic dependent launch: the kernel's set-up (barriers, tensor-memory allocation) overlaps the
-// tail of the kernel before it in the stream.
+// Programmatic dependent launch: the kernel's set-up (barriers, tensor-memory allocation; with settled
+// tile lists also the tile search and the first index loads) overlaps the tail of the kernel before it
+// in the stream.  0 = off, 1 = on, 2 = on but every list is treated as not settled.
 int umma_overlap_launches = 1;
 
 template <int NS, int SUB, bool PUSH, int SLOTS>
@@ -753,12 +761,13 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
       if (!e.push_slot[s]) e.push_base[s] = nullptr;
     }
   }
-  umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0, nullptr};
+  umma::Lists ls{nullptr, nullptr, nullptr, nullptr, 0, nullptr, 0};
   int slots = 1;
   umma::Second sec{nullptr, nullptr, 0};
   int sub = umma_force_sub == 1 || umma_force_sub == 2 ? umma_force_sub : 1;
   if (tiles) {
-    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr, tiles->identity_stage ? 1 : 0, nullptr};
+    ls = umma::Lists{tiles->order, tiles->tile_ptr, tiles->stage_kp, tiles->stage_nbr, tiles->identity_stage ? 1 : 0, nullptr,
+                     (tiles->settled && umma_overlap_launches == 1) ? 1 : 0};
     slots = tiles->slots > 1 ? tiles->slots : 1;
     if (slots != 1) {
       // several offsets per stage: the lists must match the layer's width, and the packed weights carry

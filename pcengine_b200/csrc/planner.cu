@@ -233,7 +233,7 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
     PCE_TRY(scratch_for(l, 8 * (static_cast<size_t>(n_tiles) + 1) + (1u << 20), &ws));
     PCE_TRY(pce_build_tile_lists(mask, rowptr, nbr, order, n_rows, kv, rows, identity_stage, slots, ws, l->scratch_cap,
                                  tile_ptr, stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
-    out->lists[out->n_lists++] = pce_tile_lists{order, tile_ptr, stage_kp, stage_nbr, rows, identity_stage, slots};
+    out->lists[out->n_lists++] = pce_tile_lists{order, tile_ptr, stage_kp, stage_nbr, rows, identity_stage, slots, 1};
   }
   return PCE_OK;
 }

@@ -83,6 +83,10 @@ class NeighbourCSR:
         if hit is None and not identity:
             hit = self._tiles.get((bool(sort_rows), tile_rows, True, int(slots)))
         if hit is not None:
+            # kept from an earlier call: once the kernels that built the lists have finished, a launch
+            # may read the lists during its set-up (while the kernel before it is still finishing)
+            if not hit[0].settled and (len(hit) < 6 or hit[5].query()):
+                hit[0].settled = 1
             return hit[0]
         dev = self.mask.device
         n_tiles = (self.n_rows + tile_rows - 1) // tile_rows
@@ -102,8 +106,10 @@ class NeighbourCSR:
                                             tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(), cap,
                                             _lib.stream_ptr(dev)), "pce_build_tile_lists")
         st = _lib.TileLists(order.data_ptr(), tile_ptr.data_ptr(), stage_kp.data_ptr(), stage_nbr.data_ptr(),
-                            tile_rows, 1 if identity else 0, int(slots))
-        self._tiles[key] = (st, order, tile_ptr, stage_kp, stage_nbr)
+                            tile_rows, 1 if identity else 0, int(slots), 0)
+        built = torch.cuda.Event()
+        built.record(torch.cuda.current_stream(dev))
+        self._tiles[key] = (st, order, tile_ptr, stage_kp, stage_nbr, built)
         return st
 
 

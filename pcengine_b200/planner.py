@@ -123,7 +123,8 @@ class PlannedKernelMap(KernelMap):
             for i in range(c.n_lists):
                 t = c.lists[i]
                 slots = max(int(t.slots), 1)
-                lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows, t.identity_stage, slots)
+                lists = _lib.TileLists(t.order, t.tile_ptr, t.stage_kp, t.stage_nbr, t.tile_rows, t.identity_stage, slots,
+                                       t.settled)
                 n_tiles = (csr.n_rows + t.tile_rows - 1) // t.tile_rows
                 csr._order = _DevArray(t.order, (csr.n_rows,), device, keep)
                 entries = n_tiles * ((kv + slots - 1) // slots + int(t.identity_stage)) * slots

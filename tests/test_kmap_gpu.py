@@ -117,7 +117,7 @@ def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity, slots):
     km = pce.KernelMap(torch.from_numpy(coords).cuda(), ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     csr = km.csr()
     csr.tiles(sort_rows, tile_rows, identity, slots)
-    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows, identity, slots)]
+    _, order, tile_ptr, stage_kp, stage_nbr = csr._tiles[(sort_rows, tile_rows, identity, slots)][:5]
     order, tile_ptr = order.cpu().numpy(), tile_ptr.cpu().numpy()
     stage_kp, stage_nbr = stage_kp.cpu().numpy(), stage_nbr.cpu().numpy().reshape(-1, tile_rows)
     stage_kp3, stage_nbr3 = stage_kp.reshape(-1, slots), stage_nbr.reshape(-1, slots, tile_rows)
