@@ -212,31 +212,62 @@ __global__ void k_candidates(const int4* __restrict__ coords, int n_in, GeomDev 
     }
     n_held = 0;
   };
-  for (int kp = 0; kp < g.kv; ++kp) {
-    int qx, qy, qz;
-    if (live && candidate(g, kp, c.y, c.z, c.w, qx, qy, qz)) {
-      if (!packable(c.x, qx, qy, qz)) {
-        atomicMax(status, PCE_ERR_RANGE);
-      } else {
-        bool fresh = false;
-        const unsigned s = table_claim(table, tmask, pack_key(c.x, qx, qy, qz), fresh);
-        if (s == 0xFFFFFFFFu) {
-          atomicMax(status, PCE_ERR_TABLE_FULL);
-        } else if (fresh) {
-          // candidate() keeps q inside [lo, hi], so every field fits its bits
-          const unsigned long long key = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
-                                         (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
-                                         (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
-                                         static_cast<unsigned long long>(qz - g.lo[2]);
+  // Per axis the kernel offsets are o = omin + i, i in [0, ks) (offset_of), and an offset reaches an output
+  // from this input when x + pad - o is a multiple of the stride: i = r, r + stride, ... < ks with
+  // r = (x + pad - omin) mod stride; the output is then q0 - j for the j-th of them.  Walking those directly
+  // costs three divisions per input instead of six per (input, offset).  The loop bounds are the same for
+  // every lane (the warp-wide flush sits inside).
+  int r[3], q0[3];
+  {
+    const int xyz[3] = {c.y, c.z, c.w};
+    int a[3];
 #pragma unroll
-          for (int u = 0; u < kHold; ++u)
-            if (u == n_held) held[u] = key;
-          ++n_held;
-          any_fresh = true;
+    for (int d = 0; d < 3; ++d) {
+      const int omin = -((g.ks[d] - 1) / 2) + ((g.ks[d] % 2 == 0 || g.ks[d] == 1) ? 0 : 1);
+      a[d] = xyz[d] + g.pd[d] - omin;
+    }
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      int m = a[d] % g.st[d];
+      if (m < 0) m += g.st[d];
+      r[d] = m;
+      q0[d] = (a[d] - m) / g.st[d];
+    }
+  }
+  const int nx = (g.ks[0] + g.st[0] - 1) / g.st[0], ny = (g.ks[1] + g.st[1] - 1) / g.st[1],
+            nz = (g.ks[2] + g.st[2] - 1) / g.st[2];
+  for (int jx = 0; jx < nx; ++jx) {
+    for (int jy = 0; jy < ny; ++jy) {
+      for (int jz = 0; jz < nz; ++jz) {
+        const int qx = q0[0] - jx, qy = q0[1] - jy, qz = q0[2] - jz;
+        const bool reach = live && r[0] + jx * g.st[0] < g.ks[0] && r[1] + jy * g.st[1] < g.ks[1] &&
+                           r[2] + jz * g.st[2] < g.ks[2] && qx >= g.lo[0] && qx <= g.hi[0] && qy >= g.lo[1] &&
+                           qy <= g.hi[1] && qz >= g.lo[2] && qz <= g.hi[2];
+        if (reach) {
+          if (!packable(c.x, qx, qy, qz)) {
+            atomicMax(status, PCE_ERR_RANGE);
+          } else {
+            bool fresh = false;
+            const unsigned s = table_claim(table, tmask, pack_key(c.x, qx, qy, qz), fresh);
+            if (s == 0xFFFFFFFFu) {
+              atomicMax(status, PCE_ERR_TABLE_FULL);
+            } else if (fresh) {
+              // q lies inside [lo, hi], so every field fits its bits
+              const unsigned long long key = (static_cast<unsigned long long>(c.x) << kb.sh_b) |
+                                             (static_cast<unsigned long long>(qx - g.lo[0]) << kb.sh_x) |
+                                             (static_cast<unsigned long long>(qy - g.lo[1]) << kb.sh_y) |
+                                             static_cast<unsigned long long>(qz - g.lo[2]);
+#pragma unroll
+              for (int u = 0; u < kHold; ++u)
+                if (u == n_held) held[u] = key;
+              ++n_held;
+              any_fresh = true;
+            }
+          }
         }
+        if (__any_sync(kFull, n_held == kHold)) flush();
       }
     }
-    if (__any_sync(kFull, n_held == kHold)) flush();
   }
   flush();
   // the largest batch index among the new keys (it sizes the sort key): one atomic per warp at most

@@ -174,13 +174,21 @@ class MinkUNet(nn.Module):
     # building each one inside the layer that first needs it.
     plan_ahead = True
 
+    def plan(self, x: spTensor) -> bool:
+        """Start building the kernel maps of ``x``'s pass now (eval mode, CUDA) and attach the pass to
+        ``x``; ``forward(x)`` then finds it started.  A serving loop calls this as soon as a batch's
+        coordinates are on their way to the device (``x.coords_ready``), before it runs the batch in front
+        of it, so that no layer waits for a map.  Returns False when nothing was started."""
+        if not self.plan_ahead or self.training or not x.feats.is_cuda or x.planner is not None:
+            return False
+        plans = self.__dict__.setdefault("_map_plans", {})
+        plan = plans.get(x.feats.dtype)
+        if plan is None:
+            plan = plans[x.feats.dtype] = MapPlan(self.layer_plan(), x.stride, x.feats.dtype)
+        return plan.begin(x)
+
     def forward(self, x: spTensor) -> spTensor:
-        if self.plan_ahead and not self.training and x.feats.is_cuda:
-            plans = self.__dict__.setdefault("_map_plans", {})
-            plan = plans.get(x.feats.dtype)
-            if plan is None:
-                plan = plans[x.feats.dtype] = MapPlan(self.layer_plan(), x.stride, x.feats.dtype)
-            plan.begin(x)
+        self.plan(x)
         if self.shared_skip_buffers and not self.training and x.feats.is_cuda and x.feats.dtype == torch.float16:
             return self._forward_shared(x)
         feats: List[spTensor] = [self.stem(x)]

@@ -68,7 +68,9 @@ def test_submanifold_surface():
 
 @pytest.mark.parametrize("ks,stride,pad", [((2, 2, 2), (2, 2, 2), (0, 0, 0)), ((3, 3, 3), (2, 2, 2), (0, 0, 0)),
                                            ((3, 3, 3), (2, 2, 2), (1, 1, 1)), ((2, 2, 2), (1, 2, 2), (0, 0, 0)),
-                                           ((3, 3, 3), (3, 3, 3), (0, 0, 0)), ((2, 3, 2), (2, 1, 2), (0, 1, 0))])
+                                           ((3, 3, 3), (3, 3, 3), (0, 0, 0)), ((2, 3, 2), (2, 1, 2), (0, 1, 0)),
+                                           ((5, 5, 5), (2, 2, 2), (2, 2, 2)), ((4, 4, 4), (2, 2, 2), (1, 1, 1)),
+                                           ((5, 5, 5), (3, 3, 3), (0, 0, 0)), ((4, 2, 5), (3, 2, 2), (1, 0, 2))])
 def test_strided(ks, stride, pad):
     _check(random_cloud(2, 30, 4000, batch=2), ks, stride, pad, False)
     _check(surface_cloud(5, 64), ks, stride, pad, False)

@@ -245,3 +245,35 @@ def test_shared_skip_buffers_equal_concatenation(cr):
     joined = run()
     assert torch.equal(shared, joined)
     assert PF.device_status() == 0
+
+
+def test_plan_before_forward():
+    """MinkUNet.plan(x) starts the map construction ahead of forward(x): same logits, a second call
+    is a no-op, and passes that were planned and never run are given back."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(51, 72, batch=2)
+    torch.manual_seed(3)
+    feats = torch.randn(len(coords), 4).half()
+    model = pce.MinkUNet(4, 19, cr=0.5)
+    pce.randomize_batchnorm(model, 9)
+    model = model.half().eval().cuda()
+
+    def tensor():
+        return pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), batchsize=2,
+                            init_tag=pce.MinkUNet.tags())
+    with torch.no_grad():
+        want = model(tensor()).feats
+        for _ in range(12):  # more than the planner keeps passes for: dropped passes must come back
+            x = tensor()
+            assert model.plan(x)
+            del x
+        a, b = tensor(), tensor()
+        assert model.plan(a) and model.plan(b) and not model.plan(a)
+        assert a.planner is not None and b.planner is not None
+        got_b = model(b).feats  # out of order on purpose
+        got_a = model(a).feats
+    assert torch.equal(got_a, want) and torch.equal(got_b, want)
+    model.train()
+    assert not model.plan(tensor())
+    assert PF.device_status() == 0
