@@ -153,7 +153,15 @@ def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device=None) -> int:
+    """The current CUDA stream of ``device`` as an integer handle (called once or twice per launch:
+    torch's raw-stream query, when present, costs a fraction of building a Stream object)."""
+    if _raw_stream is not None:
+        idx = device.index if isinstance(device, torch.device) else device
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
 
 

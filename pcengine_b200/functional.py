@@ -114,14 +114,18 @@ def packed_weights(kernel: torch.Tensor, as_linear: bool = False) -> Optional[to
     does not cover these channel counts.  The result is cached ON the tensor object (together
     with its version counter and address), so it lives and dies with the weights; a tensor
     that is rebuilt on every call is simply packed again."""
-    kv, c_in, c_out = ((1,) + tuple(kernel.shape)) if as_linear else kernel.shape
-    code = _lib.dtype_code(kernel.dtype)
-    if lib.pce_conv_kernel_choice(c_in, c_out, code, _lib.KERNEL_UMMA) != _lib.KERNEL_UMMA or kv > 128:
-        return None
-    tag = (kernel._version, kernel.data_ptr(), tuple(kernel.shape))
+    tag = (kernel._version, kernel.data_ptr(), kernel.shape, as_linear)
     hit = getattr(kernel, "_pce_packed", None)
     if hit is not None and hit[0] == tag:
         return hit[1]
+    kv, c_in, c_out = ((1,) + tuple(kernel.shape)) if as_linear else kernel.shape
+    code = _lib.dtype_code(kernel.dtype)
+    if lib.pce_conv_kernel_choice(c_in, c_out, code, _lib.KERNEL_UMMA) != _lib.KERNEL_UMMA or kv > 128:
+        try:
+            kernel._pce_packed = (tag, None)  # remembered like a packed layout: this tensor has none
+        except AttributeError:
+            pass
+        return None
     out = torch.empty((lib.pce_packed_weights_bytes(kv, c_in, c_out),), dtype=torch.uint8, device=kernel.device)
     _lib.check(lib.pce_pack_weights(kernel.data_ptr(), kv, c_in, c_out, code, out.data_ptr(),
                                     _lib.stream_ptr(kernel.device)), "pce_pack_weights")
@@ -176,16 +180,23 @@ def _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice):
 
 
 _SM_COUNT = {}
+_TILE_ROWS_MEMO = {}
 
 
 def _auto_tile_rows(n_rows: int, c_out: int, device) -> int:
     """Rows per tile of the tensor-core kernel (pce_tile_rows_for): 256-row tiles, which stage every
     weight block once for two accumulators, for narrow outputs on large maps, else 128."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    sms = _SM_COUNT.get(idx)
-    if sms is None:
-        sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    return int(lib.pce_tile_rows_for(n_rows, c_out, sms))
+    key = (n_rows, c_out, idx)
+    rows = _TILE_ROWS_MEMO.get(key)
+    if rows is None:
+        sms = _SM_COUNT.get(idx)
+        if sms is None:
+            sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+        if len(_TILE_ROWS_MEMO) > 4096:
+            _TILE_ROWS_MEMO.clear()
+        rows = _TILE_ROWS_MEMO[key] = int(lib.pce_tile_rows_for(n_rows, c_out, sms))
+    return rows
 
 
 def device_status(reset: bool = True) -> int:
