@@ -433,7 +433,7 @@ def run_ours(args):
         # off the other ranks' cores
         cores = sorted(os.sched_getaffinity(0))
         share = len(cores) // world
-        if share >= 2:
+        if share >= 4:  # a rank keeps four threads busy (its main thread and the planner's three)
             os.sched_setaffinity(0, cores[local * share:(local + 1) * share])
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
