@@ -101,3 +101,35 @@ def test_map_plan_specs_of_the_unet():
     import pytest
     with pytest.raises(ValueError):
         pce.MapPlan([(1, 1, False, 8, 8)])
+
+
+def test_nothing_is_planned_for_cpu_tensors_or_in_training():
+    """MinkUNet.plan starts a map construction only for CUDA tensors in eval mode; anything else is
+    left to the layers (which refuse CPU tensors themselves)."""
+    import torch
+
+    import pcengine_b200 as pce
+    coords = torch.zeros((8, 4), dtype=torch.int32)
+    coords[:, 1] = torch.arange(8, dtype=torch.int32)
+    x = pce.spTensor(torch.zeros(8, 4), coords, None, [0, 0, 0], [7, 0, 0], init_tag=pce.MinkUNet.tags())
+    model = pce.MinkUNet(4, 19, cr=0.25).eval()
+    assert model.plan(x) is False and x.planner is None
+    model.train()
+    assert model.plan(x) is False
+    model.plan_ahead = False
+    model.eval()
+    assert model.plan(x) is False
+
+
+def test_row_pitched_views():
+    """Which feature matrices the tensor-core kernel may address in place: fp16, rows contiguous, pitch a
+    multiple of 8 elements, 16-byte aligned start."""
+    import torch
+
+    from pcengine_b200.functional import _row_pitched
+    wide = torch.zeros((10, 64), dtype=torch.float16)
+    assert _row_pitched(wide) and _row_pitched(wide[:, 8:40]) and _row_pitched(wide[:, 16:])
+    assert not _row_pitched(wide[:, 3:35])          # start not 16-byte aligned
+    assert not _row_pitched(wide.t())               # rows not contiguous
+    assert not _row_pitched(torch.zeros((10, 12), dtype=torch.float16))  # pitch 12 is no multiple of 8
+    assert not _row_pitched(wide.float()[:, 8:40])  # fp32 goes through the CUDA-core kernel
