@@ -136,6 +136,8 @@ typedef struct pce_tile_lists {
 } pce_tile_lists;
 
 PCE_API const char* pce_strerror(int status);
+/* 100 * major + minor of this header's struct layouts (101: pce_epilogue.in_ld / out_ld,
+ * pce_tile_lists.settled); a binding checks it before it passes structs. */
 PCE_API int pce_version(void);
 /* cudaError_t of the most recent failing CUDA call made by this library on the
  * calling thread (0 if none). */

@@ -36,7 +36,7 @@ const char* pce_strerror(int status) {
   }
 }
 
-int pce_version(void) { return 100; }
+int pce_version(void) { return 101; }  // 101: pce_epilogue row pitches, pce_tile_lists.settled
 
 int pce_last_cuda_error(void) { return g_last_cuda_error; }
 
