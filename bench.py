@@ -621,7 +621,14 @@ def run_ours(args):
                 "share_of_step": k["t"] / (dt_prof if dt_prof > 0 else 1.0),
                 "tensor_tflops": k["flops"] / k["t"] / 1e12, "tensor_frac": k["flops"] / k["t"] / 1e12 / pk["tflops"],
                 "peak_source": pk["source"], "note": "sum of algorithmic bytes of every launch of this kernel in the "
-                "K steps run right after the timed ones / sum of their CUDA-event durations"}
+                "K steps run right after the timed ones / sum of their CUDA-event durations",
+                # DRAM bytes per launch of two of the step's launch shapes, from the ncu captures summarised under
+                # profiles/ (the aggregate over a step's 43 launch shapes has no single capture, hence traffic = null)
+                "traffic_captures": [
+                    {"layer": "subm 3x3x3 96->96, 486551 rows", "algorithmic_bytes": 194.0e6, "dram_bytes": 211.0e6,
+                     "profile": "profiles/conv_umma_subm3_96x96_lidar8.md"},
+                    {"layer": "subm 3x3x3 256->256, 486551 rows", "algorithmic_bytes": 508.4e6, "dram_bytes": 756.4e6,
+                     "profile": "profiles/conv_umma_other_shapes_lidar8.md"}]}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
