@@ -2,8 +2,10 @@
 (TEST INFRASTRUCTURE ONLY: imported by tests, the smoke check and the
 benchmark's CPU-baseline / reference legs, never by the product package).
 
-PARITY UNPINNED by reference artefacts (see oracle/kmap_oracle.py); pinned
-instead against dense ``torch.nn.functional.conv3d`` on small grids.
+PARITY PINNED: tests/test_ref_golden.py compares ``conv_forward`` with the fp32
+output of the reference's own ``conv_fwd_d2_cuda`` (fixtures tests/golden/ref_*.npz,
+written on a B200 by tests/golden/make_ref_golden.py) at rel-L2 <= 1e-5, and with
+dense ``torch.nn.functional.conv3d`` on small grids (tests/test_oracle_dense.py).
 
 Semantics restated: script/spconv.py:291-464 (dispatch, centre offset, bias,
 transposed = maps swapped), backend/spconv.cu:224-398 and the pair loop of

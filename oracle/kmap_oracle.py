@@ -4,12 +4,16 @@ This module is the parity checker for the CUDA map-build path.  Only the test
 suite, the smoke check and the benchmark's CPU-baseline leg may import it; the
 product package never does.
 
-PARITY UNPINNED: the reference ships no golden vectors, no known-answer tests
-and its only fixture and comparator are unavailable, and its code has no CPU
-path that could be executed without a GPU.  The pins this oracle has are
-(i) agreement with dense ``torch.nn.functional.conv3d`` on small grids
-(tests/test_oracle_dense.py) and (ii) the committed fixtures under
-tests/golden/ that were produced by this file.
+PARITY PINNED against the reference's own CUDA code: tests/golden/ref_*.npz hold
+what the reference's unmodified extension (compiled by oracle/build_ref.py, run on
+a B200 by tests/golden/make_ref_golden.py) returned from ``mapping_d2_cuda`` and
+``conv_fwd_d2_cuda`` for submanifold 3x3x3 and strided ks=3 / stride 2 layers, and
+tests/test_ref_golden.py checks this file against them bit for bit (output
+coordinates, indicator map, knnz, kpos, qkpos).  The reference ships no golden
+vectors or known-answer tests of its own.  Forms the reference does not compute
+correctly or deterministically (its ks == stride shortcut, odd ks >= 5 strided
+layers, atomics-ordered D1 positions) are pinned instead by agreement with dense
+``torch.nn.functional.conv3d`` on small grids (tests/test_oracle_dense.py).
 
 Every function cites the reference lines (paths relative to the reference
 project root) whose behaviour it restates.  Arithmetic is NumPy int64; nothing
