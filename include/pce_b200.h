@@ -201,7 +201,11 @@ PCE_API int pce_map_build_d2(const int32_t* in_coords, int32_t n_in, const int32
  * every GPU that loads the library holds until the process exits.
  *   - Limit: n_out <= 131072 output rows; more returns PCE_ERR_CAPACITY and launches nothing.
  *   - The first call on each device looks the array's address up; make that call during
- *     set-up, before any stream capture begins.  No call allocates or frees device memory.
+ *     set-up, before any stream capture begins.  No call allocates or frees device memory
+ *     itself; the CUDA runtime, however, may load a kernel's code the first time that kernel
+ *     is launched (lazy module loading) and take memory for it.  The kernels differ by map
+ *     kind, so the set-up calls should build one submanifold map with odd kernel sizes and
+ *     one strided map with map_out: after those two, later calls leave device memory as it is.
  *   - All calls on a device share the array and it keeps the previous call's contents (the
  *     part a call uses is cleared first), so two calls whose GPU work can overlap - different
  *     streams, or threads - race on it: serialise them on one stream. */

@@ -67,9 +67,54 @@ class _Net:
         return self._round(torch.relu(y + sc))
 
 
-def forward(state_dict, coords: np.ndarray, feats: torch.Tensor, act_dtype=torch.float16) -> torch.Tensor:
+WIDTHS = (32, 32, 64, 128, 256, 256, 128, 96, 96)
+
+
+def parameter_shapes(in_channels: int = 4, num_classes: int = 19, cr: float = 1.0) -> dict:
+    """Name -> shape of every entry of the network's state dict, written out from the architecture
+    (stem, four encoder and four decoder stages, classifier) without importing the product package;
+    tests/test_bench_cpu.py checks it against ``pcengine_b200.MinkUNet().state_dict()``."""
+    cs = [int(cr * c) for c in WIDTHS]
+    shapes = {}
+
+    def bn(prefix, c):
+        for name in ("weight", "bias", "running_mean", "running_var"):
+            shapes[f"{prefix}.{name}"] = (c,)
+        shapes[f"{prefix}.num_batches_tracked"] = ()
+
+    def conv_bn(prefix, cin, cout, kv):
+        shapes[f"{prefix}.conv.kernel"] = (kv, cin, cout)
+        bn(f"{prefix}.bn", cout)
+
+    def block(prefix, cin, cout):
+        shapes[f"{prefix}.conv1.kernel"] = (27, cin, cout)
+        bn(f"{prefix}.bn1", cout)
+        shapes[f"{prefix}.conv2.kernel"] = (27, cout, cout)
+        bn(f"{prefix}.bn2", cout)
+        if cin != cout:
+            shapes[f"{prefix}.short_conv.kernel"] = (cin, cout)
+            bn(f"{prefix}.short_bn", cout)
+
+    conv_bn("stem.0", in_channels, cs[0], 27)
+    conv_bn("stem.1", cs[0], cs[0], 27)
+    for i in range(4):
+        conv_bn(f"down.{i}", cs[i], cs[i], 8)
+        block(f"enc.{i}.0", cs[i], cs[i + 1])
+        block(f"enc.{i}.1", cs[i + 1], cs[i + 1])
+    skips = [cs[3], cs[2], cs[1], cs[0]]
+    for i in range(4):
+        conv_bn(f"up.{i}", cs[4 + i], cs[5 + i], 8)
+        block(f"dec.{i}.0", cs[5 + i] + skips[i], cs[5 + i])
+        block(f"dec.{i}.1", cs[5 + i], cs[5 + i])
+    shapes["classifier.kernel"] = (cs[8], num_classes)
+    shapes["classifier.bias"] = (num_classes,)
+    return shapes
+
+
+def forward(state_dict, coords: np.ndarray, feats: torch.Tensor, act_dtype=torch.float16, return_maps: bool = False):
     """Logits [N, classes] (fp32 values rounded to ``act_dtype``) of the network whose
-    parameters are ``state_dict`` (keys as produced by pcengine_b200.minkunet.MinkUNet)."""
+    parameters are ``state_dict`` (keys as produced by pcengine_b200.minkunet.MinkUNet).  With
+    ``return_maps`` also the kernel maps the pass built: {("subm", level): d2, ("down", level): d2}."""
     net = _Net(state_dict, coords, act_dtype)
     x = net._round(feats.float())
     x = net.conv_bn_relu(x, "stem.0", 0, "subm")
@@ -86,5 +131,9 @@ def forward(state_dict, coords: np.ndarray, feats: torch.Tensor, act_dtype=torch
         x = torch.cat([x, skips[lvl]], dim=1)
         x = net.res_block(x, f"dec.{i}.0", lvl)
         x = net.res_block(x, f"dec.{i}.1", lvl)
-    out = co.pointwise_conv(x, net.sd["classifier.kernel"], net.sd["classifier.bias"])
-    return net._round(out)
+    out = net._round(co.pointwise_conv(x, net.sd["classifier.kernel"], net.sd["classifier.bias"]))
+    if return_maps:
+        maps = {("subm", lvl): m for (lvl, _ks), m in net.subm.items()}
+        maps.update({("down", lvl): m for lvl, m in net.down.items()})
+        return out, maps
+    return out

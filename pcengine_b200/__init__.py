@@ -6,7 +6,7 @@ from . import _lib  # noqa: F401  (loads the shared library, raises when missing
 from . import backend, functional  # noqa: F401
 from .activation import LeakyReLU, ReLU
 from .batchnorm import BatchNorm, bn_scale_shift
-from .functional import FusedEpilogue
+from .functional import FusedEpilogue, invalidate_packed
 from .kmap import KernelMap
 from .minkunet import MinkUNet, randomize_batchnorm
 from .planner import MapPlan

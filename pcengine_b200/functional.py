@@ -45,6 +45,12 @@ class FusedEpilogue:
         self.extra_feats, self.extra_weight = extra_feats, extra_weight
         self.push_slots, self.push_bases = push_slots, push_bases
 
+    def replace(self, **fields) -> "FusedEpilogue":
+        """A copy with ``fields`` replaced and every other field carried over."""
+        kw = {name: getattr(self, name) for name in self.__slots__}
+        kw.update(fields)
+        return FusedEpilogue(**kw)
+
     def pack(self, c_out: int, n_out: int, dtype) -> _lib.Epilogue:
         e = _lib.Epilogue()
         for name in ("scale", "shift"):
@@ -136,6 +142,21 @@ def packed_weights(kernel: torch.Tensor, as_linear: bool = False) -> Optional[to
     return out
 
 
+def invalidate_packed(module_or_tensor) -> None:
+    """Drop the cached tensor-core layouts (packed, padded) of a weight tensor or of every parameter
+    of a module.  The caches are keyed by the tensor's version counter and address, which in-place
+    writes through ``param.copy_`` or ``load_state_dict`` advance; writes through ``.data`` (``param.data.copy_``,
+    ``param.data.uniform_``) do not, so call this after them."""
+    tensors = [module_or_tensor] if isinstance(module_or_tensor, torch.Tensor) else list(module_or_tensor.parameters())
+    for t in tensors:
+        for name in ("_pce_packed", "_pce_padded"):
+            if hasattr(t, name):
+                try:
+                    delattr(t, name)
+                except AttributeError:
+                    pass
+
+
 def _ceil16(c: int) -> int:
     return (int(c) + 15) // 16 * 16
 
@@ -167,7 +188,10 @@ def _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice):
     if feats.dtype != torch.float16 or kernel_choice == "simt" or (cin_p == c_in and cout_p == c_out) \
             or cout_p > 256 or kv > 128:
         return feats, kernel, epilogue, False
-    if cout_p != c_out and epilogue is not None and epilogue.residual is not None:
+    if cout_p != c_out and epilogue is not None and (epilogue.residual is not None or epilogue.extra_feats is not None
+                                                     or epilogue.push_slots is not None):
+        # operands shaped like the output (residual, second operand's weights, halo rows) are not
+        # widened here: such a layer keeps its channel count and runs on the CUDA-core kernel
         return feats, kernel, epilogue, False
     kernel = _padded_kernel(kernel, cin_p, cout_p)
     if cin_p != c_in:  # (torch.nn.functional.pad costs 0.3 ms of host time here; cat does not)
@@ -175,7 +199,7 @@ def _pad_for_tensor_cores(feats, kernel, epilogue, kernel_choice):
     if cout_p != c_out and epilogue is not None:
         def widen(t):
             return None if t is None else torch.cat([t, t.new_zeros((cout_p - c_out,))])
-        epilogue = FusedEpilogue(widen(epilogue.scale), widen(epilogue.shift), None, epilogue.act, epilogue.slope)
+        epilogue = epilogue.replace(scale=widen(epilogue.scale), shift=widen(epilogue.shift))
     return feats, kernel, epilogue, True
 
 

@@ -246,3 +246,6 @@ def randomize_batchnorm(model: nn.Module, seed: int = 0) -> None:
             m.running_var.copy_(0.8 + 0.4 * torch.rand(n, generator=g))
             m.weight.data.copy_(0.8 + 0.4 * torch.rand(n, generator=g))
             m.bias.data.copy_((torch.rand(n, generator=g) - 0.5) * 0.2)
+    for m in model.modules():
+        if isinstance(m, _Fusable):
+            m._folded = {}  # constants folded from the old statistics

@@ -77,6 +77,7 @@ class conv3d(nn.Module):
         self.kernel.data.uniform_(-bound, bound)
         if self.bias is not None:
             self.bias.data.uniform_(-bound, bound)
+        PF.invalidate_packed(self.kernel)  # a write through .data does not advance the version the cache keys on
 
     def forward(self, input: spTensor, epilogue: Optional[FusedEpilogue] = None,
                 out: Optional[torch.Tensor] = None) -> spTensor:
@@ -98,18 +99,27 @@ def _with_bias(epilogue: Optional[FusedEpilogue], bias) -> Optional[FusedEpilogu
     shift = b * epilogue.scale if epilogue.scale is not None else b
     if epilogue.shift is not None:
         shift = shift + epilogue.shift
-    return FusedEpilogue(epilogue.scale, shift.contiguous(), epilogue.residual, epilogue.act, epilogue.slope)
+    return epilogue.replace(shift=shift.contiguous())  # every other field (second operand, halo push) is kept
 
 
-def _choose_dataflow(tag: str, in_channel: int, out_channel: int) -> str:
-    """'D1' / 'D2' are taken as given; 'auto' is the adaptive choice.  On B200 the fused
-    output-stationary kernel (D2) was measured faster than gather -> GEMM -> scatter (D1) at every
-    channel width of the indoor sweep (16..256) and on the LiDAR layers, because D1 moves
-    2*(C_in + C_out)*pairs extra elements through memory; the selector therefore picks D2 and keeps D1
-    for the cases D2's kernels do not cover well: fp32 layers with both widths above 64, where the
-    CUDA-core D2 kernel is compute bound and D1's buffer GEMM is no worse."""
+# Measured crossover of the two dataflows on B200 (kernel-only, L2 flushed; see bench.py --workload
+# indoor and profiles/selector_sweep.md).  The explicit dataflow moves 2*(C_in + C_out)*pairs extra
+# elements through HBM; the fused one re-stages weight blocks per tile, which costs more the fewer rows
+# share a tile's offsets.  Entries: (dtype is fp16, min C_in, min C_out, min pairs per row, max rows) -> "D1".
+_D1_WINS = ()
+
+
+def _choose_dataflow(tag: str, in_channel: int, out_channel: int, pairs_per_row: Optional[float] = None,
+                     n_rows: Optional[int] = None, dtype=None) -> str:
+    """'D1' / 'D2' are taken as given; 'auto' is the adaptive choice from channel widths, sparsity
+    (pairs per output row) and map size, looked up in the measured table ``_D1_WINS``; where the table
+    has no entry the fused output-stationary dataflow (D2) runs."""
     if tag != "auto":
         return tag
+    for is_half, c_in_min, c_out_min, ppr_min, rows_max in _D1_WINS:
+        if ((dtype == torch.float16) == is_half and in_channel >= c_in_min and out_channel >= c_out_min
+                and (pairs_per_row is None or pairs_per_row >= ppr_min) and (n_rows is None or n_rows <= rows_max)):
+            return "D1"
     return "D2"
 
 

@@ -111,7 +111,7 @@ def test_gather_mm_scatter_flow(dtype, cin, cout, ks, stride):
     conv_fwd_d1_cuda(feats.to(dev), kernel.to(dev), _enc([ks] * 3), qsum, out, kpos, qkpos, imap, omap, icsr, ocsr,
                      buffer, subm, 1)
     ref = co.conv_forward(feats, kernel, d2)
-    assert co.rel_l2(out.float().cpu(), ref) <= (2e-3 if dtype == torch.half else 1e-5)
+    assert co.rel_l2(out.float().cpu(), ref) <= (1e-3 if dtype == torch.half else 1e-5)
 
 
 def test_backward_entry_point_raises():

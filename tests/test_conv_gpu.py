@@ -459,7 +459,7 @@ def test_explicit_dataflow_d1(dtype, cin, cout):
     assert km.dataflow == "D1"
     d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     ref = co.conv_forward(feats, conv.kernel.detach().cpu(), d2, bias=conv.bias.detach().cpu())
-    tol = 1e-5 if dtype == torch.float32 else 2e-3  # products are rounded to fp16 in the buffer
+    tol = TOL[dtype]
     assert co.rel_l2(y.feats.float().cpu(), ref) <= tol
     assert torch.equal(conv(x).feats, y.feats)
     down = pce.conv3d(cout, cin, 2, 2).cuda().to(dtype)
@@ -518,3 +518,45 @@ def test_negative_coordinates_and_large_batch_index():
     kd = pce.KernelMap(torch.from_numpy(coords).cuda(), (2, 2, 2), (2, 2, 2), (0, 0, 0), cmin, ds["cmax_out"], False)
     assert np.array_equal(kd.out_coords.cpu().numpy(), ds["out_coords"])
     assert np.array_equal(kd.map.cpu().numpy(), ds["map"].reshape(-1))
+
+
+def test_bias_keeps_the_second_operand_of_the_epilogue():
+    """conv3d(bias=True) called with an epilogue that carries a second operand (a block's shortcut):
+    the bias folds into the shift and the second operand still joins the sum."""
+    import pcengine_b200 as pce
+    from pcengine_b200.functional import FusedEpilogue
+    coords = surface_cloud(71, 40)
+    torch.manual_seed(4)
+    feats = torch.randn(len(coords), 32).half()
+    extra = torch.randn(len(coords), 16).half()
+    w2 = (torch.randn(16, 32) / 4).half()
+    scale = (0.5 + torch.rand(32)).float()
+    conv = pce.conv3d(32, 32, 3, bias=True).cuda().half()
+    x = _tensor(pce, coords, feats)
+    ep = FusedEpilogue(scale=scale.cuda(), act="relu", extra_feats=extra.cuda(), extra_weight=w2.cuda())
+    y = conv(x, epilogue=ep)
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    acc = co.conv_forward(feats, conv.kernel.detach().cpu(), d2) + extra.float() @ w2.float()
+    want = torch.relu((acc + conv.bias.detach().float().cpu()) * scale)
+    assert co.rel_l2(y.feats.float().cpu(), want) <= 1e-3
+
+
+def test_weights_rewritten_through_data_need_invalidate_packed():
+    """The tensor-core layout of a weight tensor is cached on it; a write through ``.data`` does not
+    advance the version the cache is keyed on, so ``invalidate_packed`` is part of that recipe."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(72, 40)
+    torch.manual_seed(5)
+    feats = torch.randn(len(coords), 64).half()
+    conv = pce.conv3d(64, 64, 3).cuda().half()
+    d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+    y0 = conv(_tensor(pce, coords, feats)).feats.clone()
+    new_w = (torch.randn(27, 64, 64) / 40).half()
+    conv.kernel.data.copy_(new_w.cuda())
+    pce.invalidate_packed(conv)
+    y1 = conv(_tensor(pce, coords, feats)).feats
+    assert co.rel_l2(y1.float().cpu(), co.conv_forward(feats, new_w, d2)) <= 1e-3
+    assert not torch.equal(y0, y1)
+    conv.reset_parameters()  # rewrites through .data and drops the cached layout itself
+    y2 = conv(_tensor(pce, coords, feats)).feats
+    assert co.rel_l2(y2.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3

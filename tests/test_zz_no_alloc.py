@@ -84,6 +84,47 @@ def test_noalloc_map_equals_workspace_map_on_consecutive_calls():
         assert ref["kpos"][-1] == len(coords)  # every input has exactly one parent
 
 
+def test_noalloc_leaves_device_memory_as_it_is_and_takes_its_full_capacity():
+    """After set-up calls of both map kinds (which also let the runtime load every kernel the entry
+    point launches), further calls change nothing in the device's free memory; 131072 rows, the
+    stated limit, are accepted and give the workspace builder's map."""
+    from pcengine_b200 import _lib
+    from pcengine_b200.kmap import make_geom
+    lib = _lib.lib
+    dev = torch.device("cuda:0")
+    n = 131072
+    rng = np.random.default_rng(5)
+    lin = rng.choice(96 ** 3, n, replace=False)
+    coords = np.stack([np.zeros(n, np.int64), lin // (96 * 96), (lin // 96) % 96, lin % 96], 1).astype(np.int32)
+    cd = torch.from_numpy(coords).to(dev)
+    oc = torch.from_numpy(np.unique(np.concatenate([coords[:, :1], coords[:, 1:] // 2], 1), axis=0)).to(dev)
+    g = make_geom((3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], [95, 95, 95], True)
+    g2 = make_geom((2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], [47, 47, 47], False)
+    st = torch.cuda.current_stream().cuda_stream
+    outs = dict(map=torch.empty((27 * n,), dtype=torch.int32, device=dev), small=torch.empty((28,), dtype=torch.int32, device=dev),
+                map2=torch.empty((8 * n,), dtype=torch.int32, device=dev), map2_out=torch.empty((8 * oc.size(0),), dtype=torch.int32, device=dev))
+    knnz, kpos, qkpos = (torch.empty((28,), dtype=torch.int32, device=dev) for _ in range(3))
+
+    def both_kinds():
+        rc = lib.pce_map_build_d2_noalloc(cd.data_ptr(), n, cd.data_ptr(), n, C.byref(g), outs["map"].data_ptr(), knnz.data_ptr(),
+                                          kpos.data_ptr(), qkpos.data_ptr(), None, None, st)
+        assert rc == 0, lib.pce_strerror(rc)
+        rc = lib.pce_map_build_d2_noalloc(cd.data_ptr(), n, oc.data_ptr(), oc.size(0), C.byref(g2), outs["map2"].data_ptr(),
+                                          knnz.data_ptr(), kpos.data_ptr(), qkpos.data_ptr(), outs["map2_out"].data_ptr(), None, st)
+        assert rc == 0, lib.pce_strerror(rc)
+        torch.cuda.synchronize()
+
+    both_kinds()  # set-up
+    free0, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(3):
+        both_kinds()
+    free1, _ = torch.cuda.mem_get_info(dev)
+    assert free1 == free0
+    ref = _build(lib, _lib, cd, cd, g, 27, False, False)
+    got = _build(lib, _lib, cd, cd, g, 27, True, False)
+    _same(ref, got)
+
+
 def test_noalloc_rejects_more_rows_than_its_table_holds():
     from pcengine_b200 import _lib
     from pcengine_b200.kmap import make_geom
