@@ -106,12 +106,14 @@ typedef struct pce_epilogue {
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output
- * rows in bitmask-sorted `order`, cut into tiles of tile_rows (128 or 256); tile t
+ * rows in bitmask-sorted `order`, cut into tiles of tile_rows (128, 256 or 512); tile t
  * owns the stages tile_ptr[t] .. tile_ptr[t+1]-1, one per offset that any of its rows
- * has; stage g applies offset stage_kp[g] and fetches input row
+ * has; stage g applies offset stage_kp[g] & 255 and fetches input row
  * stage_nbr[g*tile_rows + r] for the tile's r-th row (-1: that row lacks the offset).
- * A 256-row tile is two 128-row tensor-memory accumulators fed by one staged weight
- * block.  With identity_stage = 1 every tile ends with one more stage, stage_kp = -1, whose
+ * A tile of 256 or 512 rows is two or four 128-row sub-tiles, each with its own
+ * tensor-memory accumulator, fed by one staged weight block; with slots = 1, bit 8+s of
+ * stage_kp[g] says whether sub-tile s has a row with the offset (a sub-tile without one
+ * neither gathers nor multiplies for that stage).  With identity_stage = 1 every tile ends with one more stage, stage_kp = -1, whose
  * entry for a row is the row itself: where pce_epilogue.extra_feats joins the accumulation
  * (a launch without a second operand skips it).  With slots = 2 or 4 a stage holds that
  * many of the tile's offsets (stage_kp[g*slots + q], stage_nbr[(g*slots + q)*tile_rows + r],
@@ -125,7 +127,7 @@ typedef struct pce_tile_lists {
   const int32_t* tile_ptr;  /* [ceil(n_rows/tile_rows) + 1] */
   const int32_t* stage_kp;  /* [stages] */
   const int32_t* stage_nbr; /* [stages * tile_rows] */
-  int32_t tile_rows;        /* 128 or 256 */
+  int32_t tile_rows;        /* 128, 256 or 512 (512: slots = 1 only) */
   int32_t identity_stage;   /* 0 or 1 */
   int32_t slots;            /* offsets per stage: 1, 2 or 4 */
   int32_t settled;          /* non-zero: the lists were complete before the kernel that precedes this
@@ -286,7 +288,7 @@ PCE_API int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, 
                               size_t workspace_bytes, int32_t* order, void* stream);
 
 /* Fills the arrays of a pce_tile_lists from the neighbour CSR and a row order (NULL =
- * natural order) for tiles of tile_rows = 128 or 256 rows.  tile_ptr needs
+ * natural order) for tiles of tile_rows = 128, 256 or 512 rows.  tile_ptr needs
  * ceil(n_rows/tile_rows)+1 entries; stage_kp / stage_nbr have room for stage_cap stages of
  * `slots` entries each (tiles*(ceil(kv/slots) + identity_stage) always suffices; the stage
  * count ends up in tile_ptr[last]).  kv <= 128.
@@ -310,12 +312,20 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * 2) of the dense product, which has no tile lists to fix it; what = 2: accumulator sets in
  * tensor memory (1 or 2); what = 3: programmatic dependent launch of the tensor-core kernel (its
  * set-up overlaps the tail of the kernel before it in the stream; 1 = on, the default, 0 = off,
- * 2 = on, but tile lists are never read before that kernel has finished). */
+ * 2 = on, but tile lists are never read before that kernel has finished); what = 4: 1 runs
+ * layers with one offset per stage on the kernel with several accumulators per CTA and decoupled
+ * row / weight rings (k_conv_umma_mt), 0 (default) on the one-accumulator kernel, which measured
+ * faster; tile lists of 512 rows always run on the former. */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
  * bounded wait expired records PCE_ERR_TIMEOUT.  SYNCHRONISES the device. */
 PCE_API int pce_device_status(int32_t* status_host, int32_t reset);
+
+/* Diagnostics for PCE_ERR_TIMEOUT: where the first bounded wait since the last call gave up, as
+ * {code, CTA, item, phase parity} (code = role | sub-tile << 4 | tile-in-CTA << 8; roles are listed
+ * beside g_umma_where in csrc/conv_umma.cu); all zero when no wait expired.  Reads and clears. */
+PCE_API int pce_debug_timeout(int32_t* where4);
 
 /* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
  * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */
@@ -407,11 +417,12 @@ typedef struct pce_planned_map {
 typedef struct pce_plan pce_plan; /* specs + planning thread + stream + recycled storage */
 typedef struct pce_pass pce_pass; /* the maps of one network pass; device memory owned by it */
 
-/* Rows per tile (128 or 256) the engine uses for a layer of n_rows outputs and c_out
- * channels on a GPU with sm_count SMs: 256-row tiles stage every weight block once for two
- * accumulators but halve the tiles in flight; they pay off only for narrow outputs on maps
- * large enough to give every CTA several tiles. */
-PCE_API int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_out, int32_t sm_count);
+/* Rows per tile the engine uses for a layer of n_rows outputs with c_in / c_out channels on a
+ * GPU with sm_count SMs: 128, or 256 for layers with 16 or 32 input channels and at most 32
+ * output channels on maps large enough to give every CTA several tiles (taller tiles stage every
+ * weight block once for two or four accumulators but leave fewer independent tiles in flight per
+ * SM, which measured slower from 64 input channels up). */
+PCE_API int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t sm_count);
 
 /* Binds to the current device; starts the planning thread. */
 PCE_API int pce_plan_create(const pce_plan_map_spec* specs, int32_t n_specs, pce_plan** plan);

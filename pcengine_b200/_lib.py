@@ -11,7 +11,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libpce_b200.so")
+# PCE_B200_LIB: path of an alternative build of the library (an instrumented or debug build)
+LIB_PATH = os.environ.get("PCE_B200_LIB") or os.path.join(_HERE, "libpce_b200.so")
 
 PCE_OK = 0
 PCE_ERR_INVALID = 1
@@ -24,7 +25,7 @@ EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
-    "pce_pack_weights", "pce_device_status", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
+    "pce_pack_weights", "pce_device_status", "pce_debug_timeout", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
     "pce_quantize_workspace_bytes", "pce_quantize_unique", "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release",
 ]
 
@@ -104,6 +105,7 @@ def _load() -> C.CDLL:
     lib.pce_pack_weights.argtypes = [vp, i32, i32, i32, i32, vp, vp]
     lib.pce_device_status.argtypes = [C.POINTER(i32), i32]
     lib.pce_tune.argtypes = [i32, i32]
+    lib.pce_debug_timeout.argtypes = [C.POINTER(i32)]
     lib.pce_conv_kernel_choice.argtypes = [i32, i32, i32, i32]
     lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
                                     C.POINTER(Epilogue), vp]
@@ -113,7 +115,7 @@ def _load() -> C.CDLL:
     lib.pce_quantize_workspace_bytes.argtypes = [i32]
     lib.pce_quantize_unique.argtypes = [vp, i32, C.POINTER(C.c_float), i32, vp, sz, vp, vp, vp, C.POINTER(i32), vp]
     lib.pce_tile_rows_for.restype = i32
-    lib.pce_tile_rows_for.argtypes = [i32, i32, i32]
+    lib.pce_tile_rows_for.argtypes = [i32, i32, i32, i32]
     lib.pce_plan_create.argtypes = [C.POINTER(PlanMapSpec), i32, C.POINTER(vp)]
     lib.pce_plan_destroy.restype = None
     lib.pce_plan_destroy.argtypes = [vp]

@@ -9,10 +9,12 @@ bool conv_umma_supported(int cin, int cout, int dtype);
 size_t umma_packed_bytes(int kv, int cin, int cout);
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st);
 int umma_status_fetch(int* host_status, bool reset);
+int umma_where_fetch(int* host4);
 extern int umma_force_stages;
 extern int umma_force_sub;
 extern int umma_force_nacc;
 extern int umma_overlap_launches;
+extern int umma_multi_tile;
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -77,6 +79,10 @@ int pce_tune(int32_t what, int32_t value) {
     umma_overlap_launches = value < 0 || value > 2 ? 1 : value;
     return PCE_OK;
   }
+  if (what == 4) {
+    umma_multi_tile = value ? 1 : 0;
+    return PCE_OK;
+  }
   return PCE_ERR_INVALID;
 }
 
@@ -86,6 +92,11 @@ int pce_device_status(int32_t* status_host, int32_t reset) {
   PCE_TRY(umma_status_fetch(&v, reset != 0));
   *status_host = v;
   return PCE_OK;
+}
+
+int pce_debug_timeout(int32_t* where4) {
+  if (!where4) return PCE_ERR_INVALID;
+  return umma_where_fetch(where4);
 }
 
 int pce_conv_fwd(const void* in_feats, int32_t n_in, int32_t c_in, const void* weights, const void* packed_weights,

@@ -2,9 +2,10 @@
 // (role of ConvolutionForwardD1, ref: backend/spconv.cu:24-222).  Buffer rows
 // are addressed as qkpos[kp] + pos with (kp, pos) decoded from the CSR-coded
 // maps (kp*1186111 + pos, ref: backend/hash.cuh:7-9); row/element offsets are
-// 64-bit.  The scatter pass sums each output row's products in kp order, adds
-// the centre offset product for a submanifold layer, applies the fused
-// epilogue and stores the row once.
+// 64-bit.  The scatter pass (one warp per output row, 16-byte pieces, fp32
+// sums) adds each row's products in kp order and the centre offset product of a
+// submanifold layer (a dense product on the tensor-core kernel beforehand where
+// the widths allow), applies the fused epilogue and stores the row once.
 #include "common.cuh"
 
 namespace pce {
@@ -122,35 +123,87 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// One thread per (output row, channel): fp32 sum over the row's buffer rows,
-// plus the centre product, then the epilogue
+// One warp per output row, lanes over 16-byte pieces of the row: fp32 sums over the row's buffer rows
+// (kp ascending, as the CSR lists them), plus the centre product -- read from `centre` when the
+// tensor-core kernel computed it as a dense product beforehand, else formed here from W[centre] --
+// then the epilogue and one 16-byte store per piece
 // (ref: backend/spconv.cuh:337-422 scatter_all_output_major_csr_*).
 template <typename T>
-__global__ void k_d1_scatter(const T* __restrict__ bout, const int* __restrict__ qkpos,
-                             const int* __restrict__ ocsr, const int* __restrict__ omap, int n_out, int cout,
-                             const T* __restrict__ in, const T* __restrict__ wmid, int cin, T* __restrict__ out,
-                             EpiDev ep) {
-  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int row = static_cast<int>(t / cout);
-  const int c = static_cast<int>(t % cout);
+__global__ void __launch_bounds__(256)
+    k_d1_scatter(const T* __restrict__ bout, const int* __restrict__ qkpos, const int* __restrict__ ocsr,
+                 const int* __restrict__ omap, int n_out, int cout, const T* __restrict__ in, const T* __restrict__ wmid,
+                 const T* centre, int cin, T* out, EpiDev ep) {
+  constexpr int kVec = 16 / static_cast<int>(sizeof(T));  // elements per 16-byte piece
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
   if (row >= n_out) return;
-  float acc = 0.f;
   const int a = __ldg(ocsr + row), b = __ldg(ocsr + row + 1);
-  for (int e = a; e < b; ++e) {
-    const int code = __ldg(omap + e);
-    const size_t pos = static_cast<size_t>(__ldg(qkpos + code / kCode)) + code % kCode;
-    acc += d1_to_f(bout[pos * cout + c]);
+  const bool vec = (cout % kVec == 0) &&
+                   ((reinterpret_cast<uintptr_t>(bout) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(centre) |
+                     reinterpret_cast<uintptr_t>(ep.residual)) % 16 == 0);
+  const int pieces = vec ? cout / kVec : (cout + kVec - 1) / kVec;
+  for (int p0 = 0; p0 < pieces; p0 += 32) {
+    const int p = p0 + lane;
+    const int c0 = p * kVec;
+    float acc[kVec];
+#pragma unroll
+    for (int q = 0; q < kVec; ++q) acc[q] = 0.f;
+    if (p < pieces) {
+      for (int e = a; e < b; ++e) {
+        const int code = __ldg(omap + e);
+        const size_t pos = static_cast<size_t>(__ldg(qkpos + code / kCode)) + code % kCode;
+        const T* src = bout + pos * cout + c0;
+        if (vec) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src);
+          const T* t = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int q = 0; q < kVec; ++q) acc[q] += d1_to_f(t[q]);
+        } else {
+          for (int q = 0; q < kVec && c0 + q < cout; ++q) acc[q] += d1_to_f(src[q]);
+        }
+      }
+      if (centre != nullptr) {
+        const T* src = centre + static_cast<size_t>(row) * cout + c0;
+        if (vec) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src);
+          const T* t = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int q = 0; q < kVec; ++q) acc[q] += d1_to_f(t[q]);
+        } else {
+          for (int q = 0; q < kVec && c0 + q < cout; ++q) acc[q] += d1_to_f(src[q]);
+        }
+      } else if (wmid != nullptr) {
+        const T* x = in + static_cast<size_t>(row) * cin;
+        for (int ci = 0; ci < cin; ++ci) {
+          const float xv = d1_to_f(x[ci]);
+          const T* wr = wmid + static_cast<size_t>(ci) * cout + c0;
+#pragma unroll
+          for (int q = 0; q < kVec; ++q)
+            if (c0 + q < cout) acc[q] = fmaf(xv, d1_to_f(wr[q]), acc[q]);
+        }
+      }
+      alignas(16) T res[kVec];
+#pragma unroll
+      for (int q = 0; q < kVec; ++q) {
+        const int c = c0 + q;
+        float v = acc[q];
+        if (c < cout) {
+          if (ep.scale) v *= __ldg(ep.scale + c);
+          if (ep.shift) v += __ldg(ep.shift + c);
+          if (ep.residual) v += d1_to_f(static_cast<const T*>(ep.residual)[static_cast<size_t>(row) * cout + c]);
+          if (ep.act == PCE_ACT_RELU) v = v > 0.f ? v : 0.f;
+          if (ep.act == PCE_ACT_LEAKY) v = v > 0.f ? v : v * ep.slope;
+        }
+        res[q] = d1_from_f<T>(v);
+      }
+      T* dst = out + static_cast<size_t>(row) * cout + c0;
+      if (vec) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(res);
+      } else {
+        for (int q = 0; q < kVec && c0 + q < cout; ++q) dst[q] = res[q];
+      }
+    }
   }
-  if (wmid != nullptr) {
-    const T* x = in + static_cast<size_t>(row) * cin;
-    for (int ci = 0; ci < cin; ++ci) acc = fmaf(d1_to_f(x[ci]), d1_to_f(wmid[static_cast<size_t>(ci) * cout + c]), acc);
-  }
-  if (ep.scale) acc *= __ldg(ep.scale + c);
-  if (ep.shift) acc += __ldg(ep.shift + c);
-  if (ep.residual) acc += d1_to_f(static_cast<const T*>(ep.residual)[static_cast<size_t>(row) * cout + c]);
-  if (ep.act == PCE_ACT_RELU) acc = acc > 0.f ? acc : 0.f;
-  if (ep.act == PCE_ACT_LEAKY) acc = acc > 0.f ? acc : acc * ep.slope;
-  out[static_cast<size_t>(row) * cout + c] = d1_from_f<T>(acc);
 }
 
 template <typename T>
@@ -196,10 +249,27 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, const void* 
     }
   }
   if (n_out > 0) {
-    if (centre_kp >= 0 && w == nullptr) return PCE_ERR_INVALID;
-    const T* wmid = centre_kp >= 0 ? w_t + static_cast<size_t>(centre_kp) * cin * cout : nullptr;
-    k_d1_scatter<T><<<div_up(static_cast<long long>(n_out) * cout, 256), 256, 0, st>>>(
-        bout, qkpos, ocsr, omap, n_out, cout, in_t, wmid, cin, static_cast<T*>(out), ep);
+    const T* wmid = nullptr;
+    const T* centre = nullptr;
+    if (centre_kp >= 0) {
+      // the centre offset is a dense rows x matrix product: on the tensor-core kernel when the packed
+      // weights allow it (written into `out`, which the scatter then reads row by row and overwrites),
+      // else formed inside the scatter from W[centre]
+      const int kblocks = (cin + 63) / 64;
+      const bool tc_centre = wpacked != nullptr && conv_umma_supported(cin, cout, dtype) &&
+                             ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(wpacked)) % 16 == 0);
+      if (tc_centre) {
+        const __half* wp = static_cast<const __half*>(wpacked) + static_cast<size_t>(centre_kp) * kblocks * cout * 64;
+        PCE_TRY(conv_umma(in, n_in, wp, 1, nullptr, n_out, cin, cout, out, nullptr, st));
+        centre = static_cast<const T*>(out);
+      } else {
+        if (w == nullptr) return PCE_ERR_INVALID;
+        wmid = w_t + static_cast<size_t>(centre_kp) * cin * cout;
+      }
+    }
+    k_d1_scatter<T><<<div_up(static_cast<long long>(n_out) * 32, 256), 256, 0, st>>>(
+        qsum > 0 ? bout : nullptr, qkpos, ocsr, omap, n_out, cout, in_t, wmid, centre, cin, static_cast<T*>(out), ep);
     PCE_LAUNCH_CHECK();
   }
   return PCE_OK;

@@ -45,6 +45,11 @@
 namespace pce {
 
 __device__ int g_umma_status = 0;
+// Where the first bounded wait of a launch gave up: {code, CTA, item, extra}; code = role | sub-tile << 4 |
+// tile-in-CTA << 8 with role 1 producer/row slot free, 2 loader/weight slot free, 3 MMA/weights landed,
+// 4 MMA/accumulator drained, 5 MMA/rows landed, 6 MMA/accumulator drained (nothing written), 7 epilogue/
+// accumulator complete (k_conv_umma_mt), 9 any wait of k_conv_umma.
+__device__ int g_umma_where[4] = {0, 0, 0, 0};
 
 namespace umma {
 
@@ -124,7 +129,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait: false when the abort flag is up or the deadline passed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, SharedCtl* ctl) {
+template <class Ctl>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, int where = 9, int item = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
@@ -134,6 +140,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, SharedC
       if (clock64() - t0 > kWaitCycles) {
         ctl->abort_flag = 1;
         atomicMax(&g_umma_status, PCE_ERR_TIMEOUT);
+        if (atomicCAS(&g_umma_where[0], 0, where) == 0) {
+          g_umma_where[1] = static_cast<int>(blockIdx.x);
+          g_umma_where[2] = item;
+          g_umma_where[3] = static_cast<int>(parity);
+        }
         return false;
       }
     }
@@ -350,6 +361,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         if (ls.tile_ptr) {
           nid = __ldg(ls.stage_nbr + static_cast<size_t>(g) * kRows + tid);
           kp = __ldg(ls.stage_kp + g);
+          if (kp >= 0) kp &= 255;  // bits 8.. hold the sub-tile presence mask (read by k_conv_umma_mt)
         } else {  // dense product: stage g is tile g, every row fetches itself at offset 0
           const int row = g * kRows + tid;
           nid = row < n_out ? row : -1;
@@ -690,6 +702,423 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   }
 }
 
+
+// =====================================================================================================
+// k_conv_umma_mt: several accumulators per CTA, offsets taken in offset-major order, row ring and weight
+// ring decoupled.
+//
+// A super-tile is SUB (1, 2 or 4) consecutive 128-row sub-tiles of the processing order, each with its own
+// accumulator in tensor memory.  The tile lists of a super-tile name every offset that any of its rows has,
+// with a presence bit per sub-tile (stage_kp bits 8..).  Per listed offset and 64-channel K block the weight
+// block is staged ONCE (weight ring, nb slots of C_out x 128 B, one bulk async copy each) and multiplied
+// with the gathered rows of every sub-tile that has the offset (row ring, na slots of 128 rows x 128 B).
+// Against one ring stage = rows + weights per (128-row tile, offset) this
+//   * divides the weight traffic from L2 by the number of sub-tiles that share an offset (rows are sorted
+//     by indicator bitmask, so neighbouring sub-tiles share most of theirs), and
+//   * frees the shared memory that every stage spent on its own weight copy for row slots: what limits
+//     the fused kernel is the number of row gathers in flight per SM (a ring slot is occupied for about
+//     3 us from the first copy instruction to the release by the tensor core).
+// Warps: 4*SUB producers (one thread per row of the super-tile; the four warps of a sub-tile fill that
+// sub-tile's row slots), one MMA warp (one lane issues), one weight-loader warp (one lane), 4*EPIW
+// epilogue warps (EPIW teams; team e drains the accumulators of sub-tiles e, e+EPIW, ..).  All follow the
+// same sequence: stage g of the super-tile, K block kb, present sub-tiles in ascending order.  Every
+// sub-tile has its OWN ring of na row slots: a slot is then filled and released by the same warps in
+// strict alternation, which the parity waits of mbarriers need (a ring shared between sub-tiles lets a
+// sub-tile that skipped a use of a slot run two phases ahead of its barrier, where the parity test
+// passes wrongly).  With nsets = 2 the accumulators alternate between super-tiles, so the epilogue
+// of super-tile i overlaps the products of i+1.  Same bounded waits, abort protocol, programmatic dependent
+// launch and epilogue as k_conv_umma; results are bit-identical to it (same products, same order per row).
+constexpr int kMaxA = 16;
+constexpr int kMaxB = 4;
+constexpr int kMaxAcc = 8;
+
+struct SharedCtlMt {
+  unsigned long long afull[kMaxA];
+  unsigned long long aempty[kMaxA];
+  unsigned long long bfull[kMaxB];
+  unsigned long long bempty[kMaxB];
+  unsigned long long accfull[kMaxAcc];
+  unsigned long long accempty[kMaxAcc];
+  uint32_t tmem_base;
+  int range[2];
+  volatile int abort_flag;
+};
+
+// stage_kp entry -> (offset or -1 for the identity stage, presence mask over the sub-tiles)
+template <int SUB>
+__device__ __forceinline__ void decode_stage(int code, int& kp, uint32_t& present) {
+  constexpr uint32_t kAll = (1u << SUB) - 1u;
+  if (code < 0) {
+    kp = code;
+    present = code == -1 ? kAll : 0u;
+    return;
+  }
+  kp = code & 255;
+  present = (static_cast<uint32_t>(code) >> 8) & kAll;
+  if (present == 0u) present = kAll;  // lists without presence bits: every sub-tile takes part
+}
+
+template <int SUB, int EPIW>
+__global__ void __launch_bounds__(32 * (4 * SUB + 2 + 4 * EPIW), SUB == 1 ? 2 : 1)
+    k_conv_umma_mt(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, Second sec, int n_out, int cin,
+                   int cout, __half* __restrict__ out, Epi ep, int tmem_cols, int na, int nb, int nsets) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t* tiles = smem_raw + pad;  // 1024-byte aligned
+  const uint32_t a_base = raw_addr + pad;
+  const int b_bytes = cout * 128;
+  const uint32_t b_base = a_base + static_cast<uint32_t>(SUB * na) * kABytes;  // na row slots per sub-tile
+  constexpr int kRows = kTileM * SUB;
+  constexpr int kProd = 4 * SUB;  // producer warps
+  constexpr int kMmaWarp = kProd;
+  constexpr int kLoadWarp = kProd + 1;
+  SharedCtlMt* ctl =
+      reinterpret_cast<SharedCtlMt*>(tiles + static_cast<size_t>(SUB * na) * kABytes + static_cast<size_t>(nb) * b_bytes);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int kblocks = (cin + 63) >> 6;
+  const int kblocks2 = sec.in2 ? (sec.cin2 + 63) >> 6 : 0;
+  const int n_tiles = (n_out + kRows - 1) / kRows;
+
+  if (tid == 0) {
+    for (int s = 0; s < SUB * na; ++s) {
+      mbar_init(smem_u32(&ctl->afull[s]), kTileM);
+      mbar_init(smem_u32(&ctl->aempty[s]), 1);
+    }
+    for (int s = 0; s < nb; ++s) {
+      mbar_init(smem_u32(&ctl->bfull[s]), 1);
+      mbar_init(smem_u32(&ctl->bempty[s]), 1);
+    }
+    for (int s = 0; s < kMaxAcc; ++s) {
+      mbar_init(smem_u32(&ctl->accfull[s]), 1);
+      mbar_init(smem_u32(&ctl->accempty[s]), 128);
+    }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(static_cast<uint32_t>(tmem_cols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (!ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (warp < 2) {
+    const long long total = cost_before(ls.tile_ptr, n_tiles);
+    const unsigned b = blockIdx.x + warp;
+    const int t = b >= gridDim.x ? n_tiles : warp_tile_at_cost(ls.tile_ptr, n_tiles, total * b / gridDim.x, lane);
+    if (lane == 0) ctl->range[warp] = t;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int t0 = ctl->range[0], t1 = ctl->range[1];
+  const int g0 = __ldg(ls.tile_ptr + t0), g1 = __ldg(ls.tile_ptr + t1);
+
+  if (warp < kProd) {
+    // =========================== row producers ===========================
+    const int sub = warp >> 2;          // this warp's sub-tile
+    const int row_in_sub = tid & 127;   // this thread's row inside it
+    const int wq = warp & 3;            // warp inside the sub-tile
+    const int rsub = lane >> 3;         // row inside a 4-row group
+    const int chunk = lane & 7;         // 16-byte chunk inside a 128-byte row
+    const int ring0 = sub * na;  // this sub-tile's own row slots: ring0 .. ring0 + na - 1
+    int js = 0;                  // row items this sub-tile has produced so far
+    bool ok = true;
+    auto load_stage = [&](int g, int& nid, int& code) {
+      nid = -1;
+      code = -2;
+      if (g < g1) {
+        code = __ldg(ls.stage_kp + g);
+        int kp;
+        uint32_t present;
+        decode_stage<SUB>(code, kp, present);
+        if ((present >> sub) & 1u) nid = __ldg(ls.stage_nbr + static_cast<size_t>(g) * kRows + sub * kTileM + row_in_sub);
+      }
+    };
+    auto run_stage = [&](int nid, int code) {
+      int kp;
+      uint32_t present;
+      decode_stage<SUB>(code, kp, present);
+      if (!((present >> sub) & 1u)) return;
+      const bool second = kp == -1;
+      const int nkb = second ? kblocks2 : kblocks;
+      const __half* src_base = second ? sec.in2 : in;
+      const int width = second ? sec.cin2 : cin;
+      const int pitch = second ? sec.cin2 : ep.ld_in;
+      for (int kb = 0; kb < nkb; ++kb, ++js) {
+        const int s = ring0 + js % na;
+        const int n = js / na;
+        if (n > 0) ok = mbar_wait(smem_u32(&ctl->aempty[s]), (n - 1) & 1, ctl, 1 | (sub << 4), js);
+        ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
+        if (!ok) return;
+        const uint32_t a_addr = a_base + static_cast<uint32_t>(s) * kABytes;
+        const int kchunks = min(8, (width - kb * 64) >> 3);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int r = q * 4 + rsub;  // row inside this warp's 32
+          const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
+          if (chunk < kchunks) {
+            const uint32_t dst = a_addr + (wq * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
+            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * pitch + kb * 64 + chunk * 8 : 0);
+            cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+          }
+        }
+        cp_async_arrive_noinc(smem_u32(&ctl->afull[s]));
+      }
+    };
+    int nid0, nid1, nid2, nid3, c0, c1, c2, c3;
+    load_stage(g0, nid0, c0);
+    load_stage(g0 + 1, nid1, c1);
+    load_stage(g0 + 2, nid2, c2);
+    load_stage(g0 + 3, nid3, c3);
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int g = g0; g < g1 && ok; g += 4) {
+      run_stage(nid0, c0);
+      load_stage(g + 4, nid0, c0);
+      if (g + 1 < g1 && ok) run_stage(nid1, c1);
+      load_stage(g + 5, nid1, c1);
+      if (g + 2 < g1 && ok) run_stage(nid2, c2);
+      load_stage(g + 6, nid2, c2);
+      if (g + 3 < g1 && ok) run_stage(nid3, c3);
+      load_stage(g + 7, nid3, c3);
+    }
+    cp_async_wait_all();
+  } else if (warp == kLoadWarp) {
+    // =========================== weight loader ===========================
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (lane == 0) {
+      int jb = 0;
+      bool ok = true;
+      for (int g = g0; g < g1 && ok; ++g) {
+        int kp;
+        uint32_t present;
+        decode_stage<SUB>(__ldg(ls.stage_kp + g), kp, present);
+        const bool second = kp == -1;
+        const int nkb = second ? kblocks2 : kblocks;
+        if (present == 0u) continue;
+        for (int kb = 0; kb < nkb; ++kb, ++jb) {
+          const int s = jb % nb;
+          const int n = jb / nb;
+          if (n > 0) ok = mbar_wait(smem_u32(&ctl->bempty[s]), (n - 1) & 1, ctl, 2, jb);
+          if (!ok) break;
+          const uint32_t bbar = smem_u32(&ctl->bfull[s]);
+          mbar_arrive_expect_tx(bbar, b_bytes);
+          const __half* wsrc = second ? sec.w2 + static_cast<size_t>(kb) * cout * 64
+                                      : wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64;
+          bulk_copy_g2s(b_base + static_cast<uint32_t>(s) * b_bytes, wsrc, b_bytes, bbar);
+        }
+      }
+      if (!ok) {
+        // aborting: give the bulk copies in flight a bounded chance to land before the CTA leaves
+        for (int u = max(0, jb - nb); u < jb; ++u) {
+          const uint32_t bar = smem_u32(&ctl->bfull[u % nb]);
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (u / nb) & 1); ++spin) {
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===========================
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(cout >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+      int jb = 0;
+      int js[SUB];  // row items consumed so far, per sub-tile
+#pragma unroll
+      for (int sub = 0; sub < SUB; ++sub) js[sub] = 0;
+      bool ok = true;
+      for (int t = t0; t < t1 && ok; ++t) {
+        const int it = t - t0;
+        const int set = it % nsets;
+        const uint32_t acc_par = static_cast<uint32_t>((it / nsets) - 1) & 1u;  // phase of the previous use's release
+        uint32_t touched = 0u;
+        const int ga = __ldg(ls.tile_ptr + t), gb = __ldg(ls.tile_ptr + t + 1);
+        for (int g = ga; g < gb && ok; ++g) {
+          int kp;
+          uint32_t present;
+          decode_stage<SUB>(__ldg(ls.stage_kp + g), kp, present);
+          const bool second = kp == -1;
+          const int nkb = second ? kblocks2 : kblocks;
+          if (present == 0u) continue;
+          for (int kb = 0; kb < nkb && ok; ++kb, ++jb) {
+            const int bs = jb % nb;
+            ok = mbar_wait(smem_u32(&ctl->bfull[bs]), (jb / nb) & 1, ctl, 3 | (it << 8), jb);
+            if (!ok) break;
+            const uint64_t db = make_desc(b_base + static_cast<uint32_t>(bs) * b_bytes);
+            const int ksteps = min(4, ((second ? sec.cin2 : cin) - kb * 64) >> 4);
+#pragma unroll
+            for (int sub = 0; sub < SUB; ++sub) {
+              if (!((present >> sub) & 1u)) continue;
+              const int acc = set * SUB + sub;
+              if (!((touched >> sub) & 1u) && it >= nsets) {
+                // first product into this accumulator: its previous contents must have been drained
+                ok = mbar_wait(smem_u32(&ctl->accempty[acc]), acc_par, ctl, 4 | (sub << 4) | (it << 8), js[sub]);
+                if (!ok) break;
+              }
+              const int as = sub * na + js[sub] % na;
+              ok = mbar_wait(smem_u32(&ctl->afull[as]), (js[sub] / na) & 1, ctl, 5 | (sub << 4) | (it << 8), js[sub]);
+              if (!ok) break;
+              fence_proxy_async();  // the gathered rows were written through the generic proxy
+              tc_fence_after();
+              const uint64_t da = make_desc(a_base + static_cast<uint32_t>(as) * kABytes);
+              const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * cout);
+              for (int k = 0; k < ksteps; ++k)
+                tc_mma_f16(tmem_acc, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
+                           (((touched >> sub) & 1u) || k > 0) ? 1u : 0u);
+              touched |= 1u << sub;
+              tc_commit(smem_u32(&ctl->aempty[as]));
+              ++js[sub];
+            }
+            if (!ok) break;
+            tc_commit(smem_u32(&ctl->bempty[bs]));
+          }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int sub = 0; sub < SUB; ++sub) {
+          const int acc = set * SUB + sub;
+          if ((touched >> sub) & 1u) {
+            tc_commit(smem_u32(&ctl->accfull[acc]));  // arrives when every product issued so far has finished
+          } else {
+            // nothing went into this accumulator: the epilogue writes zeros.  The signal may still not
+            // run two phases ahead of the epilogue, so the previous use's release is waited for here too.
+            if (it >= nsets) ok = mbar_wait(smem_u32(&ctl->accempty[acc]), acc_par, ctl, 6 | (sub << 4) | (it << 8), jb);
+            if (!ok) break;
+            mbar_arrive(smem_u32(&ctl->accfull[acc]));
+          }
+        }
+      }
+    }
+    __syncwarp();
+    tc_fence_before();
+  } else {
+    // =========================== epilogue ===========================
+    const int e = warp - (kProd + 2);
+    const int team = e >> 2;
+    const int lane_quarter = warp & 3;  // the TMEM lanes this warp may read: 32*(warp%4)..+31
+    const int slot_in_sub = lane_quarter * 32 + lane;
+    if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
+    bool ok = true;
+    for (int t = t0; t < t1 && ok; ++t) {
+      const int it = t - t0;
+      const int set = it % nsets;
+      // which accumulators of this super-tile received products: OR of the stages' presence masks
+      uint32_t any_mask = 0u;
+      {
+        const int ga = __ldg(ls.tile_ptr + t), gb = __ldg(ls.tile_ptr + t + 1);
+        for (int g = ga + lane; g < gb; g += 32) {
+          int kp;
+          uint32_t present;
+          decode_stage<SUB>(__ldg(ls.stage_kp + g), kp, present);
+          if (kp == -1 && kblocks2 == 0) present = 0u;  // identity stage listed, but no second operand in this launch
+          any_mask |= present;
+        }
+        any_mask = __reduce_or_sync(0xFFFFFFFFu, any_mask);
+      }
+      if (t == t1 - 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      for (int sub = team; sub < SUB && ok; sub += EPIW) {
+        const int acc = set * SUB + sub;
+        const int slot = t * kRows + sub * kTileM + slot_in_sub;
+        int my_row = n_out;
+        if (slot < n_out) my_row = ls.order ? __ldg(ls.order + slot) : slot;
+        const bool store_row = my_row < n_out;
+        const bool any = (any_mask >> sub) & 1u;
+        if (ep.residual && store_row) {
+          const char* rp = reinterpret_cast<const char*>(ep.residual + static_cast<size_t>(my_row) * cout);
+          for (int off = 0; off < cout * 2; off += 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + off));
+        }
+        ok = mbar_wait(smem_u32(&ctl->accfull[acc]), (it / nsets) & 1, ctl, 7 | (sub << 4) | (it << 8), t);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * cout) + (static_cast<uint32_t>(lane_quarter * 32) << 16);
+        __half* orow = out + static_cast<size_t>(store_row ? my_row : 0) * ep.ld_out;
+        const __half* rrow = (ep.residual && store_row) ? ep.residual + static_cast<size_t>(my_row) * cout : nullptr;
+        for (int c0 = 0; c0 < cout; c0 += 16) {
+          uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+          if (rrow) {  // issued ahead of the tensor-memory load, consumed after it
+            ra = *reinterpret_cast<const uint4*>(rrow + c0);
+            rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
+          }
+          uint32_t r[16];
+          if (any) {  // warp-uniform: the tensor-memory load is warp-collective
+            tmem_ld16(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) r[q] = 0u;
+          }
+          float v[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(r[q]);
+          if (ep.scale) {
+#pragma unroll
+            for (int q = 0; q < 16; q += 4) {
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.scale + c0 + q));
+              v[q] *= s4.x;
+              v[q + 1] *= s4.y;
+              v[q + 2] *= s4.z;
+              v[q + 3] *= s4.w;
+            }
+          }
+          if (ep.shift) {
+#pragma unroll
+            for (int q = 0; q < 16; q += 4) {
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.shift + c0 + q));
+              v[q] += s4.x;
+              v[q + 1] += s4.y;
+              v[q + 2] += s4.z;
+              v[q + 3] += s4.w;
+            }
+          }
+          if (rrow) {
+            const __half2* ha = reinterpret_cast<const __half2*>(&ra);
+            const __half2* hb = reinterpret_cast<const __half2*>(&rb);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 fa = __half22float2(ha[q]);
+              const float2 fb = __half22float2(hb[q]);
+              v[2 * q] += fa.x;
+              v[2 * q + 1] += fa.y;
+              v[8 + 2 * q] += fb.x;
+              v[8 + 2 * q + 1] += fb.y;
+            }
+          }
+          uint4 oa, ob;
+          __half2* pa = reinterpret_cast<__half2*>(&oa);
+          __half2* pb = reinterpret_cast<__half2*>(&ob);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            pa[q] = __floats2half2_rn(act_apply(v[2 * q], ep.act, ep.slope), act_apply(v[2 * q + 1], ep.act, ep.slope));
+            pb[q] = __floats2half2_rn(act_apply(v[8 + 2 * q], ep.act, ep.slope),
+                                      act_apply(v[8 + 2 * q + 1], ep.act, ep.slope));
+          }
+          if (store_row) {
+            *reinterpret_cast<uint4*>(orow + c0) = oa;
+            *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctl->accempty[acc]));  // 128 arrivals hand the accumulator back
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(tmem_cols))
+                 : "memory");
+  }
+}
+
 }  // namespace umma
 
 bool conv_umma_supported(int cin, int cout, int dtype) {
@@ -727,6 +1156,77 @@ int umma_force_nacc = 0;
 // tile lists also the tile search and the first index loads) overlaps the tail of the kernel before it
 // in the stream.  0 = off, 1 = on, 2 = on but every list is treated as not settled.
 int umma_overlap_launches = 1;
+// 1: layers with one offset per stage and no halo push run k_conv_umma_mt (several accumulators per CTA,
+// decoupled row and weight rings); 0 (default): k_conv_umma, which measured faster at every tile height
+// both kernels share (512-row tiles exist for k_conv_umma_mt only and always run on it).
+int umma_multi_tile = 0;
+
+template <int SUB, int EPIW>
+static void launch_umma_mt(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
+                           const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e,
+                           int tmem_cols, int na, int nb, int nsets) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(32 * (4 * SUB + 2 + 4 * EPIW));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = umma_overlap_launches ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, umma::k_conv_umma_mt<SUB, EPIW>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, na, nb, nsets);
+}
+
+// Configuration of k_conv_umma_mt for a layer: sub-tiles per super-tile come with the lists; accumulator
+// sets, CTAs per SM and the two ring depths follow from tensor memory (512 columns per SM) and shared memory.
+static int conv_umma_mt(const __half* in, const __half* w, const umma::Lists& ls, const umma::Second& sec, int n_out, int cin,
+                        int cout, __half* out, const umma::Epi& e, int sub, int sm_count, cudaStream_t st) {
+  if (sub != 1 && sub != 2 && sub != 4) return PCE_ERR_INVALID;
+  if (sub * cout > 512) return PCE_ERR_UNSUPPORTED;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  PCE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
+  if (!attr_set[dev]) {
+    const int cap = 227 * 1024;
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma_mt<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma_mt<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma_mt<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    attr_set[dev] = true;
+  }
+  // two CTAs per SM only for single sub-tiles with narrow accumulators (two sets of <= 128 columns each)
+  const int ctas = (sub == 1 && 2 * cout <= 256) ? 2 : 1;
+  int nsets = (2 * sub * cout * ctas <= 512) ? 2 : 1;
+  if ((umma_force_nacc == 1 || umma_force_nacc == 2) && umma_force_nacc * sub * cout * ctas <= 512) nsets = umma_force_nacc;
+  int tmem_cols = 32;
+  while (tmem_cols < nsets * sub * cout) tmem_cols <<= 1;
+  const size_t fixed = sizeof(umma::SharedCtlMt) + 1024 + 64;
+  const size_t budget = static_cast<size_t>(227 * 1024) / ctas - fixed - (ctas > 1 ? 1024 : 0);
+  const size_t b_bytes = static_cast<size_t>(cout) * 128;
+  int nb = 3 * b_bytes * 3 <= budget ? 3 : 2;
+  if (2 * b_bytes + 2 * umma::kABytes > budget) return PCE_ERR_UNSUPPORTED;
+  // row slots per sub-tile; a third weight slot only where it does not cost a row slot per sub-tile
+  int na = static_cast<int>((budget - nb * b_bytes) / umma::kABytes) / sub;
+  if (nb == 3 && static_cast<int>((budget - 2 * b_bytes) / umma::kABytes) / sub > na) {
+    nb = 2;
+    na = static_cast<int>((budget - nb * b_bytes) / umma::kABytes) / sub;
+  }
+  if (na * sub > umma::kMaxA) na = umma::kMaxA / sub;
+  if (umma_force_stages >= 2 && umma_force_stages <= na) na = umma_force_stages;
+  if (na < 2) return PCE_ERR_UNSUPPORTED;
+  const size_t smem = static_cast<size_t>(na) * sub * umma::kABytes + nb * b_bytes + fixed;
+  const int n_tiles = div_up(n_out, umma::kTileM * sub);
+  const int grid = n_tiles < sm_count * ctas ? n_tiles : sm_count * ctas;
+  if (sub == 1)
+    launch_umma_mt<1, 1>(grid, smem, st, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, na, nb, nsets);
+  else if (sub == 2)
+    launch_umma_mt<2, 1>(grid, smem, st, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, na, nb, nsets);
+  else
+    launch_umma_mt<4, 2>(grid, smem, st, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, na, nb, nsets);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
 
 template <int NS, int SUB, bool PUSH, int SLOTS>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
@@ -775,10 +1275,11 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
       if ((slots != 2 && slots != 4) || cin * slots != 64) return PCE_ERR_INVALID;
       ls.wslots = static_cast<const __half*>(wpacked) + static_cast<size_t>(kv) * cout * 64;
     }
-    if (tiles->tile_rows != 128 && tiles->tile_rows != 256) return PCE_ERR_INVALID;
+    if (tiles->tile_rows != 128 && tiles->tile_rows != 256 && tiles->tile_rows != 512) return PCE_ERR_INVALID;
     sub = tiles->tile_rows / 128;  // the lists fix the tile height
   }
   if (sub * cout > 512) return PCE_ERR_UNSUPPORTED;
+  if (sub > 2 && (slots != 1 || !tiles)) return PCE_ERR_UNSUPPORTED;
   if (ep && ep->extra_feats) {
     // the second operand rides on the identity stage of the tile lists
     if (!ls.identity || !ep->extra_packed_weights || ep->extra_c < 16 || ep->extra_c % 16) return PCE_ERR_UNSUPPORTED;
@@ -823,6 +1324,13 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
+  }
+  {
+    const bool push_any = e.push_slot[0] || e.push_slot[1];
+    if (tiles && slots == 1 && !push_any && (umma_multi_tile || sub == 4))
+      return conv_umma_mt(static_cast<const __half*>(in), static_cast<const __half*>(wpacked), ls, sec, n_out, cin, cout,
+                          static_cast<__half*>(out), e, sub, sm_count[dev], st);
+    if (sub > 2) return PCE_ERR_UNSUPPORTED;  // 512-row super-tiles exist for k_conv_umma_mt only
   }
   // Configuration = (ring depth, accumulator sets).  What the kernel needs most is row gathers in
   // flight, i.e. stages resident per SM = resident CTAs x ring depth; the CTAs per SM are bounded by
@@ -889,6 +1397,13 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   }
 #undef PCE_GO
   PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+int umma_where_fetch(int* host4) {
+  PCE_CUDA(cudaMemcpyFromSymbol(host4, g_umma_where, 4 * sizeof(int)));
+  int z[4] = {0, 0, 0, 0};
+  PCE_CUDA(cudaMemcpyToSymbol(g_umma_where, z, 4 * sizeof(int)));
   return PCE_OK;
 }
 

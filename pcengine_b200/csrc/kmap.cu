@@ -573,8 +573,10 @@ __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const i
   if (i < n) dst[i] = src[idx[i]];
 }
 
-// Tile lists: the map re-laid for output tiles of blockDim.x (128 or 256) rows taken in
-// processing order.  One CTA per tile; thread r owns the tile's r-th row.
+// Tile lists: the map re-laid for output tiles of blockDim.x (128, 256 or 512) rows taken in
+// processing order.  One CTA per tile; thread r owns the tile's r-th row.  With one offset per stage
+// (slots == 1) stage_kp carries, above the offset's 8 bits, one presence bit per 128-row sub-tile of
+// the tile: bit 8+s is set when a row of sub-tile s has the offset.
 //   FILL = false: tile_cnt[t] = number of offsets any row of the tile has (+1 with `identity`).
 //   FILL = true : for the tile's s-th present offset (ascending kp) write stage_kp[base+s] and
 //                 stage_nbr[(base+s)*rows + r] = the row's input at that offset, or -1.
@@ -584,11 +586,11 @@ __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const i
 //   quarter) of the kernel's 64-channel K block, so 2 (4) of a tile's offsets share one stage:
 //   stage_kp[g*slots + q] and stage_nbr[(g*slots + q)*rows + r]; unused slots hold kp = -2, nbr = -1.
 template <bool FILL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
     k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
                  const int* __restrict__ order, int n_rows, int words, int identity, int slots, int* tile_cnt,
                  const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
-  __shared__ uint32_t wmask[8][4];
+  __shared__ uint32_t wmask[16][4];
   const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
   const int rows = blockDim.x, nwarps = blockDim.x >> 5;
   const int slot = t * rows + r;
@@ -627,7 +629,16 @@ __global__ void __launch_bounds__(256)
       if (g < stage_cap) {
         const size_t e = static_cast<size_t>(g) * slots + s % slots;
         stage_nbr[e * rows + r] = v;
-        if (r == 0) stage_kp[e] = w * 32 + bit;
+        if (r == 0) {
+          int code = w * 32 + bit;
+          if (slots == 1) {
+            for (int sub = 0; sub < (nwarps >> 2); ++sub) {
+              const uint32_t m4 = wmask[4 * sub][w] | wmask[4 * sub + 1][w] | wmask[4 * sub + 2][w] | wmask[4 * sub + 3][w];
+              if ((m4 >> bit) & 1u) code |= 1 << (8 + sub);
+            }
+          }
+          stage_kp[e] = code;
+        }
       }
       ++s;
     }
@@ -983,8 +994,9 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
                          void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
                          int32_t* stage_nbr, int32_t stage_cap, void* stream) {
   if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
-  if (tile_rows != 128 && tile_rows != 256) return PCE_ERR_INVALID;
+  if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return PCE_ERR_INVALID;
   if (slots != 1 && slots != 2 && slots != 4) return PCE_ERR_INVALID;
+  if (tile_rows == 512 && slots != 1) return PCE_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_tiles = div_up(n_rows, tile_rows);
   if (n_tiles == 0) {

@@ -165,11 +165,18 @@ static int scratch_for(PlanLane* l, size_t bytes, void** out) {
   return PCE_OK;
 }
 
-// 256-row tiles share every staged weight block between two accumulators, but they halve the number
-// of tiles in flight per SM; measured on 486k-row LiDAR layers they win only for narrow outputs
-// (C=32: 72 -> 67 us) and lose from C=96 up (146 -> 168 us), and they need several tiles per CTA.
-static int tile_rows_policy(int n_rows, int c_out, int sm_count) {
-  return (c_out <= 32 && static_cast<long long>(n_rows) >= 6ll * 256 * sm_count) ? 256 : 128;
+// Rows per tile of the tile lists = 128 x the sub-tiles that share every staged weight block.
+// Measured on B200 (LiDAR layers, kernel-only): taller tiles lose from 64 input channels up, on both
+// kernels.  One-accumulator kernel, 486k rows: C=96 146 -> 168 us, C=256 169 -> 205 us with 256 rows.
+// Several accumulators per CTA with decoupled row / weight rings (k_conv_umma_mt), 128 / 256 / 512 rows:
+// C=96 486k rows 121 / 184 / 201 us, C=128 149k rows 92 / 150 / 143 us, C=256 63k rows 115 / 156 us: what
+// the fused kernel needs is many independent gather -> multiply chains per SM (CTAs), and a CTA that owns
+// all of an SM's tensor memory is one chain whose sub-tiles advance in lock step.  So 128 rows, except
+// for layers with 16 or 32 input channels and narrow outputs on large maps (C=32: 72 -> 67 us with 256).
+static int tile_rows_policy(int n_rows, int c_in, int c_out, int sm_count) {
+  const int cin_p = (c_in + 15) / 16 * 16, cout_p = (c_out + 15) / 16 * 16;
+  if ((cin_p == 16 || cin_p == 32) && cout_p <= 32 && static_cast<long long>(n_rows) >= 6ll * 256 * sm_count) return 256;
+  return 128;
 }
 
 static void fill_geom(const pce_plan_map_spec& sp, const int32_t* cmin, const int32_t* cmax_out, pce_geom* g) {
@@ -207,7 +214,7 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
   // the distinct (tile height, offsets per stage) among the uses
   int want_rows[PCE_PLAN_MAX_USES], want_slots[PCE_PLAN_MAX_USES], n_want = 0;
   for (int u = 0; u < PCE_PLAN_MAX_USES && c_outs[u] > 0; ++u) {
-    const int rows = tile_rows_policy(n_rows, c_outs[u], p->sm_count);
+    const int rows = tile_rows_policy(n_rows, c_ins[u], c_outs[u], p->sm_count);
     const int slots = c_ins[u] == 32 ? 2 : (c_ins[u] == 16 ? 4 : 1);
     bool seen = false;
     for (int v = 0; v < n_want; ++v) seen = seen || (want_rows[v] == rows && want_slots[v] == slots);
@@ -395,8 +402,8 @@ static void lane_main(pce_plan* p, int lane) {
 
 extern "C" {
 
-int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_out, int32_t sm_count) {
-  return tile_rows_policy(n_rows, c_out, sm_count > 0 ? sm_count : 148);
+int32_t pce_tile_rows_for(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t sm_count) {
+  return tile_rows_policy(n_rows, c_in, c_out, sm_count > 0 ? sm_count : 148);
 }
 
 static void free_pass(pce_pass* ps) {

@@ -207,11 +207,11 @@ _SM_COUNT = {}
 _TILE_ROWS_MEMO = {}
 
 
-def _auto_tile_rows(n_rows: int, c_out: int, device) -> int:
-    """Rows per tile of the tensor-core kernel (pce_tile_rows_for): 256-row tiles, which stage every
-    weight block once for two accumulators, for narrow outputs on large maps, else 128."""
+def _auto_tile_rows(n_rows: int, c_in: int, c_out: int, device) -> int:
+    """Rows per tile of the tensor-core kernel (pce_tile_rows_for): 128 rows times the sub-tiles that
+    share every staged weight block (up to four, bounded by tensor memory and the map's size)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    key = (n_rows, c_out, idx)
+    key = (n_rows, c_in, c_out, idx)
     rows = _TILE_ROWS_MEMO.get(key)
     if rows is None:
         sms = _SM_COUNT.get(idx)
@@ -219,7 +219,7 @@ def _auto_tile_rows(n_rows: int, c_out: int, device) -> int:
             sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
         if len(_TILE_ROWS_MEMO) > 4096:
             _TILE_ROWS_MEMO.clear()
-        rows = _TILE_ROWS_MEMO[key] = int(lib.pce_tile_rows_for(n_rows, c_out, sms))
+        rows = _TILE_ROWS_MEMO[key] = int(lib.pce_tile_rows_for(n_rows, c_in, c_out, sms))
     return rows
 
 
@@ -280,8 +280,10 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         rec["start"].record()
     tiles = None
     if packed is not None:
-        tiles = C.byref(csr.tiles(SORT_ROWS, TILE_ROWS or _auto_tile_rows(csr.n_rows, c_out, feats.device), second,
-                                  stage_slots(c_in)))
+        # (the halo push lives in the one-accumulator kernel: 128-row tiles)
+        pushes = epilogue is not None and epilogue.push_slots is not None
+        rows = TILE_ROWS or (128 if pushes else _auto_tile_rows(csr.n_rows, c_in, c_out, feats.device))
+        tiles = C.byref(csr.tiles(SORT_ROWS, rows, second, stage_slots(c_in)))
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype),

@@ -224,15 +224,25 @@ def test_tile_height_is_only_scheduling(cin, cout, ks):
     w = (torch.randn(ks ** 3, cin, cout, generator=g) / 30).half().cuda()
     ep = PF.FusedEpilogue(scale=torch.rand(cout, generator=g).cuda() + 0.5, shift=torch.randn(cout, generator=g).cuda(),
                           act="relu")
+    from pcengine_b200 import _lib
+    outs = {}
     try:
-        PF.TILE_ROWS = 128
-        a = PF.conv_forward(x, w, csr, ep)
-        PF.TILE_ROWS = 256
-        b = PF.conv_forward(x, w, csr, ep)
+        for rows in (128, 256, 512):
+            if rows == 512 and (cout > 128 or cin < 64):
+                continue  # four accumulators need <= 128 columns each; 512-row lists hold one offset per stage
+            PF.TILE_ROWS = rows
+            _lib.lib.pce_tune(4, 1)  # several accumulators per CTA, decoupled row / weight rings
+            outs[("mt", rows)] = PF.conv_forward(x, w, csr, ep)
+            _lib.lib.pce_tune(4, 0)  # the one-accumulator kernel (the default)
+            if rows <= 256:
+                outs[("single", rows)] = PF.conv_forward(x, w, csr, ep)
     finally:
         PF.TILE_ROWS = None
+        _lib.lib.pce_tune(4, 0)
     assert (128 in [k[1] for k in csr._tiles]) and (256 in [k[1] for k in csr._tiles])
-    assert torch.equal(a, b)
+    a = b = outs[("mt", 128)]
+    for key, o in outs.items():
+        assert torch.equal(a, o), key
     d2 = ko.build_d2(coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     want = co.conv_forward(x.float().cpu(), w.float().cpu(), d2)
     want = torch.relu(want * ep.scale.cpu() + ep.shift.cpu())
@@ -273,7 +283,8 @@ def test_ragged_channels_run_on_tensor_cores(cin, cout):
 
 
 @pytest.mark.parametrize("cin,cout,c2,ks,tile_rows", [(64, 64, 64, 3, 128), (96, 96, 128, 3, 128), (32, 32, 32, 3, 256),
-                                                       (128, 256, 384, 3, 128), (48, 80, 16, 5, 128)])
+                                                       (128, 256, 384, 3, 128), (48, 80, 16, 5, 128), (96, 96, 128, 3, 512),
+                                                       (128, 128, 192, 3, 512), (256, 256, 256, 3, 256), (64, 32, 64, 3, None)])
 def test_second_operand_joins_the_accumulator(cin, cout, c2, ks, tile_rows):
     """FusedEpilogue.extra_feats: out = act((conv(x) + x2 @ w2) * scale + shift), against the oracle's
     convolution plus a dense product, and bit-identical between the two tile heights' code paths and
@@ -292,14 +303,19 @@ def test_second_operand_joins_the_accumulator(cin, cout, c2, ks, tile_rows):
     scale, shift = torch.rand(cout, generator=g) + 0.5, torch.randn(cout, generator=g)
     ep = PF.FusedEpilogue(scale=scale.cuda(), shift=shift.cuda(), act="relu", extra_feats=x2.cuda(), extra_weight=w2.cuda())
     plain = PF.FusedEpilogue(scale=scale.cuda(), shift=shift.cuda(), act="relu")
+    from pcengine_b200 import _lib
     try:
         PF.TILE_ROWS = tile_rows
         a = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
         b = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
         c = PF.conv_forward(x.cuda(), w.cuda(), csr, plain)  # served by the lists that have the identity stage
+        _lib.lib.pce_tune(4, 1)  # the kernel with several accumulators per CTA takes the second operand the same way
+        a_mt = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        c_mt = PF.conv_forward(x.cuda(), w.cuda(), csr, plain)
     finally:
         PF.TILE_ROWS = None
-    assert torch.equal(a, b)
+        _lib.lib.pce_tune(4, 0)
+    assert torch.equal(a, b) and torch.equal(a, a_mt) and torch.equal(c, c_mt)
     d2 = ko.build_d2(coords, (ks,) * 3, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
     want = torch.relu((co.conv_forward(x.float(), w.float(), d2) + x2.float() @ w2.float()) * scale + shift)
     assert co.rel_l2(a.float().cpu(), want) <= 1e-3  # fp16 operands, fp32 accumulation
