@@ -462,6 +462,54 @@ def indoor_rows(dev, pk, iters: int = 5, warmup: int = 2, both: bool = True):
     return rows, dict(voxels=km.n_in, surface_samples=samples, pairs=pairs, pairs_per_voxel=pairs / km.n_in)
 
 
+def selector_rows(dev, iters: int = 5, warmup: int = 2):
+    """``--workload selector``: both dataflows on clouds that span the selector's inputs -- channel width
+    (16..256), sparsity (indoor surfaces ~2.7 pairs per row, LiDAR ~3.4, a fully dense block 27) and map
+    size (about 25 k and 200 k rows) -- submanifold 3x3x3, fp16, kernel-only, L2 flushed.  The table
+    ``pcengine_b200.spconv._D1_WINS`` is what this sweep says."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import functional as PF
+    synth = _synth()
+
+    def lidar(n_target):
+        if n_target > 100000:
+            return np.concatenate([synth.with_batch(synth.lidar_scan(2000 + i), i) for i in range(3)])
+        xyz = synth.lidar_scan(2000)
+        centre = np.median(xyz, axis=0)
+        d = np.abs(xyz - centre).max(axis=1)
+        return synth.with_batch(xyz[d <= np.sort(d)[min(n_target, len(d)) - 1]])
+
+    def block(side):
+        g = np.arange(side)
+        xyz = np.stack(np.meshgrid(g, g, g, indexing="ij"), -1).reshape(-1, 3)
+        return synth.with_batch(xyz.astype(np.int32))
+
+    clouds = [("indoor", 25000, lambda: synth.with_batch(synth.indoor_room(3001, 25000)[0])),
+              ("indoor", 200000, lambda: synth.with_batch(synth.indoor_room(3001, 200000)[0])),
+              ("lidar", 25000, lambda: lidar(25000)), ("lidar", 200000, lambda: lidar(200000)),
+              ("dense", 24389, lambda: block(29)), ("dense", 195112, lambda: block(58))]
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    g = torch.Generator().manual_seed(3)
+    for name, _, make in clouds:
+        coords_h = make()
+        coords = torch.from_numpy(np.ascontiguousarray(coords_h)).to(dev)
+        km = pce.KernelMap(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], coords_h[:, 1:].max(0).tolist(), True)
+        csr = km.csr()
+        pairs = int(csr.rowptr[-1].item())
+        for c in (16, 32, 64, 96, 128, 256):
+            x = torch.randn(km.n_in, c, generator=g).half().to(dev)
+            w = (torch.randn(27, c, c, generator=g) / (27 * c) ** 0.5).half().to(dev)
+            t2 = _timed(lambda: PF.conv_forward(x, w, csr), flush, iters, warmup)
+            t1 = _timed(lambda: PF.conv_forward_d1(x, w, km), flush, iters, warmup)
+            rows.append({"cloud": name, "rows": km.n_in, "pairs_per_row": round(pairs / km.n_in, 2), "C": c,
+                         "D2_us": round(t2 * 1e6, 1), "D1_us": round(t1 * 1e6, 1), "D1_over_D2": round(t1 / t2, 2)})
+            del x, w
+        del km, csr
+        torch.cuda.empty_cache()
+    return rows
+
+
 def scene_rows(dev, pk, rank: int, world: int, cases, steps: int, warmup: int):
     """ONE large indoor scene (20 rooms tiled 5x4, about 1.5 M voxels at 2 cm) split into x-slabs, one per
     rank, with a kernel-radius halo.  Per layer shape of ``cases`` ((kernel size, channels), ...): time per
@@ -570,6 +618,12 @@ def run_indoor(args):
     torch.cuda.set_device(0)
     rows, info = indoor_rows(dev, peaks(), max(args.steps, 5), max(args.warmup, 2), both=True)
     print(json.dumps({"workload": "indoor_sweep", **info, "layers": rows}))
+
+
+def run_selector(args):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    print(json.dumps({"workload": "selector_sweep", "rows": selector_rows(dev, max(args.steps, 5), max(args.warmup, 2))}))
 
 
 def run_layer(args):
@@ -918,7 +972,7 @@ def main():
     ap.add_argument("--layer", type=str, default=None, choices=sorted(LAYERS),
                     help="run one single layer only (kernel-only timing); see --scans")
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
-    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor"],
+    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor", "selector"],
                     help="minkunet: the batch of 8 LiDAR scans (default); scene: one 1.5 M-voxel scene in x-slabs; indoor: the room sweep, both dataflows")
     ap.add_argument("--no-pin", dest="pin", action="store_false",
                     help="multi-rank runs: do not give each rank its own share of the host cores")
@@ -929,6 +983,8 @@ def main():
         run_scene(args)
     elif args.workload == "indoor":
         run_indoor(args)
+    elif args.workload == "selector":
+        run_selector(args)
     elif args.layer is not None:
         run_layer(args)
     elif args.impl == "reference":

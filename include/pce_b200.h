@@ -445,6 +445,47 @@ PCE_API int pce_pass_map(pce_pass* pass, int32_t index, void* stream, pce_planne
  * pass that recycles the storage waits for everything queued there up to this call. */
 PCE_API int pce_pass_release(pce_pass* pass, void* stream);
 
+/* ------------------------------------------------------ whole-pass execution -- */
+
+/* The reference runs a network layer by layer from Python (ref: script/spconv.py:86-98 conv3d.forward
+ * -> conv_func per layer); at ~100 k voxels the per-layer host work is longer than the kernels.
+ * pce_net_run queues EVERY feature kernel of a planned pass in one call: the caller describes the
+ * network once as a flat list of operations over feature matrices ("buffers"), each a sparse
+ * convolution through planned map `map` (kind 0) or a dense rows x matrix product (kind 1, the 1x1x1
+ * layer of ref: script/spconv.py:297-304), with the fused epilogue of pce_epilogue.  Buffers are
+ * [rows of coordinate level `level`] x width fp16 matrices placed in `arena` in order of first use
+ * (256-byte aligned; PCE_ERR_WORKSPACE when it is too small; sum over buffers of rows x width x 2
+ * bytes, rows <= the input's rows, always fits); an operation reads / writes a column range of one
+ * (col, c_in / c_out wide, multiples of 8), so skip concatenations cost nothing.  Buffer -1 is the
+ * network input (`input`, row pitch in_ld), -2 its output (`output`, out_ld).  Maps are fetched as
+ * operations first need them (pce_pass_map), so the pass's map construction overlaps the kernels.
+ * fp16, channel counts multiples of 16 (c_out <= 256), packed weights (pce_pack_weights).  Issues the
+ * same launches as one pce_conv_fwd / pce_linear_fwd call per layer: bit-identical results. */
+typedef struct pce_net_buffer {
+  int32_t level; /* coordinate level whose row count the buffer has (0 = the input's) */
+  int32_t width; /* channels per row (multiple of 8) */
+} pce_net_buffer;
+
+typedef struct pce_net_op {
+  int32_t kind;       /* 0 sparse convolution, 1 dense product */
+  int32_t map;        /* kind 0: index of the plan's map spec */
+  int32_t transposed; /* kind 0: run the map transposed (rows = the map's inputs) */
+  int32_t kv, c_in, c_out;
+  int32_t src_buf, src_col;
+  int32_t dst_buf, dst_col;
+  const void* packed_weights;
+  const float* scale; /* [c_out] or NULL */
+  const float* shift; /* [c_out] or NULL */
+  int32_t act;
+  float slope;
+  int32_t extra_buf, extra_col, extra_c; /* second operand (pce_epilogue.extra_*): a whole buffer, extra_c = its width; 0: none */
+  const void* extra_packed_weights;
+} pce_net_op;
+
+PCE_API int pce_net_run(pce_pass* pass, const pce_net_buffer* buffers, int32_t n_buffers, const pce_net_op* ops,
+                        int32_t n_ops, const void* input, int32_t in_ld, void* output, int32_t out_ld, void* arena,
+                        size_t arena_bytes, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

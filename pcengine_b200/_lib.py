@@ -26,7 +26,7 @@ EXPORTS = [
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_fwd", "pce_packed_weights_bytes",
     "pce_pack_weights", "pce_device_status", "pce_debug_timeout", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
-    "pce_quantize_workspace_bytes", "pce_quantize_unique", "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release",
+    "pce_quantize_workspace_bytes", "pce_quantize_unique", "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release", "pce_net_run",
 ]
 
 
@@ -63,6 +63,18 @@ class PlannedMap(C.Structure):
                 ("map_out", C.c_void_p), ("knnz", C.c_void_p), ("kpos", C.c_void_p), ("qkpos", C.c_void_p),
                 ("status", C.c_void_p), ("has_fwd", C.c_int32), ("has_tr", C.c_int32), ("fwd", PlannedCSR),
                 ("tr", PlannedCSR)]
+
+
+class NetBuffer(C.Structure):
+    _fields_ = [("level", C.c_int32), ("width", C.c_int32)]
+
+
+class NetOp(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("map", C.c_int32), ("transposed", C.c_int32), ("kv", C.c_int32), ("c_in", C.c_int32),
+                ("c_out", C.c_int32), ("src_buf", C.c_int32), ("src_col", C.c_int32), ("dst_buf", C.c_int32),
+                ("dst_col", C.c_int32), ("packed_weights", C.c_void_p), ("scale", C.c_void_p), ("shift", C.c_void_p),
+                ("act", C.c_int32), ("slope", C.c_float), ("extra_buf", C.c_int32), ("extra_col", C.c_int32),
+                ("extra_c", C.c_int32), ("extra_packed_weights", C.c_void_p)]
 
 
 class Epilogue(C.Structure):
@@ -122,6 +134,7 @@ def _load() -> C.CDLL:
     lib.pce_plan_begin.argtypes = [vp, vp, i32, C.POINTER(i32), C.POINTER(i32), vp, C.POINTER(vp)]
     lib.pce_pass_map.argtypes = [vp, i32, vp, C.POINTER(PlannedMap)]
     lib.pce_pass_release.argtypes = [vp, vp]
+    lib.pce_net_run.argtypes = [vp, C.POINTER(NetBuffer), i32, C.POINTER(NetOp), i32, vp, i32, vp, i32, vp, sz, i32, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("pce_version", "pce_last_cuda_error"):

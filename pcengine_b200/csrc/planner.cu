@@ -37,6 +37,9 @@
 
 namespace pce {
 
+bool conv_umma_supported(int cin, int cout, int dtype);
+int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+              int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 
 struct DeviceArena {
   struct Chunk {
@@ -584,6 +587,120 @@ int pce_pass_release(pce_pass* ps, void* stream) {
   if (e != cudaSuccess) return cuda_fail(e);  // not recycled either: its readers are unknown
   ps->has_released = true;
   p->idle.push_back(ps);
+  return PCE_OK;
+}
+
+
+// ---- whole-pass execution -------------------------------------------------------------------
+// One call queues every feature kernel of a network pass whose maps the planner builds: the host
+// walks a flat list of operations (sparse convolution through planned map i, or dense rows x matrix
+// product), fetches each map when an operation first needs it (pce_pass_map: waits on the host until
+// the map's kernels are queued, makes the stream wait for them), places the intermediate feature
+// matrices in the caller's arena as their row counts become known, and launches the tensor-core
+// kernel.  The same launches, in the same order, as calling pce_conv_fwd / pce_linear_fwd per layer.
+int pce_net_run(pce_pass* ps, const pce_net_buffer* buffers, int32_t n_buffers, const pce_net_op* ops, int32_t n_ops,
+                const void* input, int32_t in_ld, void* output, int32_t out_ld, void* arena, size_t arena_bytes,
+                int32_t dtype, void* stream) {
+  if (!ps || !ops || n_ops < 1 || n_buffers < 0 || (n_buffers > 0 && !buffers) || !input || !output) return PCE_ERR_INVALID;
+  if (dtype != PCE_F16) return PCE_ERR_UNSUPPORTED;
+  pce_plan* p = ps->plan;
+  const int n_specs = static_cast<int>(p->specs.size());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::vector<pce_planned_map> maps(n_specs);
+  std::vector<char> have(n_specs, 0);
+  std::vector<int32_t> level_rows(p->n_levels, -1);
+  level_rows[0] = ps->levels[0].n;
+  std::vector<char*> base(n_buffers, nullptr);
+  size_t used = 0;
+  char* arena_c = static_cast<char*>(arena);
+  auto fetch = [&](int i) -> int {
+    if (i < 0 || i >= n_specs) return PCE_ERR_INVALID;
+    if (!have[i]) {
+      PCE_TRY(pce_pass_map(ps, i, stream, &maps[i]));
+      have[i] = 1;
+      level_rows[p->specs[i].in_level] = maps[i].n_in;
+      level_rows[p->out_level[i]] = maps[i].n_out;
+    }
+    return PCE_OK;
+  };
+  // address, row pitch (elements) and row count of a view; places the buffer on first use
+  auto view = [&](int buf, int col, int width, const void* ext, int ext_ld, const __half** ptr, int* ld, int* rows) -> int {
+    if (buf < 0) {  // the network's input (-1) or output (-2)
+      *ptr = static_cast<const __half*>(ext) + col;
+      *ld = ext_ld;
+      *rows = level_rows[0];
+      return PCE_OK;
+    }
+    if (buf >= n_buffers) return PCE_ERR_INVALID;
+    const pce_net_buffer& b = buffers[buf];
+    if (b.level < 0 || b.level >= p->n_levels || b.width < 8 || (b.width & 7) || col < 0 || (col & 7) || col + width > b.width)
+      return PCE_ERR_INVALID;
+    const int32_t n = level_rows[b.level];
+    if (n < 0) return PCE_ERR_INVALID;  // used before the layer that creates its level
+    if (!base[buf]) {
+      const size_t bytes = pad256(static_cast<size_t>(n > 0 ? n : 1) * b.width * sizeof(__half));
+      if (!arena_c || used + bytes > arena_bytes) return PCE_ERR_WORKSPACE;
+      base[buf] = arena_c + used;
+      used += bytes;
+    }
+    *ptr = reinterpret_cast<const __half*>(base[buf]) + col;
+    *ld = b.width;
+    *rows = n;
+    return PCE_OK;
+  };
+  for (int i = 0; i < n_ops; ++i) {
+    const pce_net_op& op = ops[i];
+    if (op.c_in < 16 || op.c_out < 16 || !conv_umma_supported(op.c_in, op.c_out, dtype) || !op.packed_weights)
+      return PCE_ERR_UNSUPPORTED;
+    const pce_planned_csr* csr = nullptr;
+    if (op.kind == 0) {
+      PCE_TRY(fetch(op.map));
+      const pce_planned_map& m = maps[op.map];
+      if (op.transposed ? !m.has_tr : !m.has_fwd) return PCE_ERR_INVALID;
+      csr = op.transposed ? &m.tr : &m.fwd;
+      if (op.kv != m.kv) return PCE_ERR_INVALID;
+    } else if (op.kind != 1) {
+      return PCE_ERR_INVALID;
+    }
+    const __half *src = nullptr, *extra = nullptr;
+    const __half* dst = nullptr;
+    int src_ld = 0, dst_ld = 0, extra_ld = 0, src_rows = 0, dst_rows = 0, extra_rows = 0;
+    PCE_TRY(view(op.src_buf, op.src_col, op.c_in, input, in_ld, &src, &src_ld, &src_rows));
+    if (csr) {  // the destination's level exists once the map is known
+      if (src_rows != csr->n_src) return PCE_ERR_INVALID;
+    }
+    PCE_TRY(view(op.dst_buf, op.dst_col, op.c_out, output, out_ld, &dst, &dst_ld, &dst_rows));
+    if (csr ? dst_rows != csr->n_rows : dst_rows != src_rows) return PCE_ERR_INVALID;
+    pce_epilogue ep = {};
+    ep.scale = op.scale;
+    ep.shift = op.shift;
+    ep.act = op.act;
+    ep.slope = op.slope;
+    ep.in_ld = src_ld;
+    ep.out_ld = dst_ld;
+    if (op.extra_c > 0) {
+      if (!op.extra_packed_weights || !csr) return PCE_ERR_INVALID;
+      PCE_TRY(view(op.extra_buf, op.extra_col, op.extra_c, input, in_ld, &extra, &extra_ld, &extra_rows));
+      if (extra_rows != dst_rows || extra_ld != op.extra_c) return PCE_ERR_UNSUPPORTED;  // the second operand is read densely
+      ep.extra_feats = extra;
+      ep.extra_packed_weights = op.extra_packed_weights;
+      ep.extra_c = op.extra_c;
+    }
+    if (dst_rows == 0) continue;
+    if (!csr) {
+      PCE_TRY(conv_umma(src, src_rows, op.packed_weights, 1, nullptr, dst_rows, op.c_in, op.c_out, const_cast<__half*>(dst), &ep, st));
+      continue;
+    }
+    const int rows = tile_rows_policy(csr->n_rows, op.c_in, op.c_out, p->sm_count);
+    const int slots = op.c_in == 32 ? 2 : (op.c_in == 16 ? 4 : 1);
+    const pce_tile_lists* tl = nullptr;
+    for (int u = 0; u < csr->n_lists; ++u) {
+      const pce_tile_lists& c = csr->lists[u];
+      if (c.tile_rows == rows && (c.slots > 1 ? c.slots : 1) == slots && (c.identity_stage || op.extra_c == 0)) tl = &c;
+    }
+    if (!tl) return PCE_ERR_INVALID;  // the plan was declared without this layer's widths
+    PCE_TRY(conv_umma(src, src_rows, op.packed_weights, op.kv, tl, dst_rows, op.c_in, op.c_out, const_cast<__half*>(dst), &ep, st));
+  }
   return PCE_OK;
 }
 

@@ -148,6 +148,11 @@ def invalidate_packed(module_or_tensor) -> None:
     writes through ``param.copy_`` or ``load_state_dict`` advance; writes through ``.data`` (``param.data.copy_``,
     ``param.data.uniform_``) do not, so call this after them."""
     tensors = [module_or_tensor] if isinstance(module_or_tensor, torch.Tensor) else list(module_or_tensor.parameters())
+    if not isinstance(module_or_tensor, torch.Tensor):
+        for m in module_or_tensor.modules():  # whole-pass programs and folded constants point at the old layouts
+            m.__dict__.pop("_programs", None)
+            if hasattr(m, "_folded"):
+                m._folded = {}
     for t in tensors:
         for name in ("_pce_packed", "_pce_padded"):
             if hasattr(t, name):

@@ -19,11 +19,13 @@ from torch import nn
 
 from .activation import ReLU
 from .batchnorm import BatchNorm, bn_scale_shift
+from . import functional as PF
 from .functional import FusedEpilogue, supports_second_operand
+from .netprogram import INPUT, OUTPUT, NetProgram
 from .planner import MapPlan
 from .spconv import conv3d, conv_func
 from .sptensor import spTensor
-from .utils import cat
+from .utils import cat, output_stride_compute
 
 
 class _Fusable(nn.Module):
@@ -91,11 +93,11 @@ class ResidualBlock(_Fusable):
             self.short_conv = None
             self.short_bn = None
 
-    def _one_kernel_tail(self, x: spTensor, y: spTensor, out: Optional[torch.Tensor] = None) -> spTensor:
-        """relu(bn2(conv2(y)) + shortcut(x)) as ONE convolution launch: both BatchNorm scales are
-        folded into the weights, and the shortcut (its 1x1x1 convolution, or the identity) enters the
-        accumulator as the second operand of conv2."""
-        c2, dtype = self.conv2, x.feats.dtype
+    def _tail_operands(self, dtype, device):
+        """(conv2's weights with bn2's scale folded in, the shortcut as a [C_in, C_out] matrix -- its
+        1x1x1 convolution with its BatchNorm scale folded in, or the identity --, the summed shifts):
+        the operands of the block's one-launch tail, cached while the module stays in eval mode."""
+        c2 = self.conv2
         s2, t2 = self._fold("bn2", self.bn2)
         w_main = self._fold_weight("conv2", c2.kernel, s2, dtype)
         if self.short_conv is not None:
@@ -107,8 +109,21 @@ class ResidualBlock(_Fusable):
         else:
             key = ("eye", dtype)
             if key not in self._folded:
-                self._folded[key] = torch.eye(c2.out_channels, dtype=dtype, device=x.feats.device)
+                self._folded[key] = torch.eye(c2.out_channels, dtype=dtype, device=device)
             w_extra, shift = self._folded[key], t2
+        return w_main, w_extra, shift
+
+    def _tail_in_one_launch(self, dtype, c_x: int) -> bool:
+        return (self.one_kernel_tail and self.conv2.bias is None and self.conv2.kernel_volume <= 128
+                and (self.short_conv is None or self.short_conv.bias is None)
+                and supports_second_operand(dtype, self.conv2.in_channels, self.conv2.out_channels, c_x))
+
+    def _one_kernel_tail(self, x: spTensor, y: spTensor, out: Optional[torch.Tensor] = None) -> spTensor:
+        """relu(bn2(conv2(y)) + shortcut(x)) as ONE convolution launch: both BatchNorm scales are
+        folded into the weights, and the shortcut (its 1x1x1 convolution, or the identity) enters the
+        accumulator as the second operand of conv2."""
+        c2 = self.conv2
+        w_main, w_extra, shift = self._tail_operands(x.feats.dtype, x.feats.device)
         ep = FusedEpilogue(shift=shift, act="relu", extra_feats=x.feats.contiguous(), extra_weight=w_extra)
         return conv_func(input=y, in_channel=c2.in_channels, out_channel=c2.out_channels, kernel=w_main,
                          kernel_size_code=c2.kernel_size_code, stride_code=c2.stride_code, padding_code=c2.padding_code,
@@ -119,10 +134,7 @@ class ResidualBlock(_Fusable):
         if self._fused(x):
             s1, t1 = self._fold("bn1", self.bn1)
             y = self.conv1(x, epilogue=FusedEpilogue(scale=s1, shift=t1, act="relu"))
-            if (self.one_kernel_tail and self.conv2.bias is None and self.conv2.kernel_volume <= 128
-                    and (self.short_conv is None or self.short_conv.bias is None)
-                    and supports_second_operand(x.feats.dtype, self.conv2.in_channels, self.conv2.out_channels,
-                                                x.feats.size(1))):
+            if self._tail_in_one_launch(x.feats.dtype, x.feats.size(1)):
                 return self._one_kernel_tail(x, y, out)
             if self.short_conv is not None:
                 ss, ts = self._fold("short_bn", self.short_bn)
@@ -190,6 +202,10 @@ class MinkUNet(nn.Module):
     def forward(self, x: spTensor) -> spTensor:
         self.plan(x)
         if self.shared_skip_buffers and not self.training and x.feats.is_cuda and x.feats.dtype == torch.float16:
+            if self.one_call and x.planner is not None and not x.kmaps and PF.PROFILE is None:
+                prog = self._program(x)
+                if prog is not None:
+                    return self._forward_program(x, prog)
             return self._forward_shared(x)
         feats: List[spTensor] = [self.stem(x)]
         for i in range(4):
@@ -228,11 +244,191 @@ class MinkUNet(nn.Module):
             y = self.dec[i](u._like(joined[level]))
         return self.classifier(y)
 
+    # Inference in fp16 with planned maps: the whole pass is ONE call into the library (NetProgram)
+    # instead of one Python round trip per layer.  Same launches in the same order, bit-identical.
+    one_call = True
+
+    def train(self, mode: bool = True):
+        self.__dict__.pop("_programs", None)
+        return super().train(mode)
+
+    def _apply(self, fn, *args, **kwargs):
+        self.__dict__.pop("_programs", None)
+        return super()._apply(fn, *args, **kwargs)
+
+    def _program(self, x: spTensor) -> Optional[NetProgram]:
+        """The pass as a NetProgram for ``x``'s dtype / device / stride (built once; None when a layer
+        does not fit the one-call path, e.g. widths the tensor-core kernel does not cover)."""
+        progs = self.__dict__.setdefault("_programs", {})
+        key = (x.feats.dtype, x.feats.device, x.stride)
+        if key not in progs:
+            try:
+                progs[key] = self._build_program(x.planner.plan, x.feats.dtype, x.feats.device)
+            except (NotImplementedError, KeyError, ValueError):
+                progs[key] = None
+        return progs[key]
+
+    def _build_program(self, plan: MapPlan, dtype, device) -> NetProgram:
+        cs = self.widths
+        P = NetProgram(dtype)
+        strides = [plan.in_stride]
+        for i in range(4):
+            strides.append(output_stride_compute(self.down[i].conv.stride_code, strides[-1], 0))
+
+        def map_of(conv, level):  # level: the FINE side of the layer's map
+            return plan.index[(conv.kernel_size_code, strides[level], conv.stride_code)]
+
+        def kernel_of(conv):
+            c_in, c_out = conv.kernel.shape[-2:]
+            k = conv.kernel if conv.kernel.dim() == 3 else conv.kernel.unsqueeze(0)
+            if c_in % 16 or c_out % 16:
+                k = PF._padded_kernel(conv.kernel, PF._ceil16(c_in), PF._ceil16(c_out))
+                k = k if k.dim() == 3 else k.unsqueeze(0)
+            return k
+
+        def conv_bn_relu(m, level, src, dst, transposed=False):
+            if m.conv.bias is not None:
+                raise NotImplementedError
+            s, t = m._fold("bn", m.bn)
+            P.conv(map_of(m.conv, level), transposed, kernel_of(m.conv), src, dst, scale=s, shift=t, act="relu")
+
+        scratch = {}
+
+        def tmp(level, width):  # a block's intermediate: dead after the block's second layer, so shared per shape
+            if (level, width) not in scratch:
+                scratch[(level, width)] = P.buffer(level, width)
+            return scratch[(level, width)]
+
+        def block(m, level, src_buf, dst):
+            c_x = P.buffers[src_buf][1]
+            if m.conv1.bias is not None or not m._tail_in_one_launch(dtype, c_x) or c_x != m.conv1.in_channels:
+                raise NotImplementedError
+            s1, t1 = m._fold("bn1", m.bn1)
+            mid = tmp(level, m.conv1.out_channels)
+            P.conv(map_of(m.conv1, level), False, kernel_of(m.conv1), (src_buf, 0), (mid, 0), scale=s1, shift=t1, act="relu")
+            w_main, w_extra, shift = m._tail_operands(dtype, device)
+            P.conv(map_of(m.conv2, level), False, w_main, (mid, 0), dst, shift=shift, act="relu", extra=src_buf,
+                   extra_weight=w_extra)
+
+        joined = {}
+        for level in range(4):
+            joined[level] = P.buffer(level, cs[8 - level] + cs[level])  # [up-sampled | skip]
+        h = P.buffer(0, cs[0])
+        conv_bn_relu(self.stem[0], 0, (INPUT, 0), (h, 0))
+        conv_bn_relu(self.stem[1], 0, (h, 0), (joined[0], cs[8]))
+        y = (joined[0], cs[8])
+        for i in range(4):
+            d = P.buffer(i + 1, cs[i])
+            conv_bn_relu(self.down[i], i, y, (d, 0))
+            h = P.buffer(i + 1, cs[i + 1])
+            block(self.enc[i][0], i + 1, d, (h, 0))
+            if i < 3:
+                y = (joined[i + 1], cs[8 - (i + 1)])
+            else:
+                y = (P.buffer(4, cs[4]), 0)
+            block(self.enc[i][1], i + 1, h, y)
+        for i in range(4):
+            level = 3 - i
+            conv_bn_relu(self.up[i], level, y, (joined[level], 0), transposed=True)
+            h = P.buffer(level, cs[5 + i])
+            block(self.dec[i][0], level, joined[level], (h, 0))
+            y = (P.buffer(level, cs[5 + i]), 0)
+            block(self.dec[i][1], level, h, y)
+        head = self.classifier
+        w = kernel_of(head)[0]
+        shift = None
+        if head.bias is not None:
+            b = head.bias.detach().float()
+            shift = torch.cat([b, b.new_zeros((w.size(1) - b.numel(),))]).contiguous()
+        P.linear(w, y, (OUTPUT, 0), shift=shift)
+        P.in_width, P.out_width = PF._ceil16(self.in_channels), w.size(1)
+        P.out_channels = head.out_channels
+        return P
+
+    def _forward_program(self, x: spTensor, prog: NetProgram) -> spTensor:
+        feats = x.feats
+        n, c = feats.shape
+        if c != prog.in_width:  # the stem's input channels, zero-padded to the kernel's granularity
+            feats = torch.cat([feats, feats.new_zeros((n, prog.in_width - c))], dim=1)
+        elif not feats.is_contiguous():
+            feats = feats.contiguous()
+        out = torch.empty((n, prog.out_width), dtype=feats.dtype, device=feats.device)
+        arena = torch.empty((prog.arena_bytes(n),), dtype=torch.uint8, device=feats.device)
+        handle = x.planner._handle
+        prog.run(handle.handle, feats, out, arena)
+        handle.stream = PF._lib.stream_ptr(feats.device)
+        logits = out if prog.out_width == prog.out_channels else out[:, :prog.out_channels].contiguous()
+        y = x._like(logits)
+        y.kmaps = x.kmaps = _LazyMaps(x.planner)
+        y.cbook = x.cbook = _LazyMaps(x.planner, book=True)
+        return y
+
     @staticmethod
     def tags() -> list:
         """Dataflow tags for the nine kernel maps a forward pass builds (five submanifold
         resolutions, four down-sampling layers; the transposed layers reuse those)."""
         return ["auto"]
+
+
+class _LazyMaps(dict):
+    """``kmaps`` / ``cbook`` of a tensor whose pass ran as one library call: the planner holds the maps,
+    and the dictionary the layer-by-layer path would have filled is materialised on first access."""
+
+    def __init__(self, planner, book: bool = False):
+        super().__init__()
+        # the planner pass only (not the tensor): no reference cycle, so the pass is released by reference
+        # counting as soon as the last tensor of the pass goes away
+        self._planner, self._book, self._filled = planner, book, False
+
+    def _fill(self):
+        if self._filled:
+            return
+        self._filled = True
+        planner, self._planner = self._planner, None
+
+        class _Holder:
+            kmaps, cbook = {}, {}
+
+        holder = _Holder()
+        holder.kmaps, holder.cbook = {}, {}
+        for key, idx in planner.plan.index.items():
+            planner.fetch(holder, key, planner.plan.specs[idx]["out_stride"])
+        dict.update(self, holder.cbook if self._book else holder.kmaps)
+
+    def __getitem__(self, k):
+        self._fill()
+        return dict.__getitem__(self, k)
+
+    def get(self, k, default=None):
+        self._fill()
+        return dict.get(self, k, default)
+
+    def __contains__(self, k):
+        self._fill()
+        return dict.__contains__(self, k)
+
+    def __iter__(self):
+        self._fill()
+        return dict.__iter__(self)
+
+    def __len__(self):
+        self._fill()
+        return dict.__len__(self)
+
+    def __bool__(self):
+        return len(self) > 0
+
+    def keys(self):
+        self._fill()
+        return dict.keys(self)
+
+    def values(self):
+        self._fill()
+        return dict.values(self)
+
+    def items(self):
+        self._fill()
+        return dict.items(self)
 
 
 def randomize_batchnorm(model: nn.Module, seed: int = 0) -> None:
@@ -249,3 +445,4 @@ def randomize_batchnorm(model: nn.Module, seed: int = 0) -> None:
     for m in model.modules():
         if isinstance(m, _Fusable):
             m._folded = {}  # constants folded from the old statistics
+        m.__dict__.pop("_programs", None)

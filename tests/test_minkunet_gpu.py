@@ -277,3 +277,46 @@ def test_plan_before_forward():
     model.train()
     assert not model.plan(tensor())
     assert PF.device_status() == 0
+
+
+def test_one_call_pass_equals_the_layer_by_layer_pass():
+    """The whole pass as one library call (NetProgram / pce_net_run) issues the launches of the
+    layer-by-layer path: logits bit-identical, the tensor's kernel maps there when asked for, passes
+    recycled run after run, and a change of the weights is picked up after invalidate_packed."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(61, 72, batch=3)
+    torch.manual_seed(3)
+    feats = torch.randn(len(coords), 4).half()
+    model = pce.MinkUNet(4, 19, cr=1.0)
+    pce.randomize_batchnorm(model, 5)
+    model = model.half().eval().cuda()
+
+    def tensor():
+        return pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), batchsize=3,
+                            init_tag=pce.MinkUNet.tags())
+
+    with torch.no_grad():
+        model.one_call = False
+        want = model(tensor())
+        model.one_call = True
+        for _ in range(6):  # more passes than the planner keeps arenas for
+            x = tensor()
+            got = model(x)
+            assert torch.equal(got.feats, want.feats)
+        assert model.__dict__["_programs"] and all(p is not None for p in model.__dict__["_programs"].values())
+        assert len(got.kmaps) == 9 == len(want.kmaps)
+        for key, km in want.kmaps.items():
+            assert torch.equal(got.kmaps[key].map.tensor(), km.map.tensor())
+            assert torch.equal(got.kmaps[key].out_coords, km.out_coords)
+        ref = mo.forward(model.state_dict(), coords, feats)
+        assert co.rel_l2(got.feats.float().cpu(), ref) <= 5e-3
+        # new weights: both paths follow after the cached layouts are dropped
+        model.stem[1].conv.kernel.data.mul_(0.5)
+        pce.invalidate_packed(model)
+        model.one_call = False
+        want2 = model(tensor())
+        model.one_call = True
+        got2 = model(tensor())
+        assert torch.equal(got2.feats, want2.feats) and not torch.equal(got2.feats, want.feats)
+    from pcengine_b200 import functional as PF
+    assert PF.device_status() == 0
