@@ -102,23 +102,33 @@ def _with_bias(epilogue: Optional[FusedEpilogue], bias) -> Optional[FusedEpilogu
     return epilogue.replace(shift=shift.contiguous())  # every other field (second operand, halo push) is kept
 
 
-# Measured crossover of the two dataflows on B200 (kernel-only, L2 flushed; see bench.py --workload
-# indoor and profiles/selector_sweep.md).  The explicit dataflow moves 2*(C_in + C_out)*pairs extra
-# elements through HBM; the fused one re-stages weight blocks per tile, which costs more the fewer rows
-# share a tile's offsets.  Entries: (dtype is fp16, min C_in, min C_out, min pairs per row, max rows) -> "D1".
-_D1_WINS = ()
+# Measured crossover of the two dataflows on B200 (submanifold 3x3x3, fp16, kernel-only, L2 flushed:
+# `bench.py --workload selector`, summarised in profiles/selector_sweep.md): channel widths 16..256 x
+# {indoor surfaces, LiDAR, fully dense block} x {about 25 k, 200 k rows}.  The fused output-stationary
+# dataflow (D2) is faster in 35 of the 36 cells (by 1.0-16x; the explicit one moves 2*(C_in + C_out)*pairs
+# extra elements through HBM).  The explicit dataflow (D1) wins where D2's per-tile weight staging
+# dominates: wide layers on small, very sparse maps (256 -> 256 on 25 k rows with 1.2 pairs per row:
+# 56 vs 82 us); at 96..128 channels on such maps the two tie (1.02-1.04).  Each entry: D1 when the
+# layer is fp16, both widths >= c_min, the map has at most rows_max output rows and at most ppr_max pairs
+# per row.
+_D1_WINS = (dict(half=True, c_min=256, rows_max=40000, ppr_max=2.0),)
 
 
-def _choose_dataflow(tag: str, in_channel: int, out_channel: int, pairs_per_row: Optional[float] = None,
-                     n_rows: Optional[int] = None, dtype=None) -> str:
-    """'D1' / 'D2' are taken as given; 'auto' is the adaptive choice from channel widths, sparsity
-    (pairs per output row) and map size, looked up in the measured table ``_D1_WINS``; where the table
-    has no entry the fused output-stationary dataflow (D2) runs."""
+def _choose_dataflow(tag: str, in_channel: int, out_channel: int, pairs_per_row=None, n_rows: Optional[int] = None,
+                     dtype=None) -> str:
+    """'D1' / 'D2' are taken as given; 'auto' is the adaptive choice from channel widths, map size and
+    sparsity (pairs per output row; a number, or a callable evaluated only when the cheaper conditions
+    hold, since it costs a read-back of the pair count), looked up in the measured table ``_D1_WINS``.
+    Without the facts an entry needs (no row count or sparsity given) the fused dataflow (D2) runs."""
     if tag != "auto":
         return tag
-    for is_half, c_in_min, c_out_min, ppr_min, rows_max in _D1_WINS:
-        if ((dtype == torch.float16) == is_half and in_channel >= c_in_min and out_channel >= c_out_min
-                and (pairs_per_row is None or pairs_per_row >= ppr_min) and (n_rows is None or n_rows <= rows_max)):
+    for e in _D1_WINS:
+        if (dtype == torch.float16) != e["half"] or min(in_channel, out_channel) < e["c_min"]:
+            continue
+        if n_rows is None or n_rows > e["rows_max"] or pairs_per_row is None:
+            continue
+        ppr = pairs_per_row() if callable(pairs_per_row) else pairs_per_row
+        if ppr <= e["ppr_max"]:
             return "D1"
     return "D2"
 
@@ -155,7 +165,9 @@ def _map_for(input, in_channel, out_channel, kernel_size_code, stride_code, padd
         if tag not in _TAGS:
             raise NotImplementedError(f"no dataflow tag left for a new kernel map (init_tag[0] = {tag!r})")
         kmap = KernelMap(input.coords, ks, stride, padding, coords_min, coords_max, subm)
-        kmap.dataflow = _choose_dataflow(tag, in_channel, out_channel)
+        def pairs_per_row():  # incl. the centre offset of a submanifold map; one size read-back
+            return (kmap.sizes()[0] + (kmap.n_in if subm else 0)) / max(kmap.n_out, 1)
+        kmap.dataflow = _choose_dataflow(tag, in_channel, out_channel, pairs_per_row, kmap.n_out, input.feats.dtype)
         input.kmaps[key] = kmap
         input.cbook[output_stride] = kmap.out_coords
         if not (tag == "auto" and len(input.init_tag) == 1):

@@ -576,3 +576,24 @@ def test_weights_rewritten_through_data_need_invalidate_packed():
     conv.reset_parameters()  # rewrites through .data and drops the cached layout itself
     y2 = conv(_tensor(pce, coords, feats)).feats
     assert co.rel_l2(y2.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3
+
+
+def test_auto_tag_selects_the_measured_dataflow():
+    """Tag 'auto': a wide fp16 layer on a small, very sparse map runs the explicit dataflow (the one
+    cell of the sweep where it is faster), a dense neighbourhood or a narrow layer the fused one; both
+    give the oracle's features."""
+    import pcengine_b200 as pce
+    rng = np.random.default_rng(77)
+    lin = rng.choice(80 ** 3, 6000, replace=False)   # ~1% occupancy: hardly any neighbours
+    sparse = np.stack([np.zeros_like(lin), lin // 6400, (lin // 80) % 80, lin % 80], 1).astype(np.int32)
+    dense = surface_cloud(78, 40)
+    torch.manual_seed(6)
+    for coords, c, want_flow in ((sparse, 256, "D1"), (dense, 256, "D2"), (sparse, 64, "D2")):
+        feats = torch.randn(len(coords), c).half()
+        conv = pce.conv3d(c, c, 3).cuda().half()
+        x = _tensor(pce, coords, feats, tags=("auto",))
+        y = conv(x)
+        km = x.kmaps[(conv.kernel_size_code, x.stride, conv.stride_code)]
+        assert km.dataflow == want_flow, (len(coords), c, km.dataflow)
+        d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
+        assert co.rel_l2(y.feats.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3

@@ -133,3 +133,23 @@ def test_row_pitched_views():
     assert not _row_pitched(wide.t())               # rows not contiguous
     assert not _row_pitched(torch.zeros((10, 12), dtype=torch.float16))  # pitch 12 is no multiple of 8
     assert not _row_pitched(wide.float()[:, 8:40])  # fp32 goes through the CUDA-core kernel
+
+
+def test_dataflow_selector_follows_the_measured_table():
+    """'auto' picks the explicit gather-GEMM-scatter dataflow only where the sweep measured it faster
+    (wide fp16 layers on small, very sparse maps); tags 'D1' / 'D2' are taken as given; the sparsity
+    callable is evaluated only when width and map size already qualify."""
+    import torch
+    from pcengine_b200.spconv import _choose_dataflow
+    assert _choose_dataflow("D1", 16, 16) == "D1" and _choose_dataflow("D2", 256, 256, 1.0, 1000, torch.float16) == "D2"
+    assert _choose_dataflow("auto", 256, 256, 1.2, 25000, torch.float16) == "D1"
+    assert _choose_dataflow("auto", 256, 256, 2.7, 25000, torch.float16) == "D2"     # denser neighbourhoods
+    assert _choose_dataflow("auto", 256, 256, 1.2, 200000, torch.float16) == "D2"    # large map
+    assert _choose_dataflow("auto", 128, 256, 1.2, 25000, torch.float16) == "D2"     # narrower input
+    assert _choose_dataflow("auto", 256, 256, 1.2, 25000, torch.float32) == "D2"     # fp32 runs on CUDA cores
+    assert _choose_dataflow("auto", 256, 256) == "D2"                                # facts missing
+
+    def never():
+        raise AssertionError("sparsity was read although width / size rule the explicit dataflow out")
+    assert _choose_dataflow("auto", 64, 64, never, 25000, torch.float16) == "D2"
+    assert _choose_dataflow("auto", 256, 256, never, 10 ** 6, torch.float16) == "D2"
