@@ -315,7 +315,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * 2 = on, but tile lists are never read before that kernel has finished); what = 4: 1 runs
  * layers with one offset per stage on the kernel with several accumulators per CTA and decoupled
  * row / weight rings (k_conv_umma_mt), 0 (default) on the one-accumulator kernel, which measured
- * faster; tile lists of 512 rows always run on the former. */
+ * faster; tile lists of 512 rows always run on the former; what = 5: hash-table queries of the
+ * map builder with four cooperating lanes per query (1) or one thread per query (0, default). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose

@@ -319,20 +319,80 @@ __global__ void k_query(const int4* __restrict__ in_coords, int n_in, GeomDev g,
   }
 }
 
+// Warp-cooperative form of k_query: FOUR lanes share one (input row, offset) query and read four
+// consecutive slots of its probe sequence per round (one aligned-or-not 64-byte request instead of
+// dependent 16-byte loads); ballots over the four lanes find the key or the first empty slot.  Same
+// results as k_query (linear probing visits the slots in the same order); 64 queries per block.
+template <bool MIRROR>
+__global__ void __launch_bounds__(256)
+    k_query_coop(const int4* __restrict__ in_coords, int n_in, GeomDev g, const Slot* __restrict__ table, unsigned tmask,
+                 int* __restrict__ map, int* __restrict__ map_out, int n_out, int* knnz, int* status) {
+  const int sub = threadIdx.x & 3;
+  const int i = blockIdx.x * 64 + (threadIdx.x >> 2);
+  const int kp = blockIdx.y;
+  const unsigned group = 0xFu << (threadIdx.x & 28);  // the four lanes of this query inside the warp
+  int res = -1;
+  if (i < n_in && !(g.subm && kp == g.mid)) {
+    const int4 c = __ldg(in_coords + i);
+    int qx, qy, qz;
+    if (candidate(g, kp, c.y, c.z, c.w, qx, qy, qz) && packable(c.x, qx, qy, qz)) {
+      const unsigned long long key = pack_key(c.x, qx, qy, qz);
+      unsigned s = static_cast<unsigned>(mix64(key)) & tmask;
+      for (unsigned n = 0; n <= tmask; n += 4) {  // bounded: at most one pass over the table
+        const Slot sl = load_slot(table, (s + sub) & tmask);
+        const unsigned hit = __ballot_sync(group, sl.key == key) & group;
+        const unsigned empty = __ballot_sync(group, sl.key == kEmptyKey) & group;
+        if (hit) {  // keys are unique and never behind an empty slot of their own probe sequence
+          res = __shfl_sync(group, sl.val, __ffs(hit) - 1);
+          break;
+        }
+        if (empty) break;
+        s = (s + 4) & tmask;
+      }
+    }
+  }
+  const bool writer = sub == 0 && i < n_in;
+  if (writer) map[static_cast<size_t>(kp) * n_in + i] = res;
+  if (writer && res >= 0) {
+    if (MIRROR)
+      map[static_cast<size_t>(g.kv - 1 - kp) * n_in + res] = i;
+    else if (map_out != nullptr)
+      map_out[static_cast<size_t>(kp) * n_out + res] = i;
+  }
+  const int cnt = __syncthreads_count(writer && res >= 0);
+  if (threadIdx.x == 0 && cnt) {
+    atomicAdd(&knnz[kp], cnt);
+    if (MIRROR) atomicAdd(&knnz[g.kv - 1 - kp], cnt);
+  }
+}
+
+// 0: one thread per query (k_query, the default: measured faster); 1: four lanes per query (k_query_coop).
+int kmap_query_lanes4 = 0;
+
 // Launches the query for all offsets; n_in, n_out > 0.
 static int run_query(const int32_t* in_coords, int n_in, const GeomDev& gd, const Slot* table, unsigned tsize, int* map,
                      int* map_out, int n_out, int* knnz, int* st_word, cudaStream_t st) {
   const bool odd = (gd.ks[0] & 1) && (gd.ks[1] & 1) && (gd.ks[2] & 1);
+  const bool coop = kmap_query_lanes4 != 0;
+  const int per_block = coop ? 64 : 256;
   if (gd.subm && odd && gd.kv > 1 && map_out == nullptr && n_in == n_out) {
     PCE_CUDA(cudaMemsetAsync(map + static_cast<size_t>(gd.mid) * n_in, 0xFF,
                              sizeof(int) * static_cast<size_t>(gd.kv - gd.mid) * n_in, st));
-    dim3 grid(div_up(n_in, 256), gd.mid);
-    k_query<true><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
-                                        nullptr, n_out, knnz, st_word);
+    dim3 grid(div_up(n_in, per_block), gd.mid);
+    if (coop)
+      k_query_coop<true><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                               nullptr, n_out, knnz, st_word);
+    else
+      k_query<true><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                          nullptr, n_out, knnz, st_word);
   } else {
-    dim3 grid(div_up(n_in, 256), gd.kv);
-    k_query<false><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
-                                         map_out, n_out, knnz, st_word);
+    dim3 grid(div_up(n_in, per_block), gd.kv);
+    if (coop)
+      k_query_coop<false><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                                map_out, n_out, knnz, st_word);
+    else
+      k_query<false><<<grid, 256, 0, st>>>(reinterpret_cast<const int4*>(in_coords), n_in, gd, table, tsize - 1, map,
+                                           map_out, n_out, knnz, st_word);
   }
   PCE_LAUNCH_CHECK();
   return PCE_OK;

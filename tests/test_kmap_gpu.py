@@ -106,12 +106,14 @@ def test_out_of_range_coordinate_reports_status():
     ((3, 3, 3), True, 128, False, 1), ((3, 3, 3), False, 128, False, 1), ((5, 5, 5), True, 128, False, 1),
     ((2, 2, 2), True, 128, False, 1), ((3, 3, 3), True, 256, False, 1), ((5, 5, 5), False, 256, False, 1),
     ((3, 3, 3), True, 128, True, 1), ((3, 3, 3), True, 256, True, 1), ((3, 3, 3), True, 128, False, 2),
-    ((3, 3, 3), True, 128, True, 4), ((5, 5, 5), True, 256, True, 2), ((2, 2, 2), False, 128, False, 4)])
+    ((3, 3, 3), True, 128, True, 4), ((5, 5, 5), True, 256, True, 2), ((2, 2, 2), False, 128, False, 4),
+    ((3, 3, 3), True, 512, False, 1), ((5, 5, 5), True, 512, True, 1)])
 def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity, slots):
-    """Tile lists are the oracle's neighbour CSR re-laid: per tile of 128 or 256 rows (in processing
+    """Tile lists are the oracle's neighbour CSR re-laid: per tile of 128, 256 or 512 rows (in processing
     order) one stage per offset present in the tile, with each row's neighbour at that offset or -1;
     with ``identity`` one more stage (offset -1) in which every row names itself; with ``slots`` > 1 the
-    tile's offsets are taken ``slots`` per stage (unused slots: offset -2, rows -1)."""
+    tile's offsets are taken ``slots`` per stage (unused slots: offset -2, rows -1); with one offset per
+    stage the entry also says, in bit 8+s, whether the tile's s-th 128-row sub-tile has the offset."""
     import pcengine_b200 as pce
     coords = surface_cloud(14, 56, batch=2)
     d2 = ko.build_d2(coords, ks, (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
@@ -145,8 +147,15 @@ def test_tile_lists_match_the_csr(ks, sort_rows, tile_rows, identity, slots):
             assert np.array_equal(stage_nbr3[b, 0, :len(rws)], rws) and (stage_nbr3[b, 0, len(rws):] == -1).all()
             assert (stage_nbr3[b, 1:] == -1).all()
         assert b - a == (len(present) + slots - 1) // slots
-        kps = stage_kp3[a:b].reshape(-1)
+        kps = stage_kp3[a:b].reshape(-1).copy()
         nbrs = stage_nbr3[a:b].reshape(-1, tile_rows)
+        if slots == 1:  # offset in the low byte, sub-tile presence above it
+            has = want[rws][:, present] >= 0                                   # [rows of the tile, present offsets]
+            has = np.concatenate([has, np.zeros((tile_rows - len(rws), len(present)), bool)])
+            bits = has.reshape(tile_rows // 128, 128, -1).any(axis=1)            # [sub-tile, offset]
+            want_bits = (bits * (1 << np.arange(tile_rows // 128))[:, None]).sum(axis=0)
+            assert np.array_equal(kps[:len(present)] >> 8, want_bits)
+            kps[:len(present)] &= 255
         assert np.array_equal(kps[:len(present)], present) and (kps[len(present):] == -2).all()
         assert np.array_equal(nbrs[:len(present), :len(rws)], want[rws][:, present].T)
         assert (nbrs[:len(present), len(rws):] == -1).all() and (nbrs[len(present):] == -1).all()
@@ -212,3 +221,28 @@ def test_device_voxelisation_edge_cases():
         pce.sparse_quantize(torch.tensor([[1e9, 0.0, 0.0]], device="cuda"), 0.01)
     with pytest.raises(NotImplementedError):
         pce.sparse_quantize(torch.zeros((4, 3), dtype=torch.float64, device="cuda"), 0.1)
+
+
+def test_cooperative_query_builds_the_same_maps():
+    """Four lanes per query (64-byte probe rounds, ballots) and one thread per query give identical
+    kernel maps: submanifold (mirrored probes), strided with the transposed table, 5x5x5."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import _lib
+    coords = surface_cloud(19, 80, batch=2)
+    cd = torch.from_numpy(coords).cuda()
+    cmax = cmax_of(coords)
+    cases = [((3, 3, 3), (1, 1, 1), True, cmax), ((5, 5, 5), (1, 1, 1), True, cmax),
+             ((2, 2, 2), (2, 2, 2), False, [(c - 1) // 2 for c in cmax]), ((3, 3, 3), (2, 2, 2), False, [(c - 2) // 2 for c in cmax])]
+    for ks, stride, subm, cm in cases:
+        maps = []
+        try:
+            for lanes4 in (0, 1):
+                _lib.lib.pce_tune(5, lanes4)
+                km = pce.KernelMap(cd, ks, stride, (0, 0, 0), [0, 0, 0], cm, subm)
+                maps.append((km.map.clone(), None if km.map_out is None else km.map_out.clone(), km.knnz.clone(), km.kpos.clone()))
+        finally:
+            _lib.lib.pce_tune(5, 0)
+        for a, b in zip(*maps):
+            assert (a is None and b is None) or torch.equal(a, b)
+        d2 = ko.build_d2(coords, ks, stride, (0, 0, 0), [0, 0, 0], cmax, subm)
+        assert np.array_equal(maps[1][0].cpu().numpy(), d2["map"].reshape(-1))
