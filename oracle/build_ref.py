@@ -8,9 +8,10 @@ What it produces:
 * ``oracle/_ref/PCEngine/backend.so`` -- the reference's pybind module (``backend/pybind_cuda.cpp``,
   ``backend/hash.cu``, ``backend/spconv.cu``), compiled unmodified with plain ``nvcc``/``g++`` calls
   for ``sm_100`` against this interpreter's torch headers (the reference's ``setup.py`` is not run).
-* ``oracle/_ref/script/*.pyc`` -- byte-compiled images of the reference's Python operator layer
-  (``script/*.py``), so the drop-in test can run the reference's own ``conv3d`` on this library's
-  ``PCEngine.backend`` replacement on a machine that does not hold the reference tree.
+* ``oracle/_ref/script/*.code`` -- byte-compiled images (marshalled code objects of this interpreter)
+  of the reference's Python operator layer (``script/*.py``), so the drop-in test can run the
+  reference's own ``conv3d`` on this library's ``PCEngine.backend`` replacement on a machine that does
+  not hold the reference tree (``load_reference_script`` below imports them).
 
 Only ``tests/golden/make_ref_golden.py`` (fixture generation on a GPU), the GPU tests that compare
 against the reference and ``bench.py``'s reference-on-GPU comparator load these files. Without the
@@ -18,8 +19,8 @@ reference tree this script does nothing and says so.
 """
 from __future__ import annotations
 
+import marshal
 import os
-import py_compile
 import subprocess
 import sys
 import sysconfig
@@ -92,20 +93,62 @@ def build(ref: str = DEFAULT_REF, force: bool = False) -> str | None:
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"linking the reference's extension failed:\n{r.stdout[-4000:]}")
-    # byte-compiled operator layer (sourceless import: script/<name>.pyc)
+    # byte-compiled operator layer: one marshalled code object per module
     sdir = os.path.join(OUT, "script")
     os.makedirs(sdir, exist_ok=True)
     for name in SCRIPTS:
         src = os.path.join(ref, "script", name + ".py")
-        dst = os.path.join(sdir, name + ".pyc")
-        if os.path.exists(src):
-            if force or _stale(dst, [src]):
-                py_compile.compile(src, cfile=dst, dfile=f"script/{name}.py", doraise=True)
-        elif name == "__init__" and not os.path.exists(dst):
-            empty = os.path.join(objdir, "__init__.py")
-            open(empty, "w").close()
-            py_compile.compile(empty, cfile=dst, dfile="script/__init__.py", doraise=True)
+        dst = os.path.join(sdir, name + ".code")
+        text = open(src).read() if os.path.exists(src) else ""
+        if not os.path.exists(src) and name != "__init__":
+            continue
+        if force or not os.path.exists(dst) or (os.path.exists(src) and _stale(dst, [src])):
+            with open(dst, "wb") as f:
+                marshal.dump(compile(text, f"script/{name}.py", "exec"), f)
     return lib
+
+
+def load_reference_script(root: str = OUT):
+    """Imports the reference's ``script`` package from the marshalled images under ``root``/script
+    (``sys.modules`` must already hold whatever it imports: ``PCEngine.backend``, ``open3d``).  Returns
+    the package; its modules are ``script.spconv``, ``script.sptensor``, ``script.utils`` ..."""
+    import importlib.abc
+    import importlib.util
+    import sys
+
+    sdir = os.path.join(root, "script")
+
+    class _Loader(importlib.abc.Loader):
+        def __init__(self, path, is_pkg):
+            self.path, self.is_pkg = path, is_pkg
+
+        def create_module(self, spec):
+            return None
+
+        def exec_module(self, module):
+            with open(self.path, "rb") as f:
+                exec(marshal.load(f), module.__dict__)
+
+    class _Finder(importlib.abc.MetaPathFinder):
+        def find_spec(self, fullname, path=None, target=None):
+            if fullname == "script":
+                p = os.path.join(sdir, "__init__.code")
+                return importlib.util.spec_from_loader(fullname, _Loader(p, True), is_package=True) if os.path.exists(p) else None
+            if fullname.startswith("script."):
+                p = os.path.join(sdir, fullname.split(".", 1)[1] + ".code")
+                return importlib.util.spec_from_loader(fullname, _Loader(p, False)) if os.path.exists(p) else None
+            return None
+
+    finder = _Finder()
+    sys.meta_path.insert(0, finder)
+    try:
+        import importlib
+        pkg = importlib.import_module("script")
+        for name in ("utils", "sptensor", "spconv"):
+            importlib.import_module("script." + name)
+        return pkg
+    finally:
+        sys.meta_path.remove(finder)
 
 
 if __name__ == "__main__":

@@ -16,6 +16,7 @@ extern int umma_force_nacc;
 extern int umma_overlap_launches;
 extern int umma_multi_tile;
 extern int kmap_query_lanes4;
+extern int kmap_sort_top_bits;
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 }  // namespace pce
@@ -86,6 +87,10 @@ int pce_tune(int32_t what, int32_t value) {
   }
   if (what == 5) {
     kmap_query_lanes4 = value ? 1 : 0;
+    return PCE_OK;
+  }
+  if (what == 6) {
+    kmap_sort_top_bits = value > 0 ? value : 0;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

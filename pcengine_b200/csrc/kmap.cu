@@ -368,6 +368,8 @@ __global__ void __launch_bounds__(256)
 
 // 0: one thread per query (k_query, the default: measured faster); 1: four lanes per query (k_query_coop).
 int kmap_query_lanes4 = 0;
+// Row-order sort on the most significant N bits of the rarity-permuted bitmask key only (0 = all bits).
+int kmap_sort_top_bits = 0;
 
 // Launches the query for all offsets; n_in, n_out > 0.
 static int run_query(const int32_t* in_coords, int n_in, const GeomDev& gd, const Slot* table, unsigned tsize, int* map,
@@ -1032,15 +1034,20 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
   PCE_LAUNCH_CHECK();
   // least significant word first; the radix sort is stable, so the second pass keeps its order
   const int lo_bits = kv < 64 ? kv : 64;
+  // The key's low bits are the COMMON offsets (bit kv-1-rank, rank 0 = rarest): most rows of a tile
+  // have them whatever the order, so the sort may leave them out (kmap_sort_top_bits > 0: only that
+  // many of the most significant bits are sorted on; one radix pass per 8 bits).
+  int lo_begin = 0;
+  if (!two && kmap_sort_top_bits > 0 && kmap_sort_top_bits < lo_bits) lo_begin = lo_bits - kmap_sort_top_bits;
   size_t need = 0, need_hi = 0;
-  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, lo, sorted, vals, by_lo, n_rows, 0, lo_bits, st));
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, lo, sorted, vals, by_lo, n_rows, lo_begin, lo_bits, st));
   if (two) {
     PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need_hi, hi_by_lo, sorted, by_lo, order, n_rows, 0, kv - 64, st));
     if (need_hi > need) need = need_hi;
   }
   char* tmp = ar.take<char>(need);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
-  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, lo, sorted, vals, by_lo, n_rows, 0, lo_bits, st));
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, lo, sorted, vals, by_lo, n_rows, lo_begin, lo_bits, st));
   if (two) {
     k_gather_u64<<<div_up(n_rows, 256), 256, 0, st>>>(hi, by_lo, n_rows, hi_by_lo);
     PCE_LAUNCH_CHECK();

@@ -4,9 +4,10 @@ stub stands in for the ``open3d`` import of script/utils.py:2 (file reading, not
 reference's ``conv3d`` modules are run and compared with the oracle.
 
 The operator layer is taken from the reference tree when it is on this machine, else from its byte-compiled
-image under oracle/_ref/script (oracle/build_ref.py); the tests skip when neither is there.
+image under oracle/_ref/script (written and loaded by oracle/build_ref.py); the tests skip when neither is there.
 """
 import importlib
+import importlib.util
 import os
 import sys
 import types
@@ -23,22 +24,24 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _reference_script_root():
-    for cand in (os.environ.get("PCE_REFERENCE_TREE", "/root/reference"), os.path.join(ROOT, "oracle", "_ref")):
-        d = os.path.join(cand, "script")
-        if os.path.exists(os.path.join(d, "spconv.py")) or os.path.exists(os.path.join(d, "spconv.pyc")):
-            return cand
-    return None
+    tree = os.environ.get("PCE_REFERENCE_TREE", "/root/reference")
+    if os.path.exists(os.path.join(tree, "script", "spconv.py")):
+        return tree, "source"
+    image = os.path.join(ROOT, "oracle", "_ref")
+    if os.path.exists(os.path.join(image, "script", "spconv.code")):
+        return image, "image"
+    return None, None
 
 
 @pytest.fixture(scope="module")
 def ref():
     """script.spconv / script.sptensor of the reference, bound to this library's backend module."""
-    root = _reference_script_root()
+    root, kind = _reference_script_root()
     if root is None:
         pytest.skip("neither the reference tree nor oracle/_ref/script is on this machine")
     import pcengine_b200.backend as backend
-    saved = {k: sys.modules.get(k) for k in ("PCEngine", "PCEngine.backend", "open3d", "script", "script.spconv",
-                                             "script.sptensor", "script.utils")}
+    names = ("PCEngine", "PCEngine.backend", "open3d")
+    saved = {k: sys.modules.get(k) for k in names}
     pkg = types.ModuleType("PCEngine")
     pkg.backend = backend
     sys.modules["PCEngine"] = pkg
@@ -47,14 +50,22 @@ def ref():
         sys.modules["open3d"] = types.ModuleType("open3d")
     for k in [k for k in sys.modules if k == "script" or k.startswith("script.")]:
         del sys.modules[k]
-    sys.path.insert(0, root)
     try:
-        spconv = importlib.import_module("script.spconv")
-        sptensor = importlib.import_module("script.sptensor")
+        if kind == "source":
+            sys.path.insert(0, root)
+            try:
+                importlib.import_module("script.spconv")
+            finally:
+                sys.path.remove(root)
+        else:
+            spec = importlib.util.spec_from_file_location("pce_b200_build_ref", os.path.join(ROOT, "oracle", "build_ref.py"))
+            build_ref = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(build_ref)
+            build_ref.load_reference_script(root)
+        spconv, sptensor = sys.modules["script.spconv"], sys.modules["script.sptensor"]
         assert spconv.mapping_d2_cuda is backend.mapping_d2_cuda
         yield types.SimpleNamespace(conv3d=spconv.conv3d, spTensor=sptensor.spTensor)
     finally:
-        sys.path.remove(root)
         for k in [k for k in sys.modules if k == "script" or k.startswith("script.")]:
             del sys.modules[k]
         for k, v in saved.items():
