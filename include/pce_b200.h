@@ -103,6 +103,15 @@ typedef struct pce_epilogue {
    * be a multiple of 8 elements and the pointers 16-byte aligned. */
   int32_t in_ld;
   int32_t out_ld;
+  /* Scratch for maps with few tiles (optional).  A 128-row tile is one sequential chain of
+   * (offset, K block) stages on one CTA; a map with fewer tiles than the GPU has CTA slots leaves
+   * SMs idle while those chains run.  With pce_conv_split_parts(...) = P > 1 and split_scratch of at
+   * least P * n_out * c_out * 4 bytes (16-byte aligned), P CTAs take consecutive parts of every
+   * tile's stage list, store their fp32 partial sums here, and a second kernel adds the parts in
+   * order and applies the epilogue (deterministic; the fp32 sum is associated differently than in
+   * the one-CTA chain).  Without scratch the layer runs unsplit. */
+  void* split_scratch;
+  size_t split_scratch_bytes;
 } pce_epilogue;
 
 /* The kernel map re-laid for the tensor-core kernel (pce_build_tile_lists): output
@@ -316,7 +325,9 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * layers with one offset per stage on the kernel with several accumulators per CTA and decoupled
  * row / weight rings (k_conv_umma_mt), 0 (default) on the one-accumulator kernel, which measured
  * faster; tile lists of 512 rows always run on the former; what = 5: hash-table queries of the
- * map builder with four cooperating lanes per query (1) or one thread per query (0, default). */
+ * map builder with four cooperating lanes per query (1) or one thread per query (0, default);
+ * what = 6: sort the rows on the most significant `value` bits of their key only (0 = all, default);
+ * what = 7: 0 never splits a tile's stage chain over several CTAs (1 = by pce_conv_split_parts). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
@@ -327,6 +338,11 @@ PCE_API int pce_device_status(int32_t* status_host, int32_t reset);
  * {code, CTA, item, phase parity} (code = role | sub-tile << 4 | tile-in-CTA << 8; roles are listed
  * beside g_umma_where in csrc/conv_umma.cu); all zero when no wait expired.  Reads and clears. */
 PCE_API int pce_debug_timeout(int32_t* where4);
+
+/* Parts per tile (1, 4 or 8) that pce_conv_fwd uses for a tensor-core layer of n_rows outputs
+ * when pce_epilogue.split_scratch is given; 1 = the layer is not split (large maps, layers with 16 or
+ * 32 input channels, short stage chains). */
+PCE_API int32_t pce_conv_split_parts(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count);
 
 /* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
  * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */
@@ -456,7 +472,8 @@ PCE_API int pce_pass_release(pce_pass* pass, void* stream);
  * layer of ref: script/spconv.py:297-304), with the fused epilogue of pce_epilogue.  Buffers are
  * [rows of coordinate level `level`] x width fp16 matrices placed in `arena` in order of first use
  * (256-byte aligned; PCE_ERR_WORKSPACE when it is too small; sum over buffers of rows x width x 2
- * bytes, rows <= the input's rows, always fits); an operation reads / writes a column range of one
+ * bytes with rows <= the input's rows, plus 400 MB for the fp32 partial sums of layers on small maps
+ * that are split over several CTAs per tile (pce_conv_split_parts), always fits); an operation reads / writes a column range of one
  * (col, c_in / c_out wide, multiples of 8), so skip concatenations cost nothing.  Buffer -1 is the
  * network input (`input`, row pitch in_ld), -2 its output (`output`, out_ld).  Maps are fetched as
  * operations first need them (pce_pass_map), so the pass's map construction overlaps the kernels.

@@ -72,6 +72,10 @@ struct Epi {
   // may read and write a column range of a wider row-major matrix
   int ld_in;
   int ld_out;
+  // parts > 1: `parts` CTAs share every tile (CTA b: tile b / parts, part b % parts of its stage list) and
+  // store raw fp32 sums to partial[(part * n_out + row) * cout + c]; k_sum_parts finishes the layer
+  float* partial;
+  int parts;
 };
 
 struct Lists {
@@ -300,12 +304,6 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   const int kblocks = (cin + 63) >> 6;
   const int kblocks2 = sec.in2 ? (sec.cin2 + 63) >> 6 : 0;  // ring stages of the identity stage
   const int n_tiles = (n_out + kRows - 1) / kRows;
-  // ring stages of tile t: its listed offsets times the K blocks, the identity stage counted with
-  // the second operand's K blocks (none when this launch has no second operand)
-  auto tile_main_stages = [&](int t) {
-    return (first_stage(ls.tile_ptr, t + 1) - first_stage(ls.tile_ptr, t) - (ls.identity ? 1 : 0)) * kblocks;
-  };
-
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&ctl->afull[s]), kRows);
@@ -331,7 +329,14 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   // older than that kernel (ls.settled): the search for this CTA's tiles and the first index loads
   // then overlap its tail as well.
   if (!ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (warp < 2) {
+  const int parts = ep.parts > 1 ? ep.parts : 1;
+  if (parts > 1) {
+    // split tiles: this CTA owns ONE tile and one part of its stage list
+    if (tid == 0) {
+      ctl->range[0] = static_cast<int>(blockIdx.x) / parts;
+      ctl->range[1] = static_cast<int>(blockIdx.x) / parts + 1;
+    }
+  } else if (warp < 2) {
     // this CTA's contiguous share of the tiles, balanced by work: warp 0 finds its first tile,
     // warp 1 the next CTA's first tile
     const long long total = cost_before(ls.tile_ptr, n_tiles);
@@ -345,10 +350,34 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   const uint32_t tmem_base = ctl->tmem_base;
 
   const int t0 = ctl->range[0], t1 = ctl->range[1];
+  // stage range of tile t that this CTA works on: the whole tile, or its part
+  auto stage_range = [&](int t, int& sa, int& sb) {
+    sa = first_stage(ls.tile_ptr, t);
+    sb = first_stage(ls.tile_ptr, t + 1);
+    if (parts > 1) {
+      const int n = sb - sa, part = static_cast<int>(blockIdx.x) % parts;
+      const int a = sa + static_cast<int>(static_cast<long long>(n) * part / parts);
+      sb = sa + static_cast<int>(static_cast<long long>(n) * (part + 1) / parts);
+      sa = a;
+    }
+  };
+  // ring stages of tile t (this CTA's part of it): its listed offsets times the K blocks; the identity
+  // stage, which is the tile's last, counts with the second operand's K blocks (none without one)
+  auto tile_ident = [&](int t) {
+    int sa, sb;
+    stage_range(t, sa, sb);
+    return (ls.identity && sb > sa && sb == first_stage(ls.tile_ptr, t + 1)) ? 1 : 0;
+  };
+  auto tile_main_stages = [&](int t) {
+    int sa, sb;
+    stage_range(t, sa, sb);
+    return (sb - sa - tile_ident(t)) * kblocks;
+  };
 
   if (warp < kMmaWarp) {
     // =========================== producers ===========================
-    const int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
+    int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
+    if (parts > 1) stage_range(t0, g0, g1);
     const int rsub = lane >> 3;  // row inside a 4-row group
     const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
     int j = 0;  // smem stages issued so far (continuous over tiles)
@@ -527,7 +556,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         const int it = t - t0;
         const int buf = it % nacc;
         const int nst_main = tile_main_stages(t);
-        const int nst = nst_main + (ls.identity ? kblocks2 : 0);
+        const int nst = nst_main + (tile_ident(t) ? kblocks2 : 0);
         // the accumulator must have been drained by the epilogue (two tiles ago)
         if (it >= nacc) ok = mbar_wait(smem_u32(&ctl->accempty[buf]), ((it / nacc) - 1) & 1, ctl);
         if (!ok) break;
@@ -582,7 +611,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         rows_of[sub] = n_out;
         if (slot < n_out) rows_of[sub] = ls.order ? __ldg(ls.order + slot) : slot;
       }
-      const bool any = tile_main_stages(t) + (ls.identity ? kblocks2 : 0) > 0;
+      const bool any = tile_main_stages(t) + (tile_ident(t) ? kblocks2 : 0) > 0;
       if (ep.residual) {
         // the rows are known before the accumulator is: pull the residual rows into L2 while waiting
 #pragma unroll
@@ -633,6 +662,15 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         float v[16];
 #pragma unroll
         for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(r[q]);
+        if (parts > 1) {  // a part of a split tile: the raw sums go to the scratch, k_sum_parts finishes the row
+          if (store_row) {
+            float4* dst = reinterpret_cast<float4*>(
+                ep.partial + (static_cast<size_t>(blockIdx.x % parts) * n_out + my_row) * cout + c0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+          continue;
+        }
         if (ep.scale) {
 #pragma unroll
           for (int q = 0; q < 16; q += 4) {
@@ -1119,6 +1157,46 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 2 + 4 * EPIW), SUB == 1 ? 2 : 
   }
 }
 
+// Second kernel of a split layer: out[row] = act((sum over parts of partial[part][row]) * scale + shift +
+// residual), parts added in ascending order in fp32; one thread per 8 output channels.
+__global__ void __launch_bounds__(256)
+    k_sum_parts(const float* __restrict__ partial, int parts, int n_out, int cout, __half* __restrict__ out, Epi ep) {
+  const int chunks = cout >> 3;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(n_out) * chunks) return;
+  const int row = static_cast<int>(i / chunks), c0 = static_cast<int>(i % chunks) * 8;
+  float v[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) v[q] = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(partial + (static_cast<size_t>(p) * n_out + row) * cout + c0);
+    const float4 a = __ldg(src), b = __ldg(src + 1);
+    v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+    v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    if (ep.scale) v[q] *= __ldg(ep.scale + c0 + q);
+    if (ep.shift) v[q] += __ldg(ep.shift + c0 + q);
+  }
+  if (ep.residual) {
+    const uint4 r = *reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * cout + c0);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = __half22float2(h[q]);
+      v[2 * q] += f.x;
+      v[2 * q + 1] += f.y;
+    }
+  }
+  uint4 o;
+  __half2* po = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    po[q] = __floats2half2_rn(act_apply(v[2 * q], ep.act, ep.slope), act_apply(v[2 * q + 1], ep.act, ep.slope));
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * ep.ld_out + c0) = o;
+}
+
 }  // namespace umma
 
 bool conv_umma_supported(int cin, int cout, int dtype) {
@@ -1243,6 +1321,31 @@ static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in
   cfg.attrs = attr;
   cfg.numAttrs = umma_overlap_launches ? 1 : 0;
   cudaLaunchKernelEx(&cfg, umma::k_conv_umma<NS, SUB, PUSH, SLOTS>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, nacc);
+}
+
+// 1: maps with few tiles are split over several CTAs per tile when the caller gives scratch (see
+// conv_split_parts); 0: never.
+int umma_split_enabled = 1;
+
+// Parts per tile for a layer of n_rows outputs: 8 or 4 CTAs per tile where all of them are resident at once
+// (tiles x parts <= the SMs' CTA slots) and every part keeps a chain of at least 8 stages.  The chain of a
+// tile is estimated as min(kv, 16) offsets x K blocks: deep levels of a network, where maps are small, are
+// also where tiles have many offsets.  Measured on B200 (one LiDAR scan, kernel-only): 256 -> 256 on 3.4 k
+// rows (27 tiles) 104 -> 42 us with 8 parts, on 8.6 k rows (68 tiles) 100 -> 54 us with 4, 384 -> 256 143 -> 66 us;
+// two parts, or more parts than slots, do not pay for the second kernel and the fp32 round trip (189 tiles
+// 128 -> 256: 63 -> 74 us), so those maps stay unsplit.  Layers with 16 or 32 input channels (shallow levels)
+// are never split.
+int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
+  if (!umma_split_enabled || n_rows < 1) return 1;
+  const int cin_p = (cin + 15) / 16 * 16;
+  if (cin_p == 16 || cin_p == 32) return 1;
+  const int kblocks = (cin + 63) / 64;
+  const int chain = (kv < 16 ? kv : 16) * kblocks;
+  const long long n_tiles = (static_cast<long long>(n_rows) + umma::kTileM - 1) / umma::kTileM;
+  const long long slots = static_cast<long long>(sm_count > 0 ? sm_count : 148) * (cout <= 128 ? 3 : 2);
+  int p = 8;
+  while (p > 1 && (n_tiles * p > slots || chain < 8 * p)) p >>= 1;
+  return p >= 4 ? p : 1;
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
@@ -1375,7 +1478,19 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   const size_t smem = ns * stage + fixed;
   if (smem > 227 * 1024) return PCE_ERR_UNSUPPORTED;
   const int n_tiles = div_up(n_out, umma::kTileM * sub);
-  const int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
+  int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
+  // few tiles, long stage chains: several CTAs per tile, partial sums through the caller's scratch
+  int parts = 1;
+  if (tiles && sub == 1 && slots == 1 && !push && ep && ep->split_scratch &&
+      (reinterpret_cast<uintptr_t>(ep->split_scratch) & 15) == 0) {
+    parts = conv_split_parts(n_out, cin, cout, kv, sm_count[dev]);
+    while (parts > 1 && static_cast<size_t>(parts) * n_out * cout * sizeof(float) > ep->split_scratch_bytes) parts >>= 1;
+    if (parts > 1) {
+      grid = n_tiles * parts;
+      e.partial = static_cast<float*>(ep->split_scratch);
+      e.parts = parts;
+    }
+  }
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
@@ -1397,6 +1512,11 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   }
 #undef PCE_GO
   PCE_LAUNCH_CHECK();
+  if (parts > 1) {
+    const long long work = static_cast<long long>(n_out) * (cout >> 3);
+    umma::k_sum_parts<<<div_up(work, 256), 256, 0, st>>>(e.partial, parts, n_out, cout, out_h, e);
+    PCE_LAUNCH_CHECK();
+  }
   return PCE_OK;
 }
 

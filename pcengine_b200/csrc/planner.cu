@@ -38,6 +38,7 @@
 namespace pce {
 
 bool conv_umma_supported(int cin, int cout, int dtype);
+int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count);
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 
@@ -613,6 +614,8 @@ int pce_net_run(pce_pass* ps, const pce_net_buffer* buffers, int32_t n_buffers, 
   std::vector<char*> base(n_buffers, nullptr);
   size_t used = 0;
   char* arena_c = static_cast<char*>(arena);
+  char* split = nullptr;  // scratch of split layers (fp32 partial sums)
+  size_t split_bytes = 0;
   auto fetch = [&](int i) -> int {
     if (i < 0 || i >= n_specs) return PCE_ERR_INVALID;
     if (!have[i]) {
@@ -699,6 +702,20 @@ int pce_net_run(pce_pass* ps, const pce_net_buffer* buffers, int32_t n_buffers, 
       if (c.tile_rows == rows && (c.slots > 1 ? c.slots : 1) == slots && (c.identity_stage || op.extra_c == 0)) tl = &c;
     }
     if (!tl) return PCE_ERR_INVALID;  // the plan was declared without this layer's widths
+    // small maps: several CTAs per tile; the fp32 partial sums live behind the buffers (one region,
+    // reused by every split layer: the layers run in stream order)
+    const int parts = conv_split_parts(dst_rows, op.c_in, op.c_out, op.kv, p->sm_count);
+    if (parts > 1) {
+      const size_t need = pad256(static_cast<size_t>(parts) * dst_rows * op.c_out * sizeof(float));
+      if (need > split_bytes) {  // a larger region behind what is placed so far (the old one stays unused)
+        if (!arena_c || used + need > arena_bytes) return PCE_ERR_WORKSPACE;
+        split = arena_c + used;
+        split_bytes = need;
+        used += need;
+      }
+      ep.split_scratch = split;
+      ep.split_scratch_bytes = split_bytes;
+    }
     PCE_TRY(conv_umma(src, src_rows, op.packed_weights, op.kv, tl, dst_rows, op.c_in, op.c_out, const_cast<__half*>(dst), &ep, st));
   }
   return PCE_OK;

@@ -100,12 +100,32 @@ def supports_second_operand(dtype, c_in: int, c_out: int, c2: int) -> bool:
             and c2 >= 16)
 
 
-def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype, in_ld: int = 0, out_ld: int = 0):
-    if ep is None and not in_ld and not out_ld:
+def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype, in_ld: int = 0, out_ld: int = 0, split=None):
+    if ep is None and not in_ld and not out_ld and split is None:
         return None
     e = ep.pack(c_out, n_out, dtype) if ep is not None else _lib.Epilogue()
     e.in_ld, e.out_ld = in_ld, out_ld
+    if split is not None:
+        e.split_scratch, e.split_scratch_bytes = split.data_ptr(), split.numel() * split.element_size()
     return C.byref(e)
+
+
+# Split the stage chains of maps with few tiles over several CTAs per tile (pce_conv_split_parts).
+SPLIT_TILES = True
+
+
+def _split_scratch(n_rows: int, c_in: int, c_out: int, kv: int, device):
+    """fp32 scratch for the partial sums of a layer that the library will split, or None."""
+    if not SPLIT_TILES:
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNT.get(idx)
+    if sms is None:
+        sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    parts = int(lib.pce_conv_split_parts(n_rows, c_in, c_out, kv, sms))
+    if parts <= 1:
+        return None
+    return torch.empty((parts * n_rows * c_out,), dtype=torch.float32, device=device)
 
 
 def _row_pitched(t: torch.Tensor) -> bool:
@@ -283,16 +303,18 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                    residual=epilogue is not None and epilogue.residual is not None,
                    start=torch.cuda.Event(enable_timing=True), end=torch.cuda.Event(enable_timing=True))
         rec["start"].record()
-    tiles = None
+    tiles = split = None
     if packed is not None:
         # (the halo push lives in the one-accumulator kernel: 128-row tiles)
         pushes = epilogue is not None and epilogue.push_slots is not None
         rows = TILE_ROWS or (128 if pushes else _auto_tile_rows(csr.n_rows, c_in, c_out, feats.device))
         tiles = C.byref(csr.tiles(SORT_ROWS, rows, second, stage_slots(c_in)))
+        if rows == 128 and not pushes:
+            split = _split_scratch(csr.n_rows, c_in, c_out, kv, feats.device)
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype),
-                                _pack(epilogue, c_out, csr.n_rows, feats.dtype, in_ld, out_ld),
+                                _pack(epilogue, c_out, csr.n_rows, feats.dtype, in_ld, out_ld, split),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
         rec["end"].record()

@@ -115,7 +115,9 @@ class NetProgram:
     def arena_bytes(self, n_rows: int) -> int:
         if self._c is None:
             self._compile()
-        return 2 * n_rows * self.row_width + 256 * (len(self.buffers) + 1)
+        # + room for the fp32 partial sums of split layers (small maps): a part count P is chosen so that
+        # P x tiles <= 1.5 x the GPU's CTA slots, i.e. at most ~90 MB per layer, placed afresh when it grows
+        return 2 * n_rows * self.row_width + 256 * (len(self.buffers) + 1) + (400 << 20)
 
     def run(self, pass_handle: int, feats: torch.Tensor, out: torch.Tensor, arena: torch.Tensor) -> None:
         """Queue the whole pass on the current stream.  ``feats`` [N, C_in of the first layer] and ``out``

@@ -597,3 +597,50 @@ def test_auto_tag_selects_the_measured_dataflow():
         assert km.dataflow == want_flow, (len(coords), c, km.dataflow)
         d2 = ko.build_d2(coords, (3, 3, 3), (1, 1, 1), (0, 0, 0), [0, 0, 0], cmax_of(coords), True)
         assert co.rel_l2(y.feats.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3
+
+
+@pytest.mark.split_tiles
+@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 20, 3), (128, 256, 30, 3), (96, 96, 48, 3), (64, 128, 26, 5), (256, 128, 24, 2)])
+def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
+    """A map with few 128-row tiles runs with several CTAs per tile: every CTA takes a part of the tile's
+    stage list, the fp32 partial sums are added in order by a second kernel that also applies the epilogue
+    (scale, shift, residual or second operand, activation).  Same features as the oracle and as the unsplit
+    kernel within fp16 rounding, bit-identical run to run."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import _lib
+    from pcengine_b200 import functional as PF
+    coords = surface_cloud(200 + n_side, n_side, batch=2)
+    n = len(coords)
+    subm = ks != 2
+    d2 = ko.build_d2(coords, (ks,) * 3, (1, 1, 1) if subm else (2, 2, 2), (0, 0, 0), [0, 0, 0], cmax_of(coords), subm)
+    km = pce.KernelMap(torch.from_numpy(coords).cuda(), (ks,) * 3, (1, 1, 1) if subm else (2, 2, 2), (0, 0, 0), [0, 0, 0],
+                       d2["cmax_out"], subm)
+    csr = km.csr()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    parts = _lib.lib.pce_conv_split_parts(csr.n_rows, cin, cout, ks ** 3, sms)
+    assert parts > 1, "the case is meant to be split"
+    g = torch.Generator().manual_seed(cin + cout + n_side)
+    x = torch.randn(n, cin, generator=g).half()
+    w = (torch.randn(ks ** 3, cin, cout, generator=g) / (ks ** 3 * cin) ** 0.5).half()
+    scale, shift = torch.rand(cout, generator=g) + 0.5, torch.randn(cout, generator=g)
+    res = torch.randn(csr.n_rows, cout, generator=g).half()
+    want = co.conv_forward(x, w, d2)
+    eps = [None, PF.FusedEpilogue(scale=scale.cuda(), shift=shift.cuda(), residual=res.cuda(), act="leaky", slope=0.2)]
+    wants = [want, torch.nn.functional.leaky_relu(want * scale + shift + res.float(), 0.2)]
+    if subm:
+        x2 = torch.randn(n, 64, generator=g).half()
+        w2 = (torch.randn(64, cout, generator=g) / 8).half()
+        eps.append(PF.FusedEpilogue(shift=shift.cuda(), act="relu", extra_feats=x2.cuda(), extra_weight=w2.cuda()))
+        wants.append(torch.relu(want + x2.float() @ w2.float() + shift))
+    for ep, ref in zip(eps, wants):
+        a = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        b = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        assert torch.equal(a, b)
+        assert co.rel_l2(a.float().cpu(), ref) <= 1e-3
+        PF.SPLIT_TILES = False
+        try:
+            whole = PF.conv_forward(x.cuda(), w.cuda(), csr, ep)
+        finally:
+            PF.SPLIT_TILES = True
+        assert co.rel_l2(a.float().cpu(), whole.float().cpu()) <= 5e-4  # same products, another fp32 association
+    assert PF.device_status() == 0
