@@ -629,6 +629,31 @@ __global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int w
   vals[r] = r;
 }
 
+// The same key in 32 bits (kv <= 32): half the key bytes through the radix sort's passes.
+__global__ void k_mask_keys32(const uint32_t* __restrict__ mask, int n_rows, int kv, const int* __restrict__ counts,
+                              uint32_t* keys, int* vals) {
+  __shared__ int pos[32];
+  if (threadIdx.x < 32) {
+    const int k = threadIdx.x;
+    int rank = 0;
+    if (k < kv) {
+      const int ck = counts[k];
+      for (int j = 0; j < kv; ++j) {
+        const int cj = counts[j];
+        rank += (cj < ck || (cj == ck && j < k)) ? 1 : 0;
+      }
+    }
+    pos[k] = kv - 1 - rank;
+  }
+  __syncthreads();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  uint32_t key = 0;
+  for (uint32_t m = mask[r]; m; m &= m - 1) key |= 1u << pos[__ffs(m) - 1];
+  keys[r] = key;
+  vals[r] = r;
+}
+
 __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const int* __restrict__ idx, int n,
                              unsigned long long* dst) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1030,6 +1055,21 @@ int pce_csr_sort_rows(const uint32_t* mask, int32_t n_rows, int32_t kv, void* wo
   PCE_CUDA(cudaMemsetAsync(counts, 0, 128 * sizeof(int), st));
   k_offset_counts<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, counts);
   PCE_LAUNCH_CHECK();
+  if (kv <= 32) {
+    // the key fits 32 bits (3x3x3 and 2x2x2 kernels): same order, half the bytes per radix pass
+    uint32_t* k32 = reinterpret_cast<uint32_t*>(lo);
+    uint32_t* s32 = reinterpret_cast<uint32_t*>(sorted);
+    k_mask_keys32<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, kv, counts, k32, vals);
+    PCE_LAUNCH_CHECK();
+    int begin = 0;
+    if (kmap_sort_top_bits > 0 && kmap_sort_top_bits < kv) begin = kv - kmap_sort_top_bits;
+    size_t need32 = 0;
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need32, k32, s32, vals, order, n_rows, begin, kv, st));
+    char* tmp32 = ar.take<char>(need32);
+    if (!ar.ok) return PCE_ERR_WORKSPACE;
+    PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp32, need32, k32, s32, vals, order, n_rows, begin, kv, st));
+    return PCE_OK;
+  }
   k_mask_keys<<<div_up(n_rows, 256), 256, 0, st>>>(mask, n_rows, words, kv, counts, lo, hi, vals);
   PCE_LAUNCH_CHECK();
   // least significant word first; the radix sort is stable, so the second pass keeps its order

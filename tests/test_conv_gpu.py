@@ -600,7 +600,7 @@ def test_auto_tag_selects_the_measured_dataflow():
 
 
 @pytest.mark.split_tiles
-@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 20, 3), (128, 256, 30, 3), (96, 96, 48, 3), (64, 128, 26, 5), (256, 128, 24, 2)])
+@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 20, 3), (128, 256, 30, 3), (96, 96, 48, 3), (128, 128, 26, 5), (256, 128, 24, 2)])
 def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
     """A map with few 128-row tiles runs with several CTAs per tile: every CTA takes a part of the tile's
     stage list, the fp32 partial sums are added in order by a second kernel that also applies the epilogue

@@ -115,9 +115,14 @@ def test_reference_strided_then_transposed_on_this_backend(ref, dtype, tol):
     coords = random_cloud(402, 24, 3000, batch=2)
     g = torch.Generator().manual_seed(6)
     feats = torch.randn(len(coords), 32, generator=g).to(dtype)
+    stem = ref.conv3d(32, 32, 3, 1).to(dev).to(dtype)
     down = ref.conv3d(32, 64, 3, 2, padding=1, bias=True).to(dev).to(dtype)
     up = ref.conv3d(64, 32, 3, 2, padding=1, transposed=True).to(dev).to(dtype)
-    x = _tensor(ref, coords, feats, ["D2", "end"], dev)
+    x = _tensor(ref, coords, feats, ["D2", "D2", "end"], dev)
+    # the reference's transposed layer reads the fine coordinates from cbook[fine stride], which only a layer
+    # whose OUTPUT has that stride registers (script/spconv.py:309,384): a network starts with such a layer
+    feats = stem(x).feats.detach().cpu()
+    x.feats = feats.to(dev)
     y = down(x)
     u = up(y)
     torch.cuda.synchronize()
