@@ -339,7 +339,7 @@ PCE_API int pce_device_status(int32_t* status_host, int32_t reset);
  * beside g_umma_where in csrc/conv_umma.cu); all zero when no wait expired.  Reads and clears. */
 PCE_API int pce_debug_timeout(int32_t* where4);
 
-/* Parts per tile (1, 4 or 8) that pce_conv_fwd uses for a tensor-core layer of n_rows outputs
+/* Parts per tile (1, 2, 4 or 8) that pce_conv_fwd uses for a tensor-core layer of n_rows outputs
  * when pce_epilogue.split_scratch is given; 1 = the layer is not split (large maps, layers with 16 or
  * 32 input channels, short stage chains). */
 PCE_API int32_t pce_conv_split_parts(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count);

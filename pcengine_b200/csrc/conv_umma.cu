@@ -1327,14 +1327,14 @@ static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in
 // conv_split_parts); 0: never.
 int umma_split_enabled = 1;
 
-// Parts per tile for a layer of n_rows outputs: 8 or 4 CTAs per tile where all of them are resident at once
-// (tiles x parts <= the SMs' CTA slots) and every part keeps a chain of at least 8 stages.  The chain of a
-// tile is estimated as min(kv, 16) offsets x K blocks: deep levels of a network, where maps are small, are
-// also where tiles have many offsets.  Measured on B200 (one LiDAR scan, kernel-only): 256 -> 256 on 3.4 k
-// rows (27 tiles) 104 -> 42 us with 8 parts, on 8.6 k rows (68 tiles) 100 -> 54 us with 4, 384 -> 256 143 -> 66 us;
-// two parts, or more parts than slots, do not pay for the second kernel and the fp32 round trip (189 tiles
-// 128 -> 256: 63 -> 74 us), so those maps stay unsplit.  Layers with 16 or 32 input channels (shallow levels)
-// are never split.
+// Parts per tile for a layer of n_rows outputs: 8, 4 or 2 CTAs per tile where all of them are resident at
+// once (tiles x parts <= the SMs' CTA slots) and every part keeps a chain of at least 8 stages.  The chain of
+// a tile is estimated as min(kv, 16) offsets x K blocks: deep levels of a network, where maps are small, are
+// also where tiles have many offsets.  Measured on B200 (LiDAR scans, kernel-only): 256 -> 256 on 27 tiles
+// 104 -> 42 us with 8 parts, on 68 tiles 100 -> 54 us with 4, on 132 tiles 102 -> 77 us with 2; 384 -> 256 on
+// 132 tiles 144 -> 99 us; more parts than slots do not pay for the second kernel and the fp32 round trip
+// (189 tiles, 128 -> 256, two parts on 296 slots: 63 -> 74 us), so such maps stay unsplit.  Layers with 16 or
+// 32 input channels (shallow levels) are never split.
 int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
   if (!umma_split_enabled || n_rows < 1) return 1;
   const int cin_p = (cin + 15) / 16 * 16;
@@ -1345,7 +1345,7 @@ int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
   const long long slots = static_cast<long long>(sm_count > 0 ? sm_count : 148) * (cout <= 128 ? 3 : 2);
   int p = 8;
   while (p > 1 && (n_tiles * p > slots || chain < 8 * p)) p >>= 1;
-  return p >= 4 ? p : 1;
+  return p;
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
