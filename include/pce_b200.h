@@ -105,11 +105,13 @@ typedef struct pce_epilogue {
   int32_t out_ld;
   /* Scratch for maps with few tiles (optional).  A 128-row tile is one sequential chain of
    * (offset, K block) stages on one CTA; a map with fewer tiles than the GPU has CTA slots leaves
-   * SMs idle while those chains run.  With pce_conv_split_parts(...) = P > 1 and split_scratch of at
-   * least P * n_out * c_out * 4 bytes (16-byte aligned), P CTAs take consecutive parts of every
-   * tile's stage list, store their fp32 partial sums here, and a second kernel adds the parts in
-   * order and applies the epilogue (deterministic; the fp32 sum is associated differently than in
-   * the one-CTA chain).  Without scratch the layer runs unsplit. */
+   * SMs idle while those chains run, and one with a few times as many ends in a half-empty wave.
+   * With split_scratch of at least pce_conv_split_scratch_bytes(...) bytes (16-byte aligned) the
+   * tiles are split between CTAs -- 2, 4 or 8 CTAs per tile on small maps, equal shares of the
+   * stages whatever tiles they fall in on mid-size ones --, the CTAs leave fp32 partial sums here
+   * and a second kernel adds them in a fixed order and applies the epilogue (deterministic; the
+   * fp32 sum is associated differently than in the one-CTA chain).  Without scratch the layer runs
+   * whole. */
   void* split_scratch;
   size_t split_scratch_bytes;
 } pce_epilogue;
@@ -327,7 +329,8 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * faster; tile lists of 512 rows always run on the former; what = 5: hash-table queries of the
  * map builder with four cooperating lanes per query (1) or one thread per query (0, default);
  * what = 6: sort the rows on the most significant `value` bits of their key only (0 = all, default);
- * what = 7: 0 never splits a tile's stage chain over several CTAs (1 = by pce_conv_split_parts). */
+ * what = 7: 0 never splits tiles between CTAs; 1 (default) as pce_conv_split_scratch_bytes says;
+ *           2 only the split of small maps into parts, no shares of stages on mid-size maps. */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
@@ -343,6 +346,11 @@ PCE_API int pce_debug_timeout(int32_t* where4);
  * when pce_epilogue.split_scratch is given; 1 = the layer is not split (large maps, layers with 16 or
  * 32 input channels, short stage chains). */
 PCE_API int32_t pce_conv_split_parts(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count);
+
+/* Bytes of pce_epilogue.split_scratch with which pce_conv_fwd splits a tensor-core layer of n_rows
+ * outputs; 0 = the layer runs whole. */
+PCE_API size_t pce_conv_split_scratch_bytes(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv,
+                                            int32_t sm_count);
 
 /* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
  * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */

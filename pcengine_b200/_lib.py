@@ -24,7 +24,7 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_UMMA = 0, 1, 2
 EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
-    "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_split_parts", "pce_conv_fwd", "pce_packed_weights_bytes",
+    "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_split_parts", "pce_conv_split_scratch_bytes", "pce_conv_fwd", "pce_packed_weights_bytes",
     "pce_pack_weights", "pce_device_status", "pce_debug_timeout", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
     "pce_quantize_workspace_bytes", "pce_quantize_unique", "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release", "pce_net_run",
 ]
@@ -121,6 +121,8 @@ def _load() -> C.CDLL:
     lib.pce_conv_kernel_choice.argtypes = [i32, i32, i32, i32]
     lib.pce_conv_split_parts.restype = i32
     lib.pce_conv_split_parts.argtypes = [i32, i32, i32, i32, i32]
+    lib.pce_conv_split_scratch_bytes.restype = sz
+    lib.pce_conv_split_scratch_bytes.argtypes = [i32, i32, i32, i32, i32]
     lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
                                     C.POINTER(Epilogue), vp]
     lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, vp, i32, vp, i32, C.POINTER(Epilogue), vp]

@@ -76,6 +76,11 @@ struct Epi {
   // store raw fp32 sums to partial[(part * n_out + row) * cout + c]; k_sum_parts finishes the layer
   float* partial;
   int parts;
+  // streamk: every CTA takes an equal share of the layer's STAGES (CTA b: stages S*b/G .. S*(b+1)/G of the
+  // concatenated tile lists), whatever tiles they fall in.  A tile that lies in one CTA's share is finished by
+  // it; a tile cut between CTAs leaves raw fp32 sums in partial[((cta*2 + slot)*128 + row-in-tile)*cout + c]
+  // (slot 0: the CTA's first tile, 1: its last) and k_sum_cut_tiles finishes it.
+  int streamk;
 };
 
 struct Lists {
@@ -275,6 +280,28 @@ __device__ __forceinline__ int warp_tile_at_cost(const int* tile_ptr, int n_tile
 
 __device__ __forceinline__ int first_stage(const int* tile_ptr, int t) { return tile_ptr ? __ldg(tile_ptr + t) : t; }
 
+// First tile t in [0, n_tiles) with tile_ptr[t + 1] > s (the tile that holds stage s), by a whole warp;
+// n_tiles when there is none.
+__device__ __forceinline__ int warp_tile_of_stage(const int* tile_ptr, int n_tiles, int s, int lane) {
+  int lo = 0, hi = n_tiles;
+  while (lo < hi) {
+    const int step = (hi - lo + 31) / 32;
+    const int p = min(lo + (lane + 1) * step - 1, hi - 1);
+    const unsigned m = __ballot_sync(0xFFFFFFFFu, __ldg(tile_ptr + p + 1) > s);
+    if (m == 0) return hi;
+    const int f = __ffs(m) - 1;
+    const int hit = min(lo + (f + 1) * step - 1, hi - 1);
+    lo = f == 0 ? lo : min(lo + f * step - 1, hi - 1) + 1;
+    hi = hit;
+  }
+  return lo;
+}
+
+// Share of CTA b of G in S stages: [S*b/G, S*(b+1)/G).
+__host__ __device__ __forceinline__ int share_begin(long long total, int b, int g) {
+  return static_cast<int>(total * b / g);
+}
+
 // kStages = depth of the smem stage ring.  SUB = 128-row sub-tiles per tile (1 or 2): a tile of 128*SUB output rows
 // has SUB accumulators and every staged weight block feeds SUB MMAs, which halves the weight
 // traffic per row for SUB = 2.  Threads: 4*SUB producer warps, the MMA warp, 4 epilogue warps.
@@ -330,7 +357,18 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   // then overlap its tail as well.
   if (!ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
   const int parts = ep.parts > 1 ? ep.parts : 1;
-  if (parts > 1) {
+  const bool streamk = ep.streamk != 0;
+  int sk_begin = 0, sk_end = 0;  // this CTA's share of the stages (streamk)
+  if (streamk) {
+    const long long total = __ldg(ls.tile_ptr + n_tiles);
+    sk_begin = share_begin(total, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    sk_end = share_begin(total, static_cast<int>(blockIdx.x) + 1, static_cast<int>(gridDim.x));
+    if (warp < 2) {
+      int t = 0;
+      if (sk_end > sk_begin) t = warp_tile_of_stage(ls.tile_ptr, n_tiles, warp == 0 ? sk_begin : sk_end - 1, lane) + warp;
+      if (lane == 0) ctl->range[warp] = t;
+    }
+  } else if (parts > 1) {
     // split tiles: this CTA owns ONE tile and one part of its stage list
     if (tid == 0) {
       ctl->range[0] = static_cast<int>(blockIdx.x) / parts;
@@ -354,12 +392,19 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   auto stage_range = [&](int t, int& sa, int& sb) {
     sa = first_stage(ls.tile_ptr, t);
     sb = first_stage(ls.tile_ptr, t + 1);
-    if (parts > 1) {
+    if (streamk) {
+      sa = max(sa, sk_begin);
+      sb = min(sb, sk_end);
+    } else if (parts > 1) {
       const int n = sb - sa, part = static_cast<int>(blockIdx.x) % parts;
       const int a = sa + static_cast<int>(static_cast<long long>(n) * part / parts);
       sb = sa + static_cast<int>(static_cast<long long>(n) * (part + 1) / parts);
       sa = a;
     }
+  };
+  // streamk: does this CTA hold only a piece of tile t?
+  auto tile_cut = [&](int t) {
+    return streamk && (sk_begin > first_stage(ls.tile_ptr, t) || sk_end < first_stage(ls.tile_ptr, t + 1));
   };
   // ring stages of tile t (this CTA's part of it): its listed offsets times the K blocks; the identity
   // stage, which is the tile's last, counts with the second operand's K blocks (none without one)
@@ -378,6 +423,10 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     // =========================== producers ===========================
     int g0 = first_stage(ls.tile_ptr, t0), g1 = first_stage(ls.tile_ptr, t1);
     if (parts > 1) stage_range(t0, g0, g1);
+    if (streamk) {
+      g0 = sk_begin;
+      g1 = sk_end;
+    }
     const int rsub = lane >> 3;  // row inside a 4-row group
     const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
     int j = 0;  // smem stages issued so far (continuous over tiles)
@@ -612,6 +661,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         if (slot < n_out) rows_of[sub] = ls.order ? __ldg(ls.order + slot) : slot;
       }
       const bool any = tile_main_stages(t) + (tile_ident(t) ? kblocks2 : 0) > 0;
+      const bool cut = tile_cut(t);
       if (ep.residual) {
         // the rows are known before the accumulator is: pull the residual rows into L2 while waiting
 #pragma unroll
@@ -669,6 +719,13 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
 #pragma unroll
             for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
           }
+          continue;
+        }
+        if (cut) {  // a piece of a tile cut between CTAs: k_sum_cut_tiles adds the pieces
+          float4* dst = reinterpret_cast<float4*>(
+              ep.partial + ((static_cast<size_t>(blockIdx.x) * 2 + (t == t0 ? 0 : 1)) * kTileM + slot_in_tile) * cout + c0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
           continue;
         }
         if (ep.scale) {
@@ -1197,6 +1254,66 @@ __global__ void __launch_bounds__(256)
   *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * ep.ld_out + c0) = o;
 }
 
+// Second kernel of a stream-K layer: for every tile that was cut between CTAs, adds the pieces in CTA order
+// (fp32) and applies the epilogue; tiles that one CTA finished are left alone.  One thread per (tile row, 8
+// output channels); `ctas` = the grid of the convolution launch.
+__global__ void __launch_bounds__(256)
+    k_sum_cut_tiles(const float* __restrict__ partial, const int* __restrict__ tile_ptr, const int* __restrict__ order,
+                    int n_tiles, int ctas, int n_out, int cout, __half* __restrict__ out, Epi ep) {
+  const int chunks = cout >> 3;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(n_tiles) * kTileM * chunks) return;
+  const int c0 = static_cast<int>(i % chunks) * 8;
+  const int slot = static_cast<int>(i / chunks);
+  const int t = slot / kTileM, r = slot % kTileM;
+  if (slot >= n_out) return;
+  const int a = __ldg(tile_ptr + t), e = __ldg(tile_ptr + t + 1);
+  const long long total = __ldg(tile_ptr + n_tiles);
+  int b_lo = total > 0 ? static_cast<int>(static_cast<long long>(a) * ctas / total) - 1 : 0;
+  int b_hi = total > 0 ? static_cast<int>(static_cast<long long>(e) * ctas / total) + 1 : -1;
+  b_lo = b_lo < 0 ? 0 : b_lo;
+  b_hi = b_hi > ctas - 1 ? ctas - 1 : b_hi;
+  if (e <= a) b_hi = b_lo - 1;  // a tile without stages belongs to no share: its rows get the epilogue of zero here
+  float v[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) v[q] = 0.f;
+  int pieces = 0;
+  for (int b = b_lo; b <= b_hi; ++b) {
+    const int sb = share_begin(total, b, ctas), se = share_begin(total, b + 1, ctas);
+    if ((sb > a ? sb : a) >= (se < e ? se : e)) continue;  // this CTA's share misses the tile
+    if (sb <= a && se >= e) return;                        // one CTA held the whole tile and finished it
+    ++pieces;
+    const int which = sb >= a ? 0 : 1;  // the tile is the CTA's first tile when its share starts inside it
+    const float4* src = reinterpret_cast<const float4*>(partial + ((static_cast<size_t>(b) * 2 + which) * kTileM + r) * cout + c0);
+    const float4 x = __ldg(src), y = __ldg(src + 1);
+    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+    v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+  }
+  if (pieces == 0 && e > a) return;
+  const int row = order ? __ldg(order + slot) : slot;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    if (ep.scale) v[q] *= __ldg(ep.scale + c0 + q);
+    if (ep.shift) v[q] += __ldg(ep.shift + c0 + q);
+  }
+  if (ep.residual) {
+    const uint4 rr = *reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * cout + c0);
+    const __half2* h = reinterpret_cast<const __half2*>(&rr);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = __half22float2(h[q]);
+      v[2 * q] += f.x;
+      v[2 * q + 1] += f.y;
+    }
+  }
+  uint4 o;
+  __half2* po = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    po[q] = __floats2half2_rn(act_apply(v[2 * q], ep.act, ep.slope), act_apply(v[2 * q + 1], ep.act, ep.slope));
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * ep.ld_out + c0) = o;
+}
+
 }  // namespace umma
 
 bool conv_umma_supported(int cin, int cout, int dtype) {
@@ -1323,8 +1440,8 @@ static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in
   cudaLaunchKernelEx(&cfg, umma::k_conv_umma<NS, SUB, PUSH, SLOTS>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, nacc);
 }
 
-// 1: maps with few tiles are split over several CTAs per tile when the caller gives scratch (see
-// conv_split_parts); 0: never.
+// 1: maps with few tiles are split over several CTAs per tile, mid-size maps into equal shares of stages,
+// when the caller gives scratch (see conv_split_parts, conv_streamk_grid); 2: only the former; 0: never.
 int umma_split_enabled = 1;
 
 // Parts per tile for a layer of n_rows outputs: 8, 4 or 2 CTAs per tile where all of them are resident at
@@ -1346,6 +1463,36 @@ int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
   int p = 8;
   while (p > 1 && (n_tiles * p > slots || chain < 8 * p)) p >>= 1;
   return p;
+}
+
+// Maps of half a wave to one wave of tiles (tiles / CTA slots in (0.5, 1]) that conv_split_parts leaves
+// whole: CTAs take equal shares of the STAGES instead of whole tiles (stream-K), wherever the cuts fall, so
+// every CTA slot works for the same time instead of some running a whole chain while others idle.  A tile
+// that two or more CTAs worked on costs fp32 partial sums (written, then read by k_sum_cut_tiles), which is
+// why it pays only for long chains on less than one wave.  Measured on B200 (LiDAR scans, kernel-only, us,
+// whole -> shares): 256->256 on 189 tiles 111 -> 82, on 273 tiles 111 -> 97, 384->256 on 273 tiles 156 -> 114;
+// but 256->256 on 489 tiles (1.65 waves) 119 -> 136, 128->128 on 273 tiles 59 -> 58, and the 2x2x2
+// strided / transposed layers (chains of 8 offsets at most) 35-49 -> 56-65: those run whole.
+// Returns the grid (= the CTA slots) or 0.
+int conv_streamk_grid(int n_rows, int cin, int cout, int kv, int sm_count) {
+  if (!umma_split_enabled || umma_split_enabled == 2 || n_rows < 1) return 0;
+  const int cin_p = (cin + 15) / 16 * 16;
+  if (cin_p == 16 || cin_p == 32) return 0;
+  if (conv_split_parts(n_rows, cin, cout, kv, sm_count) > 1) return 0;
+  const int kblocks = (cin + 63) / 64;
+  const int chain = (kv < 16 ? kv : 16) * kblocks;
+  const long long n_tiles = (static_cast<long long>(n_rows) + umma::kTileM - 1) / umma::kTileM;
+  const long long slots = static_cast<long long>(sm_count > 0 ? sm_count : 148) * (cout <= 128 ? 3 : 2);
+  if (chain < 48 || 2 * n_tiles <= slots || n_tiles > slots) return 0;
+  return static_cast<int>(slots);
+}
+
+// Scratch (bytes of fp32 partial sums) that lets a layer be split, 0 when it runs whole.
+size_t conv_split_scratch_bytes(int n_rows, int cin, int cout, int kv, int sm_count) {
+  const int parts = conv_split_parts(n_rows, cin, cout, kv, sm_count);
+  if (parts > 1) return static_cast<size_t>(parts) * n_rows * cout * sizeof(float);
+  const int grid = conv_streamk_grid(n_rows, cin, cout, kv, sm_count);
+  return grid > 0 ? static_cast<size_t>(grid) * 2 * umma::kTileM * cout * sizeof(float) : 0;
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
@@ -1481,6 +1628,7 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   int grid = n_tiles < sm_count[dev] * per_sm ? n_tiles : sm_count[dev] * per_sm;
   // few tiles, long stage chains: several CTAs per tile, partial sums through the caller's scratch
   int parts = 1;
+  bool streamk = false;
   if (tiles && sub == 1 && slots == 1 && !push && ep && ep->split_scratch &&
       (reinterpret_cast<uintptr_t>(ep->split_scratch) & 15) == 0) {
     parts = conv_split_parts(n_out, cin, cout, kv, sm_count[dev]);
@@ -1489,6 +1637,15 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
       grid = n_tiles * parts;
       e.partial = static_cast<float*>(ep->split_scratch);
       e.parts = parts;
+    } else {
+      const int g = conv_streamk_grid(n_out, cin, cout, kv, sm_count[dev]);
+      if (g > 0 && g <= sm_count[dev] * per_sm &&
+          static_cast<size_t>(g) * 2 * umma::kTileM * cout * sizeof(float) <= ep->split_scratch_bytes) {
+        grid = g;
+        streamk = true;
+        e.partial = static_cast<float*>(ep->split_scratch);
+        e.streamk = 1;
+      }
     }
   }
   const __half* in_h = static_cast<const __half*>(in);
@@ -1515,6 +1672,11 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   if (parts > 1) {
     const long long work = static_cast<long long>(n_out) * (cout >> 3);
     umma::k_sum_parts<<<div_up(work, 256), 256, 0, st>>>(e.partial, parts, n_out, cout, out_h, e);
+    PCE_LAUNCH_CHECK();
+  } else if (streamk) {
+    const long long work = static_cast<long long>(n_tiles) * umma::kTileM * (cout >> 3);
+    umma::k_sum_cut_tiles<<<div_up(work, 256), 256, 0, st>>>(e.partial, ls.tile_ptr, ls.order, n_tiles, grid, n_out, cout,
+                                                            out_h, e);
     PCE_LAUNCH_CHECK();
   }
   return PCE_OK;

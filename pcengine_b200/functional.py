@@ -122,10 +122,10 @@ def _split_scratch(n_rows: int, c_in: int, c_out: int, kv: int, device):
     sms = _SM_COUNT.get(idx)
     if sms is None:
         sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    parts = int(lib.pce_conv_split_parts(n_rows, c_in, c_out, kv, sms))
-    if parts <= 1:
+    nbytes = int(lib.pce_conv_split_scratch_bytes(n_rows, c_in, c_out, kv, sms))
+    if nbytes <= 0:
         return None
-    return torch.empty((parts * n_rows * c_out,), dtype=torch.float32, device=device)
+    return torch.empty((nbytes // 4,), dtype=torch.float32, device=device)
 
 
 def _row_pitched(t: torch.Tensor) -> bool:

@@ -599,13 +599,7 @@ def test_auto_tag_selects_the_measured_dataflow():
         assert co.rel_l2(y.feats.float().cpu(), co.conv_forward(feats, conv.kernel.detach().cpu(), d2)) <= 1e-3
 
 
-@pytest.mark.split_tiles
-@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 20, 3), (128, 256, 30, 3), (96, 96, 48, 3), (128, 128, 26, 5), (256, 128, 24, 2)])
-def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
-    """A map with few 128-row tiles runs with several CTAs per tile: every CTA takes a part of the tile's
-    stage list, the fp32 partial sums are added in order by a second kernel that also applies the epilogue
-    (scale, shift, residual or second operand, activation).  Same features as the oracle and as the unsplit
-    kernel within fp16 rounding, bit-identical run to run."""
+def _split_layer_case(cin, cout, n_side, ks, stream_k):
     import pcengine_b200 as pce
     from pcengine_b200 import _lib
     from pcengine_b200 import functional as PF
@@ -618,7 +612,11 @@ def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
     csr = km.csr()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     parts = _lib.lib.pce_conv_split_parts(csr.n_rows, cin, cout, ks ** 3, sms)
-    assert parts > 1, "the case is meant to be split"
+    scratch = _lib.lib.pce_conv_split_scratch_bytes(csr.n_rows, cin, cout, ks ** 3, sms)
+    if stream_k:
+        assert parts == 1 and scratch > 0, "the case is meant to be cut into shares of stages"
+    else:
+        assert parts > 1 and scratch == parts * csr.n_rows * cout * 4, "the case is meant to be split into parts"
     g = torch.Generator().manual_seed(cin + cout + n_side)
     x = torch.randn(n, cin, generator=g).half()
     w = (torch.randn(ks ** 3, cin, cout, generator=g) / (ks ** 3 * cin) ** 0.5).half()
@@ -644,3 +642,22 @@ def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
             PF.SPLIT_TILES = True
         assert co.rel_l2(a.float().cpu(), whole.float().cpu()) <= 5e-4  # same products, another fp32 association
     assert PF.device_status() == 0
+
+
+@pytest.mark.split_tiles
+@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 20, 3), (128, 256, 30, 3), (96, 96, 48, 3), (128, 128, 26, 5), (256, 128, 24, 2)])
+def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
+    """A map with few 128-row tiles runs with several CTAs per tile: every CTA takes a part of the tile's
+    stage list, the fp32 partial sums are added in order by a second kernel that also applies the epilogue
+    (scale, shift, residual or second operand, activation).  Same features as the oracle and as the unsplit
+    kernel within fp16 rounding, bit-identical run to run."""
+    _split_layer_case(cin, cout, n_side, ks, stream_k=False)
+
+
+@pytest.mark.split_tiles
+@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 128, 3), (192, 96, 150, 3), (384, 256, 110, 3)])
+def test_mid_size_maps_cut_into_equal_shares_of_stages(cin, cout, n_side, ks):
+    """A map of half a wave to one wave of tiles with long stage chains is cut into equal shares of ring stages, one share per CTA slot,
+    wherever the cuts fall inside the tiles; tiles that two or more CTAs worked on are summed in CTA order
+    and finished by a second kernel.  Same checks as for the split into parts."""
+    _split_layer_case(cin, cout, n_side, ks, stream_k=True)
