@@ -343,14 +343,16 @@ PCE_API int pce_device_status(int32_t* status_host, int32_t reset);
 PCE_API int pce_debug_timeout(int32_t* where4);
 
 /* Parts per tile (1, 2, 4 or 8) that pce_conv_fwd uses for a tensor-core layer of n_rows outputs
- * when pce_epilogue.split_scratch is given; 1 = the layer is not split (large maps, layers with 16 or
- * 32 input channels, short stage chains). */
-PCE_API int32_t pce_conv_split_parts(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count);
+ * gathered from n_src input rows when pce_epilogue.split_scratch is given; 1 = the layer is not split
+ * into parts (large maps, layers with 16 or 32 input channels, short stage chains, up-sampling
+ * layers: few pairs per output row). */
+PCE_API int32_t pce_conv_split_parts(int32_t n_rows, int32_t n_src, int32_t c_in, int32_t c_out, int32_t kv,
+                                     int32_t sm_count);
 
 /* Bytes of pce_epilogue.split_scratch with which pce_conv_fwd splits a tensor-core layer of n_rows
- * outputs; 0 = the layer runs whole. */
-PCE_API size_t pce_conv_split_scratch_bytes(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv,
-                                            int32_t sm_count);
+ * outputs gathered from n_src input rows; 0 = the layer runs whole. */
+PCE_API size_t pce_conv_split_scratch_bytes(int32_t n_rows, int32_t n_src, int32_t c_in, int32_t c_out,
+                                            int32_t kv, int32_t sm_count);
 
 /* Which kernel family pce_conv_fwd runs for these channel counts: PCE_KERNEL_SIMT,
  * PCE_KERNEL_UMMA, or -1 when the forced choice is unsupported. */

@@ -120,9 +120,9 @@ def _load() -> C.CDLL:
     lib.pce_debug_timeout.argtypes = [C.POINTER(i32)]
     lib.pce_conv_kernel_choice.argtypes = [i32, i32, i32, i32]
     lib.pce_conv_split_parts.restype = i32
-    lib.pce_conv_split_parts.argtypes = [i32, i32, i32, i32, i32]
+    lib.pce_conv_split_parts.argtypes = [i32, i32, i32, i32, i32, i32]
     lib.pce_conv_split_scratch_bytes.restype = sz
-    lib.pce_conv_split_scratch_bytes.argtypes = [i32, i32, i32, i32, i32]
+    lib.pce_conv_split_scratch_bytes.argtypes = [i32, i32, i32, i32, i32, i32]
     lib.pce_conv_fwd_d1.argtypes = [vp, i32, i32, vp, vp, i32, i32, vp, i32, vp, vp, vp, vp, i32, vp, sz, vp, i32, i32,
                                     C.POINTER(Epilogue), vp]
     lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, vp, i32, vp, i32, C.POINTER(Epilogue), vp]

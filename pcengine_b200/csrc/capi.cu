@@ -17,8 +17,8 @@ extern int umma_overlap_launches;
 extern int umma_multi_tile;
 extern int kmap_query_lanes4;
 extern int umma_split_enabled;
-int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count);
-size_t conv_split_scratch_bytes(int n_rows, int cin, int cout, int kv, int sm_count);
+int conv_split_parts(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
+size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 extern int kmap_sort_top_bits;
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
@@ -111,14 +111,15 @@ int pce_device_status(int32_t* status_host, int32_t reset) {
   return PCE_OK;
 }
 
-int32_t pce_conv_split_parts(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count) {
+int32_t pce_conv_split_parts(int32_t n_rows, int32_t n_src, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count) {
   if (!conv_umma_supported(c_in, c_out, PCE_F16) || kv > 128) return 1;
-  return conv_split_parts(n_rows, c_in, c_out, kv, sm_count);
+  return conv_split_parts(n_rows, n_src, c_in, c_out, kv, sm_count);
 }
 
-size_t pce_conv_split_scratch_bytes(int32_t n_rows, int32_t c_in, int32_t c_out, int32_t kv, int32_t sm_count) {
+size_t pce_conv_split_scratch_bytes(int32_t n_rows, int32_t n_src, int32_t c_in, int32_t c_out, int32_t kv,
+                                    int32_t sm_count) {
   if (!conv_umma_supported(c_in, c_out, PCE_F16) || kv > 128) return 0;
-  return conv_split_scratch_bytes(n_rows, c_in, c_out, kv, sm_count);
+  return conv_split_scratch_bytes(n_rows, n_src, c_in, c_out, kv, sm_count);
 }
 
 int pce_debug_timeout(int32_t* where4) {

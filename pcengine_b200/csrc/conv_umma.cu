@@ -1218,6 +1218,7 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 2 + 4 * EPIW), SUB == 1 ? 2 : 
 // residual), parts added in ascending order in fp32; one thread per 8 output channels.
 __global__ void __launch_bounds__(256)
     k_sum_parts(const float* __restrict__ partial, int parts, int n_out, int cout, __half* __restrict__ out, Epi ep) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched while the convolution kernel drains
   const int chunks = cout >> 3;
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<long long>(n_out) * chunks) return;
@@ -1255,42 +1256,66 @@ __global__ void __launch_bounds__(256)
 }
 
 // Second kernel of a stream-K layer: for every tile that was cut between CTAs, adds the pieces in CTA order
-// (fp32) and applies the epilogue; tiles that one CTA finished are left alone.  One thread per (tile row, 8
-// output channels); `ctas` = the grid of the convolution launch.
+// (fp32) and applies the epilogue; tiles that one CTA finished are left alone.  Block (x, t) handles 256 of the
+// tile's (row, 8 output channels) items: its first warp works out which CTAs hold pieces of tile t (consecutive
+// CTAs, one per lane, 32 per round; the divisions are done once per block, not per item), then every thread sums
+// its item over them.  `ctas` = the grid of the convolution launch.
 __global__ void __launch_bounds__(256)
     k_sum_cut_tiles(const float* __restrict__ partial, const int* __restrict__ tile_ptr, const int* __restrict__ order,
                     int n_tiles, int ctas, int n_out, int cout, __half* __restrict__ out, Epi ep) {
-  const int chunks = cout >> 3;
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<long long>(n_tiles) * kTileM * chunks) return;
-  const int c0 = static_cast<int>(i % chunks) * 8;
-  const int slot = static_cast<int>(i / chunks);
-  const int t = slot / kTileM, r = slot % kTileM;
-  if (slot >= n_out) return;
+  __shared__ int s_slot[32];  // per CTA of the round: 2*b + which, or -1 (its share misses the tile)
+  __shared__ int s_whole;     // some CTA held the whole tile: nothing to do
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched while the convolution kernel drains
+  const int t = blockIdx.y;
   const int a = __ldg(tile_ptr + t), e = __ldg(tile_ptr + t + 1);
   const long long total = __ldg(tile_ptr + n_tiles);
-  int b_lo = total > 0 ? static_cast<int>(static_cast<long long>(a) * ctas / total) - 1 : 0;
-  int b_hi = total > 0 ? static_cast<int>(static_cast<long long>(e) * ctas / total) + 1 : -1;
-  b_lo = b_lo < 0 ? 0 : b_lo;
-  b_hi = b_hi > ctas - 1 ? ctas - 1 : b_hi;
-  if (e <= a) b_hi = b_lo - 1;  // a tile without stages belongs to no share: its rows get the epilogue of zero here
+  const int chunks = cout >> 3;
+  const int item = static_cast<int>(blockIdx.x) * 256 + static_cast<int>(threadIdx.x);
+  const bool live = item < kTileM * chunks;
+  const int r = live ? item / chunks : 0, c0 = live ? (item % chunks) * 8 : 0;
+  // CTAs that can hold stages of [a, e): b with share_begin(b) < e and share_begin(b + 1) > a
+  int b0 = 0, b1 = -1;
+  if (e > a && total > 0) {
+    b0 = static_cast<int>(static_cast<long long>(a) * ctas / total) - 1;
+    b1 = static_cast<int>(static_cast<long long>(e) * ctas / total) + 1;
+    b0 = b0 < 0 ? 0 : b0;
+    b1 = b1 > ctas - 1 ? ctas - 1 : b1;
+  }
+  if (threadIdx.x == 0) s_whole = 0;
   float v[8];
 #pragma unroll
   for (int q = 0; q < 8; ++q) v[q] = 0.f;
-  int pieces = 0;
-  for (int b = b_lo; b <= b_hi; ++b) {
-    const int sb = share_begin(total, b, ctas), se = share_begin(total, b + 1, ctas);
-    if ((sb > a ? sb : a) >= (se < e ? se : e)) continue;  // this CTA's share misses the tile
-    if (sb <= a && se >= e) return;                        // one CTA held the whole tile and finished it
-    ++pieces;
-    const int which = sb >= a ? 0 : 1;  // the tile is the CTA's first tile when its share starts inside it
-    const float4* src = reinterpret_cast<const float4*>(partial + ((static_cast<size_t>(b) * 2 + which) * kTileM + r) * cout + c0);
-    const float4 x = __ldg(src), y = __ldg(src + 1);
-    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-    v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+  for (int base = b0; base <= b1; base += 32) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int b = base + static_cast<int>(threadIdx.x);
+      int slot = -1;
+      if (b <= b1) {
+        const int sb = share_begin(total, b, ctas), se = share_begin(total, b + 1, ctas);
+        if ((sb > a ? sb : a) < (se < e ? se : e)) {
+          if (sb <= a && se >= e) s_whole = 1;
+          slot = 2 * b + (sb >= a ? 0 : 1);  // the tile is the CTA's first tile when its share starts inside it
+        }
+      }
+      s_slot[threadIdx.x] = slot;
+    }
+    __syncthreads();
+    if (s_whole) return;
+    if (live) {
+      for (int k = 0; k < 32; ++k) {
+        const int slot = s_slot[k];
+        if (slot < 0) continue;
+        const float4* src = reinterpret_cast<const float4*>(partial + (static_cast<size_t>(slot) * kTileM + r) * cout + c0);
+        const float4 x = __ldg(src), y = __ldg(src + 1);
+        v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+        v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+      }
+    }
   }
-  if (pieces == 0 && e > a) return;
-  const int row = order ? __ldg(order + slot) : slot;
+  // (a tile without stages belongs to no share: its rows get the epilogue of zero here)
+  const int slot_row = t * kTileM + r;
+  if (!live || slot_row >= n_out) return;
+  const int row = order ? __ldg(order + slot_row) : slot_row;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     if (ep.scale) v[q] *= __ldg(ep.scale + c0 + q);
@@ -1452,12 +1477,23 @@ int umma_split_enabled = 1;
 // 132 tiles 144 -> 99 us; more parts than slots do not pay for the second kernel and the fp32 round trip
 // (189 tiles, 128 -> 256, two parts on 296 slots: 63 -> 74 us), so such maps stay unsplit.  Layers with 16 or
 // 32 input channels (shallow levels) are never split.
-int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
+// Estimated ring stages per tile: min(kv, 16) offsets x K blocks, fewer where the map has fewer source rows than
+// output rows (a transposed 2x2x2 layer has ONE pair per output row: its tiles list up to 8 offsets, each nearly
+// empty, and splitting them only adds the partial sums; measured 16 -> 30 us on 159 tiles of 128 -> 128).
+static int chain_estimate(int n_rows, int n_src, int cin, int kv) {
+  long long offsets = kv < 16 ? kv : 16;
+  if (n_src < n_rows) {
+    const long long per_row = static_cast<long long>(kv) * n_src / n_rows;
+    offsets = per_row < offsets ? (per_row > 1 ? per_row : 1) : offsets;
+  }
+  return static_cast<int>(offsets) * ((cin + 63) / 64);
+}
+
+int conv_split_parts(int n_rows, int n_src, int cin, int cout, int kv, int sm_count) {
   if (!umma_split_enabled || n_rows < 1) return 1;
   const int cin_p = (cin + 15) / 16 * 16;
   if (cin_p == 16 || cin_p == 32) return 1;
-  const int kblocks = (cin + 63) / 64;
-  const int chain = (kv < 16 ? kv : 16) * kblocks;
+  const int chain = chain_estimate(n_rows, n_src, cin, kv);
   const long long n_tiles = (static_cast<long long>(n_rows) + umma::kTileM - 1) / umma::kTileM;
   const long long slots = static_cast<long long>(sm_count > 0 ? sm_count : 148) * (cout <= 128 ? 3 : 2);
   int p = 8;
@@ -1474,29 +1510,29 @@ int conv_split_parts(int n_rows, int cin, int cout, int kv, int sm_count) {
 // but 256->256 on 489 tiles (1.65 waves) 119 -> 136, 128->128 on 273 tiles 59 -> 58, and the 2x2x2
 // strided / transposed layers (chains of 8 offsets at most) 35-49 -> 56-65: those run whole.
 // Returns the grid (= the CTA slots) or 0.
-int conv_streamk_grid(int n_rows, int cin, int cout, int kv, int sm_count) {
+int conv_streamk_grid(int n_rows, int n_src, int cin, int cout, int kv, int sm_count) {
   if (!umma_split_enabled || umma_split_enabled == 2 || n_rows < 1) return 0;
   const int cin_p = (cin + 15) / 16 * 16;
   if (cin_p == 16 || cin_p == 32) return 0;
-  if (conv_split_parts(n_rows, cin, cout, kv, sm_count) > 1) return 0;
-  const int kblocks = (cin + 63) / 64;
-  const int chain = (kv < 16 ? kv : 16) * kblocks;
+  if (conv_split_parts(n_rows, n_src, cin, cout, kv, sm_count) > 1) return 0;
+  const int chain = chain_estimate(n_rows, n_src, cin, kv);
   const long long n_tiles = (static_cast<long long>(n_rows) + umma::kTileM - 1) / umma::kTileM;
   const long long slots = static_cast<long long>(sm_count > 0 ? sm_count : 148) * (cout <= 128 ? 3 : 2);
-  if (chain < 48 || 2 * n_tiles <= slots || n_tiles > slots) return 0;
+  if (umma_split_enabled == 3) return (chain >= 8 && 2 * n_tiles > slots && n_tiles <= 4 * slots) ? static_cast<int>(slots) : 0;
+  if (kv <= 8 || chain < 16 || 2 * n_tiles <= slots || n_tiles > slots) return 0;
   return static_cast<int>(slots);
 }
 
 // Scratch (bytes of fp32 partial sums) that lets a layer be split, 0 when it runs whole.
-size_t conv_split_scratch_bytes(int n_rows, int cin, int cout, int kv, int sm_count) {
-  const int parts = conv_split_parts(n_rows, cin, cout, kv, sm_count);
+size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count) {
+  const int parts = conv_split_parts(n_rows, n_src, cin, cout, kv, sm_count);
   if (parts > 1) return static_cast<size_t>(parts) * n_rows * cout * sizeof(float);
-  const int grid = conv_streamk_grid(n_rows, cin, cout, kv, sm_count);
+  const int grid = conv_streamk_grid(n_rows, n_src, cin, cout, kv, sm_count);
   return grid > 0 ? static_cast<size_t>(grid) * 2 * umma::kTileM * cout * sizeof(float) : 0;
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
-int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st) {
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}, cin, cout};
   if (ep) {
@@ -1631,14 +1667,14 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   bool streamk = false;
   if (tiles && sub == 1 && slots == 1 && !push && ep && ep->split_scratch &&
       (reinterpret_cast<uintptr_t>(ep->split_scratch) & 15) == 0) {
-    parts = conv_split_parts(n_out, cin, cout, kv, sm_count[dev]);
+    parts = conv_split_parts(n_out, n_in, cin, cout, kv, sm_count[dev]);
     while (parts > 1 && static_cast<size_t>(parts) * n_out * cout * sizeof(float) > ep->split_scratch_bytes) parts >>= 1;
     if (parts > 1) {
       grid = n_tiles * parts;
       e.partial = static_cast<float*>(ep->split_scratch);
       e.parts = parts;
     } else {
-      const int g = conv_streamk_grid(n_out, cin, cout, kv, sm_count[dev]);
+      const int g = conv_streamk_grid(n_out, n_in, cin, cout, kv, sm_count[dev]);
       if (g > 0 && g <= sm_count[dev] * per_sm &&
           static_cast<size_t>(g) * 2 * umma::kTileM * cout * sizeof(float) <= ep->split_scratch_bytes) {
         grid = g;
@@ -1669,14 +1705,27 @@ int conv_umma(const void* in, int /*n_in*/, const void* wpacked, int kv, const p
   }
 #undef PCE_GO
   PCE_LAUNCH_CHECK();
-  if (parts > 1) {
-    const long long work = static_cast<long long>(n_out) * (cout >> 3);
-    umma::k_sum_parts<<<div_up(work, 256), 256, 0, st>>>(e.partial, parts, n_out, cout, out_h, e);
-    PCE_LAUNCH_CHECK();
-  } else if (streamk) {
-    const long long work = static_cast<long long>(n_tiles) * umma::kTileM * (cout >> 3);
-    umma::k_sum_cut_tiles<<<div_up(work, 256), 256, 0, st>>>(e.partial, ls.tile_ptr, ls.order, n_tiles, grid, n_out, cout,
-                                                            out_h, e);
+  if (parts > 1 || streamk) {
+    // the second kernel of a split layer is set up on the SMs while the convolution's last CTAs drain
+    // (programmatic dependent launch; it waits for that grid before it reads a partial sum)
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = umma_overlap_launches ? 1 : 0;
+    const float* partial = e.partial;
+    if (parts > 1) {
+      cfg.gridDim = dim3(div_up(static_cast<long long>(n_out) * (cout >> 3), 256));
+      cudaLaunchKernelEx(&cfg, umma::k_sum_parts, partial, parts, n_out, cout, out_h, e);
+    } else {
+      cfg.gridDim = dim3(div_up(umma::kTileM * (cout >> 3), 256), n_tiles);
+      const int* tile_ptr = ls.tile_ptr;
+      const int* order = ls.order;
+      cudaLaunchKernelEx(&cfg, umma::k_sum_cut_tiles, partial, tile_ptr, order, n_tiles, grid, n_out, cout, out_h, e);
+    }
     PCE_LAUNCH_CHECK();
   }
   return PCE_OK;

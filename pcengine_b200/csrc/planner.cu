@@ -38,7 +38,7 @@
 namespace pce {
 
 bool conv_umma_supported(int cin, int cout, int dtype);
-size_t conv_split_scratch_bytes(int n_rows, int cin, int cout, int kv, int sm_count);
+size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 
@@ -702,7 +702,7 @@ static int net_run_on(pce_pass* ps, const pce_net_buffer* buffers, int32_t n_buf
     if (!tl) return PCE_ERR_INVALID;  // the plan was declared without this layer's widths
     // small and mid-size maps: tiles split between CTAs; the fp32 partial sums live behind the buffers
     // (one region, reused by every split layer: the layers run in stream order)
-    const size_t want = conv_split_scratch_bytes(dst_rows, op.c_in, op.c_out, op.kv, p->sm_count);
+    const size_t want = conv_split_scratch_bytes(dst_rows, src_rows, op.c_in, op.c_out, op.kv, p->sm_count);
     if (want > 0) {
       const size_t need = pad256(want);
       if (need > split_bytes) {  // a larger region behind what is placed so far (the old one stays unused)

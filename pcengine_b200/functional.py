@@ -114,7 +114,7 @@ def _pack(ep: Optional[FusedEpilogue], c_out, n_out, dtype, in_ld: int = 0, out_
 SPLIT_TILES = True
 
 
-def _split_scratch(n_rows: int, c_in: int, c_out: int, kv: int, device):
+def _split_scratch(n_rows: int, n_src: int, c_in: int, c_out: int, kv: int, device):
     """fp32 scratch for the partial sums of a layer that the library will split, or None."""
     if not SPLIT_TILES:
         return None
@@ -122,7 +122,7 @@ def _split_scratch(n_rows: int, c_in: int, c_out: int, kv: int, device):
     sms = _SM_COUNT.get(idx)
     if sms is None:
         sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    nbytes = int(lib.pce_conv_split_scratch_bytes(n_rows, c_in, c_out, kv, sms))
+    nbytes = int(lib.pce_conv_split_scratch_bytes(n_rows, n_src, c_in, c_out, kv, sms))
     if nbytes <= 0:
         return None
     return torch.empty((nbytes // 4,), dtype=torch.float32, device=device)
@@ -310,7 +310,7 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         rows = TILE_ROWS or (128 if pushes else _auto_tile_rows(csr.n_rows, c_in, c_out, feats.device))
         tiles = C.byref(csr.tiles(SORT_ROWS, rows, second, stage_slots(c_in)))
         if rows == 128 and not pushes:
-            split = _split_scratch(csr.n_rows, c_in, c_out, kv, feats.device)
+            split = _split_scratch(csr.n_rows, feats.size(0), c_in, c_out, kv, feats.device)
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
                                 csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype),

@@ -611,8 +611,8 @@ def _split_layer_case(cin, cout, n_side, ks, stream_k):
                        d2["cmax_out"], subm)
     csr = km.csr()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    parts = _lib.lib.pce_conv_split_parts(csr.n_rows, cin, cout, ks ** 3, sms)
-    scratch = _lib.lib.pce_conv_split_scratch_bytes(csr.n_rows, cin, cout, ks ** 3, sms)
+    parts = _lib.lib.pce_conv_split_parts(csr.n_rows, n, cin, cout, ks ** 3, sms)
+    scratch = _lib.lib.pce_conv_split_scratch_bytes(csr.n_rows, n, cin, cout, ks ** 3, sms)
     if stream_k:
         assert parts == 1 and scratch > 0, "the case is meant to be cut into shares of stages"
     else:
@@ -655,7 +655,7 @@ def test_small_maps_split_over_several_ctas(cin, cout, n_side, ks):
 
 
 @pytest.mark.split_tiles
-@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 128, 3), (192, 96, 150, 3), (384, 256, 110, 3)])
+@pytest.mark.parametrize("cin,cout,n_side,ks", [(256, 256, 128, 3), (192, 96, 150, 3), (384, 256, 110, 3), (64, 64, 140, 3)])
 def test_mid_size_maps_cut_into_equal_shares_of_stages(cin, cout, n_side, ks):
     """A map of half a wave to one wave of tiles with long stage chains is cut into equal shares of ring stages, one share per CTA slot,
     wherever the cuts fall inside the tiles; tiles that two or more CTAs worked on are summed in CTA order
