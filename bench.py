@@ -903,6 +903,7 @@ def run_ours(args):
                 "because the aggregate spans every launch shape of a step (DRAM bytes of single shapes: profiles/)"}
     # ---- extras ------------------------------------------------------------------------------
     layers = cpu = parity = config1 = indoor = scene = None
+    cores_per_rank = len(os.sched_getaffinity(0))
     if not args.lean:
         scene = scene_rows(dev, pk, rank, world, ((3, 64), (3, 256)), 3, 2)  # every rank takes part
     if rank != 0:
@@ -918,6 +919,15 @@ def run_ours(args):
         cpu_v, cpu_dt, cores, sample, o_logits, o_maps = oracle_pass(my_ids, 1, 0, want_outputs=True)
         cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
         parity = check_parity(maps, gpu_logits, o_logits, o_maps)
+    elif not args.lean:
+        # N > 1: the other ranks have left; rank 0 checks ITS shard of the batch against the oracle on all
+        # host cores (the CPU baseline itself is the N = 1 line's and the reference arm's)
+        dist.destroy_process_group()
+        cores_per_rank = len(os.sched_getaffinity(0))
+        os.sched_setaffinity(0, all_cores)
+        _, _, _, _, o_logits, o_maps = oracle_pass(my_ids, 1, 0, want_outputs=True)
+        parity = check_parity(maps, gpu_logits, o_logits, o_maps)
+        parity["scans_checked"] = list(my_ids)
     del maps, last
     total_scans = BATCH_SCANS * steps
     value = total_scans / dt
@@ -956,10 +966,10 @@ def run_ours(args):
     }
     if world > 1:
         line["weak_scans_per_s"] = weak
-        line["per_rank"] = {**per_rank, "host_cores": host_cores, "cores_per_rank": len(os.sched_getaffinity(0)),
+        line["per_rank"] = {**per_rank, "host_cores": host_cores, "cores_per_rank": cores_per_rank,
                             "pinned": bool(args.pin)}
     print(json.dumps(line))
-    if world > 1:
+    if world > 1 and dist.is_initialized():
         dist.destroy_process_group()
 
 
