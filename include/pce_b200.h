@@ -330,7 +330,9 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * map builder with four cooperating lanes per query (1) or one thread per query (0, default);
  * what = 6: sort the rows on the most significant `value` bits of their key only (0 = all, default);
  * what = 7: 0 never splits tiles between CTAs; 1 (default) as pce_conv_split_scratch_bytes says;
- *           2 only the split of small maps into parts, no shares of stages on mid-size maps. */
+ *           2 only the split of small maps into parts, no shares of stages on mid-size maps.
+ * what = 8: 0 runs layers whose width is an odd multiple of 32 channels with 64-channel K blocks
+ *           like every other layer (1, default: with 32-channel blocks, every ring stage full). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose

@@ -17,6 +17,7 @@ extern int umma_overlap_launches;
 extern int umma_multi_tile;
 extern int kmap_query_lanes4;
 extern int umma_split_enabled;
+extern int umma_kb32_enabled;
 int conv_split_parts(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 extern int kmap_sort_top_bits;
@@ -98,6 +99,10 @@ int pce_tune(int32_t what, int32_t value) {
   }
   if (what == 7) {
     umma_split_enabled = value < 0 ? 0 : value;
+    return PCE_OK;
+  }
+  if (what == 8) {
+    umma_kb32_enabled = value ? 1 : 0;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

@@ -13,6 +13,8 @@ namespace pce {
 bool conv_umma_supported(int cin, int cout, int dtype);
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
+int conv_umma_kb64(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+                   int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
 
 struct EpiDev {
   const float* scale;
@@ -261,7 +263,7 @@ static int run_d1(const void* in, int n_in, int cin, const void* w, const void* 
                                reinterpret_cast<uintptr_t>(wpacked)) % 16 == 0);
       if (tc_centre) {
         const __half* wp = static_cast<const __half*>(wpacked) + static_cast<size_t>(centre_kp) * kblocks * cout * 64;
-        PCE_TRY(conv_umma(in, n_in, wp, 1, nullptr, n_out, cin, cout, out, nullptr, st));
+        PCE_TRY(conv_umma_kb64(in, n_in, wp, 1, nullptr, n_out, cin, cout, out, nullptr, st));
         centre = static_cast<const T*>(out);
       } else {
         if (w == nullptr) return PCE_ERR_INVALID;

@@ -54,7 +54,7 @@ __device__ int g_umma_where[4] = {0, 0, 0, 0};
 namespace umma {
 
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 6;
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows x 64 fp16
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s at 2 GHz
 
@@ -201,6 +201,15 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
+// The same for operand tiles of KB channels per row: KB = 64 as above; KB = 32 rows of 64 B, 64-byte swizzle
+// (16-byte chunk c of row r at chunk c ^ ((r >> 1) & 3)), 8-row groups 512 B apart.
+template <int KB>
+__device__ __forceinline__ uint64_t make_desc_kb(uint32_t smem_addr) {
+  if constexpr (KB == 64) return make_desc(smem_addr);
+  const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = (512u >> 4) | (1u << 14) | (4u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -213,6 +222,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 32 bytes of a row in ONE store (256-bit vector access): half the store instructions, and half the requests to
+// the load/store unit, of two 16-byte stores; `p` must be 32-byte aligned.
+__device__ __forceinline__ void store32(void* p, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+
+__device__ __forceinline__ void load32(const void* p, uint4& a, uint4& b) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p)
+               : "memory");
+}
+
 __device__ __forceinline__ float act_apply(float v, int act, float slope) {
   if (act == PCE_ACT_RELU) return v > 0.f ? v : 0.f;
   if (act == PCE_ACT_LEAKY) return v > 0.f ? v : v * slope;
@@ -221,8 +245,28 @@ __device__ __forceinline__ float act_apply(float v, int act, float slope) {
 
 // Weights [kv][cin][cout] fp16 -> per (kp, k-block) shared-memory images of cout rows x 128 B
 // (64 K elements, zero padded), 16-byte chunks XOR-swizzled with the row index.
+// kb_size = 32: images of cout rows x 64 B (32 K elements), 64-byte swizzle (chunk ^ ((row >> 1) & 3)).
 __global__ void k_pack_weights(const __half* __restrict__ w, int kv, int cin, int cout, int kblocks,
-                               __half* __restrict__ packed) {
+                               __half* __restrict__ packed, int kb_size) {
+  if (kb_size == 32) {
+    const long long total32 = static_cast<long long>(kv) * kblocks * cout * 32;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total32;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const int kk = static_cast<int>(i % 32);
+      long long t = i / 32;
+      const int co = static_cast<int>(t % cout);
+      t /= cout;
+      const int kb = static_cast<int>(t % kblocks);
+      const int kp = static_cast<int>(t / kblocks);
+      const int ci = kb * 32 + kk;
+      __half v = __float2half(0.f);
+      if (ci < cin) v = w[(static_cast<size_t>(kp) * cin + ci) * cout + co];
+      const int chunk = kk >> 3, within = kk & 7;
+      const size_t img = (static_cast<size_t>(kp) * kblocks + kb) * cout * 32;
+      packed[img + static_cast<size_t>(co) * 32 + ((chunk ^ ((co >> 1) & 3)) << 3) + within] = v;
+    }
+    return;
+  }
   const long long total = static_cast<long long>(kv) * kblocks * cout * 64;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -309,7 +353,9 @@ __host__ __device__ __forceinline__ int share_begin(long long total, int b, int 
 // of the 64-channel K block, so SLOTS offsets of a tile share one ring stage: every row gathers one
 // neighbour per slot into its part of the 128-byte row, and the producers assemble the stage's weight
 // block from the per-offset images with cp.async (covered by the same barrier as the rows).
-template <int kStages, int SUB, bool PUSH, int SLOTS>
+// KB = channels per K block (64, or 32 for layers whose width is an odd multiple of 32: every stage is then
+// full, where 64-channel blocks would spend half of every second stage's rows and weights on padding).
+template <int kStages, int SUB, bool PUSH, int SLOTS, int KB = 64>
 __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     k_conv_umma(const __half* __restrict__ in, const __half* __restrict__ wpacked, Lists ls, Second sec, int n_out, int cin,
                 int cout, __half* __restrict__ out, Epi ep, int tmem_cols, int nacc) {
@@ -318,9 +364,11 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t* tiles = smem_raw + pad;  // 1024-byte aligned
   const uint32_t tiles_addr = raw_addr + pad;
-  const int b_bytes = cout * 128;
+  static_assert(KB == 64 || (KB == 32 && SUB == 1 && SLOTS == 1), "32-channel K blocks: plain variant only");
+  constexpr int kRowBytes = KB * 2;            // one operand row of a stage
+  const int b_bytes = cout * kRowBytes;
   constexpr int kRows = kTileM * SUB;          // output rows per tile
-  constexpr int kAStage = kABytes * SUB;       // gathered rows of one stage
+  constexpr int kAStage = kTileM * kRowBytes * SUB;  // gathered rows of one stage
   constexpr int kMmaWarp = 4 * SUB;
   const int stage_bytes = kAStage + b_bytes;   // both multiples of 1024
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * stage_bytes);
@@ -328,8 +376,8 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int kblocks = (cin + 63) >> 6;
-  const int kblocks2 = sec.in2 ? (sec.cin2 + 63) >> 6 : 0;  // ring stages of the identity stage
+  const int kblocks = (cin + KB - 1) / KB;
+  const int kblocks2 = sec.in2 ? (sec.cin2 + KB - 1) / KB : 0;  // ring stages of the identity stage
   const int n_tiles = (n_out + kRows - 1) / kRows;
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -427,8 +475,10 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
       g0 = sk_begin;
       g1 = sk_end;
     }
-    const int rsub = lane >> 3;  // row inside a 4-row group
-    const int chunk = lane & 7;  // 16-byte chunk inside a 128-byte row
+    constexpr int kCpr = KB / 8;                // 16-byte chunks per operand row (8 or 4)
+    constexpr int kRowsPerInstr = 32 / kCpr;    // rows one warp instruction covers (4 or 8)
+    const int rsub = lane / kCpr;   // row inside the group of rows of one instruction
+    const int chunk = lane % kCpr;  // 16-byte chunk inside the row
     int j = 0;  // smem stages issued so far (continuous over tiles)
     bool ok = true;
     if constexpr (SLOTS == 1) {
@@ -462,18 +512,19 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         if (tid == 0) {
           const uint32_t bbar = smem_u32(&ctl->bfull[s]);
           mbar_arrive_expect_tx(bbar, b_bytes);
-          const __half* wsrc = second ? sec.w2 + static_cast<size_t>(kb) * cout * 64
-                                      : wpacked + (static_cast<size_t>(kp) * kblocks + kb) * cout * 64;
+          const __half* wsrc = second ? sec.w2 + static_cast<size_t>(kb) * cout * KB
+                                      : wpacked + (static_cast<size_t>(kb) + static_cast<size_t>(kp) * kblocks) * cout * KB;
           bulk_copy_g2s(a_addr + kAStage, wsrc, b_bytes, bbar);
         }
-        const int kchunks = min(8, (width - kb * 64) >> 3);
+        const int kchunks = min(kCpr, (width - kb * KB) >> 3);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int r = q * 4 + rsub;  // row inside this warp's 32
+        for (int q = 0; q < kCpr; ++q) {
+          const int r = q * kRowsPerInstr + rsub;  // row inside this warp's 32
           const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
           if (chunk < kchunks) {
-            const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * pitch + kb * 64 + chunk * 8 : 0);
+            const int sw = KB == 64 ? (chunk ^ (r & 7)) : (chunk ^ ((r >> 1) & 3));
+            const uint32_t dst = a_addr + (warp * 32 + r) * kRowBytes + (sw << 4);
+            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * pitch + kb * KB + chunk * 8 : 0);
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
@@ -620,15 +671,15 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
           fence_proxy_async();  // the gathered rows were written through the generic proxy
           tc_fence_after();
           const uint32_t a_addr = tiles_addr + s * stage_bytes;
-          const uint64_t db = make_desc(a_addr + kAStage);
+          const uint64_t db = make_desc_kb<KB>(a_addr + kAStage);
           const bool second = st >= nst_main;
           const int kb = second ? st - nst_main : st % kblocks;
           // with several offsets per stage the whole 64-channel block is always filled (unused slots with zeros)
-          const int ksteps = (SLOTS > 1 && !second) ? 4 : min(4, ((second ? sec.cin2 : cin) - kb * 64) >> 4);
+          const int ksteps = (SLOTS > 1 && !second) ? 4 : min(KB / 16, ((second ? sec.cin2 : cin) - kb * KB) >> 4);
           for (int k = 0; k < ksteps; ++k) {
 #pragma unroll
             for (int sub = 0; sub < SUB; ++sub) {  // the same weight block feeds every sub-tile
-              const uint64_t da = make_desc(a_addr + sub * kABytes);
+              const uint64_t da = make_desc_kb<KB>(a_addr + sub * (kTileM * kRowBytes));
               tc_mma_f16(tmem_acc + static_cast<uint32_t>(sub * cout), da + static_cast<uint64_t>(k * 2),
                          db + static_cast<uint64_t>(k * 2), idesc, accumulate);
             }
@@ -649,6 +700,9 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     // =========================== epilogue ===========================
     const int lane_quarter = warp & 3;  // the TMEM lanes this warp may read: 32*(warp%4)..+31
     const int slot_in_tile = lane_quarter * 32 + lane;
+    // every 16-channel piece of an output row is 32-byte aligned: one 256-bit store per piece
+    const bool wide_out = (ep.ld_out & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+    const bool wide_res = (reinterpret_cast<uintptr_t>(ep.residual) & 31) == 0;  // (rows of C_out = 16k channels)
     if (ls.settled) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int t = t0; t < t1; ++t) {
       const int it = t - t0;
@@ -698,8 +752,12 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
       for (int c0 = 0; c0 < cout; c0 += 16) {
         uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
         if (rrow) {  // issued ahead of the tensor-memory load, consumed after it
-          ra = *reinterpret_cast<const uint4*>(rrow + c0);
-          rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
+          if (wide_res) {
+            load32(rrow + c0, ra, rb);
+          } else {
+            ra = *reinterpret_cast<const uint4*>(rrow + c0);
+            rb = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
+          }
         }
         uint32_t r[16];
         if (any) {  // warp-uniform: the tensor-memory load is warp-collective
@@ -771,8 +829,12 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
                                     act_apply(v[8 + 2 * q + 1], ep.act, ep.slope));
         }
         if (store_row) {
-          *reinterpret_cast<uint4*>(orow + c0) = oa;
-          *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
+          if (wide_out) {
+            store32(orow + c0, oa, ob);
+          } else {
+            *reinterpret_cast<uint4*>(orow + c0) = oa;
+            *reinterpret_cast<uint4*>(orow + c0 + 8) = ob;
+          }
         }
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
@@ -1347,9 +1409,17 @@ bool conv_umma_supported(int cin, int cout, int dtype) {
 
 // Per-offset blocks, and for 16 or 32 input channels also the per-offset [cout][cin] images from which
 // stages that hold several offsets assemble their weight block.
-size_t umma_packed_bytes(int kv, int cin, int cout) {
+// Behind them, a second copy as 32-channel blocks (cout rows x 64 B, 64-byte swizzle) for widths that are an odd
+// multiple of 32 (the kernel variant with 32-channel K blocks) and for every single-offset weight (a second
+// operand is read in the K-block size of the layer it joins).
+static bool has_kb32_image(int kv, int cin) { return kv == 1 || (cin > 32 && cin % 64 == 32); }
+static size_t kb64_image_bytes(int kv, int cin, int cout) {
   const size_t blocks = static_cast<size_t>(kv) * ((cin + 63) / 64) * cout * 128;
   return blocks + ((cin == 16 || cin == 32) ? static_cast<size_t>(kv) * cout * cin * 2 : 0);
+}
+size_t umma_packed_bytes(int kv, int cin, int cout) {
+  const size_t kb32 = has_kb32_image(kv, cin) ? static_cast<size_t>(kv) * ((cin + 31) / 32) * cout * 64 : 0;
+  return kb64_image_bytes(kv, cin, cout) + kb32;
 }
 
 int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cudaStream_t st) {
@@ -1357,8 +1427,16 @@ int umma_pack_weights(const void* w, int kv, int cin, int cout, void* packed, cu
   const long long total = static_cast<long long>(kv) * kblocks * cout * 64;
   const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148ll * 8));
   umma::k_pack_weights<<<grid, 256, 0, st>>>(static_cast<const __half*>(w), kv, cin, cout, kblocks,
-                                             static_cast<__half*>(packed));
+                                             static_cast<__half*>(packed), 64);
   PCE_LAUNCH_CHECK();
+  if (has_kb32_image(kv, cin)) {
+    const int kblocks32 = (cin + 31) / 32;
+    const long long total32 = static_cast<long long>(kv) * kblocks32 * cout * 32;
+    umma::k_pack_weights<<<static_cast<int>(std::min<long long>((total32 + 255) / 256, 148ll * 8)), 256, 0, st>>>(
+        static_cast<const __half*>(w), kv, cin, cout, kblocks32,
+        reinterpret_cast<__half*>(static_cast<char*>(packed) + kb64_image_bytes(kv, cin, cout)), 32);
+    PCE_LAUNCH_CHECK();
+  }
   if (cin == 16 || cin == 32) {
     const long long n = static_cast<long long>(kv) * cout * cin;
     umma::k_pack_weight_slots<<<static_cast<int>(std::min<long long>((n + 255) / 256, 148ll * 8)), 256, 0, st>>>(
@@ -1448,7 +1526,7 @@ static int conv_umma_mt(const __half* in, const __half* w, const umma::Lists& ls
   return PCE_OK;
 }
 
-template <int NS, int SUB, bool PUSH, int SLOTS>
+template <int NS, int SUB, bool PUSH, int SLOTS, int KB = 64>
 static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in, const __half* w, const umma::Lists& ls,
                         const umma::Second& sec, int n_out, int cin, int cout, __half* out, const umma::Epi& e, int tmem_cols,
                         int nacc) {
@@ -1462,8 +1540,13 @@ static void launch_umma(int grid, size_t smem, cudaStream_t st, const __half* in
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = umma_overlap_launches ? 1 : 0;
-  cudaLaunchKernelEx(&cfg, umma::k_conv_umma<NS, SUB, PUSH, SLOTS>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols, nacc);
+  cudaLaunchKernelEx(&cfg, umma::k_conv_umma<NS, SUB, PUSH, SLOTS, KB>, in, w, ls, sec, n_out, cin, cout, out, e, tmem_cols,
+                     nacc);
 }
+
+// 1: layers whose width is an odd multiple of 32 channels (96, 160, 224) run with 32-channel K blocks, where every
+// ring stage is full (64-channel blocks pad half of every second stage); 0: 64-channel blocks everywhere.
+int umma_kb32_enabled = 1;
 
 // 1: maps with few tiles are split over several CTAs per tile, mid-size maps into equal shares of stages,
 // when the caller gives scratch (see conv_split_parts, conv_streamk_grid); 2: only the former; 0: never.
@@ -1532,8 +1615,23 @@ size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv
 }
 
 // tiles == nullptr: the dense rows x matrix product (every row fetches itself, one offset).
+static int conv_umma_impl(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out,
+                          int cin, int cout, void* out, const pce_epilogue* ep, cudaStream_t st, bool kb64_slice);
+
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st) {
+  return conv_umma_impl(in, n_in, wpacked, kv, tiles, n_out, cin, cout, out, ep, st, false);
+}
+
+// The same for weights that are a SLICE of a larger packed buffer (one offset's 64-channel blocks): there is no
+// second image behind them, so the layer runs with 64-channel K blocks whatever its width.
+int conv_umma_kb64(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
+                   int cout, void* out, const pce_epilogue* ep, cudaStream_t st) {
+  return conv_umma_impl(in, n_in, wpacked, kv, tiles, n_out, cin, cout, out, ep, st, true);
+}
+
+static int conv_umma_impl(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out,
+                          int cin, int cout, void* out, const pce_epilogue* ep, cudaStream_t st, bool kb64_slice) {
   umma::Epi e{nullptr, nullptr, nullptr, PCE_ACT_NONE, 0.f, {nullptr, nullptr}, {nullptr, nullptr}, cin, cout};
   if (ep) {
     e = umma::Epi{ep->scale, ep->shift, static_cast<const __half*>(ep->residual), ep->act, ep->slope,
@@ -1573,11 +1671,17 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
                        ep->extra_c};
   }
   const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
-  const size_t stage = static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
+  // 32-channel K blocks for widths that are an odd multiple of 32 (plain variant: one sub-tile, one offset per
+  // stage, no halo push); operands then come from the second image of the packed weights
+  const bool kb32 = umma_kb32_enabled && !kb64_slice && sub == 1 && slots == 1 && !(e.push_slot[0] || e.push_slot[1]) && cin > 32 &&
+                    cin % 64 == 32 && !(tiles && umma_multi_tile);
+  const size_t stage = kb32 ? static_cast<size_t>(umma::kTileM) * 64 + static_cast<size_t>(cout) * 64
+                            : static_cast<size_t>(umma::kABytes) * sub + static_cast<size_t>(cout) * 128;
   static int sm_count[64] = {};
   // registers per thread by kernel variant (plain, push, 2 slots, 4 slots) and sub-tile count, in
   // allocation units of 8; read back from the compiled kernels at set-up
   static int regs_per_thread[4][2] = {{72, 72}, {80, 80}, {80, 80}, {96, 88}};
+  static int regs_kb32 = 72;
   int dev = 0;
   PCE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PCE_ERR_UNSUPPORTED;
@@ -1588,6 +1692,9 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
   PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));  \
   PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); \
   PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<NS, SB, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap))
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<4, 1, false, 1, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<5, 1, false, 1, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    PCE_CUDA(cudaFuncSetAttribute(umma::k_conv_umma<6, 1, false, 1, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
     PCE_SET_SMEM(4, 1);
     PCE_SET_SMEM(3, 1);
     PCE_SET_SMEM(2, 1);
@@ -1607,6 +1714,8 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
     PCE_REGS(3, 1, (umma::k_conv_umma<2, 1, false, 4>));
     PCE_REGS(3, 2, (umma::k_conv_umma<2, 2, false, 4>));
 #undef PCE_REGS
+    if (cudaFuncGetAttributes(&fa, umma::k_conv_umma<4, 1, false, 1, 32>) == cudaSuccess && fa.numRegs > 0)
+      regs_kb32 = (fa.numRegs + 7) / 8 * 8;
     int n = 0;
     PCE_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     sm_count[dev] = n > 0 ? n : 1;
@@ -1628,7 +1737,7 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
   const bool push = e.push_slot[0] || e.push_slot[1];
   if (push && slots != 1) return PCE_ERR_UNSUPPORTED;  // the halo push has no several-offsets-per-stage variant
   const int variant = push ? 1 : (slots == 2 ? 2 : (slots == 4 ? 3 : 0));
-  const int by_regs = 65536 / (threads * regs_per_thread[variant][sub - 1]);
+  const int by_regs = 65536 / (threads * (kb32 ? regs_kb32 : regs_per_thread[variant][sub - 1]));
   auto tmem_for = [&](int sets) {
     int cols = 32;
     while (cols < sets * sub * cout) cols <<= 1;
@@ -1642,7 +1751,7 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
     return c > 4 ? 4 : c;
   };
   int ns = 2, nacc = 1, per_sm = 0;
-  for (int n = 4; n >= 2; --n) {
+  for (int n = (kb32 ? 6 : 4); n >= (kb32 ? 4 : 2); --n) {  // (32-channel blocks: half-size stages, rings of 4 to 6)
     for (int sets = 2; sets >= 1; --sets) {
       const int c = ctas_for(n, sets);
       const bool better = c * n > per_sm * ns || (c * n == per_sm * ns && c > per_sm);
@@ -1653,7 +1762,7 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
       }
     }
   }
-  if (umma_force_stages >= 2 && umma_force_stages <= 4) ns = umma_force_stages;
+  if (umma_force_stages >= (kb32 ? 4 : 2) && umma_force_stages <= (kb32 ? 6 : 4)) ns = umma_force_stages;
   if ((umma_force_nacc == 1 || umma_force_nacc == 2) && umma_force_nacc * sub * cout <= 512) nacc = umma_force_nacc;
   per_sm = ctas_for(ns, nacc);
   const int tmem_cols = tmem_for(nacc);
@@ -1687,6 +1796,17 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
   const __half* in_h = static_cast<const __half*>(in);
   const __half* w_h = static_cast<const __half*>(wpacked);
   __half* out_h = static_cast<__half*>(out);
+  if (kb32) {
+    w_h = reinterpret_cast<const __half*>(static_cast<const char*>(wpacked) + kb64_image_bytes(kv, cin, cout));
+    if (sec.in2)
+      sec.w2 = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(sec.w2) + kb64_image_bytes(1, sec.cin2, cout));
+    if (ns == 6)
+      launch_umma<6, 1, false, 1, 32>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);
+    else if (ns == 5)
+      launch_umma<5, 1, false, 1, 32>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);
+    else
+      launch_umma<4, 1, false, 1, 32>(grid, smem, st, in_h, w_h, ls, sec, n_out, cin, cout, out_h, e, tmem_cols, nacc);
+  } else {
 #define PCE_GO(NS, SB)                                                                                              \
   do {                                                                                                              \
     if (push)                                                                                                         \
@@ -1704,6 +1824,7 @@ int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_t
     if (ns == 4) PCE_GO(4, 2); else if (ns == 3) PCE_GO(3, 2); else PCE_GO(2, 2);
   }
 #undef PCE_GO
+  }
   PCE_LAUNCH_CHECK();
   if (parts > 1 || streamk) {
     // the second kernel of a split layer is set up on the SMs while the convolution's last CTAs drain

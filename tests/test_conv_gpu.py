@@ -20,7 +20,7 @@ def _tensor(pce, coords, feats, tags=("D2", "D2", "D2", "end")):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("cin,cout", [(16, 16), (4, 32), (32, 32), (64, 64), (32, 64), (96, 96), (128, 128), (24, 19),
-                                      (3, 5)])
+                                      (3, 5), (160, 48), (224, 256)])
 @pytest.mark.parametrize("kernel_choice", ["auto", "simt"])
 def test_submanifold_features(dtype, cin, cout, kernel_choice):
     import pcengine_b200 as pce
