@@ -496,17 +496,27 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         }
       }
     };
+    // destination of this thread's copy q inside a stage: row q * kRowsPerInstr + rsub of the warp's 32, chunk
+    // swizzled with the row; the swizzle term takes two values (q even / odd), everything else is q * constant
+    const int sw_even = KB == 64 ? (chunk ^ rsub) : (chunk ^ ((rsub >> 1) & 3));
+    const int sw_odd = KB == 64 ? (chunk ^ (rsub + 4)) : sw_even;
+    const uint32_t dst_even = (warp * 32 + rsub) * kRowBytes + (sw_even << 4);
+    const uint32_t dst_odd = (warp * 32 + rsub) * kRowBytes + (sw_odd << 4);
     auto run_stage = [&](int nid, int kp) {
       const bool second = kp < 0;  // the identity stage
-      const __half* src_base = second ? sec.in2 : in;
+      const char* src_base = reinterpret_cast<const char*>(second ? sec.in2 : in) + chunk * 16;
       const int width = second ? sec.cin2 : cin;
-      const int pitch = second ? sec.cin2 : ep.ld_in;
+      const int pitch_bytes = (second ? sec.cin2 : ep.ld_in) * 2;
       const int nkb = second ? kblocks2 : kblocks;  // 0: listed, but this launch has no second operand
+      // the rows this thread fetches in this stage (the same for every K block)
+      int rows[kCpr];
+#pragma unroll
+      for (int q = 0; q < kCpr; ++q) rows[q] = __shfl_sync(0xFFFFFFFFu, nid, q * kRowsPerInstr + rsub);
       for (int kb = 0; kb < nkb; ++kb, ++j) {
         const int s = j % kStages;
         const int n = j / kStages;
         if (n > 0) ok = mbar_wait(smem_u32(&ctl->empty[s]), (n - 1) & 1, ctl);
-        ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for the shuffles below
+        ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent
         if (!ok) return;
         const uint32_t a_addr = tiles_addr + s * stage_bytes;
         if (tid == 0) {
@@ -516,16 +526,14 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
                                       : wpacked + (static_cast<size_t>(kb) + static_cast<size_t>(kp) * kblocks) * cout * KB;
           bulk_copy_g2s(a_addr + kAStage, wsrc, b_bytes, bbar);
         }
-        const int kchunks = min(kCpr, (width - kb * KB) >> 3);
+        if (chunk < min(kCpr, (width - kb * KB) >> 3)) {
+          const char* src_kb = src_base + kb * (KB * 2);
 #pragma unroll
-        for (int q = 0; q < kCpr; ++q) {
-          const int r = q * kRowsPerInstr + rsub;  // row inside this warp's 32
-          const int src_row = __shfl_sync(0xFFFFFFFFu, nid, r);
-          if (chunk < kchunks) {
-            const int sw = KB == 64 ? (chunk ^ (r & 7)) : (chunk ^ ((r >> 1) & 3));
-            const uint32_t dst = a_addr + (warp * 32 + r) * kRowBytes + (sw << 4);
-            const __half* src = src_base + (src_row >= 0 ? static_cast<size_t>(src_row) * pitch + kb * KB + chunk * 8 : 0);
-            cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
+          for (int q = 0; q < kCpr; ++q) {
+            const int row = rows[q];
+            const uint32_t dst = a_addr + ((q & 1) ? dst_odd : dst_even) + q * (kRowsPerInstr * kRowBytes);
+            const char* src = src_kb + static_cast<long long>(row > 0 ? row : 0) * pitch_bytes;
+            cp_async16(dst, src, row >= 0 ? 16u : 0u);
           }
         }
         // the stage's "rows landed" barrier fires by itself when this thread's copies are done, so a
