@@ -481,6 +481,12 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     const int chunk = lane % kCpr;  // 16-byte chunk inside the row
     int j = 0;  // smem stages issued so far (continuous over tiles)
     bool ok = true;
+    // destination of this thread's copy q inside a stage: row q * kRowsPerInstr + rsub of the warp's 32, chunk
+    // swizzled with the row; the swizzle term takes two values (q even / odd), everything else is q * constant
+    const int sw_even = KB == 64 ? (chunk ^ rsub) : (chunk ^ ((rsub >> 1) & 3));
+    const int sw_odd = KB == 64 ? (chunk ^ (rsub + 4)) : sw_even;
+    const uint32_t dst_even = (warp * 32 + rsub) * kRowBytes + (sw_even << 4);
+    const uint32_t dst_odd = (warp * 32 + rsub) * kRowBytes + (sw_odd << 4);
     if constexpr (SLOTS == 1) {
     auto load_stage = [&](int g, int& nid, int& kp) {
       nid = -1;
@@ -496,12 +502,6 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
         }
       }
     };
-    // destination of this thread's copy q inside a stage: row q * kRowsPerInstr + rsub of the warp's 32, chunk
-    // swizzled with the row; the swizzle term takes two values (q even / odd), everything else is q * constant
-    const int sw_even = KB == 64 ? (chunk ^ rsub) : (chunk ^ ((rsub >> 1) & 3));
-    const int sw_odd = KB == 64 ? (chunk ^ (rsub + 4)) : sw_even;
-    const uint32_t dst_even = (warp * 32 + rsub) * kRowBytes + (sw_even << 4);
-    const uint32_t dst_odd = (warp * 32 + rsub) * kRowBytes + (sw_odd << 4);
     auto run_stage = [&](int nid, int kp) {
       const bool second = kp < 0;  // the identity stage
       const char* src_base = reinterpret_cast<const char*>(second ? sec.in2 : in) + chunk * 16;
@@ -606,15 +606,19 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
           if (tid == 0) mbar_arrive(smem_u32(&ctl->bfull[s]));  // the weights below ride on afull; keep bfull's phase in step
           // weight block: per slot the offset's [cout][cin] image, chunk by chunk into the swizzled
           // K-major block; unused slots are zero-filled so that the MMA can always run all K steps
-          const int per_slot = cout * kSlotChunks;
-          for (int c = tid; c < per_slot * SLOTS; c += kRows) {
-            const int q = c / per_slot, e = c - q * per_slot;
-            const int co = e / kSlotChunks, cc = e % kSlotChunks;
-            const int kq = kp[q];
-            const uint32_t dst = b_addr + co * 128 + (((q * kSlotChunks + cc) ^ (co & 7)) << 4);
+          // (chunk ch of output channel co's 128-byte row belongs to slot ch / kSlotChunks: no run-time division)
+          for (int c = tid; c < cout * 8; c += kRows) {
+            const int co = c >> 3, ch = c & 7;
+            const int q = ch / kSlotChunks, cc = ch % kSlotChunks;
+            int kq = kp[0];
+#pragma unroll
+            for (int u = 1; u < SLOTS; ++u) kq = q == u ? kp[u] : kq;
+            const uint32_t dst = b_addr + co * 128 + ((ch ^ (co & 7)) << 4);
             const __half* src = ls.wslots + (kq >= 0 ? (static_cast<size_t>(kq) * cout + co) * cin + cc * 8 : 0);
             cp_async16(dst, src, kq >= 0 ? 16u : 0u);
           }
+          const char* src_lane = reinterpret_cast<const char*>(in) + my_cc * 16;
+          const int pitch_bytes = ep.ld_in * 2;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const int r = q * 4 + rsub;
@@ -624,8 +628,8 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
               const int v = __shfl_sync(0xFFFFFFFFu, nid[u], r);
               if (u == my_slot) src_row = v;
             }
-            const uint32_t dst = a_addr + (warp * 32 + r) * 128 + ((chunk ^ (r & 7)) << 4);
-            const __half* src = in + (src_row >= 0 ? static_cast<size_t>(src_row) * ep.ld_in + my_cc * 8 : 0);
+            const uint32_t dst = a_addr + ((q & 1) ? dst_odd : dst_even) + q * (4 * 128);
+            const char* src = src_lane + static_cast<long long>(src_row > 0 ? src_row : 0) * pitch_bytes;
             cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
           }
         }
