@@ -372,6 +372,11 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
   constexpr int kMmaWarp = 4 * SUB;
   const int stage_bytes = kAStage + b_bytes;   // both multiples of 1024
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * stage_bytes);
+  // per-channel scale [cout] and shift [cout] of the epilogue (1 and 0 where absent), staged once per CTA: every
+  // epilogue thread needs all of them for every tile, and read through the global path they cost the epilogue
+  // eight 16-byte loads per 16-channel piece (96->96 on 486 k rows: 104 us without scale/shift, 146 us with)
+  float* affine = reinterpret_cast<float*>(ctl + 1);
+  static_assert(sizeof(SharedCtl) % 16 == 0, "the staged scale/shift are read as float4");
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -391,6 +396,12 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
     }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp > kMmaWarp && (ep.scale || ep.shift)) {  // (constants of the layer, not outputs of the previous kernel)
+    for (int c = tid - 32 * (kMmaWarp + 1); c < cout; c += 128) {
+      affine[c] = ep.scale ? __ldg(ep.scale + c) : 1.f;
+      affine[cout + c] = ep.shift ? __ldg(ep.shift + c) : 0.f;
+    }
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -798,24 +809,15 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 5), SUB == 1 ? 3 : 2)
           for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
           continue;
         }
-        if (ep.scale) {
+        if (ep.scale || ep.shift) {
 #pragma unroll
           for (int q = 0; q < 16; q += 4) {
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.scale + c0 + q));
-            v[q] *= s4.x;
-            v[q + 1] *= s4.y;
-            v[q + 2] *= s4.z;
-            v[q + 3] *= s4.w;
-          }
-        }
-        if (ep.shift) {
-#pragma unroll
-          for (int q = 0; q < 16; q += 4) {
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.shift + c0 + q));
-            v[q] += s4.x;
-            v[q + 1] += s4.y;
-            v[q + 2] += s4.z;
-            v[q + 3] += s4.w;
+            const float4 s4 = *reinterpret_cast<const float4*>(affine + c0 + q);
+            const float4 t4 = *reinterpret_cast<const float4*>(affine + cout + c0 + q);
+            v[q] = fmaf(v[q], s4.x, t4.x);
+            v[q + 1] = fmaf(v[q + 1], s4.y, t4.y);
+            v[q + 2] = fmaf(v[q + 2], s4.z, t4.z);
+            v[q + 3] = fmaf(v[q + 3], s4.w, t4.w);
           }
         }
         if (rrow) {
@@ -1226,24 +1228,15 @@ __global__ void __launch_bounds__(32 * (4 * SUB + 2 + 4 * EPIW), SUB == 1 ? 2 : 
           float v[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(r[q]);
-          if (ep.scale) {
+          if (ep.scale || ep.shift) {  // one fused multiply-add per value, as in k_conv_umma (bit-identical results)
 #pragma unroll
             for (int q = 0; q < 16; q += 4) {
-              const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.scale + c0 + q));
-              v[q] *= s4.x;
-              v[q + 1] *= s4.y;
-              v[q + 2] *= s4.z;
-              v[q + 3] *= s4.w;
-            }
-          }
-          if (ep.shift) {
-#pragma unroll
-            for (int q = 0; q < 16; q += 4) {
-              const float4 s4 = __ldg(reinterpret_cast<const float4*>(ep.shift + c0 + q));
-              v[q] += s4.x;
-              v[q + 1] += s4.y;
-              v[q + 2] += s4.z;
-              v[q + 3] += s4.w;
+              const float4 s4 = ep.scale ? __ldg(reinterpret_cast<const float4*>(ep.scale + c0 + q)) : make_float4(1.f, 1.f, 1.f, 1.f);
+              const float4 t4 = ep.shift ? __ldg(reinterpret_cast<const float4*>(ep.shift + c0 + q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+              v[q] = fmaf(v[q], s4.x, t4.x);
+              v[q + 1] = fmaf(v[q + 1], s4.y, t4.y);
+              v[q + 2] = fmaf(v[q + 2], s4.z, t4.z);
+              v[q + 3] = fmaf(v[q + 3], s4.w, t4.w);
             }
           }
           if (rrow) {
@@ -1308,8 +1301,8 @@ __global__ void __launch_bounds__(256)
   }
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
-    if (ep.scale) v[q] *= __ldg(ep.scale + c0 + q);
-    if (ep.shift) v[q] += __ldg(ep.shift + c0 + q);
+    if (ep.scale || ep.shift)
+      v[q] = fmaf(v[q], ep.scale ? __ldg(ep.scale + c0 + q) : 1.f, ep.shift ? __ldg(ep.shift + c0 + q) : 0.f);
   }
   if (ep.residual) {
     const uint4 r = *reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * cout + c0);
@@ -1392,8 +1385,8 @@ __global__ void __launch_bounds__(256)
   const int row = order ? __ldg(order + slot_row) : slot_row;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
-    if (ep.scale) v[q] *= __ldg(ep.scale + c0 + q);
-    if (ep.shift) v[q] += __ldg(ep.shift + c0 + q);
+    if (ep.scale || ep.shift)
+      v[q] = fmaf(v[q], ep.scale ? __ldg(ep.scale + c0 + q) : 1.f, ep.shift ? __ldg(ep.shift + c0 + q) : 0.f);
   }
   if (ep.residual) {
     const uint4 rr = *reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * cout + c0);
@@ -1682,7 +1675,7 @@ static int conv_umma_impl(const void* in, int n_in, const void* wpacked, int kv,
     sec = umma::Second{static_cast<const __half*>(ep->extra_feats), static_cast<const __half*>(ep->extra_packed_weights),
                        ep->extra_c};
   }
-  const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64;
+  const size_t fixed = sizeof(umma::SharedCtl) + 1024 + 64 + 2 * sizeof(float) * cout;  // (+ staged scale / shift)
   // 32-channel K blocks for widths that are an odd multiple of 32 (plain variant: one sub-tile, one offset per
   // stage, no halo push); operands then come from the second image of the packed weights
   const bool kb32 = umma_kb32_enabled && !kb64_slice && sub == 1 && slots == 1 && !(e.push_slot[0] || e.push_slot[1]) && cin > 32 &&
