@@ -780,6 +780,45 @@ static int wait_for_stream(cudaStream_t st) {
   return PCE_OK;
 }
 
+// Exclusive sum of a SHORT array by one block (tile counts: a few thousand entries): out[i] = in[0] + .. + in[i-1] for
+// i < n, out[n] = the total; one launch where the library scan takes two (tile-state set-up + scan) and a memset for
+// the extra element, for every tile list of every map of a pass.
+__global__ void __launch_bounds__(1024) k_scan_small(const int* __restrict__ in, int* __restrict__ out, int n) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base <= n; base += 1024) {
+    const int i = base + tid;
+    const int v = i < n ? in[i] : 0;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int u = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+      if (lane >= d) incl += u;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sum[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int u = __shfl_up_sync(0xFFFFFFFFu, w, d);
+        if (lane >= d) w += u;
+      }
+      warp_sum[lane] = w;  // inclusive over the warps
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    const int before = carry + (warp > 0 ? warp_sum[warp - 1] : 0) + incl - v;
+    if (i <= n) out[i] = before;
+    __syncthreads();
+    if (tid == 0) carry_s = carry + warp_sum[31];
+    __syncthreads();
+  }
+}
+
 static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, cudaStream_t st) {
   size_t need = 0;
   PCE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, in, out, static_cast<int>(n), st));
@@ -1115,11 +1154,16 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
   Arena ar(workspace, workspace_bytes);
   int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
   if (!ar.ok) return PCE_ERR_WORKSPACE;
-  PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
   k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
                                                      cnt, nullptr, nullptr, nullptr, 0);
   PCE_LAUNCH_CHECK();
-  PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
+  if (n_tiles <= (1 << 16)) {
+    k_scan_small<<<1, 1024, 0, st>>>(cnt, tile_ptr, n_tiles);
+    PCE_LAUNCH_CHECK();
+  } else {
+    PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
+    PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
+  }
   k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
                                                     nullptr, tile_ptr, stage_kp, stage_nbr, stage_cap);
   PCE_LAUNCH_CHECK();
