@@ -332,7 +332,9 @@ PCE_API int pce_pack_weights(const void* weights, int32_t kv, int32_t c_in, int3
  * what = 7: 0 never splits tiles between CTAs; 1 (default) as pce_conv_split_scratch_bytes says;
  *           2 only the split of small maps into parts, no shares of stages on mid-size maps.
  * what = 8: 0 runs layers whose width is an odd multiple of 32 channels with 64-channel K blocks
- *           like every other layer (1, default: with 32-channel blocks, every ring stage full). */
+ *           like every other layer (1, default: with 32-channel blocks, every ring stage full).
+ * what = 9: 0 makes the planner build the neighbour CSR of every map and the tile lists from it; 1 (default)
+ *           lets it skip the CSR where only tile lists are used (pce_planned_csr.rowptr == NULL). */
 PCE_API int pce_tune(int32_t what, int32_t value);
 
 /* Reads (and optionally clears) the library's device status word, where a kernel whose
@@ -422,10 +424,13 @@ typedef struct pce_plan_map_spec {
 
 typedef struct pce_planned_csr {
   const uint32_t* mask;
-  const int32_t* rowptr;
-  const int32_t* nbr;
+  const int32_t* rowptr; /* NULL (with nbr) where the planner took the short route: a map of at most 32 offsets */
+  const int32_t* nbr;    /* whose uses all run on tile lists; pce_csr_from_dense(table, kv, n_rows, reverse_kp,
+                          * identity_kp, ...) with nbr_cap entries builds both on demand */
   int32_t n_rows, n_src, nbr_cap;
   int32_t n_lists;
+  const int32_t* table;  /* the dense table this direction reads (the map's `map` or `map_out`) */
+  int32_t reverse_kp, identity_kp;
   pce_tile_lists lists[PCE_PLAN_MAX_USES]; /* distinct (tile_rows, slots) among the uses; the
                                             * forward lists of a submanifold map carry the
                                             * identity stage */

@@ -54,6 +54,7 @@ class PlanMapSpec(C.Structure):
 class PlannedCSR(C.Structure):
     _fields_ = [("mask", C.c_void_p), ("rowptr", C.c_void_p), ("nbr", C.c_void_p), ("n_rows", C.c_int32),
                 ("n_src", C.c_int32), ("nbr_cap", C.c_int32), ("n_lists", C.c_int32),
+                ("table", C.c_void_p), ("reverse_kp", C.c_int32), ("identity_kp", C.c_int32),
                 ("lists", TileLists * PLAN_MAX_USES)]
 
 

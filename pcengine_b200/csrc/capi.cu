@@ -18,6 +18,7 @@ extern int umma_multi_tile;
 extern int kmap_query_lanes4;
 extern int umma_split_enabled;
 extern int umma_kb32_enabled;
+extern int plan_short_route;
 int conv_split_parts(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 extern int kmap_sort_top_bits;
@@ -44,7 +45,7 @@ const char* pce_strerror(int status) {
   }
 }
 
-int pce_version(void) { return 101; }  // 101: pce_epilogue row pitches, pce_tile_lists.settled
+int pce_version(void) { return 102; }  // 102: pce_planned_csr.table / reverse_kp / identity_kp, rowptr may be NULL
 
 int pce_last_cuda_error(void) { return g_last_cuda_error; }
 
@@ -103,6 +104,10 @@ int pce_tune(int32_t what, int32_t value) {
   }
   if (what == 8) {
     umma_kb32_enabled = value ? 1 : 0;
+    return PCE_OK;
+  }
+  if (what == 9) {
+    plan_short_route = value ? 1 : 0;
     return PCE_OK;
   }
   return PCE_ERR_INVALID;

@@ -629,6 +629,19 @@ __global__ void k_mask_keys(const uint32_t* __restrict__ mask, int n_rows, int w
   vals[r] = r;
 }
 
+// pos[k] = bit position of offset k in the sort key: kv-1-rank(k), rank 0 = the rarest offset (ties by
+// index).  count_of(k) = rows that have offset k.
+template <typename CountOf>
+__device__ __forceinline__ int key_position(int k, int kv, CountOf count_of) {
+  int rank = 0;
+  const int ck = count_of(k);
+  for (int j = 0; j < kv; ++j) {
+    const int cj = count_of(j);
+    rank += (cj < ck || (cj == ck && j < k)) ? 1 : 0;
+  }
+  return kv - 1 - rank;
+}
+
 // The same key in 32 bits (kv <= 32): half the key bytes through the radix sort's passes.
 __global__ void k_mask_keys32(const uint32_t* __restrict__ mask, int n_rows, int kv, const int* __restrict__ counts,
                               uint32_t* keys, int* vals) {
@@ -654,6 +667,38 @@ __global__ void k_mask_keys32(const uint32_t* __restrict__ mask, int n_rows, int
   vals[r] = r;
 }
 
+// One pass over the dense table for maps of at most 32 offsets: the row's bitmask and its sort key (what
+// k_row_count, k_offset_counts and k_mask_keys32 produce in three passes).  The number of rows that have
+// offset k is known without counting: it is the map's knnz at the table column the offset reads (every row
+// holds at most one pair per offset), and n_rows for the identity offset.
+__global__ void k_row_mask_key32(RowArgs a, const int* __restrict__ knnz, uint32_t* mask, int* counts, uint32_t* keys,
+                                 int* vals) {
+  __shared__ int pos[32];
+  if (threadIdx.x < 32) {
+    const int k = threadIdx.x;
+    auto count_of = [&](int j) { return j == a.identity_kp ? a.n_rows : __ldg(knnz + (a.reverse ? a.kv - 1 - j : j)); };
+    pos[k] = k < a.kv ? key_position(k, a.kv, count_of) : 0;
+  }
+  __syncthreads();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r > a.n_rows) return;
+  if (r == a.n_rows) {
+    if (counts) counts[r] = 0;
+    return;
+  }
+  uint32_t m = 0, key = 0;
+  for (int b = 0; b < a.kv; ++b) {
+    if (row_entry(a, b, r) >= 0) {
+      m |= 1u << b;
+      key |= 1u << pos[b];
+    }
+  }
+  mask[r] = m;
+  if (counts) counts[r] = __popc(m);
+  keys[r] = key;
+  vals[r] = r;
+}
+
 __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const int* __restrict__ idx, int n,
                              unsigned long long* dst) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -672,11 +717,13 @@ __global__ void k_gather_u64(const unsigned long long* __restrict__ src, const i
 //   slots (1, 2 or 4): offsets per stage.  A layer with 32 (16) input channels fills only half (a
 //   quarter) of the kernel's 64-channel K block, so 2 (4) of a tile's offsets share one stage:
 //   stage_kp[g*slots + q] and stage_nbr[(g*slots + q)*rows + r]; unused slots hold kp = -2, nbr = -1.
-template <bool FILL>
+//   DENSE: the row's input at an offset is read from the dense table (`dense`, as k_row_count reads it)
+//   instead of from the neighbour CSR, which then need not exist.
+template <bool FILL, bool DENSE = false>
 __global__ void __launch_bounds__(512)
     k_tile_lists(const uint32_t* __restrict__ mask, const int* __restrict__ rowptr, const int* __restrict__ nbr,
                  const int* __restrict__ order, int n_rows, int words, int identity, int slots, int* tile_cnt,
-                 const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap) {
+                 const int* __restrict__ tile_ptr, int* stage_kp, int* stage_nbr, int stage_cap, RowArgs dense = RowArgs{}) {
   __shared__ uint32_t wmask[16][4];
   const int t = blockIdx.x, r = threadIdx.x, warp = r >> 5, lane = r & 31;
   const int rows = blockDim.x, nwarps = blockDim.x >> 5;
@@ -703,7 +750,7 @@ __global__ void __launch_bounds__(512)
     return;
   }
   const int base = __ldg(tile_ptr + t);
-  int cursor = row >= 0 ? __ldg(rowptr + row) : 0;
+  int cursor = (!DENSE && row >= 0) ? __ldg(rowptr + row) : 0;
   int s = 0;
   for (int w = 0; w < words; ++w) {
     uint32_t m = tm[w];
@@ -711,7 +758,7 @@ __global__ void __launch_bounds__(512)
       const int bit = __ffs(m) - 1;
       m &= m - 1;
       int v = -1;
-      if ((my[w] >> bit) & 1u) v = __ldg(nbr + cursor++);
+      if ((my[w] >> bit) & 1u) v = DENSE ? row_entry(dense, w * 32 + bit, row) : __ldg(nbr + cursor++);
       const int g = base + s / slots;
       if (g < stage_cap) {
         const size_t e = static_cast<size_t>(g) * slots + s % slots;
@@ -826,6 +873,79 @@ static int exclusive_scan_i32(Arena& ar, const int* in, int* out, long long n, c
   if (!ar.ok) return PCE_ERR_WORKSPACE;
   PCE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, need, in, out, static_cast<int>(n), st));
   return PCE_OK;
+}
+
+
+// Tile lists from the neighbour CSR (dense == nullptr) or straight from the dense table the CSR would be
+// built from (rowptr / nbr unused).  Same lists either way.
+static int tile_lists_impl(const uint32_t* mask, const int32_t* rowptr, const int32_t* nbr, const RowArgs* dense,
+                           const int32_t* order, int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage,
+                           int32_t slots, void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                           int32_t* stage_nbr, int32_t stage_cap, cudaStream_t st) {
+  if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
+  if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return PCE_ERR_INVALID;
+  if (slots != 1 && slots != 2 && slots != 4) return PCE_ERR_INVALID;
+  if (tile_rows == 512 && slots != 1) return PCE_ERR_INVALID;
+  const int n_tiles = div_up(n_rows, tile_rows);
+  if (n_tiles == 0) {
+    PCE_CUDA(cudaMemsetAsync(tile_ptr, 0, sizeof(int), st));
+    return PCE_OK;
+  }
+  if (!mask || !stage_kp || !stage_nbr) return PCE_ERR_INVALID;
+  if (!dense && (!rowptr || !nbr)) return PCE_ERR_INVALID;
+  const int words = (kv + 31) / 32;
+  Arena ar(workspace, workspace_bytes);
+  int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
+                                                     cnt, nullptr, nullptr, nullptr, 0);
+  PCE_LAUNCH_CHECK();
+  if (n_tiles <= (1 << 16)) {
+    k_scan_small<<<1, 1024, 0, st>>>(cnt, tile_ptr, n_tiles);
+    PCE_LAUNCH_CHECK();
+  } else {
+    PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
+    PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
+  }
+  if (dense)
+    k_tile_lists<true, true><<<n_tiles, tile_rows, 0, st>>>(mask, nullptr, nullptr, order, n_rows, words, identity_stage ? 1 : 0,
+                                                            slots, nullptr, tile_ptr, stage_kp, stage_nbr, stage_cap, *dense);
+  else
+    k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
+                                                      nullptr, tile_ptr, stage_kp, stage_nbr, stage_cap);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
+
+// The planner's route for one direction of a map with at most 32 offsets: bitmask and row order in one pass over
+// the dense table plus the radix sort (no neighbour CSR: the tile lists are filled from the table).
+int map_mask_and_order32(const int32_t* table, int kv, int n_rows, int reverse, int identity_kp, const int32_t* knnz,
+                         void* workspace, size_t workspace_bytes, uint32_t* mask, int32_t* order, cudaStream_t st) {
+  if (kv < 1 || kv > 32 || n_rows < 1 || !table || !knnz || !mask || !order) return PCE_ERR_INVALID;
+  Arena ar(workspace, workspace_bytes);
+  uint32_t* k32 = ar.take<uint32_t>(n_rows);
+  uint32_t* s32 = ar.take<uint32_t>(n_rows);
+  int* vals = ar.take<int>(n_rows);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  RowArgs a{table, kv, n_rows, reverse, identity_kp, nullptr, nullptr, n_rows};
+  k_row_mask_key32<<<div_up(n_rows + 1, 256), 256, 0, st>>>(a, knnz, mask, nullptr, k32, vals);
+  PCE_LAUNCH_CHECK();
+  size_t need = 0;
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, need, k32, s32, vals, order, n_rows, 0, kv, st));
+  char* tmp = ar.take<char>(need);
+  if (!ar.ok) return PCE_ERR_WORKSPACE;
+  PCE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, need, k32, s32, vals, order, n_rows, 0, kv, st));
+  return PCE_OK;
+}
+
+int tile_lists_from_dense(const uint32_t* mask, const int32_t* table, int reverse, int identity_kp, const int32_t* order,
+                          int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, int32_t slots,
+                          void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                          int32_t* stage_nbr, int32_t stage_cap, cudaStream_t st) {
+  if (!table) return PCE_ERR_INVALID;
+  const RowArgs a{table, kv, n_rows, reverse, identity_kp, nullptr, nullptr, n_rows};
+  return tile_lists_impl(mask, nullptr, nullptr, &a, order, n_rows, kv, tile_rows, identity_stage, slots, workspace,
+                         workspace_bytes, tile_ptr, stage_kp, stage_nbr, stage_cap, st);
 }
 
 }  // namespace pce
@@ -1139,35 +1259,8 @@ int pce_build_tile_lists(const uint32_t* mask, const int32_t* rowptr, const int3
                          int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, int32_t slots,
                          void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
                          int32_t* stage_nbr, int32_t stage_cap, void* stream) {
-  if (n_rows < 0 || kv < 1 || kv > 128 || stage_cap < 0 || !tile_ptr) return PCE_ERR_INVALID;
-  if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return PCE_ERR_INVALID;
-  if (slots != 1 && slots != 2 && slots != 4) return PCE_ERR_INVALID;
-  if (tile_rows == 512 && slots != 1) return PCE_ERR_INVALID;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int n_tiles = div_up(n_rows, tile_rows);
-  if (n_tiles == 0) {
-    PCE_CUDA(cudaMemsetAsync(tile_ptr, 0, sizeof(int), st));
-    return PCE_OK;
-  }
-  if (!mask || !rowptr || !nbr || !stage_kp || !stage_nbr) return PCE_ERR_INVALID;
-  const int words = (kv + 31) / 32;
-  Arena ar(workspace, workspace_bytes);
-  int* cnt = ar.take<int>(static_cast<size_t>(n_tiles) + 1);
-  if (!ar.ok) return PCE_ERR_WORKSPACE;
-  k_tile_lists<false><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
-                                                     cnt, nullptr, nullptr, nullptr, 0);
-  PCE_LAUNCH_CHECK();
-  if (n_tiles <= (1 << 16)) {
-    k_scan_small<<<1, 1024, 0, st>>>(cnt, tile_ptr, n_tiles);
-    PCE_LAUNCH_CHECK();
-  } else {
-    PCE_CUDA(cudaMemsetAsync(cnt + n_tiles, 0, sizeof(int), st));
-    PCE_TRY(exclusive_scan_i32(ar, cnt, tile_ptr, n_tiles + 1, st));
-  }
-  k_tile_lists<true><<<n_tiles, tile_rows, 0, st>>>(mask, rowptr, nbr, order, n_rows, words, identity_stage ? 1 : 0, slots,
-                                                    nullptr, tile_ptr, stage_kp, stage_nbr, stage_cap);
-  PCE_LAUNCH_CHECK();
-  return PCE_OK;
+  return tile_lists_impl(mask, rowptr, nbr, nullptr, order, n_rows, kv, tile_rows, identity_stage, slots, workspace,
+                         workspace_bytes, tile_ptr, stage_kp, stage_nbr, stage_cap, static_cast<cudaStream_t>(stream));
 }
 
 size_t pce_csr_from_pairs_workspace_bytes(int32_t n_pairs, int32_t n_rows) {

@@ -41,6 +41,12 @@ bool conv_umma_supported(int cin, int cout, int dtype);
 size_t conv_split_scratch_bytes(int n_rows, int n_src, int cin, int cout, int kv, int sm_count);
 int conv_umma(const void* in, int n_in, const void* wpacked, int kv, const pce_tile_lists* tiles, int n_out, int cin,
               int cout, void* out, const pce_epilogue* ep, cudaStream_t st);
+int map_mask_and_order32(const int32_t* table, int kv, int n_rows, int reverse, int identity_kp, const int32_t* knnz,
+                         void* workspace, size_t workspace_bytes, uint32_t* mask, int32_t* order, cudaStream_t st);
+int tile_lists_from_dense(const uint32_t* mask, const int32_t* table, int reverse, int identity_kp, const int32_t* order,
+                          int32_t n_rows, int32_t kv, int32_t tile_rows, int32_t identity_stage, int32_t slots,
+                          void* workspace, size_t workspace_bytes, int32_t* tile_ptr, int32_t* stage_kp,
+                          int32_t* stage_nbr, int32_t stage_cap, cudaStream_t st);
 
 struct DeviceArena {
   struct Chunk {
@@ -155,6 +161,10 @@ struct pce_plan {
 
 namespace pce {
 
+// 1: maps of at most 32 offsets whose uses all run on tile lists are planned without their neighbour CSR (build_csr);
+// 0: every map gets its CSR first and the lists from it (same lists).
+int plan_short_route = 1;
+
 static int scratch_for(PlanLane* l, size_t bytes, void** out) {
   if (bytes > l->scratch_cap) {
     PCE_CUDA(cudaStreamSynchronize(l->stream));  // nothing queued may still use the old buffer
@@ -194,27 +204,16 @@ static void fill_geom(const pce_plan_map_spec& sp, const int32_t* cmin, const in
   g->submanifold = sp.submanifold ? 1 : 0;
 }
 
-// One direction of a map: neighbour CSR, row order and the requested tile lists.
+// One direction of a map: bitmask, row order and the requested tile lists.  Maps of at most 32 offsets whose
+// uses all run on tile lists take the short route: one pass over the dense table gives bitmask and sort key (the
+// rarity of an offset is its knnz), the lists are filled from the table, and the neighbour CSR (rowptr / nbr) is
+// left to whoever asks for it (pce_csr_from_dense on the fields kept in the record).  Every other map gets the
+// CSR first and the lists from it.  The lists are the same either way.
 static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* table, int kv, int n_rows, int n_src, int reverse,
                      int ident, size_t nbr_cap, const int32_t* c_outs, const int32_t* c_ins, int identity_stage,
-                     pce_planned_csr* out) {
+                     const int32_t* knnz, pce_planned_csr* out) {
   cudaStream_t st = l->stream;
   const int words = (kv + 31) / 32;
-  uint32_t* mask = ps->take_n<uint32_t>(static_cast<size_t>(n_rows > 0 ? n_rows : 1) * words);
-  int32_t* rowptr = ps->take_n<int32_t>(static_cast<size_t>(n_rows) + 1);
-  int32_t* nbr = ps->take_n<int32_t>(nbr_cap);
-  if (!mask || !rowptr || !nbr) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
-  void* ws = nullptr;
-  PCE_TRY(scratch_for(l, 8 * (static_cast<size_t>(n_rows) + 1) + (8u << 20), &ws));
-  PCE_TRY(pce_csr_from_dense(table, kv, n_rows, reverse, ident, ws, l->scratch_cap, mask, rowptr, nbr,
-                             static_cast<int32_t>(nbr_cap), st));
-  out->mask = mask;
-  out->rowptr = rowptr;
-  out->nbr = nbr;
-  out->n_rows = n_rows;
-  out->n_src = n_src;
-  out->nbr_cap = static_cast<int32_t>(nbr_cap);
-  out->n_lists = 0;
   // the distinct (tile height, offsets per stage) among the uses
   int want_rows[PCE_PLAN_MAX_USES], want_slots[PCE_PLAN_MAX_USES], n_want = 0;
   for (int u = 0; u < PCE_PLAN_MAX_USES && c_outs[u] > 0; ++u) {
@@ -228,11 +227,41 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
       ++n_want;
     }
   }
-  if (n_want == 0 || kv > 128 || n_rows == 0) return PCE_OK;
+  const bool lists_wanted = n_want > 0 && kv <= 128 && n_rows > 0;
+  const bool short_route = lists_wanted && kv <= 32 && plan_short_route;
+  uint32_t* mask = ps->take_n<uint32_t>(static_cast<size_t>(n_rows > 0 ? n_rows : 1) * words);
+  if (!mask) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
+  out->mask = mask;
+  out->rowptr = nullptr;
+  out->nbr = nullptr;
+  out->n_rows = n_rows;
+  out->n_src = n_src;
+  out->nbr_cap = static_cast<int32_t>(nbr_cap);
+  out->n_lists = 0;
+  out->table = table;
+  out->reverse_kp = reverse;
+  out->identity_kp = ident;
+  void* ws = nullptr;
+  int32_t* rowptr = nullptr;
+  int32_t* nbr = nullptr;
+  if (!short_route) {
+    rowptr = ps->take_n<int32_t>(static_cast<size_t>(n_rows) + 1);
+    nbr = ps->take_n<int32_t>(nbr_cap);
+    if (!rowptr || !nbr) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
+    PCE_TRY(scratch_for(l, 8 * (static_cast<size_t>(n_rows) + 1) + (8u << 20), &ws));
+    PCE_TRY(pce_csr_from_dense(table, kv, n_rows, reverse, ident, ws, l->scratch_cap, mask, rowptr, nbr,
+                               static_cast<int32_t>(nbr_cap), st));
+    out->rowptr = rowptr;
+    out->nbr = nbr;
+  }
+  if (!lists_wanted) return PCE_OK;
   int32_t* order = ps->take_n<int32_t>(n_rows);
   if (!order) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
   PCE_TRY(scratch_for(l, 64 * static_cast<size_t>(n_rows) + (16u << 20), &ws));
-  PCE_TRY(pce_csr_sort_rows(mask, n_rows, kv, ws, l->scratch_cap, order, st));
+  if (short_route)
+    PCE_TRY(map_mask_and_order32(table, kv, n_rows, reverse, ident, knnz, ws, l->scratch_cap, mask, order, st));
+  else
+    PCE_TRY(pce_csr_sort_rows(mask, n_rows, kv, ws, l->scratch_cap, order, st));
   for (int h = 0; h < n_want; ++h) {
     const int rows = want_rows[h], slots = want_slots[h];
     const int n_tiles = div_up(n_rows, rows);
@@ -242,8 +271,12 @@ static int build_csr(pce_plan* p, PlanLane* l, pce_pass* ps, const int32_t* tabl
     int32_t* stage_nbr = ps->take_n<int32_t>(cap * slots * rows);
     if (!tile_ptr || !stage_kp || !stage_nbr) return ps->arena.error ? ps->arena.error : PCE_ERR_CUDA;
     PCE_TRY(scratch_for(l, 8 * (static_cast<size_t>(n_tiles) + 1) + (1u << 20), &ws));
-    PCE_TRY(pce_build_tile_lists(mask, rowptr, nbr, order, n_rows, kv, rows, identity_stage, slots, ws, l->scratch_cap,
-                                 tile_ptr, stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
+    if (short_route)
+      PCE_TRY(tile_lists_from_dense(mask, table, reverse, ident, order, n_rows, kv, rows, identity_stage, slots, ws,
+                                    l->scratch_cap, tile_ptr, stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
+    else
+      PCE_TRY(pce_build_tile_lists(mask, rowptr, nbr, order, n_rows, kv, rows, identity_stage, slots, ws, l->scratch_cap,
+                                   tile_ptr, stage_kp, stage_nbr, static_cast<int32_t>(cap), st));
     out->lists[out->n_lists++] = pce_tile_lists{order, tile_ptr, stage_kp, stage_nbr, rows, identity_stage, slots, 1};
   }
   return PCE_OK;
@@ -347,12 +380,12 @@ static int build_map(pce_plan* p, PlanLane* l, pce_pass* ps, int i) {
     // output-major table: the map itself read with kp reversed when symmetric, else map_out
     // residual blocks live on submanifold maps: their lists carry the identity stage
     PCE_TRY(build_csr(p, l, ps, symmetric ? map : map_out, kv, n_out, n_in, symmetric ? 1 : 0, ident, cap_nbr,
-                      sp.c_out_fwd, sp.c_in_fwd, sp.submanifold ? 1 : 0, &out.fwd));
+                      sp.c_out_fwd, sp.c_in_fwd, sp.submanifold ? 1 : 0, knnz, &out.fwd));
     out.has_fwd = 1;
   }
   if (sp.want_tr) {
     // roles swapped: the input-major table is the output-major one of the transposed layer
-    PCE_TRY(build_csr(p, l, ps, map, kv, n_in, n_out, 0, ident, cap_nbr, sp.c_out_tr, sp.c_in_tr, 0, &out.tr));
+    PCE_TRY(build_csr(p, l, ps, map, kv, n_in, n_out, 0, ident, cap_nbr, sp.c_out_tr, sp.c_in_tr, 0, knnz, &out.tr));
     out.has_tr = 1;
   }
   PCE_CUDA(cudaEventRecord(ps->ready[i], st));

@@ -311,19 +311,33 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
         tiles = C.byref(csr.tiles(SORT_ROWS, rows, second, stage_slots(c_in)))
         if rows == 128 and not pushes:
             split = _split_scratch(csr.n_rows, feats.size(0), c_in, c_out, kv, feats.device)
+    # the tensor-core kernel reads the tile lists only: a planned map's rowptr / nbr are not built for its sake
+    rowptr, nbr = (csr._rowptr, csr._nbr) if tiles is not None else (csr.rowptr, csr.nbr)
     _lib.check(lib.pce_conv_fwd(feats.data_ptr(), feats.size(0), c_in, kernel.data_ptr(), _lib.ptr(packed), kv, c_out,
-                                csr.mask.data_ptr(), csr.rowptr.data_ptr(), csr.nbr.data_ptr(), tiles, csr.n_rows,
+                                csr.mask.data_ptr(), _lib.ptr(rowptr), _lib.ptr(nbr), tiles, csr.n_rows,
                                 out.data_ptr(), _lib.dtype_code(feats.dtype),
                                 _pack(epilogue, c_out, csr.n_rows, feats.dtype, in_ld, out_ld, split),
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
         rec["end"].record()
-        rec["pairs"] = csr.rowptr[-1:].clone()  # a copy: the record must not keep the map's storage alive
+        rec["pairs"] = _mask_popcount(csr.mask)  # (a new tensor: the record must not keep the map's storage alive)
         PROFILE.append(rec)
     if given is not None:
         given.copy_(out[:, :c_out_true])
         return given
     return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
+
+
+_POPCOUNT8 = None
+
+
+def _mask_popcount(mask) -> torch.Tensor:
+    """Number of (row, offset) pairs of a CSR = set bits of its bitmask, as a one-element device tensor."""
+    global _POPCOUNT8
+    m = mask.tensor() if hasattr(mask, "tensor") else mask
+    if _POPCOUNT8 is None or _POPCOUNT8.device != m.device:
+        _POPCOUNT8 = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int32, device=m.device)
+    return _POPCOUNT8[m.contiguous().view(torch.uint8).long()].sum().reshape(1)
 
 
 def conv_forward_d1(feats: torch.Tensor, kernel: torch.Tensor, kmap, transposed: bool = False,

@@ -40,15 +40,34 @@ TILE_ROWS = 128
 
 
 class NeighbourCSR:
-    """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap]."""
+    """mask [rows, ceil(kv/32)] uint32 (as int32 storage), rowptr [rows+1], nbr [cap].
 
-    __slots__ = ("mask", "rowptr", "nbr", "n_rows", "n_src", "kv", "_order", "_tiles")
+    ``fill``: a callable returning (rowptr, nbr) for a CSR that arrives without them (a planned map
+    whose tile lists were filled straight from the dense table); they are then built on first use."""
 
-    def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None):
-        self.mask, self.rowptr, self.nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
+    __slots__ = ("mask", "_rowptr", "_nbr", "n_rows", "n_src", "kv", "_order", "_tiles", "_fill")
+
+    def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None, fill=None):
+        self.mask, self._rowptr, self._nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
         self.kv = kv
         self._order = None
         self._tiles = {}
+        self._fill = fill
+
+    def _materialise(self):
+        if self._rowptr is None and self._fill is not None:
+            self._rowptr, self._nbr = self._fill()
+            self._fill = None
+
+    @property
+    def rowptr(self):
+        self._materialise()
+        return self._rowptr
+
+    @property
+    def nbr(self):
+        self._materialise()
+        return self._nbr
 
     def restrict(self, n_rows: int) -> "NeighbourCSR":
         """The CSR of the first ``n_rows`` output rows only (same inputs, shared storage): what a

@@ -87,6 +87,23 @@ class _PassHandle:
             lib.pce_pass_release(h, self.stream)
 
 
+def _csr_filler(table: int, kv: int, n_rows: int, reverse_kp: int, identity_kp: int, cap: int, device, keep):
+    """rowptr / nbr of one direction of a planned map, from its dense table (pce_csr_from_dense)."""
+    def fill():
+        words = (kv + 31) // 32
+        mask = torch.empty((max(n_rows, 1), words), dtype=torch.int32, device=device)
+        rowptr = torch.empty((n_rows + 1,), dtype=torch.int32, device=device)
+        nbr = torch.empty((max(cap, 1),), dtype=torch.int32, device=device)
+        ws = _lib.workspace(8 * (n_rows + 1) + (8 << 20), device)
+        _lib.check(lib.pce_csr_from_dense(table, kv, n_rows, reverse_kp, identity_kp, ws.data_ptr(), ws.numel(),
+                                          mask.data_ptr(), rowptr.data_ptr(), nbr.data_ptr(), max(cap, 1),
+                                          _lib.stream_ptr(device)), "pce_csr_from_dense")
+        return rowptr, nbr
+
+    fill.keep = keep  # the table lives in the pass's arena: the pass stays alive as long as this does
+    return fill
+
+
 class PlannedKernelMap(KernelMap):
     """A :class:`KernelMap` whose arrays were produced by the planner."""
 
@@ -117,9 +134,15 @@ class PlannedKernelMap(KernelMap):
             if not has:
                 continue
             words = (kv + 31) // 32
-            csr = NeighbourCSR(_DevArray(c.mask, (max(c.n_rows, 1), words), device, keep),
-                               _DevArray(c.rowptr, (c.n_rows + 1,), device, keep),
-                               _DevArray(c.nbr, (c.nbr_cap,), device, keep), int(c.n_rows), int(c.n_src), kv)
+            mask = _DevArray(c.mask, (max(c.n_rows, 1), words), device, keep)
+            if c.rowptr:
+                csr = NeighbourCSR(mask, _DevArray(c.rowptr, (c.n_rows + 1,), device, keep),
+                                   _DevArray(c.nbr, (c.nbr_cap,), device, keep), int(c.n_rows), int(c.n_src), kv)
+            else:
+                # planned without its neighbour CSR (only tile lists were needed): built on first use
+                csr = NeighbourCSR(mask, None, None, int(c.n_rows), int(c.n_src), kv,
+                                   fill=_csr_filler(int(c.table), kv, int(c.n_rows), int(c.reverse_kp), int(c.identity_kp),
+                                                    int(c.nbr_cap), device, keep))
             for i in range(c.n_lists):
                 t = c.lists[i]
                 slots = max(int(t.slots), 1)

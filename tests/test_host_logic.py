@@ -153,3 +153,22 @@ def test_dataflow_selector_follows_the_measured_table():
         raise AssertionError("sparsity was read although width / size rule the explicit dataflow out")
     assert _choose_dataflow("auto", 64, 64, never, 25000, torch.float16) == "D2"
     assert _choose_dataflow("auto", 256, 256, never, 10 ** 6, torch.float16) == "D2"
+
+
+def test_neighbour_csr_builds_missing_arrays_once():
+    """A CSR that arrives without rowptr / nbr (a planned map whose tile lists came straight from the dense
+    table) asks its `fill` for them on first use, once, and keeps the result; a complete one never does."""
+    from pcengine_b200.kmap import NeighbourCSR
+    calls = []
+    rowptr, nbr = torch.tensor([0, 2, 3], dtype=torch.int32), torch.tensor([1, 0, 1], dtype=torch.int32)
+
+    def fill():
+        calls.append(1)
+        return rowptr, nbr
+    mask = torch.tensor([[3], [2]], dtype=torch.int32)
+    lazy = NeighbourCSR(mask, None, None, 2, 2, kv=2, fill=fill)
+    assert lazy._rowptr is None and not calls
+    assert lazy.nbr is nbr and lazy.rowptr is rowptr and lazy.rowptr is rowptr and len(calls) == 1
+    assert lazy.restrict(1).rowptr.tolist() == [0, 2]
+    whole = NeighbourCSR(mask, rowptr, nbr, 2, 2, kv=2, fill=fill)
+    assert whole.rowptr is rowptr and len(calls) == 1

@@ -87,8 +87,10 @@ def test_planned_maps_equal_lazy_maps(dtype):
         for tr, ca in a._csr.items():
             cb = b._csr[tr]
             p = int(ca.rowptr[-1])
-            assert torch.equal(ca.mask, cb.mask.tensor()) and torch.equal(ca.rowptr, cb.rowptr.tensor())
-            assert torch.equal(ca.nbr[:p], cb.nbr.tensor()[:p])
+            # (a planned map that only needed tile lists builds rowptr / nbr on this first access)
+            as_tensor = lambda v: v if isinstance(v, torch.Tensor) else v.tensor()
+            assert torch.equal(ca.mask, cb.mask.tensor()) and torch.equal(ca.rowptr, as_tensor(cb.rowptr))
+            assert torch.equal(ca.nbr[:p], as_tensor(cb.nbr)[:p])
             assert bool(cb._tiles) == (dtype == torch.float16)  # tile lists feed the tensor-core kernel only
             for tk, tb in cb._tiles.items():
                 ca.tiles(*tk)
@@ -320,3 +322,57 @@ def test_one_call_pass_equals_the_layer_by_layer_pass():
         assert torch.equal(got2.feats, want2.feats) and not torch.equal(got2.feats, want.feats)
     from pcengine_b200 import functional as PF
     assert PF.device_status() == 0
+
+
+def test_planner_routes_build_the_same_lists():
+    """A planned map of at most 32 offsets whose layers all run on tile lists arrives without rowptr / nbr
+    (the lists were filled straight from the dense table, the row order came from knnz): its bitmask, row order
+    and tile lists are those of the route through the neighbour CSR (pce_tune(9, 0)), the logits are the same
+    bit for bit, and rowptr / nbr appear, equal to the other route's, when they are first asked for."""
+    import pcengine_b200 as pce
+    from pcengine_b200 import _lib
+    coords = surface_cloud(46, 72, batch=2)
+    torch.manual_seed(12)
+    feats = torch.randn(len(coords), 4).half()
+    model = pce.MinkUNet(4, 19, cr=0.5)
+    pce.randomize_batchnorm(model, 6)
+    model = model.half().eval().cuda()
+
+    def run(short):
+        assert _lib.lib.pce_tune(9, short) == 0
+        x = pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cmax_of(coords), batchsize=2,
+                         init_tag=pce.MinkUNet.tags())
+        with torch.no_grad():
+            y = model(x)
+        torch.cuda.synchronize()
+        return y
+    try:
+        run(1)
+        through_csr, short = run(0), run(1)
+    finally:
+        _lib.lib.pce_tune(9, 1)
+    assert torch.equal(through_csr.feats, short.feats)
+    assert len(short.kmaps) == 9
+    skipped = 0
+    for key, a in through_csr.kmaps.items():
+        b = short.kmaps[key]
+        assert type(b).__name__ == "PlannedKernelMap"
+        for tr, ca in a._csr.items():
+            cb = b._csr[tr]
+            assert ca._rowptr is not None and ca._fill is None
+            skipped += cb._rowptr is None
+            assert torch.equal(ca.mask.tensor(), cb.mask.tensor())
+            assert sorted(ca._tiles) == sorted(cb._tiles) and cb._tiles
+            for tk, ta in ca._tiles.items():
+                tb = cb._tiles[tk]
+                stages = int(ta[2].tensor()[-1])
+                assert torch.equal(ta[1].tensor(), tb[1].tensor()) and torch.equal(ta[2].tensor(), tb[2].tensor())
+                assert torch.equal(ta[3].tensor()[:stages], tb[3].tensor()[:stages])
+                assert torch.equal(ta[4].tensor()[:stages * tk[1]], tb[4].tensor()[:stages * tk[1]])
+            p = int(ca.rowptr.tensor()[-1])
+            assert torch.equal(ca.rowptr.tensor(), cb.rowptr if isinstance(cb.rowptr, torch.Tensor) else cb.rowptr.tensor())
+            got_nbr = cb.nbr if isinstance(cb.nbr, torch.Tensor) else cb.nbr.tensor()
+            assert torch.equal(ca.nbr.tensor()[:p], got_nbr[:p])
+            assert cb._rowptr is not None and cb._fill is None
+    total = sum(len(a._csr) for a in through_csr.kmaps.values())
+    assert skipped == total == 13  # five submanifold maps (one direction each) and four strided ones (two each)
