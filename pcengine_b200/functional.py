@@ -320,24 +320,12 @@ def conv_forward(feats: torch.Tensor, kernel: torch.Tensor, csr: NeighbourCSR, e
                                 _KERNEL[kernel_choice], _lib.stream_ptr(feats.device)), "pce_conv_fwd")
     if rec is not None:
         rec["end"].record()
-        rec["pairs"] = _mask_popcount(csr.mask)  # (a new tensor: the record must not keep the map's storage alive)
+        rec["pairs"] = csr.pair_count()  # (a new tensor: the record must not keep the map's storage alive)
         PROFILE.append(rec)
     if given is not None:
         given.copy_(out[:, :c_out_true])
         return given
     return out[:, :c_out_true].contiguous() if padded and c_out != c_out_true else out
-
-
-_POPCOUNT8 = None
-
-
-def _mask_popcount(mask) -> torch.Tensor:
-    """Number of (row, offset) pairs of a CSR = set bits of its bitmask, as a one-element device tensor."""
-    global _POPCOUNT8
-    m = mask.tensor() if hasattr(mask, "tensor") else mask
-    if _POPCOUNT8 is None or _POPCOUNT8.device != m.device:
-        _POPCOUNT8 = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int32, device=m.device)
-    return _POPCOUNT8[m.contiguous().view(torch.uint8).long()].sum().reshape(1)
 
 
 def conv_forward_d1(feats: torch.Tensor, kernel: torch.Tensor, kmap, transposed: bool = False,

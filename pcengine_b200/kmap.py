@@ -45,14 +45,22 @@ class NeighbourCSR:
     ``fill``: a callable returning (rowptr, nbr) for a CSR that arrives without them (a planned map
     whose tile lists were filled straight from the dense table); they are then built on first use."""
 
-    __slots__ = ("mask", "_rowptr", "_nbr", "n_rows", "n_src", "kv", "_order", "_tiles", "_fill")
+    __slots__ = ("mask", "_rowptr", "_nbr", "n_rows", "n_src", "kv", "_order", "_tiles", "_fill", "_pairs")
 
-    def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None, fill=None):
+    def __init__(self, mask, rowptr, nbr, n_rows, n_src, kv=None, fill=None, pairs=None):
         self.mask, self._rowptr, self._nbr, self.n_rows, self.n_src = mask, rowptr, nbr, n_rows, n_src
         self.kv = kv
         self._order = None
         self._tiles = {}
         self._fill = fill
+        self._pairs = pairs  # callable -> one-element device tensor, for a CSR without rowptr
+
+    def pair_count(self) -> torch.Tensor:
+        """Number of (row, offset) pairs as a NEW one-element device tensor (no read-back, and nothing that
+        keeps the map's storage alive)."""
+        if self._rowptr is None and self._pairs is not None:
+            return self._pairs()
+        return self.rowptr[-1:].clone()
 
     def _materialise(self):
         if self._rowptr is None and self._fill is not None:

@@ -104,6 +104,14 @@ def _csr_filler(table: int, kv: int, n_rows: int, reverse_kp: int, identity_kp: 
     return fill
 
 
+def _pair_counter(knnz, identity_rows: int):
+    """Pairs of one direction of a map = the sum of its knnz, plus one per row where the rows name themselves
+    at the identity offset (whose knnz is 0)."""
+    def count():
+        return (knnz.tensor().sum(dtype=torch.int64) + identity_rows).to(torch.int32).reshape(1)
+    return count
+
+
 class PlannedKernelMap(KernelMap):
     """A :class:`KernelMap` whose arrays were produced by the planner."""
 
@@ -142,7 +150,8 @@ class PlannedKernelMap(KernelMap):
                 # planned without its neighbour CSR (only tile lists were needed): built on first use
                 csr = NeighbourCSR(mask, None, None, int(c.n_rows), int(c.n_src), kv,
                                    fill=_csr_filler(int(c.table), kv, int(c.n_rows), int(c.reverse_kp), int(c.identity_kp),
-                                                    int(c.nbr_cap), device, keep))
+                                                    int(c.nbr_cap), device, keep),
+                                   pairs=_pair_counter(self.knnz, int(c.n_rows) if c.identity_kp >= 0 else 0))
             for i in range(c.n_lists):
                 t = c.lists[i]
                 slots = max(int(t.slots), 1)

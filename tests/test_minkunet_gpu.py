@@ -370,6 +370,7 @@ def test_planner_routes_build_the_same_lists():
                 assert torch.equal(ta[3].tensor()[:stages], tb[3].tensor()[:stages])
                 assert torch.equal(ta[4].tensor()[:stages * tk[1]], tb[4].tensor()[:stages * tk[1]])
             p = int(ca.rowptr.tensor()[-1])
+            assert cb._rowptr is None and int(cb.pair_count()) == p == int(ca.pair_count())  # (from knnz, nothing built)
             assert torch.equal(ca.rowptr.tensor(), cb.rowptr if isinstance(cb.rowptr, torch.Tensor) else cb.rowptr.tensor())
             got_nbr = cb.nbr if isinstance(cb.nbr, torch.Tensor) else cb.nbr.tensor()
             assert torch.equal(ca.nbr.tensor()[:p], got_nbr[:p])
