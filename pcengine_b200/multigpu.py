@@ -9,7 +9,11 @@ multi-GPU support at all, so nothing here mirrors reference code):
   neighbour-only point-to-point messages (``torch.distributed`` isend/irecv: NCCL over NVLink between
   GPUs, gloo in the CPU tests) or, between GPUs, by the convolution kernel itself storing its boundary
   rows into the neighbours' halo rows (``PeerPush``).  Halo rows land in the rank's own memory before
-  any kernel reads them.
+  any kernel reads them.  A network with down- and up-sampling layers runs on a ``SlabLevels``: one
+  slab decomposition per coordinate level, with cut planes that are multiples of the coarsest level's
+  stride, so that a down-sampling layer with kernel size == stride (and its transposed layer) reads
+  and writes owned rows only and exchanges nothing; the submanifold layers of every level exchange
+  that level's halo.
 """
 from __future__ import annotations
 
@@ -56,6 +60,56 @@ def slab_cuts(x: np.ndarray, world: int, radius: int) -> List[int]:
         if cuts[g + 1] - cuts[g] < max(radius, 1):
             raise ValueError("scene too thin along x for this many slabs and this kernel radius")
     return cuts
+
+
+def aligned_slab_cuts(x: np.ndarray, world: int, radius: int, align: int) -> List[int]:
+    """``slab_cuts`` with every plane a multiple of ``align`` (the product of the strides down to the
+    coarsest level that is cut): a coarse voxel's children then all belong to one rank on every level.
+    Every slab is at least ``radius * align`` wide, so the coarsest level's halo (``radius`` coarse
+    voxels) still lies inside the neighbouring slab.  Coordinates must be non-negative."""
+    x = np.asarray(x, dtype=np.int64)
+    if align < 1:
+        raise ValueError("align must be positive")
+    if x.size and int(x.min()) < 0:
+        raise ValueError("aligned slabs need non-negative coordinates")
+    coarse = x // align
+    cuts = slab_cuts(coarse, world, radius)
+    return [c * align for c in cuts]
+
+
+def coarse_bounds(cmax: Sequence[int], stride: int) -> List[int]:
+    """coords_max of the level below a down-sampling layer with kernel size == stride and no padding:
+    the last output whose ``stride`` inputs all lie within ``cmax`` (the map builder's bound rule)."""
+    return [(int(m) - (stride - 1)) // stride for m in cmax]
+
+
+def coarsen(coords: torch.Tensor, stride: int, cmax: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Output coordinates of a down-sampling layer with kernel size == stride and no padding: the
+    distinct floor(coords / stride), int32 [M,4] sorted by (b, x, y, z), the order in which the map
+    builder returns them.  ``cmax`` (the input level's coords_max) drops the outputs beyond
+    :func:`coarse_bounds`, as the map builder does."""
+    if coords.numel() == 0:
+        return coords.clone()
+    c = coords.to(torch.int64).clone()
+    if int(c[:, 1:].min()) < 0:
+        raise ValueError("coarsen needs non-negative coordinates")
+    c[:, 1:] = torch.div(c[:, 1:], stride, rounding_mode="floor")
+    if cmax is not None:
+        bound = torch.tensor(coarse_bounds(cmax, stride), dtype=torch.int64, device=c.device)
+        c = c[(c[:, 1:] <= bound).all(dim=1)]
+        if c.numel() == 0:
+            return c.to(coords.dtype)
+    ext = (c.max(dim=0).values + 1).tolist()
+    key = ((c[:, 0] * ext[1] + c[:, 1]) * ext[2] + c[:, 2]) * ext[3] + c[:, 3]
+    key = torch.unique(key)  # sorted
+    out = torch.empty((key.numel(), 4), dtype=torch.int64, device=coords.device)
+    out[:, 3] = key % ext[3]
+    key = torch.div(key, ext[3], rounding_mode="floor")
+    out[:, 2] = key % ext[2]
+    key = torch.div(key, ext[2], rounding_mode="floor")
+    out[:, 1] = key % ext[1]
+    out[:, 0] = torch.div(key, ext[1], rounding_mode="floor")
+    return out.to(coords.dtype).contiguous()
 
 
 class SlabScene:
@@ -221,8 +275,47 @@ class PeerPush:
         self.handles[k].barrier(channel=0)
 
 
-def split_scene(coords: np.ndarray, world: int, radius: int):
-    """Host-side split of a whole scene (int32 [N,4]) into per-rank owned row indices + the cuts."""
-    cuts = slab_cuts(coords[:, 1], world, radius)
+class SlabLevels:
+    """A slab decomposition of every coordinate level of a network with down-/up-sampling layers.
+
+    ``coords`` are the rows this rank owns at the finest level, ``cuts`` come from
+    :func:`aligned_slab_cuts` with ``align`` = the product of ``strides``, ``cmax`` is the whole scene's
+    coords_max (``cmax[l]`` afterwards: the same per level).  ``scenes[l]`` is the
+    :class:`SlabScene` of level l (level l+1 = level l down-sampled by ``strides[l]`` with kernel size ==
+    stride and no padding): its owned rows are exactly the level's voxels inside this rank's slab, in the
+    order a map builder returns them, and its halo (exchanged once, here) serves the level's submanifold
+    layers.  Because every cut is a multiple of the level's stride, all children of a coarse voxel belong
+    to the rank that owns it: the down-sampling layer and its transposed layer run on
+    (``scenes[l].coords`` -> ``scenes[l+1].coords``) with no exchange at all, and what they return for the
+    owned rows is what an undivided run returns for those voxels."""
+
+    def __init__(self, coords: torch.Tensor, cuts: Sequence[int], rank: int, world: int, radius: int,
+                 strides: Sequence[int], cmax: Sequence[int]):
+        self.strides = [int(s) for s in strides]
+        self.scenes: List[SlabScene] = []
+        self.cmax: List[List[int]] = []  # the WHOLE scene's coords_max per level (what every map is built with)
+        level_cuts, level_cmax = [int(c) for c in cuts], [int(m) for m in cmax]
+        for l in range(len(self.strides) + 1):
+            self.scenes.append(SlabScene(coords, level_cuts, rank, world, radius).setup())
+            self.cmax.append(level_cmax)
+            if l < len(self.strides):
+                s = self.strides[l]
+                if s < 1 or any(c % s for c in level_cuts):
+                    raise ValueError("slab cuts must be multiples of the cumulative stride (aligned_slab_cuts)")
+                coords = coarsen(coords, s, level_cmax)
+                level_cuts = [c // s for c in level_cuts]
+                level_cmax = coarse_bounds(level_cmax, s)
+
+    def __len__(self) -> int:
+        return len(self.scenes)
+
+    def __getitem__(self, level: int) -> SlabScene:
+        return self.scenes[level]
+
+
+def split_scene(coords: np.ndarray, world: int, radius: int, align: int = 1):
+    """Host-side split of a whole scene (int32 [N,4]) into per-rank owned row indices + the cuts
+    (multiples of ``align``: see :func:`aligned_slab_cuts`)."""
+    cuts = aligned_slab_cuts(coords[:, 1], world, radius, align) if align > 1 else slab_cuts(coords[:, 1], world, radius)
     owned = [np.nonzero((coords[:, 1] >= cuts[g]) & (coords[:, 1] < cuts[g + 1]))[0] for g in range(world)]
     return cuts, owned

@@ -66,6 +66,97 @@ def _worker(rank, world, port, ks, out_q):
         dist.destroy_process_group()
 
 
+def _levels_worker(rank, world, port, out_q):
+    """A small U-shaped network (3x3x3 -> 2x2x2 stride 2 -> 3x3x3 -> transposed 2x2x2 -> 3x3x3) on slabs whose
+    cuts are multiples of the stride: only the submanifold layers exchange rows."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pcengine_b200 import multigpu as mg
+        coords = surface_cloud(78, 63, batch=1)   # odd extent: the bound rule drops the last coarse plane
+        cm = cmax_of(coords)
+        torch.manual_seed(6)
+        feats = torch.randn(len(coords), 8)
+        w0, wd, w1, wu, w2 = (torch.randn(27, 8, 8) / 10, torch.randn(8, 8, 12) / 4, torch.randn(27, 12, 12) / 10,
+                              torch.randn(8, 12, 8) / 4, torch.randn(27, 8, 6) / 10)
+        sub, down = ((3, 3, 3), (1, 1, 1)), ((2, 2, 2), (2, 2, 2))
+        z = (0, 0, 0)
+        # the undivided scene
+        d0 = ko.build_d2(coords, *sub, z, [0, 0, 0], cm, True)
+        dd = ko.build_d2(coords, *down, z, [0, 0, 0], cm, False)
+        d1 = ko.build_d2(dd["out_coords"], *sub, z, [0, 0, 0], dd["cmax_out"], True)
+        a = co.conv_forward(feats, w0, d0)
+        b = co.conv_forward(a, wd, dd)
+        c = co.conv_forward(b, w1, d1)
+        u = co.conv_forward(c, wu, dd, transposed=True)
+        y = co.conv_forward(u, w2, d0)
+        # slabs
+        cuts, owned = mg.split_scene(coords, world, 1, align=2)
+        assert all(k % 2 == 0 for k in cuts)
+        idx = owned[rank]
+        levels = mg.SlabLevels(torch.from_numpy(coords[idx]), cuts, rank, world, 1, [2], cm)
+        s0, s1 = levels[0], levels[1]
+        assert len(levels) == 2 and levels.cmax == [list(cm), list(dd["cmax_out"])]
+        l0 = ko.build_d2(s0.local_coords.numpy(), *sub, z, [0, 0, 0], cm, True)
+        ld = ko.build_d2(coords[idx], *down, z, [0, 0, 0], cm, False)          # owned rows only: no halo
+        assert np.array_equal(ld["out_coords"], s1.coords.numpy())
+        l1 = ko.build_d2(s1.local_coords.numpy(), *sub, z, [0, 0, 0], levels.cmax[1], True)
+        a_l = co.conv_forward(s0.local_feats(feats[idx]), w0, l0)[: s0.n_owned]
+        b_l = co.conv_forward(a_l, wd, ld)
+        c_l = co.conv_forward(s1.local_feats(b_l), w1, l1)[: s1.n_owned]
+        u_l = co.conv_forward(c_l, wu, ld, transposed=True)
+        y_l = co.conv_forward(s0.local_feats(u_l), w2, l0)[: s0.n_owned]
+        lut = {tuple(r): i for i, r in enumerate(dd["out_coords"].tolist())}
+        idx1 = [lut[tuple(r)] for r in s1.coords.tolist()]
+        assert torch.allclose(b_l, b[idx1], rtol=0, atol=1e-5) and torch.allclose(c_l, c[idx1], rtol=0, atol=1e-5)
+        assert torch.allclose(u_l, u[idx], rtol=0, atol=1e-5) and torch.allclose(y_l, y[idx], rtol=0, atol=1e-5)
+        # every coarse voxel is owned by exactly one rank
+        counts = [None] * world
+        dist.all_gather_object(counts, s1.n_owned)
+        assert sum(counts) == len(dd["out_coords"])
+        out_q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        out_q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_down_and_up_sampling_layers_on_aligned_slabs(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_levels_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
+def test_aligned_cuts_and_coarsening():
+    from pcengine_b200 import multigpu as mg
+    rng = np.random.default_rng(1)
+    x = rng.integers(0, 1000, 50000)
+    cuts = mg.aligned_slab_cuts(x, 4, 1, 8)
+    assert len(cuts) == 5 and all(c % 8 == 0 for c in cuts) and cuts[0] <= x.min() and cuts[-1] > x.max()
+    assert all(b - a >= 8 for a, b in zip(cuts[:-1], cuts[1:]))
+    with pytest.raises(ValueError):
+        mg.aligned_slab_cuts(np.array([-1, 5]), 2, 1, 2)
+    coords = surface_cloud(79, 47, batch=2)
+    cm = cmax_of(coords)
+    d = ko.build_d2(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], cm, False)
+    assert np.array_equal(mg.coarsen(torch.from_numpy(coords), 2, cm).numpy(), d["out_coords"])
+    assert mg.coarse_bounds(cm, 2) == list(d["cmax_out"])
+    assert (cm[0] + 1) % 2 == 1
+    one = mg.SlabLevels(torch.from_numpy(coords), [0, cm[0] + 2], 0, 1, 1, [2], cm)   # one slab: nothing to exchange
+    assert np.array_equal(one[1].coords.numpy(), d["out_coords"]) and one[1].n_local == one[1].n_owned
+    with pytest.raises(ValueError, match="multiples"):
+        mg.SlabLevels(torch.from_numpy(coords), [0, cm[0] + 1], 0, 1, 1, [2], cm)      # an odd cut under stride 2
+
+
 @pytest.mark.parametrize("world,ks", [(2, 3), (3, 5)])
 def test_slabs_and_sharding_under_gloo(world, ks):
     ctx = mp.get_context("spawn")
