@@ -377,3 +377,34 @@ def test_planner_routes_build_the_same_lists():
             assert cb._rowptr is not None and cb._fill is None
     total = sum(len(a._csr) for a in through_csr.kmaps.values())
     assert skipped == total == 13  # five submanifold maps (one direction each) and four strided ones (two each)
+
+
+def test_planned_map_with_more_than_32_offsets_keeps_its_csr():
+    """A 5x5x5 layer in a plan (125 offsets: two-word sort keys) goes through the neighbour CSR inside the
+    planner, a 3x3x3 layer of the same plan does not; both give the lazy path's results bit for bit."""
+    import pcengine_b200 as pce
+    coords = surface_cloud(47, 40)
+    cm = cmax_of(coords)
+    feats = torch.randn(len(coords), 32, generator=torch.Generator().manual_seed(4)).half()
+
+    def tensor():
+        return pce.spTensor(feats.cuda(), torch.from_numpy(coords).cuda(), None, [0, 0, 0], cm, init_tag=["auto"])
+    three = pce.conv3d(32, 32, 3).cuda().half()
+    five = pce.conv3d(32, 64, 5).cuda().half()
+    plan = pce.MapPlan([(3, 1, False, 32, 32), (5, 1, False, 32, 64)])
+    outs = []
+    for planned in (False, True):
+        x = tensor()
+        assert plan.begin(x) if planned else True
+        with torch.no_grad():
+            a = three(x)
+            b = five(a)
+        outs.append((a.feats, b.feats))
+        if planned:
+            k3 = x.kmaps[(three.kernel_size_code, x.stride, three.stride_code)]
+            k5 = x.kmaps[(five.kernel_size_code, x.stride, five.stride_code)]
+            assert type(k5).__name__ == "PlannedKernelMap" and k5.kv == 125
+            assert k3._csr[False]._rowptr is None and k5._csr[False]._rowptr is not None
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    plan.close()
