@@ -108,7 +108,8 @@ def _pair_counter(knnz, identity_rows: int):
     """Pairs of one direction of a map = the sum of its knnz, plus one per row where the rows name themselves
     at the identity offset (whose knnz is 0)."""
     def count():
-        return (knnz.tensor().sum(dtype=torch.int64) + identity_rows).to(torch.int32).reshape(1)
+        total = knnz.tensor().sum(0, keepdim=True, dtype=torch.int32)
+        return total.add_(identity_rows) if identity_rows else total
     return count
 
 
