@@ -193,6 +193,8 @@ class MinkUNet(nn.Module):
         of it, so that no layer waits for a map.  Returns False when nothing was started."""
         if not self.plan_ahead or self.training or not x.feats.is_cuda or x.planner is not None:
             return False
+        if x.slabs is not None:  # one rank's slab of a scene: its submanifold maps span halo rows (spconv.conv_func)
+            return False
         plans = self.__dict__.setdefault("_map_plans", {})
         plan = plans.get(x.feats.dtype)
         if plan is None:
@@ -201,7 +203,8 @@ class MinkUNet(nn.Module):
 
     def forward(self, x: spTensor) -> spTensor:
         self.plan(x)
-        if self.shared_skip_buffers and not self.training and x.feats.is_cuda and x.feats.dtype == torch.float16:
+        if (self.shared_skip_buffers and not self.training and x.feats.is_cuda and x.feats.dtype == torch.float16
+                and x.slabs is None):
             if self.one_call and x.planner is not None and not x.kmaps and PF.PROFILE is None:
                 prog = self._program(x)
                 if prog is not None:

@@ -312,6 +312,17 @@ class SlabLevels:
     def __getitem__(self, level: int) -> SlabScene:
         return self.scenes[level]
 
+    def level_of(self, stride: Sequence[int]) -> int:
+        """The level whose voxels are ``stride`` finest-level voxels wide (the same along x, y, z)."""
+        s = [int(v) for v in stride]
+        total = 1
+        for level in range(len(self.scenes)):
+            if s == [total] * 3:
+                return level
+            if level < len(self.strides):
+                total *= self.strides[level]
+        raise ValueError(f"no slab level with stride {s}")
+
 
 def split_scene(coords: np.ndarray, world: int, radius: int, align: int = 1):
     """Host-side split of a whole scene (int32 [N,4]) into per-rank owned row indices + the cuts

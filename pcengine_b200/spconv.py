@@ -175,12 +175,38 @@ def _map_for(input, in_channel, out_channel, kernel_size_code, stride_code, padd
     return kmap, output_stride, coords_max, coords_min
 
 
+def _slab_submanifold(input, slabs, w, kernel_size_code, ep, out):
+    """A submanifold layer on ONE RANK'S SLAB of a scene (``input.slabs``, a multigpu.SlabLevels): ``input`` holds
+    the rows this rank owns at its level.  The level's halo rows are fetched from the neighbouring ranks, the map
+    is built once per level and kernel size over [owned | halo] rows, and only the owned output rows are computed:
+    they are the rows an undivided run returns for these voxels."""
+    scene = slabs[slabs.level_of(conv_info_decoder(input.stride))]
+    ks = conv_info_decoder(kernel_size_code)
+    if any(k % 2 == 0 for k in ks) or max(ks) // 2 > scene.radius:
+        raise NotImplementedError("a submanifold layer on slabs needs odd kernel sizes within the slabs' halo radius")
+    if input.feats.size(0) != scene.n_owned:
+        raise ValueError("the tensor's rows are not the rows this rank owns at its level")
+    key = ("slab", kernel_size_code, input.stride)
+    entry = input.kmaps.get(key)
+    if entry is None:
+        tag = input.init_tag[0] if len(input.init_tag) else "end"
+        if tag not in _TAGS:
+            raise NotImplementedError(f"no dataflow tag left for a new kernel map (init_tag[0] = {tag!r})")
+        kmap = KernelMap(scene.local_coords, ks, (1, 1, 1), (0, 0, 0), input.coords_min, input.coords_max, True)
+        kmap.dataflow = "D2"  # (the restricted CSR below is the fused dataflow's)
+        entry = input.kmaps[key] = (kmap, kmap.csr().restrict(scene.n_owned))
+        if not (tag == "auto" and len(input.init_tag) == 1):
+            input.init_tag = input.init_tag[1:]
+    return PF.conv_forward(scene.local_feats(input.feats), w, entry[1], ep, out=out)
+
+
 def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_code, padding_code, bias, transposed,
               tensorcore, epilogue: Optional[FusedEpilogue] = None, out: Optional[torch.Tensor] = None):
     """Run one sparse convolution on ``input`` and return the output ``spTensor`` (its features written
     into ``out`` when given)."""
     ep = _with_bias(epilogue, bias)
     planner = getattr(input, "planner", None)
+    slabs = getattr(input, "slabs", None)  # one rank's slab of a scene: see _slab_submanifold
     w = kernel  # the Parameter itself: the packed tensor-core layout is cached on it
 
     if kernel_size_code == _ONES and stride_code == _ONES:
@@ -208,7 +234,15 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
                           stride=output_stride, init_tag=input.init_tag, coords_max=input.coords_max,
                           coords_min=input.coords_min)
 
+    elif slabs is not None and stride_code == _ONES:
+        out_feats = _slab_submanifold(input, slabs, w, kernel_size_code, ep, out)
+        output = spTensor(feats=out_feats, coords=input.coords, buffer=input.buffer, batchsize=input.batchsize,
+                          stride=input.stride, init_tag=input.init_tag, coords_max=input.coords_max,
+                          coords_min=input.coords_min)
+
     else:
+        if slabs is not None and (kernel_size_code != stride_code or any(conv_info_decoder(padding_code))):
+            raise NotImplementedError("a down-sampling layer on slabs needs kernel size == stride and no padding")
         kmap, output_stride, coords_max, coords_min = _map_for(input, in_channel, out_channel, kernel_size_code,
                                                                stride_code, padding_code)
         out_feats = _run_conv(input.feats, w, kmap, False, ep, input.buffer, out)
@@ -219,4 +253,5 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
     output.kmaps = input.kmaps
     output.cbook = input.cbook
     output.planner = planner
+    output.slabs = slabs
     return output

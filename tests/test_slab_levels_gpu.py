@@ -1,7 +1,10 @@
-"""A U-shaped chain of layers (3x3x3, 2x2x2 stride 2 down, 3x3x3, transposed 2x2x2 up, 3x3x3) on a scene cut
+"""Two things on a scene cut into two slabs, one per GPU.  (1) A U-shaped chain of layers (3x3x3, 2x2x2 stride 2 down, 3x3x3, transposed 2x2x2 up, 3x3x3) on a scene cut
 into two slabs whose planes are multiples of the stride, one slab per GPU: the down- and up-sampling layers run
 on owned rows with no exchange, the submanifold layers exchange their level's halo (NCCL point-to-point), and
-the owned rows of both slabs equal the undivided scene computed on one GPU.  Needs two GPUs; skipped otherwise."""
+the owned rows of both slabs equal the undivided scene computed on one GPU.  (2) The MinkUNet module itself on
+``spTensor.slabs`` (four down-sampling levels, cuts at multiples of 16): conv_func exchanges every submanifold
+layer's halo, and each rank's logits are the undivided network's logits for its voxels.  Needs two GPUs; skipped
+otherwise."""
 import os
 import socket
 
@@ -76,13 +79,31 @@ def _worker(rank, world, port, ret):
         counts = [None] * world
         dist.all_gather_object(counts, s1.n_owned)
         ok = ok and sum(counts) == fd.n_out and s1.halo_left.size(0) + s1.halo_right.size(0) > 0
-        ret[rank] = (ok and err_b <= 1e-3 and err_y <= 1e-3 and PF.device_status() == 0, err_b, err_y)
+        # (2) the whole network
+        model = pce.MinkUNet(4, 19, cr=0.5)
+        pce.randomize_batchnorm(model, 8)
+        model = model.half().eval().to(dev)
+        feats4 = torch.randn(len(coords_h), 4, generator=g).half()
+        with torch.no_grad():
+            whole = model(pce.spTensor(feats4.to(dev), full, None, [0, 0, 0], cmax, init_tag=pce.MinkUNet.tags())).feats
+            cuts16, owned16 = mg.split_scene(coords_h, world, 1, align=16)
+            mine = owned16[rank]
+            x = pce.spTensor(feats4[mine].to(dev), torch.from_numpy(coords_h[mine]).to(dev), None, [0, 0, 0], cmax,
+                             init_tag=pce.MinkUNet.tags())
+            x.slabs = mg.SlabLevels(x.coords, cuts16, rank, world, 1, [2, 2, 2, 2], cmax)
+            part = model(x)
+        torch.cuda.synchronize()
+        err_net = co.rel_l2(part.feats.float().cpu(), whole[torch.from_numpy(mine).to(dev)].float().cpu())
+        ok = ok and part.slabs is x.slabs and part.feats.shape == (len(mine), 19) and x.planner is None
+        ok = ok and any(isinstance(k, tuple) and k[0] == "slab" for k in part.kmaps)
+        ret[rank] = (ok and err_b <= 1e-3 and err_y <= 1e-3 and err_net <= 2e-3 and PF.device_status() == 0,
+                     err_b, err_y, err_net)
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_down_and_up_sampling_layers_on_two_slabs_match_the_undivided_scene():
+def test_layers_and_network_on_two_slabs_match_the_undivided_scene():
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
