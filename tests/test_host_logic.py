@@ -1,5 +1,6 @@
 """Host-side pieces of the operator surface that need no GPU."""
 import numpy as np
+import pytest
 import torch
 
 import pcengine_b200 as pce
@@ -172,3 +173,20 @@ def test_neighbour_csr_builds_missing_arrays_once():
     assert lazy.restrict(1).rowptr.tolist() == [0, 2]
     whole = NeighbourCSR(mask, rowptr, nbr, 2, 2, kv=2, fill=fill)
     assert whole.rowptr is rowptr and len(calls) == 1
+
+
+def test_slab_tensors_refuse_layers_that_would_need_rows_across_a_cut():
+    """On a tensor that holds one rank's slab of a scene, a down-sampling layer must have kernel size == stride
+    and no padding (its inputs then all lie in the slab): anything else is refused before any kernel runs, and
+    the marker travels with the tensor through the feature-wise operators."""
+    from pcengine_b200 import multigpu as mg
+    coords = synth.with_batch(synth.uniform_grid(500, 16, seed=3))
+    cmax = coords[:, 1:].max(0).tolist()
+    x = pce.spTensor(torch.randn(len(coords), 8), torch.from_numpy(coords), None, [0, 0, 0], cmax, init_tag=["auto"])
+    x.slabs = mg.SlabLevels(x.coords, [0, 16], 0, 1, 1, [2], cmax)
+    assert pce.ReLU()(x).slabs is x.slabs and pce.cat([x, x]).slabs is x.slabs and (x + x).slabs is x.slabs
+    with pytest.raises(NotImplementedError, match="kernel size == stride"):
+        pce.conv3d(8, 8, 3, 2)(x)
+    with pytest.raises(NotImplementedError, match="kernel size == stride"):
+        pce.conv3d(8, 8, 2, 2, padding=1)(x)
+    assert x.slabs.level_of([2, 2, 2]) == 1
