@@ -348,15 +348,21 @@ def _reference_subm3(ref, coords, cmax):
     return dict(kpos=kpos, qkpos=qkpos, imap=imap, omap=omap, qsum=int(qkpos[-1].cpu()), code=code((3, 3, 3)))
 
 
-def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: int = 3, with_reference: bool = False):
+def layer_table(dev, pk, names=None, scans: int = 1, iters: int = 10, warmup: int = 3, with_reference: bool = False,
+                level: int = 0):
     """Single LiDAR-shaped layers on ``scans`` collated scans (seeds 2000..): kernel-only time per layer
     with an L2 flush between launches; algorithmic bytes / flops per launch against the measured peaks.
-    ``with_reference``: the reference's own fp16 kernels on the same submanifold layers, same timing."""
+    ``with_reference``: the reference's own fp16 kernels on the same submanifold layers, same timing.
+    ``level``: run on the coordinates after that many 2x2x2 / stride-2 down-samplings (the deeper levels
+    of the network: fewer, denser rows)."""
     import pcengine_b200 as pce
     from pcengine_b200 import functional as PF
     coords_h, _, _ = make_scans(list(range(scans)))
     coords = torch.from_numpy(coords_h).to(dev)
     cmax = coords_h[:, 1:].max(0).tolist()
+    for _ in range(level):
+        cmax = [(c - 1) // 2 for c in cmax]
+        coords = pce.KernelMap(coords, (2, 2, 2), (2, 2, 2), (0, 0, 0), [0, 0, 0], cmax, False).out_coords.contiguous()
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
     names = list(names or DEFAULT_LAYERS)
     maps = {}
@@ -633,8 +639,9 @@ def run_layer(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    rows, n = layer_table(dev, peaks(), [args.layer], scans=args.scans, iters=args.steps, warmup=args.warmup)
-    print(json.dumps({"workload": "single_layer", "voxels": n, "scans": args.scans, **rows[0]}))
+    rows, n = layer_table(dev, peaks(), [args.layer], scans=args.scans, iters=args.steps, warmup=args.warmup,
+                          level=args.level)
+    print(json.dumps({"workload": "single_layer", "voxels": n, "scans": args.scans, "level": args.level, **rows[0]}))
 
 
 def _host_array(a) -> np.ndarray:
@@ -982,6 +989,8 @@ def main():
     ap.add_argument("--layer", type=str, default=None, choices=sorted(LAYERS),
                     help="run one single layer only (kernel-only timing); see --scans")
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
+    ap.add_argument("--level", type=int, default=0, choices=range(5),
+                    help="--layer: run on the coordinates after this many 2x2x2 / stride-2 down-samplings")
     ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor", "selector"],
                     help="minkunet: the batch of 8 LiDAR scans (default); scene: one 1.5 M-voxel scene in x-slabs; indoor: the room sweep, both dataflows")
     ap.add_argument("--no-pin", dest="pin", action="store_false",
