@@ -904,10 +904,14 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
                 "traffic": None, "kernel": name, "launches_timed": k["n"], "avg_launch_us": k["t"] / k["n"] * 1e6,
                 "share_of_step": k["t"] / (dt_prof if dt_prof > 0 else 1.0),
+                "timed_loop_ms_per_step": dt_prof / steps * 1e3,
                 "tensor_tflops": k["flops"] / k["t"] / 1e12, "tensor_frac": k["flops"] / k["t"] / 1e12 / pk["tflops"],
                 "peak_source": pk["source"], "note": "sum of algorithmic bytes of every launch of this kernel in the "
                 "K steps run right after the timed ones / sum of their CUDA-event durations; traffic is null "
-                "because the aggregate spans every launch shape of a step (DRAM bytes of single shapes: profiles/)"}
+                "because the aggregate spans every launch shape of a step (DRAM bytes of single shapes: profiles/). The "
+                "event pairs sit around per-layer launches (timed_loop_ms_per_step is that loop's own step): where "
+                "the host, not the GPU, paces that loop (a scan or two per rank) a pair also holds launch latency, "
+                "and the launches of a step can sum to more than the one-call step the headline times"}
     # ---- extras ------------------------------------------------------------------------------
     layers = cpu = parity = config1 = indoor = scene = None
     cores_per_rank = len(os.sched_getaffinity(0))
