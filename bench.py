@@ -618,6 +618,86 @@ def run_scene(args):
         dist.destroy_process_group()
 
 
+def run_scene_unet(args):
+    """``--workload scene_unet``: the MinkUNet over the ONE large indoor scene (about 1.5 M voxels), the scene
+    cut into x-slabs at multiples of 16 voxels, one slab per rank (``spTensor.slabs``): every submanifold layer
+    exchanges its level's halo rows, the 2x2x2 layers exchange nothing.  Forward passes per second (kernel maps
+    kept: the scene is static), max over ranks; at one rank also the ordinary pass on the undivided tensor and
+    the largest difference between the two."""
+    import torch.distributed as dist
+
+    import pcengine_b200 as pce
+    from pcengine_b200 import multigpu as mg
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    synth = _synth()
+    coords_h = synth.with_batch(synth.tiled_scene())
+    cmax = coords_h[:, 1:].max(0).tolist()
+    model = pce.MinkUNet(IN_CHANNELS, NUM_CLASSES)
+    model.load_state_dict(seeded_state_dict({k: tuple(v.shape) for k, v in model.state_dict().items()}))
+    model = model.half().eval().to(dev)
+    feats_h = torch.randn(len(coords_h), IN_CHANNELS, generator=torch.Generator().manual_seed(21)).half()
+    cuts, owned = mg.split_scene(coords_h, world, 1, align=16)
+    idx = owned[rank]
+    coords = torch.from_numpy(coords_h[idx]).to(dev)
+    feats = feats_h[idx].to(dev)
+    levels = mg.SlabLevels(coords, cuts, rank, world, 1, [2, 2, 2, 2], cmax)
+    kept = {}
+
+    def forward(slabs):
+        x = pce.spTensor(feats, coords, None, [0, 0, 0], cmax, init_tag=pce.MinkUNet.tags())
+        x.slabs = slabs
+        x.kmaps = kept.setdefault(id(slabs), {})  # a static scene: the maps of the first pass serve the later ones
+        if x.kmaps:
+            x.init_tag = ["auto"]
+        with torch.no_grad():
+            return model(x).feats
+
+    def timed(slabs):
+        for _ in range(max(args.warmup, 2)):
+            forward(slabs)
+        ts = []
+        for _ in range(max(args.steps, 5)):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = forward(slabs)
+            b.record()
+            b.synchronize()
+            ts.append(mg.max_over_ranks(a.elapsed_time(b) * 1e-3, dev))
+        return float(np.median(ts)), out
+    t_slab, y_slab = timed(levels)
+    halo = sum(int(sc.n_local - sc.n_owned) for sc in levels.scenes)
+    if world > 1:
+        h = torch.tensor([halo], dtype=torch.int64, device=dev)
+        dist.all_reduce(h)
+        halo = int(h)
+    res = {"workload": "scene_unet", "n_gpus": world, "voxels": len(coords_h), "cuts": cuts, "ms_per_pass": t_slab * 1e3,
+           "voxels_per_s": len(coords_h) / t_slab, "halo_rows_all_levels": halo,
+           "exchange": "none (one slab)"}
+    if world > 1:
+        boxed = [k for k, v in levels.__dict__.get("_mailboxes", {}).items() if v is not None]
+        res["exchange"] = ("boundary rows stored into the neighbours' mailboxes (peer stores) + one symmetric-memory "
+                           f"barrier per submanifold layer ({len(boxed)} level/width pairs; NCCL messages for the rest)"
+                           if boxed else "NCCL isend/irecv of the halo rows before every submanifold layer")
+    if world == 1:
+        model.plan_ahead = False  # the ordinary per-layer pass on the undivided tensor, maps kept as well
+        t_whole, y_whole = timed(None)
+        res["ms_per_pass_without_slabs"] = t_whole * 1e3
+        res["max_abs_diff"] = float((y_slab.float() - y_whole.float()).abs().max())
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_indoor(args):
     """``--workload indoor``: the indoor-room sweep with both dataflows."""
     dev = torch.device("cuda", 0)
@@ -995,13 +1075,16 @@ def main():
     ap.add_argument("--scans", type=int, default=8, help="collated scans for --layer")
     ap.add_argument("--level", type=int, default=0, choices=range(5),
                     help="--layer: run on the coordinates after this many 2x2x2 / stride-2 down-samplings")
-    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "indoor", "selector"],
-                    help="minkunet: the batch of 8 LiDAR scans (default); scene: one 1.5 M-voxel scene in x-slabs; indoor: the room sweep, both dataflows")
+    ap.add_argument("--workload", type=str, default="minkunet", choices=["minkunet", "scene", "scene_unet", "indoor", "selector"],
+                    help="minkunet: the batch of 8 LiDAR scans (default); scene: one 1.5 M-voxel scene in x-slabs, single layers; "
+                         "scene_unet: the MinkUNet over that scene on slabs; indoor: the room sweep, both dataflows")
     ap.add_argument("--no-pin", dest="pin", action="store_false",
                     help="multi-rank runs: do not give each rank its own share of the host cores")
     ap.add_argument("--lean", action="store_true",
                     help="skip the per-layer tables, the scene, the parity check and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
+    if args.workload == "scene_unet":
+        return run_scene_unet(args)
     if args.workload == "scene":
         run_scene(args)
     elif args.workload == "indoor":

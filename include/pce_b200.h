@@ -390,6 +390,14 @@ PCE_API int pce_linear_fwd(const void* in_feats, int32_t n, int32_t c_in, const 
 PCE_API int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dtype,
                         const pce_epilogue* ep, void* stream);
 
+/* Copies rows rows[i] (rows == NULL: row i) of a row-major matrix into consecutive rows of dst, 16 bytes per
+ * store.  dst may be a neighbouring GPU's memory mapped into this process (a peer pointer): the halo exchange
+ * of a slab-parallel scene outside a convolution's epilogue (pce_epilogue.push_*): a rank stores its boundary
+ * rows straight into the neighbour's mailbox, no message.  Only stores go to dst, nothing is loaded from it.
+ * No reference counterpart (the reference is single-GPU).  row_bytes and both pitches are multiples of 16. */
+PCE_API int pce_push_rows(const void* src, int64_t src_pitch_bytes, const int32_t* rows, int32_t n_rows,
+                          int32_t row_bytes, void* dst, int64_t dst_pitch_bytes, void* stream);
+
 /* ------------------------------------------------------ kernel-map planner -- */
 
 /* The reference builds a kernel map inside the first convolution that needs it and keeps

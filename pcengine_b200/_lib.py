@@ -25,7 +25,7 @@ EXPORTS = [
     "pce_strerror", "pce_version", "pce_last_cuda_error", "pce_kernel_launches", "pce_map_workspace_bytes", "pce_downsample_coords",
     "pce_map_build_d2", "pce_map_build_d2_noalloc", "pce_map_pairs", "pce_map_build_d1", "pce_csr_from_dense", "pce_csr_from_pairs",
     "pce_csr_from_pairs_workspace_bytes", "pce_csr_sort_rows", "pce_build_tile_lists", "pce_conv_kernel_choice", "pce_conv_split_parts", "pce_conv_split_scratch_bytes", "pce_conv_fwd", "pce_packed_weights_bytes",
-    "pce_pack_weights", "pce_device_status", "pce_debug_timeout", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act",
+    "pce_pack_weights", "pce_device_status", "pce_debug_timeout", "pce_tune", "pce_conv_fwd_d1", "pce_linear_fwd", "pce_scale_shift_act", "pce_push_rows",
     "pce_quantize_workspace_bytes", "pce_quantize_unique", "pce_tile_rows_for", "pce_plan_create", "pce_plan_destroy", "pce_plan_begin", "pce_pass_map", "pce_pass_release", "pce_net_run",
 ]
 
@@ -128,6 +128,7 @@ def _load() -> C.CDLL:
                                     C.POINTER(Epilogue), vp]
     lib.pce_linear_fwd.argtypes = [vp, i32, i32, vp, vp, i32, vp, i32, C.POINTER(Epilogue), vp]
     lib.pce_scale_shift_act.argtypes = [vp, i64, i32, vp, i32, C.POINTER(Epilogue), vp]
+    lib.pce_push_rows.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp]
     lib.pce_quantize_workspace_bytes.restype = sz
     lib.pce_quantize_workspace_bytes.argtypes = [i32]
     lib.pce_quantize_unique.argtypes = [vp, i32, C.POINTER(C.c_float), i32, vp, sz, vp, vp, vp, C.POINTER(i32), vp]

@@ -228,11 +228,38 @@ int conv_simt(const void* in, const void* w, const uint32_t* mask, const int* ro
   return PCE_ERR_UNSUPPORTED;
 }
 
+// Rows rows[i] (or i where rows == nullptr) of a row-major matrix, copied into consecutive rows of `dst` in
+// 16-byte pieces.  `dst` may be another GPU's memory mapped into this process: plain stores, no loads from it.
+__global__ void k_push_rows(const char* __restrict__ src, long long src_pitch, const int* __restrict__ rows, int n_rows,
+                            int pieces, char* __restrict__ dst, long long dst_pitch) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= static_cast<long long>(n_rows) * pieces) return;
+  const int r = static_cast<int>(i / pieces), p = static_cast<int>(i % pieces);
+  const long long from = rows ? __ldg(rows + r) : r;
+  const uint4 v = *reinterpret_cast<const uint4*>(src + from * src_pitch + 16ll * p);
+  *reinterpret_cast<uint4*>(dst + r * dst_pitch + 16ll * p) = v;
+}
+
 }  // namespace pce
 
 using namespace pce;
 
 extern "C" {
+
+int pce_push_rows(const void* src, int64_t src_pitch_bytes, const int32_t* rows, int32_t n_rows, int32_t row_bytes,
+                  void* dst, int64_t dst_pitch_bytes, void* stream) {
+  if (n_rows < 0 || row_bytes < 16 || (row_bytes & 15) || src_pitch_bytes < row_bytes || dst_pitch_bytes < row_bytes ||
+      (src_pitch_bytes & 15) || (dst_pitch_bytes & 15))
+    return PCE_ERR_INVALID;
+  if (n_rows == 0) return PCE_OK;
+  if (!src || !dst || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return PCE_ERR_INVALID;
+  const int pieces = row_bytes / 16;
+  const long long total = static_cast<long long>(n_rows) * pieces;
+  k_push_rows<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const char*>(src), src_pitch_bytes, rows, n_rows, pieces, static_cast<char*>(dst), dst_pitch_bytes);
+  PCE_LAUNCH_CHECK();
+  return PCE_OK;
+}
 
 int pce_scale_shift_act(const void* x, int64_t n, int32_t c, void* y, int32_t dtype, const pce_epilogue* ep,
                         void* stream) {

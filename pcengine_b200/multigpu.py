@@ -312,6 +312,28 @@ class SlabLevels:
     def __getitem__(self, level: int) -> SlabScene:
         return self.scenes[level]
 
+    # Halo rows travel through symmetric-memory mailboxes (HaloMailbox) where that is available, else as
+    # messages (SlabScene.exchange_into); set to False to use messages throughout.
+    use_mailboxes = True
+
+    def exchange_into(self, level: int, buf: torch.Tensor) -> torch.Tensor:
+        """Fill the halo rows of ``buf`` ([owned | halo] rows of ``level``) from the neighbouring ranks."""
+        scene = self.scenes[level]
+        if scene.world == 1:
+            return buf
+        row_bytes = buf.size(1) * buf.element_size()
+        if self.use_mailboxes and buf.is_cuda and row_bytes % 16 == 0 and (buf.stride(0) * buf.element_size()) % 16 == 0:
+            boxes = self.__dict__.setdefault("_mailboxes", {})
+            key = (level, buf.size(1), buf.dtype)
+            if key not in boxes:
+                try:   # (collective: every rank reaches this for the same layer)
+                    boxes[key] = HaloMailbox(scene, buf.size(1), buf.dtype)
+                except Exception:  # no symmetric memory on this system
+                    boxes[key] = None
+            if boxes[key] is not None:
+                return boxes[key].exchange_into(buf)
+        return scene.exchange_into(buf)
+
     def level_of(self, stride: Sequence[int]) -> int:
         """The level whose voxels are ``stride`` finest-level voxels wide (the same along x, y, z)."""
         s = [int(v) for v in stride]
@@ -322,6 +344,61 @@ class SlabLevels:
             if level < len(self.strides):
                 total *= self.strides[level]
         raise ValueError(f"no slab level with stride {s}")
+
+
+class HaloMailbox:
+    """Halo exchange of a :class:`SlabScene` without messages, for feature matrices of one width and dtype.
+
+    Every rank keeps two mailboxes [halo rows, C] in symmetric memory, laid out like the halo part of a local
+    feature matrix ([from the left | from the right]).  ``exchange_into(buf)`` stores this rank's boundary rows
+    straight into the neighbours' mailboxes (``pce_push_rows``: plain peer stores over NVLink, nothing is loaded
+    from a peer and no multicast is involved), passes one barrier between the GPUs, and copies its own mailbox
+    behind the owned rows of ``buf``.  The two mailboxes alternate, so the barrier of one exchange also orders
+    the next exchange's stores after this exchange's copy."""
+
+    def __init__(self, scene: "SlabScene", channels: int, dtype=torch.float16, group=None):
+        import torch.distributed._symmetric_memory as symm
+        if scene.local_coords is None:
+            raise RuntimeError("SlabScene.setup() must run first")
+        if (channels * torch.empty((), dtype=dtype).element_size()) % 16:
+            raise ValueError("a mailbox row must be a multiple of 16 bytes")
+        self.scene, self.channels, self.dtype = scene, channels, dtype
+        dev = scene.coords.device
+        group = group if group is not None else dist.group.WORLD
+        self.nl, self.nr = int(scene.halo_left.size(0)), int(scene.halo_right.size(0))
+        mine = torch.tensor([self.nl, self.nr], dtype=torch.int64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(scene.world)]
+        dist.all_gather(every, mine, group=group)
+        self.every = [t.cpu().tolist() for t in every]
+        rows = max(max(e[0] + e[1] for e in self.every), 1)
+        self.boxes = [symm.empty((rows, channels), dtype=dtype, device=dev) for _ in range(2)]
+        self.handles = [symm.rendezvous(t, group) for t in self.boxes]
+        self.send_left = scene.send_left.to(torch.int32).contiguous()
+        self.send_right = scene.send_right.to(torch.int32).contiguous()
+        self.k = 0
+
+    def exchange_into(self, buf: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        sc = self.scene
+        if buf.size(1) != self.channels or buf.dtype != self.dtype or buf.size(0) != sc.n_local or buf.stride(1) != 1:
+            raise ValueError("the buffer is not an [n_local, C] matrix of this mailbox's width and type")
+        k, self.k = self.k, self.k ^ 1
+        row_bytes = self.channels * buf.element_size()
+        pitch = buf.stride(0) * buf.element_size()
+        stream = _lib.stream_ptr(buf.device)
+        ptrs = self.handles[k].buffer_ptrs
+        if sc.rank > 0 and self.send_left.numel():    # my left boundary: the left neighbour's rows "from the right"
+            dst = int(ptrs[sc.rank - 1]) + self.every[sc.rank - 1][0] * row_bytes
+            _lib.check(_lib.lib.pce_push_rows(buf.data_ptr(), pitch, self.send_left.data_ptr(), self.send_left.numel(),
+                                              row_bytes, dst, row_bytes, stream), "pce_push_rows")
+        if sc.rank < sc.world - 1 and self.send_right.numel():  # my right boundary: the right neighbour's rows "from the left"
+            _lib.check(_lib.lib.pce_push_rows(buf.data_ptr(), pitch, self.send_right.data_ptr(), self.send_right.numel(),
+                                              row_bytes, int(ptrs[sc.rank + 1]), row_bytes, stream), "pce_push_rows")
+        self.handles[k].barrier(channel=0)
+        n = self.nl + self.nr
+        if n:
+            buf[sc.n_owned: sc.n_owned + n].copy_(self.boxes[k][:n])
+        return buf
 
 
 def split_scene(coords: np.ndarray, world: int, radius: int, align: int = 1):

@@ -197,7 +197,29 @@ def _slab_submanifold(input, slabs, w, kernel_size_code, ep, out):
         entry = input.kmaps[key] = (kmap, kmap.csr().restrict(scene.n_owned))
         if not (tag == "auto" and len(input.init_tag) == 1):
             input.init_tag = input.init_tag[1:]
-    return PF.conv_forward(scene.local_feats(input.feats), w, entry[1], ep, out=out)
+    level = slabs.level_of(conv_info_decoder(input.stride))
+    room = getattr(input, "halo_room", None)
+    if scene.n_local == scene.n_owned:
+        local = input.feats                   # nothing to fetch (one slab, or no voxel near a cut)
+    elif (room is not None and room.size(0) == scene.n_local and room.dtype == input.feats.dtype
+            and room.data_ptr() == input.feats.data_ptr() and room.size(1) == input.feats.size(1)):
+        local = room                          # the layer that produced the rows left room for the halo behind them
+    else:
+        local = scene.alloc_local(input.feats.size(1), input.feats.dtype)
+        local[: scene.n_owned] = input.feats
+    slabs.exchange_into(level, local)
+    return PF.conv_forward(local, w, entry[1], ep, out=out)
+
+
+def _with_halo_room(slabs, stride_code: int, c_out: int, like: torch.Tensor, out):
+    """Output storage of a layer on a slab tensor: ``out`` as given, else the first rows of an
+    [owned | halo] matrix of the output's level, so that a submanifold layer that reads the result next
+    receives its halo rows in place instead of copying the owned rows first.  Returns (out, matrix or None)."""
+    if out is not None:
+        return out, None
+    scene = slabs[slabs.level_of(conv_info_decoder(stride_code))]
+    room = torch.empty((scene.n_local, c_out), dtype=like.dtype, device=like.device)
+    return room[: scene.n_owned], room
 
 
 def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_code, padding_code, bias, transposed,
@@ -229,26 +251,36 @@ def conv_func(input, in_channel, out_channel, kernel, kernel_size_code, stride_c
         # the reference reads cbook[output_stride] and fails when no layer registered that
         # stride (script/spconv.py:309); the map itself remembers its fine side.
         out_coords = input.cbook.get(output_stride, kmap.in_coords)
+        room = None
+        if slabs is not None:
+            out, room = _with_halo_room(slabs, output_stride, out_channel, input.feats, out)
         out_feats = _run_conv(input.feats, w, kmap, True, ep, input.buffer, out)
         output = spTensor(feats=out_feats, coords=out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=input.coords_max,
                           coords_min=input.coords_min)
+        output.halo_room = room
 
     elif slabs is not None and stride_code == _ONES:
+        out, room = _with_halo_room(slabs, input.stride, out_channel, input.feats, out)
         out_feats = _slab_submanifold(input, slabs, w, kernel_size_code, ep, out)
         output = spTensor(feats=out_feats, coords=input.coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=input.stride, init_tag=input.init_tag, coords_max=input.coords_max,
                           coords_min=input.coords_min)
+        output.halo_room = room
 
     else:
         if slabs is not None and (kernel_size_code != stride_code or any(conv_info_decoder(padding_code))):
             raise NotImplementedError("a down-sampling layer on slabs needs kernel size == stride and no padding")
         kmap, output_stride, coords_max, coords_min = _map_for(input, in_channel, out_channel, kernel_size_code,
                                                                stride_code, padding_code)
+        room = None
+        if slabs is not None:
+            out, room = _with_halo_room(slabs, output_stride, out_channel, input.feats, out)
         out_feats = _run_conv(input.feats, w, kmap, False, ep, input.buffer, out)
         output = spTensor(feats=out_feats, coords=kmap.out_coords, buffer=input.buffer, batchsize=input.batchsize,
                           stride=output_stride, init_tag=input.init_tag, coords_max=coords_max,
                           coords_min=coords_min)
+        output.halo_room = room
 
     output.kmaps = input.kmaps
     output.cbook = input.cbook

@@ -25,6 +25,7 @@ class spTensor:
         self.planner = None       # the planner pass that builds this network pass's kernel maps (planner.MapPlan)
         self.coords_ready = None  # optional CUDA event after which `coords` is valid (read by MapPlan.begin)
         self.slabs = None         # multigpu.SlabLevels when the rows are one rank's slab of a scene (spconv.conv_func)
+        self.halo_room = None     # slab tensors: the [owned | halo] matrix whose first rows `feats` are, if any
         self.init_tag = ["end"] if init_tag is None else init_tag
         self.coords_min = [0, 0, 0] if coords_min is None else coords_min
         if coords_max is None:

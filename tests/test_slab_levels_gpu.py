@@ -96,6 +96,17 @@ def _worker(rank, world, port, ret):
         err_net = co.rel_l2(part.feats.float().cpu(), whole[torch.from_numpy(mine).to(dev)].float().cpu())
         ok = ok and part.slabs is x.slabs and part.feats.shape == (len(mine), 19) and x.planner is None
         ok = ok and any(isinstance(k, tuple) and k[0] == "slab" for k in part.kmaps)
+        # the halo rows went through symmetric-memory mailboxes (peer stores), not messages, wherever a row is a
+        # multiple of 16 bytes; the same pass with messages throughout gives the same logits bit for bit
+        boxes = x.slabs.__dict__.get("_mailboxes", {})
+        ok = ok and len(boxes) > 0 and all(v is not None for v in boxes.values())
+        with torch.no_grad():
+            x2 = pce.spTensor(feats4[mine].to(dev), torch.from_numpy(coords_h[mine]).to(dev), None, [0, 0, 0], cmax,
+                              init_tag=pce.MinkUNet.tags())
+            x2.slabs = x.slabs
+            x2.slabs.use_mailboxes = False
+            ok = ok and bool(torch.equal(model(x2).feats, part.feats))
+            x2.slabs.use_mailboxes = True
         ret[rank] = (ok and err_b <= 1e-3 and err_y <= 1e-3 and err_net <= 2e-3 and PF.device_status() == 0,
                      err_b, err_y, err_net)
     finally:
