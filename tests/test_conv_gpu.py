@@ -661,3 +661,23 @@ def test_mid_size_maps_cut_into_equal_shares_of_stages(cin, cout, n_side, ks):
     wherever the cuts fall inside the tiles; tiles that two or more CTAs worked on are summed in CTA order
     and finished by a second kernel.  Same checks as for the split into parts."""
     _split_layer_case(cin, cout, n_side, ks, stream_k=True)
+
+
+def test_push_rows_gathers_into_consecutive_rows():
+    """pce_push_rows (the halo mailbox's store kernel) on local memory: selected rows of a row-pitched matrix land
+    in consecutive rows of the destination; without a row list it is a row-wise copy; rows that are not a
+    multiple of 16 bytes are refused."""
+    from pcengine_b200 import _lib
+    g = torch.Generator().manual_seed(9)
+    wide = torch.randn(300, 48, generator=g).half().cuda()
+    src = wide[:, 8:40]                                   # 32 channels inside a 48-channel matrix: pitch 96 B
+    rows = torch.tensor([5, 0, 299, 17, 17, 123], dtype=torch.int32, device="cuda")
+    dst = torch.zeros(8, 64, dtype=torch.float16, device="cuda")
+    st = _lib.stream_ptr(src.device)
+    _lib.check(_lib.lib.pce_push_rows(src.data_ptr(), 96, rows.data_ptr(), 6, 64, dst.data_ptr(), 128, st), "pce_push_rows")
+    assert torch.equal(dst[:6, :32], src[rows.long()]) and not dst[6:].any() and not dst[:, 32:].any()
+    _lib.check(_lib.lib.pce_push_rows(src.data_ptr(), 96, None, 8, 64, dst.data_ptr(), 128, st), "pce_push_rows")
+    assert torch.equal(dst[:, :32], src[:8])
+    with pytest.raises(ValueError):
+        _lib.check(_lib.lib.pce_push_rows(src.data_ptr(), 96, None, 8, 24, dst.data_ptr(), 128, st), "pce_push_rows")
+    assert _lib.lib.pce_push_rows(src.data_ptr(), 96, None, 0, 64, dst.data_ptr(), 128, st) == 0
