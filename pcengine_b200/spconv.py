@@ -180,7 +180,8 @@ def _slab_submanifold(input, slabs, w, kernel_size_code, ep, out):
     the rows this rank owns at its level.  The level's halo rows are fetched from the neighbouring ranks, the map
     is built once per level and kernel size over [owned | halo] rows, and only the owned output rows are computed:
     they are the rows an undivided run returns for these voxels."""
-    scene = slabs[slabs.level_of(conv_info_decoder(input.stride))]
+    level = slabs.level_of(conv_info_decoder(input.stride))
+    scene = slabs[level]
     ks = conv_info_decoder(kernel_size_code)
     if any(k % 2 == 0 for k in ks) or max(ks) // 2 > scene.radius:
         raise NotImplementedError("a submanifold layer on slabs needs odd kernel sizes within the slabs' halo radius")
@@ -197,7 +198,6 @@ def _slab_submanifold(input, slabs, w, kernel_size_code, ep, out):
         entry = input.kmaps[key] = (kmap, kmap.csr().restrict(scene.n_owned))
         if not (tag == "auto" and len(input.init_tag) == 1):
             input.init_tag = input.init_tag[1:]
-    level = slabs.level_of(conv_info_decoder(input.stride))
     room = getattr(input, "halo_room", None)
     if scene.n_local == scene.n_owned:
         local = input.feats                   # nothing to fetch (one slab, or no voxel near a cut)
