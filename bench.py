@@ -687,11 +687,18 @@ def run_scene_unet(args):
         res["exchange"] = ("boundary rows stored into the neighbours' mailboxes (peer stores) + one symmetric-memory "
                            f"barrier per submanifold layer ({len(boxed)} level/width pairs; NCCL messages for the rest)"
                            if boxed else "NCCL isend/irecv of the halo rows before every submanifold layer")
+    model.plan_ahead = False  # the ordinary per-layer pass on the undivided tensor, maps kept as well
     if world == 1:
-        model.plan_ahead = False  # the ordinary per-layer pass on the undivided tensor, maps kept as well
         t_whole, y_whole = timed(None)
         res["ms_per_pass_without_slabs"] = t_whole * 1e3
         res["max_abs_diff"] = float((y_slab.float() - y_whole.float()).abs().max())
+    else:  # every rank also runs the undivided scene once and compares the rows it owns
+        with torch.no_grad():
+            whole = model(pce.spTensor(feats_h.to(dev), torch.from_numpy(coords_h).to(dev), None, [0, 0, 0], cmax,
+                                       init_tag=pce.MinkUNet.tags())).feats
+        want = whole[torch.from_numpy(idx).to(dev)].float()
+        err = (y_slab.float() - want).norm() / want.norm().clamp_min(1e-20)
+        res["rel_l2_vs_undivided_max_over_ranks"] = mg.max_over_ranks(float(err), dev)
     if rank == 0:
         print(json.dumps(res))
     if world > 1:
