@@ -136,6 +136,65 @@ def test_down_and_up_sampling_layers_on_aligned_slabs(world):
     assert all(msg == "ok" for _, msg in results), results
 
 
+def _deep_worker(rank, world, port, out_q):
+    """Three coordinate levels (strides 2, 2; cuts at multiples of 4): down, down, 3x3x3 at the coarsest level,
+    up, up, 3x3x3 at the finest, every strided layer on owned rows only."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pcengine_b200 import multigpu as mg
+        coords = surface_cloud(80, 62, batch=1)
+        cm = cmax_of(coords)
+        torch.manual_seed(7)
+        feats = torch.randn(len(coords), 6)
+        wd0, wd1, w2, wu1, wu0, w0 = (torch.randn(8, 6, 8) / 4, torch.randn(8, 8, 10) / 4, torch.randn(27, 10, 10) / 10,
+                                      torch.randn(8, 10, 8) / 4, torch.randn(8, 8, 6) / 4, torch.randn(27, 6, 5) / 10)
+        sub, down, z = ((3, 3, 3), (1, 1, 1)), ((2, 2, 2), (2, 2, 2)), (0, 0, 0)
+
+        def run(c0, f, local0=None, local2=None, grow0=lambda t: t, grow2=lambda t: t, n0=None, n2=None):
+            m01 = ko.build_d2(c0, *down, z, [0, 0, 0], cm, False)
+            m12 = ko.build_d2(m01["out_coords"], *down, z, [0, 0, 0], m01["cmax_out"], False)
+            s2 = ko.build_d2(m12["out_coords"] if local2 is None else local2, *sub, z, [0, 0, 0], m12["cmax_out"], True)
+            s0 = ko.build_d2(c0 if local0 is None else local0, *sub, z, [0, 0, 0], cm, True)
+            a = co.conv_forward(f, wd0, m01)
+            b = co.conv_forward(a, wd1, m12)
+            c = co.conv_forward(grow2(b), w2, s2)[: (n2 if n2 is not None else len(b))]
+            d = co.conv_forward(c, wu1, m12, transposed=True)
+            e = co.conv_forward(d, wu0, m01, transposed=True)
+            y = co.conv_forward(grow0(e), w0, s0)[: (n0 if n0 is not None else len(e))]
+            return m12["out_coords"], c, y
+        coarse, c_full, y_full = run(coords, feats)
+        cuts, owned = mg.split_scene(coords, world, 1, align=4)
+        idx = owned[rank]
+        levels = mg.SlabLevels(torch.from_numpy(coords[idx]), cuts, rank, world, 1, [2, 2], cm)
+        assert len(levels) == 3 and all(k % 4 == 0 for k in cuts)
+        mine, c_l, y_l = run(coords[idx], feats[idx], levels[0].local_coords.numpy(), levels[2].local_coords.numpy(),
+                             levels[0].local_feats, levels[2].local_feats, levels[0].n_owned, levels[2].n_owned)
+        assert np.array_equal(mine, levels[2].coords.numpy())
+        lut = {tuple(r): i for i, r in enumerate(coarse.tolist())}
+        idx2 = [lut[tuple(r)] for r in mine.tolist()]
+        assert torch.allclose(c_l, c_full[idx2], rtol=0, atol=1e-5) and torch.allclose(y_l, y_full[idx], rtol=0, atol=1e-5)
+        out_q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        out_q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_three_levels_on_aligned_slabs():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_deep_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
 def test_aligned_cuts_and_coarsening():
     from pcengine_b200 import multigpu as mg
     rng = np.random.default_rng(1)
